@@ -1,0 +1,382 @@
+// Persistent, warp-specialised bf16 GEMM for sm_100a.
+//
+//   warp 0      : TMA producer   (cp.async.bulk.tensor into a STAGES-deep smem ring)
+//   warp 1      : MMA issuer     (one thread issues tcgen05.mma; accumulators live in TMEM)
+//   warps 2..9  : epilogue       (tcgen05.ld TMEM -> registers -> fused epilogue -> global)
+//
+// The 512 TMEM columns hold two 128 x BN fp32 accumulators, so the epilogue of
+// work unit i overlaps the main loop of unit i+1.  Work units are
+// (output tile, K split) pairs handed out round-robin to a grid of at most one
+// CTA per SM.  Operands may be K-major or MN-major in memory (the UMMA
+// descriptors express both), which covers forward (X*W), dgrad (dY*W^T) and
+// wgrad (X^T*dY) of a layer whose weight is stored [in][out] without any
+// transposed copies.  No TMA multicast is used anywhere.
+#include "gemm_tc.cuh"
+#include "ptx.cuh"
+
+namespace ab {
+
+EncodeTiledFn get_encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+            cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+int make_tmap_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                 uint32_t box_rows, uint32_t box_cols, int elem_bytes, bool swizzle128) {
+  EncodeTiledFn enc = get_encode_tiled();
+  if (!enc) return -100;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * static_cast<uint64_t>(elem_bytes)};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMapDataType dt = elem_bytes == 2   ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                           : elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                             : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  CUresult r = enc(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -200 - static_cast<int>(r);
+}
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int NUM_EPI_WARPS = 8;
+constexpr int NUM_THREADS = 64 + 32 * NUM_EPI_WARPS;
+
+struct GemmArgs {
+  int M, N, K;
+  int k_splits;
+  AbGemmEpilogue ep;
+  int* status;
+};
+
+template <int BN>
+__device__ __forceinline__ void epilogue_chunk(const GemmArgs& g, const uint32_t* r, int m, int n0,
+                                               bool row_ok) {
+  const AbGemmEpilogue& ep = g.ep;
+  if (!row_ok) return;
+#pragma unroll
+  for (int grp = 0; grp < 4; ++grp) {
+    const int n = n0 + grp * 8;
+    if (n >= g.N) break;
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[grp * 8 + j]) * ep.alpha;
+    if (ep.bias) {
+      const float4 b0 = __ldg(reinterpret_cast<const float4*>(ep.bias + n));
+      const float4 b1 = __ldg(reinterpret_cast<const float4*>(ep.bias + n + 4));
+      v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
+      v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+    }
+    if (ep.act == 1) {
+      uint4 pre;
+      pre.x = pack_bf16x2(v[0], v[1]); pre.y = pack_bf16x2(v[2], v[3]);
+      pre.z = pack_bf16x2(v[4], v[5]); pre.w = pack_bf16x2(v[6], v[7]);
+      *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(ep.aux) + (long long)m * ep.ldaux + n) =
+          pre;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = gelu_tanh(v[j]);
+    } else if (ep.act == 2) {
+      const uint4 pre = *reinterpret_cast<const uint4*>(
+          static_cast<const __nv_bfloat16*>(ep.aux) + (long long)m * ep.ldaux + n);
+      v[0] *= gelu_tanh_grad(bf16_lo(pre.x)); v[1] *= gelu_tanh_grad(bf16_hi(pre.x));
+      v[2] *= gelu_tanh_grad(bf16_lo(pre.y)); v[3] *= gelu_tanh_grad(bf16_hi(pre.y));
+      v[4] *= gelu_tanh_grad(bf16_lo(pre.z)); v[5] *= gelu_tanh_grad(bf16_hi(pre.z));
+      v[6] *= gelu_tanh_grad(bf16_lo(pre.w)); v[7] *= gelu_tanh_grad(bf16_hi(pre.w));
+    }
+    if (ep.resid) {
+      if (ep.drop_thr16) {
+        const uint64_t group = (static_cast<uint64_t>(m) * g.N + n) >> 3;
+        const uint32_t keep = dropout_keep8(ep.drop_seed, ep.drop_stream, group, ep.drop_thr16);
+        const float s = dropout_scale(ep.drop_thr16);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = ((keep >> j) & 1u) ? v[j] * s : 0.f;
+      }
+      const float4 r0 = *reinterpret_cast<const float4*>(ep.resid + (long long)m * ep.ldr + n);
+      const float4 r1 = *reinterpret_cast<const float4*>(ep.resid + (long long)m * ep.ldr + n + 4);
+      v[0] += r0.x; v[1] += r0.y; v[2] += r0.z; v[3] += r0.w;
+      v[4] += r1.x; v[5] += r1.y; v[6] += r1.z; v[7] += r1.w;
+    }
+    if (ep.out_fp32) {
+      float* o = static_cast<float*>(ep.out) + (long long)m * ep.ldo + n;
+      if (ep.accumulate) {
+        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o), "f"(v[0]),
+                     "f"(v[1]), "f"(v[2]), "f"(v[3])
+                     : "memory");
+        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o + 4), "f"(v[4]),
+                     "f"(v[5]), "f"(v[6]), "f"(v[7])
+                     : "memory");
+      } else {
+        *reinterpret_cast<float4*>(o) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(o + 4) = make_float4(v[4], v[5], v[6], v[7]);
+      }
+    } else {
+      uint4 o;
+      o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
+      o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
+      *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(ep.out) + (long long)m * ep.ldo + n) =
+          o;
+    }
+  }
+}
+
+template <int BN, int STAGES, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
+                         const __grid_constant__ CUtensorMap tmB, const GemmArgs g) {
+  constexpr int A_BYTES = BM * BK * 2;
+  constexpr int B_BYTES = BN * BK * 2;
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int TMEM_COLS = 2 * BN;  // 256 or 512, power of two
+  static_assert(TMEM_COLS == 256 || TMEM_COLS == 512 || TMEM_COLS == 128, "bad BN");
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + STAGES;
+  uint64_t* tfull_bar = bars + 2 * STAGES;
+  uint64_t* tempty_bar = bars + 2 * STAGES + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tfull_bar[i], 1);
+      mbar_init(&tempty_bar[i], NUM_EPI_WARPS);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int m_tiles = (g.M + BM - 1) / BM;
+  const int n_tiles = (g.N + BN - 1) / BN;
+  const int kb_total = (g.K + BK - 1) / BK;
+  const int kb_per = (kb_total + g.k_splits - 1) / g.k_splits;
+  const int num_units = m_tiles * n_tiles * g.k_splits;
+
+  if (warp == 0) {
+    // ------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
+        const int ks = u % g.k_splits;
+        const int tile = u / g.k_splits;
+        const int m0 = (tile / n_tiles) * BM;
+        const int n0 = (tile % n_tiles) * BN;
+        const int kb0 = ks * kb_per;
+        const int kb1 = min(kb_total, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
+            *abort_flag = ST_TIMEOUT_EMPTY;
+            atomicCAS(g.status, 0, ST_TIMEOUT_EMPTY);
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * STAGE_BYTES;
+          uint8_t* sb = sa + A_BYTES;
+          mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
+          const int k0 = kb * BK;
+          if constexpr (!A_MN) {
+            tma_load_2d(sa, &tmA, &full_bar[stage], k0, m0);
+          } else {
+#pragma unroll
+            for (int i = 0; i < BM / 64; ++i)
+              tma_load_2d(sa + i * (BK * 128), &tmA, &full_bar[stage], m0 + i * 64, k0);
+          }
+          if constexpr (!B_MN) {
+            tma_load_2d(sb, &tmB, &full_bar[stage], k0, n0);
+          } else {
+#pragma unroll
+            for (int i = 0; i < BN / 64; ++i)
+              tma_load_2d(sb + i * (BK * 128), &tmB, &full_bar[stage], n0 + i * 64, k0);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // --------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      constexpr uint32_t A_LBO = A_MN ? BK * 128 : 16;
+      constexpr uint32_t B_LBO = B_MN ? BK * 128 : 16;
+      constexpr uint32_t A_KADV = A_MN ? UMMA_K * 128 : UMMA_K * 2;  // bytes per UMMA_K step
+      constexpr uint32_t B_KADV = B_MN ? UMMA_K * 128 : UMMA_K * 2;
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t acc_phase[2] = {0, 0};
+      int it = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x, ++it) {
+        const int ks = u % g.k_splits;
+        const int kb0 = ks * kb_per;
+        const int kb1 = min(kb_total, kb0 + kb_per);
+        if (kb0 >= kb1) continue;
+        const int ab = it & 1;
+        if (!mbar_wait(&tempty_bar[ab], acc_phase[ab] ^ 1, abort_flag)) {
+          *abort_flag = ST_TIMEOUT_TMEM_EMPTY;
+          atomicCAS(g.status, 0, ST_TIMEOUT_TMEM_EMPTY);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + ab * BN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
+            *abort_flag = ST_TIMEOUT_FULL;
+            atomicCAS(g.status, 0, ST_TIMEOUT_FULL);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t adesc = make_sdesc_sw128(sa + k * A_KADV, A_LBO, 1024);
+            const uint64_t bdesc = make_sdesc_sw128(sb + k * B_KADV, B_LBO, 1024);
+            umma_bf16(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);  // frees the smem stage once these MMAs retire
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(&tfull_bar[ab]);  // accumulator complete -> epilogue
+        acc_phase[ab] ^= 1;
+      }
+    }
+  } else {
+    // ----------------------------------------------------------- epilogue
+    const int e = warp - 2;
+    const int quad = warp & 3;           // TMEM lane quarter this warp may read
+    const int half = e >> 2;             // which half of the BN columns
+    constexpr int COLS_PER_WARP = BN / 2;
+    uint32_t acc_phase[2] = {0, 0};
+    int it = 0;
+    for (int u = blockIdx.x; u < num_units; u += gridDim.x, ++it) {
+      const int ks = u % g.k_splits;
+      const int tile = u / g.k_splits;
+      const int kb0 = ks * kb_per;
+      const int kb1 = min(kb_total, kb0 + kb_per);
+      if (kb0 >= kb1) continue;
+      const int ab = it & 1;
+      const int m = (tile / n_tiles) * BM + quad * 32 + lane;
+      const int nbase = (tile % n_tiles) * BN + half * COLS_PER_WARP;
+      if (!mbar_wait(&tfull_bar[ab], acc_phase[ab], abort_flag)) {
+        *abort_flag = ST_TIMEOUT_TMEM_FULL;
+        atomicCAS(g.status, 0, ST_TIMEOUT_TMEM_FULL);
+        break;
+      }
+      acc_phase[ab] ^= 1;
+      tc_fence_after();
+      const uint32_t taddr =
+          tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + ab * BN + half * COLS_PER_WARP;
+#pragma unroll 1
+      for (int c = 0; c < COLS_PER_WARP / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(taddr + c * 32, r);
+        tmem_ld_wait();
+        epilogue_chunk<BN>(g, r, m, nbase + c * 32, m < g.M);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[ab]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int BN, int STAGES, bool A_MN, bool B_MN>
+static int launch(const void* A, long long lda, const void* B, long long ldb, const GemmArgs& g,
+                  int max_ctas, cudaStream_t stream) {
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (!A_MN) rc = make_tmap_2d(&tmA, A, g.M, g.K, lda, BM, BK, 2, true);
+  else       rc = make_tmap_2d(&tmA, A, g.K, g.M, lda, BK, 64, 2, true);
+  if (rc) return rc;
+  if (!B_MN) rc = make_tmap_2d(&tmB, B, g.N, g.K, ldb, BN, BK, 2, true);
+  else       rc = make_tmap_2d(&tmB, B, g.K, g.N, ldb, BK, 64, 2, true);
+  if (rc) return rc;
+  constexpr int SMEM = 1024 + STAGES * (BM * BK * 2 + BN * BK * 2) + 256;
+  auto kern = gemm_bf16_tcgen05_kernel<BN, STAGES, A_MN, B_MN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_set = true;
+  }
+  const int m_tiles = (g.M + BM - 1) / BM, n_tiles = (g.N + BN - 1) / BN;
+  const int units = m_tiles * n_tiles * g.k_splits;
+  int grid = units < max_ctas ? units : max_ctas;
+  if (grid < 1) grid = 1;
+  kern<<<grid, NUM_THREADS, SMEM, stream>>>(tmA, tmB, g);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace ab
+
+extern "C" int ab_gemm_bf16(const void* A, int a_mn, long long lda, const void* B, int b_mn,
+                            long long ldb, int M, int N, int K, const AbGemmEpilogue* ep,
+                            int k_splits, int max_ctas, int* status, cudaStream_t stream) {
+  using namespace ab;
+  if (M <= 0 || N <= 0 || K <= 0 || (N & 7) || (lda & 7) || (ldb & 7) || !ep || !ep->out ||
+      !status)
+    return -1;
+  if (k_splits < 1) k_splits = 1;
+  if (k_splits > 1 && !(ep->out_fp32 && ep->accumulate)) return -2;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) |
+       reinterpret_cast<uintptr_t>(ep->out)) & 15)
+    return -3;
+  GemmArgs g;
+  g.M = M; g.N = N; g.K = K; g.k_splits = k_splits; g.ep = *ep; g.status = status;
+  if (max_ctas <= 0) max_ctas = 148;
+  const bool narrow = (N <= 128);
+  if (narrow) {
+    if (!a_mn && !b_mn) return launch<128, 6, false, false>(A, lda, B, ldb, g, max_ctas, stream);
+    if (!a_mn && b_mn) return launch<128, 6, false, true>(A, lda, B, ldb, g, max_ctas, stream);
+    if (a_mn && !b_mn) return launch<128, 6, true, false>(A, lda, B, ldb, g, max_ctas, stream);
+    return launch<128, 6, true, true>(A, lda, B, ldb, g, max_ctas, stream);
+  }
+  if (!a_mn && !b_mn) return launch<256, 4, false, false>(A, lda, B, ldb, g, max_ctas, stream);
+  if (!a_mn && b_mn) return launch<256, 4, false, true>(A, lda, B, ldb, g, max_ctas, stream);
+  if (a_mn && !b_mn) return launch<256, 4, true, false>(A, lda, B, ldb, g, max_ctas, stream);
+  return launch<256, 4, true, true>(A, lda, B, ldb, g, max_ctas, stream);
+}

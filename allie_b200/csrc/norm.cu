@@ -1,0 +1,239 @@
+// LayerNorm / RMSNorm forward and backward for the fp32 residual stream.
+//
+// forward : x fp32 [M,d] -> y bf16 [M,d] (the A operand of the next GEMM), mean/rstd fp32 [M]
+// backward: dy bf16 (+ optional rank-2 term from the scalar heads) -> dx fp32, added to the
+//           incoming residual gradient; optionally also emits the bf16, dropout-masked copy of
+//           dx that the previous branch's projection GEMMs consume, and accumulates
+//           dgamma/dbeta into the fp32 gradient buffers with one atomic per column per block.
+// One warp owns one row; a lane owns float4 columns lane*4 + 128*i.
+#include "ptx.cuh"
+
+namespace ab {
+
+constexpr int LN_WARPS = 8;
+
+template <int NV_MAX>
+__global__ void __launch_bounds__(LN_WARPS * 32)
+ln_fwd_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
+              const float* __restrict__ beta, __nv_bfloat16* __restrict__ y,
+              float* __restrict__ mean_out, float* __restrict__ rstd_out, int M, int d, float eps,
+              int rms) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nv = d >> 7;  // float4 per lane
+  for (int row = blockIdx.x * LN_WARPS + warp; row < M; row += gridDim.x * LN_WARPS) {
+    const float4* xr = reinterpret_cast<const float4*>(x + (long long)row * d);
+    float4 v[NV_MAX];
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV_MAX; ++i)
+      if (i < nv) {
+        v[i] = xr[lane + 32 * i];
+        s += v[i].x + v[i].y + v[i].z + v[i].w;
+      }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    const float mean = rms ? 0.f : s / d;
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV_MAX; ++i)
+      if (i < nv) {
+        float a = v[i].x - mean, b = v[i].y - mean, c = v[i].z - mean, e = v[i].w - mean;
+        q += a * a + b * b + c * c + e * e;
+      }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) q += __shfl_xor_sync(0xffffffffu, q, o);
+    const float rstd = rsqrtf(q / d + eps);
+    if (lane == 0) {
+      if (mean_out) mean_out[row] = mean;
+      if (rstd_out) rstd_out[row] = rstd;
+    }
+    uint2* yr = reinterpret_cast<uint2*>(y + (long long)row * d);
+#pragma unroll
+    for (int i = 0; i < NV_MAX; ++i)
+      if (i < nv) {
+        const float4 g = __ldg(reinterpret_cast<const float4*>(gamma) + lane + 32 * i);
+        float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (beta) b = __ldg(reinterpret_cast<const float4*>(beta) + lane + 32 * i);
+        uint2 o;
+        o.x = pack_bf16x2((v[i].x - mean) * rstd * g.x + b.x, (v[i].y - mean) * rstd * g.y + b.y);
+        o.y = pack_bf16x2((v[i].z - mean) * rstd * g.z + b.z, (v[i].w - mean) * rstd * g.w + b.w);
+        yr[lane + 32 * i] = o;
+      }
+  }
+}
+
+struct LnBwdArgs {
+  const __nv_bfloat16* dy;   // [M,d] grad wrt normalised output (may be null if only heads feed)
+  const float* x;            // [M,d] forward input
+  const float* mean;         // [M]
+  const float* rstd;         // [M]
+  const float* gamma;        // [d]
+  const float* dres_in;      // [M,d] incoming residual gradient or null
+  float* dx;                 // [M,d] out (may alias dres_in)
+  __nv_bfloat16* dbranch;    // [M,d] out or null: bf16(dropout_mask * dx)
+  float* dgamma;             // [d] accumulated
+  float* dbeta;              // [d] accumulated or null
+  // optional rank-2 term: dy_eff[m,c] = dy[m,c] + s0[m]*w0[c] + s1[m]*w1[c]
+  const float* s0; const float* w0; const float* s1; const float* w1;
+  int M, d, rms;
+  unsigned long long drop_seed; unsigned int drop_stream, drop_thr16;
+};
+
+template <int NV_MAX>
+__global__ void __launch_bounds__(LN_WARPS * 32)
+ln_bwd_kernel(const LnBwdArgs a) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int d = a.d, nv = d >> 7;
+  float4 dg[NV_MAX], db[NV_MAX];
+#pragma unroll
+  for (int i = 0; i < NV_MAX; ++i) {
+    dg[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    db[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  const float dscale = dropout_scale(a.drop_thr16);
+  for (int row = blockIdx.x * LN_WARPS + warp; row < a.M; row += gridDim.x * LN_WARPS) {
+    const float mean = a.rms ? 0.f : a.mean[row];
+    const float rstd = a.rstd[row];
+    const float4* xr = reinterpret_cast<const float4*>(a.x + (long long)row * d);
+    const uint2* dyr = a.dy ? reinterpret_cast<const uint2*>(a.dy + (long long)row * d) : nullptr;
+    const float sc0 = a.s0 ? a.s0[row] : 0.f, sc1 = a.s1 ? a.s1[row] : 0.f;
+    float4 xh[NV_MAX], gy[NV_MAX];  // xhat and gamma*dy
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV_MAX; ++i)
+      if (i < nv) {
+        const int c4 = lane + 32 * i;
+        const float4 xv = xr[c4];
+        float4 dyv = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (dyr) {
+          const uint2 p = dyr[c4];
+          dyv = make_float4(bf16_lo(p.x), bf16_hi(p.x), bf16_lo(p.y), bf16_hi(p.y));
+        }
+        if (a.s0) {
+          const float4 w = __ldg(reinterpret_cast<const float4*>(a.w0) + c4);
+          dyv.x += sc0 * w.x; dyv.y += sc0 * w.y; dyv.z += sc0 * w.z; dyv.w += sc0 * w.w;
+        }
+        if (a.s1) {
+          const float4 w = __ldg(reinterpret_cast<const float4*>(a.w1) + c4);
+          dyv.x += sc1 * w.x; dyv.y += sc1 * w.y; dyv.z += sc1 * w.z; dyv.w += sc1 * w.w;
+        }
+        const float4 g = __ldg(reinterpret_cast<const float4*>(a.gamma) + c4);
+        xh[i] = make_float4((xv.x - mean) * rstd, (xv.y - mean) * rstd, (xv.z - mean) * rstd,
+                            (xv.w - mean) * rstd);
+        dg[i].x += dyv.x * xh[i].x; dg[i].y += dyv.y * xh[i].y;
+        dg[i].z += dyv.z * xh[i].z; dg[i].w += dyv.w * xh[i].w;
+        db[i].x += dyv.x; db[i].y += dyv.y; db[i].z += dyv.z; db[i].w += dyv.w;
+        gy[i] = make_float4(dyv.x * g.x, dyv.y * g.y, dyv.z * g.z, dyv.w * g.w);
+        s1 += gy[i].x + gy[i].y + gy[i].z + gy[i].w;
+        s2 += gy[i].x * xh[i].x + gy[i].y * xh[i].y + gy[i].z * xh[i].z + gy[i].w * xh[i].w;
+      }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+      s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+      s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+    }
+    const float m1 = a.rms ? 0.f : s1 / d, m2 = s2 / d;
+    const float4* rr =
+        a.dres_in ? reinterpret_cast<const float4*>(a.dres_in + (long long)row * d) : nullptr;
+    float4* dxr = reinterpret_cast<float4*>(a.dx + (long long)row * d);
+    uint2* dbr = a.dbranch ? reinterpret_cast<uint2*>(a.dbranch + (long long)row * d) : nullptr;
+#pragma unroll
+    for (int i = 0; i < NV_MAX; ++i)
+      if (i < nv) {
+        const int c4 = lane + 32 * i;
+        float4 o;
+        o.x = (gy[i].x - m1 - xh[i].x * m2) * rstd;
+        o.y = (gy[i].y - m1 - xh[i].y * m2) * rstd;
+        o.z = (gy[i].z - m1 - xh[i].z * m2) * rstd;
+        o.w = (gy[i].w - m1 - xh[i].w * m2) * rstd;
+        if (rr) {
+          const float4 r = rr[c4];
+          o.x += r.x; o.y += r.y; o.z += r.z; o.w += r.w;
+        }
+        dxr[c4] = o;
+        if (dbr) {
+          float4 m = o;
+          if (a.drop_thr16) {
+            const uint64_t e0 = static_cast<uint64_t>(row) * d + c4 * 4;
+            const uint32_t keep =
+                dropout_keep8(a.drop_seed, a.drop_stream, e0 >> 3, a.drop_thr16) >> (e0 & 7);
+            m.x = (keep & 1u) ? m.x * dscale : 0.f;
+            m.y = (keep & 2u) ? m.y * dscale : 0.f;
+            m.z = (keep & 4u) ? m.z * dscale : 0.f;
+            m.w = (keep & 8u) ? m.w * dscale : 0.f;
+          }
+          uint2 p;
+          p.x = pack_bf16x2(m.x, m.y);
+          p.y = pack_bf16x2(m.z, m.w);
+          dbr[c4] = p;
+        }
+      }
+  }
+  // block-level reduction of dgamma / dbeta, then one atomic per column
+  __shared__ float4 red[LN_WARPS][32];
+  for (int pass = 0; pass < 2; ++pass) {
+    float* dst = pass == 0 ? a.dgamma : a.dbeta;
+    if (!dst) continue;
+#pragma unroll
+    for (int i = 0; i < NV_MAX; ++i) {
+      if (i < nv) {  // uniform across the block
+        __syncthreads();
+        red[warp][lane] = pass == 0 ? dg[i] : db[i];
+        __syncthreads();
+        if (warp == 0) {
+          float4 t = red[0][lane];
+#pragma unroll
+          for (int w = 1; w < LN_WARPS; ++w) {
+            t.x += red[w][lane].x; t.y += red[w][lane].y;
+            t.z += red[w][lane].z; t.w += red[w][lane].w;
+          }
+          float* p = dst + (lane + 32 * i) * 4;
+          asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(t.x),
+                       "f"(t.y), "f"(t.z), "f"(t.w)
+                       : "memory");
+        }
+      }
+    }
+  }
+}
+
+}  // namespace ab
+
+extern "C" {
+
+// d must be a multiple of 128 and at most 2048.
+int ab_layernorm_fwd(const float* x, const float* gamma, const float* beta, void* y, float* mean,
+                     float* rstd, int M, int d, float eps, int rms, cudaStream_t stream) {
+  using namespace ab;
+  if (d % 128 != 0 || d > 2048 || M <= 0) return -1;
+  int grid = (M + LN_WARPS - 1) / LN_WARPS;
+  if (grid > 148 * 8) grid = 148 * 8;
+  if (d <= 1024)
+    ln_fwd_kernel<8><<<grid, LN_WARPS * 32, 0, stream>>>(x, gamma, beta, (__nv_bfloat16*)y, mean,
+                                                         rstd, M, d, eps, rms);
+  else
+    ln_fwd_kernel<16><<<grid, LN_WARPS * 32, 0, stream>>>(x, gamma, beta, (__nv_bfloat16*)y, mean,
+                                                          rstd, M, d, eps, rms);
+  return (int)cudaGetLastError();
+}
+
+int ab_layernorm_bwd(const void* dy, const float* x, const float* mean, const float* rstd,
+                     const float* gamma, const float* dres_in, float* dx, void* dbranch,
+                     float* dgamma, float* dbeta, const float* s0, const float* w0,
+                     const float* s1, const float* w1, int M, int d, int rms,
+                     unsigned long long drop_seed, unsigned int drop_stream,
+                     unsigned int drop_thr16, cudaStream_t stream) {
+  using namespace ab;
+  if (d % 128 != 0 || d > 2048 || M <= 0) return -1;
+  LnBwdArgs a;
+  a.dy = (const __nv_bfloat16*)dy; a.x = x; a.mean = mean; a.rstd = rstd; a.gamma = gamma;
+  a.dres_in = dres_in; a.dx = dx; a.dbranch = (__nv_bfloat16*)dbranch; a.dgamma = dgamma;
+  a.dbeta = dbeta; a.s0 = s0; a.w0 = w0; a.s1 = s1; a.w1 = w1; a.M = M; a.d = d; a.rms = rms;
+  a.drop_seed = drop_seed; a.drop_stream = drop_stream; a.drop_thr16 = drop_thr16;
+  int grid = (M + LN_WARPS - 1) / LN_WARPS;
+  if (grid > 148 * 2) grid = 148 * 2;
+  if (d <= 1024) ln_bwd_kernel<8><<<grid, LN_WARPS * 32, 0, stream>>>(a);
+  else           ln_bwd_kernel<16><<<grid, LN_WARPS * 32, 0, stream>>>(a);
+  return (int)cudaGetLastError();
+}
+}

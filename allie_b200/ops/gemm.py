@@ -1,0 +1,111 @@
+"""Python entry to the tcgen05 GEMM (``csrc/gemm_tc.cu``).
+
+``gemm(a, b, a_mn=..., b_mn=..., ...)`` computes ``C[M,N] = A[M,K] @ B[K,N]``
+where each operand may be given K-major or MN-major in memory:
+
+=========  ======================  ==========================
+flag       tensor passed           meaning
+=========  ======================  ==========================
+a_mn=False ``a`` of shape [M, K]   A as is
+a_mn=True  ``a`` of shape [K, M]   A = a.T
+b_mn=False ``b`` of shape [N, K]   B = b.T   (nn.Linear weight layout)
+b_mn=True  ``b`` of shape [K, N]   B as is   (GPT-2 Conv1D weight layout)
+=========  ======================  ==========================
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_int, c_longlong
+
+import torch
+
+from . import _lib
+
+_NUM_SMS: dict[int, int] = {}
+
+
+def num_sms() -> int:
+    dev = torch.cuda.current_device()
+    if dev not in _NUM_SMS:
+        _NUM_SMS[dev] = torch.cuda.get_device_properties(dev).multi_processor_count
+    return _NUM_SMS[dev]
+
+
+def pick_k_splits(M: int, N: int, K: int) -> int:
+    """Split K when the output alone has too few 128x256 tiles to fill the GPU
+    (the weight-gradient case: small output, very long contraction)."""
+    bn = 128 if N <= 128 else 256
+    tiles = ((M + 127) // 128) * ((N + bn - 1) // bn)
+    sms = num_sms()
+    if tiles >= 4 * sms:
+        return 1
+    kb = (K + 63) // 64
+    best, best_eff = 1, 0.0
+    for s in (1, 2, 3, 4, 6, 8, 12, 16, 24, 32):
+        if kb // s < 8:
+            break
+        units = tiles * s
+        waves = (units + sms - 1) // sms
+        eff = units / (waves * sms)
+        # prefer fewer splits on near-ties: each split re-reads/atomically adds C
+        if eff > best_eff + 0.04:
+            best, best_eff = s, eff
+    return best
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
+         out: torch.Tensor | None = None, out_dtype: torch.dtype = torch.bfloat16,
+         accumulate: bool = False, bias: torch.Tensor | None = None, act: int = 0,
+         aux: torch.Tensor | None = None, resid: torch.Tensor | None = None,
+         drop_p: float = 0.0, drop_seed: int = 0, drop_stream: int = 0,
+         alpha: float = 1.0, k_splits: int | None = None) -> torch.Tensor:
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    assert a.dim() == 2 and b.dim() == 2 and a.stride(1) == 1 and b.stride(1) == 1
+    if a_mn:
+        K, M = a.shape
+    else:
+        M, K = a.shape
+    if b_mn:
+        Kb, N = b.shape
+    else:
+        N, Kb = b.shape
+    assert K == Kb, (a.shape, b.shape, a_mn, b_mn)
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+        assert not accumulate
+    assert out.shape == (M, N) and out.stride(1) == 1
+    assert out.dtype in (torch.bfloat16, torch.float32)
+    out_fp32 = out.dtype == torch.float32
+    if accumulate:
+        assert out_fp32
+    if k_splits is None:
+        k_splits = pick_k_splits(M, N, K) if (accumulate and out_fp32) else 1
+    ep = _lib.GemmEpilogue()
+    ep.out = out.data_ptr()
+    ep.ldo = out.stride(0)
+    ep.out_fp32 = int(out_fp32)
+    ep.accumulate = int(accumulate)
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.numel() == N
+        ep.bias = bias.data_ptr()
+    ep.act = act
+    if act:
+        assert aux is not None and aux.dtype == torch.bfloat16 and aux.shape == (M, N)
+        ep.aux = aux.data_ptr()
+        ep.ldaux = aux.stride(0)
+    if resid is not None:
+        assert resid.dtype == torch.float32 and resid.shape == (M, N) and out_fp32
+        ep.resid = resid.data_ptr()
+        ep.ldr = resid.stride(0)
+        ep.drop_seed = drop_seed
+        ep.drop_stream = drop_stream
+        ep.drop_thr16 = _lib.dropout_thr16(drop_p)
+    ep.alpha = alpha
+    rc = _lib.cuda().ab_gemm_bf16(
+        _lib.ptr(a), c_int(int(a_mn)), c_longlong(a.stride(0)),
+        _lib.ptr(b), c_int(int(b_mn)), c_longlong(b.stride(0)),
+        c_int(M), c_int(N), c_int(K), ctypes.byref(ep), c_int(k_splits), c_int(num_sms()),
+        _lib.ptr(_lib.status_word()), _lib.stream_ptr())
+    if rc != 0:
+        raise RuntimeError(f"ab_gemm_bf16 failed with code {rc} for M={M} N={N} K={K}")
+    return out
