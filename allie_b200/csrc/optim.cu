@@ -136,3 +136,37 @@ int ab_cast_bf16(const float* src, void* dst, long long n, cudaStream_t stream) 
   return (int)cudaGetLastError();
 }
 }
+
+// ---------------------------------------------------------------------------------------------
+// colsum: out[n] += sum_m x[m][n] for a bf16 matrix (bias gradients).  A block covers
+// ROWS rows and 2048 columns; each thread owns 8 adjacent columns.
+namespace ab {
+__global__ void __launch_bounds__(256)
+colsum_bf16_kernel(const __nv_bfloat16* __restrict__ x, long long ld, int M, int N,
+                   float* __restrict__ out, int rows_per_blk) {
+  const int c = (blockIdx.x * 256 + threadIdx.x) * 8;
+  if (c >= N) return;
+  const int r0 = blockIdx.y * rows_per_blk;
+  const int r1 = min(M, r0 + rows_per_blk);
+  float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int r = r0; r < r1; ++r) {
+    const uint4 v = *reinterpret_cast<const uint4*>(x + (long long)r * ld + c);
+    s[0] += bf16_lo(v.x); s[1] += bf16_hi(v.x); s[2] += bf16_lo(v.y); s[3] += bf16_hi(v.y);
+    s[4] += bf16_lo(v.z); s[5] += bf16_hi(v.z); s[6] += bf16_lo(v.w); s[7] += bf16_hi(v.w);
+  }
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(out + c), "f"(s[0]),
+               "f"(s[1]), "f"(s[2]), "f"(s[3]) : "memory");
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(out + c + 4), "f"(s[4]),
+               "f"(s[5]), "f"(s[6]), "f"(s[7]) : "memory");
+}
+}  // namespace ab
+
+extern "C" int ab_colsum_bf16(const void* x, long long ld, int M, int N, float* out,
+                              cudaStream_t stream) {
+  if ((N & 7) || (ld & 7)) return -1;
+  const int rows_per_blk = 128;
+  dim3 grid((N / 8 + 255) / 256, (M + rows_per_blk - 1) / rows_per_blk);
+  ab::colsum_bf16_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, ld, M, N, out,
+                                                   rows_per_blk);
+  return (int)cudaGetLastError();
+}

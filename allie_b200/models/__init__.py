@@ -1,0 +1,72 @@
+"""Model construction (``initialize_model`` mirrors reference ``src/modeling/model.py:155-198``)."""
+from __future__ import annotations
+
+import logging
+import os
+from typing import Any
+
+import torch
+
+from ..config import ModelConfig, resolve_model_config
+from .oracle import (CausalLMWithControlToken, CausalLMWithRegressionHead, GPT2LM)
+
+logger = logging.getLogger(__name__)
+
+Model = GPT2LM | CausalLMWithControlToken | CausalLMWithRegressionHead
+
+
+def _load_pretrained_body(model: GPT2LM, base_model: str) -> bool:
+    """Copies GPT-2 body weights (everything except the token embedding / LM head) from a local
+    HF checkpoint directory and re-draws ``wte`` from N(mean, std) of the pretrained embedding
+    (reference ``model.py:175-188``).  Returns False when no local weights exist."""
+    cand = [os.path.join(base_model, n) for n in ("pytorch_model.bin", "model.safetensors")]
+    path = next((p for p in cand if os.path.exists(p)), None)
+    if path is None:
+        return False
+    if path.endswith(".safetensors"):
+        from safetensors.torch import load_file
+
+        sd = load_file(path)
+    else:
+        sd = torch.load(path, map_location="cpu")
+    sd = {k.removeprefix("transformer.") if not k.startswith("lm_head") else k: v for k, v in sd.items()}
+    wte = sd.get("wte.weight")
+    body = {"transformer." + k: v for k, v in sd.items()
+            if k not in ("wte.weight", "lm_head.weight") and not k.endswith(".attn.bias")
+            and not k.endswith(".attn.masked_bias")}
+    missing, unexpected = model.load_state_dict(body, strict=False)
+    if unexpected:
+        logger.warning("unexpected pretrained keys: %s", unexpected[:5])
+    if wte is not None:
+        torch.nn.init.normal_(model.transformer.wte.weight, wte.float().mean().item(),
+                              wte.float().std().item())
+    return True
+
+
+def initialize_model(tokenizer, base_model: str, use_control_token: bool = False,
+                     use_regression_head: bool = False, use_pretrained: bool = False,
+                     lm_loss_coef: float = 1.0, value_loss_coef: float = 1.0,
+                     **overrides: Any) -> Model:
+    cfg: ModelConfig = resolve_model_config(
+        base_model, vocab_size=len(tokenizer), bos_token_id=tokenizer.bos_token_id,
+        eos_token_id=tokenizer.eos_token_id, pad_token_id=tokenizer.pad_token_id, **overrides)
+    model: Any = GPT2LM(cfg)
+    if use_pretrained:
+        if not _load_pretrained_body(model, base_model):
+            logger.warning("use_pretrained: no local GPT-2 weights for %r (no network access); "
+                           "continuing from random initialisation", base_model)
+    if use_control_token:
+        model = CausalLMWithControlToken(model)
+    if use_regression_head:
+        model = CausalLMWithRegressionHead(model, lm_loss_coef, value_loss_coef)
+    return model
+
+
+def unwrap(model) -> tuple[GPT2LM, CausalLMWithControlToken | None, CausalLMWithRegressionHead | None]:
+    """(decoder, control wrapper or None, regression wrapper or None)."""
+    reg = model if isinstance(model, CausalLMWithRegressionHead) else None
+    inner = reg.model if reg is not None else model
+    ctrl = inner if isinstance(inner, CausalLMWithControlToken) else None
+    lm = ctrl.model if ctrl is not None else inner
+    assert isinstance(lm, GPT2LM)
+    return lm, ctrl, reg

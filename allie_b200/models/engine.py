@@ -1,0 +1,428 @@
+"""The Blackwell execution engine: runs the model as an explicit schedule of sm_100a kernels.
+
+There is no autograd and no tracing compiler on this path.  ``B200Engine`` takes the module tree
+of :mod:`allie_b200.models.oracle` (which only *holds* the parameters, under the reference's
+state-dict names), moves every parameter into one flat fp32 arena (with matching flat arenas for
+gradients, Adam moments and the bf16 shadow copy the tensor cores read), and then executes
+
+    forward  : unpack -> embed -> L x [LN, QKV GEMM, attention, proj GEMM(+bias+dropout+residual),
+               LN, fc GEMM(+bias+GELU), proj GEMM(+bias+dropout+residual)] -> LN -> lm_head GEMM
+               -> fused cross-entropy (loss and d logits in one pass) -> fused value/time heads
+    backward : hand-scheduled mirror image; weight gradients are accumulated in fp32 straight into
+               the gradient arena by the GEMM epilogue (split-K with vector atomics)
+    step     : global-norm clip + AdamW + bf16 refresh over the flat arenas (two launches)
+
+which replaces the autocast + ``torch.compile`` + fused-AdamW stack of the reference trainer
+(``src/modeling/trainer.py:193-289``).  The residual stream stays fp32 as it does there under
+autocast; GEMM operands are bf16 with fp32 accumulation.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Iterable
+
+import torch
+import torch.nn as nn
+
+from ..config import ModelConfig
+from ..data import TIME_MEAN, TIME_STDEV
+from ..ops import _lib, kernels as K
+from ..ops.gemm import gemm
+from . import unwrap
+from .oracle import Conv1D, MoEMLP
+
+ALIGN = 64  # elements; keeps every parameter view 256-byte (fp32) / 128-byte (bf16) aligned
+
+
+def partition_parameter_names(model: nn.Module) -> tuple[list[str], list[str]]:
+    """(decay, no_decay) parameter names, each sorted by name -- the optimizer ordering of the
+    reference (``src/modeling/utils.py:58-98``): weights of linear layers decay; biases, norm and
+    embedding weights (and an untied lm_head) do not."""
+    decay, no_decay = set(), set()
+    params = dict(model.named_parameters())
+    for mn, m in model.named_modules():
+        for pn, _p in m.named_parameters(recurse=False):
+            fpn = f"{mn}.{pn}" if mn else pn
+            if fpn not in params:
+                continue  # tied duplicate
+            if pn.endswith("bias"):
+                no_decay.add(fpn)
+            elif fpn.endswith("lm_head.weight"):
+                no_decay.add(fpn)
+            elif isinstance(m, (nn.Linear, Conv1D)) or type(m).__name__ == "ExpertBank":
+                decay.add(fpn)
+            else:
+                no_decay.add(fpn)
+    missing = params.keys() - (decay | no_decay)
+    assert not missing and not (decay & no_decay), (missing, decay & no_decay)
+    return sorted(decay), sorted(no_decay)
+
+
+class ParamArena:
+    """Flat storage for parameters / gradients / Adam state / bf16 shadows."""
+
+    def __init__(self, model: nn.Module, device: torch.device):
+        decay, no_decay = partition_parameter_names(model)
+        params = dict(model.named_parameters())
+        decay_set = set(decay)
+        self.names = decay + no_decay
+        self.offsets: dict[str, int] = {}
+        off = 0
+        self.decay_end = 0
+        for n in self.names:
+            self.offsets[n] = off
+            off += (params[n].numel() + ALIGN - 1) // ALIGN * ALIGN
+            if n in decay_set:
+                self.decay_end = off
+        self.total = off
+        self.master = torch.zeros(off, dtype=torch.float32, device=device)
+        self.grad = torch.zeros(off, dtype=torch.float32, device=device)
+        self.shadow = torch.zeros(off, dtype=torch.bfloat16, device=device)
+        self.exp_avg: torch.Tensor | None = None
+        self.exp_avg_sq: torch.Tensor | None = None
+        self.shapes = {n: tuple(params[n].shape) for n in self.names}
+        for n in self.names:
+            p = params[n]
+            view = self.view(self.master, n)
+            view.copy_(p.data.to(device=device, dtype=torch.float32))
+            p.data = view
+            p.grad = self.view(self.grad, n)
+        K.cast_bf16(self.master, self.shadow)
+
+    def view(self, flat: torch.Tensor, name: str) -> torch.Tensor:
+        o = self.offsets[name]
+        shape = self.shapes[name]
+        return flat[o:o + math.prod(shape)].view(shape)
+
+    def ensure_state(self) -> None:
+        if self.exp_avg is None:
+            self.exp_avg = torch.zeros_like(self.master)
+            self.exp_avg_sq = torch.zeros_like(self.master)
+
+    def refresh_shadow(self) -> None:
+        K.cast_bf16(self.master, self.shadow)
+
+
+@dataclass
+class LayerRefs:
+    ln1_w: torch.Tensor; ln1_b: torch.Tensor | None
+    ln2_w: torch.Tensor; ln2_b: torch.Tensor | None
+    qkv_w: torch.Tensor; qkv_b: torch.Tensor
+    o_w: torch.Tensor; o_b: torch.Tensor
+    fc_w: torch.Tensor | None = None; fc_b: torch.Tensor | None = None
+    pr_w: torch.Tensor | None = None; pr_b: torch.Tensor | None = None
+
+
+class B200Engine:
+    def __init__(self, model: nn.Module, device: str | torch.device = "cuda", seed: int = 1234):
+        self.device = torch.device(device)
+        assert self.device.type == "cuda"
+        if self.device.index is None:
+            self.device = torch.device("cuda", torch.cuda.current_device())
+        torch.cuda.set_device(self.device)
+        _lib.cuda()  # fail loudly if the kernel library is missing
+        self.model = model
+        self.lm, self.ctrl, self.reg = unwrap(model)
+        self.cfg: ModelConfig = self.lm.config
+        assert self.cfg.activation_function == "gelu_new"
+        model.to(self.device)
+        self.arena = ParamArena(model, self.device)
+        self.rms = self.cfg.norm_type == "rmsnorm"
+        self.seed = seed
+        self.step_count = 0      # optimizer steps taken
+        self.fwd_count = 0       # forward passes (dropout streams)
+        self._bufs: dict[tuple, dict] = {}
+        self._names = {id(p): n for n, p in model.named_parameters()}
+        self._bind()
+        self.gnorm_sq = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self.loss_acc = torch.zeros(4, dtype=torch.float32, device=self.device)
+        self.loss_out = torch.zeros(4, dtype=torch.float32, device=self.device)
+        self.counts = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self.kernel_launches = 0
+
+    # ---------------------------------------------------------------- views
+    def _n(self, p: nn.Parameter) -> str:
+        return self._names[id(p)]
+
+    def _views(self, p: nn.Parameter | None):
+        """(fp32 master view, bf16 shadow view, fp32 grad view) of a parameter."""
+        if p is None:
+            return None, None, None
+        n = self._n(p)
+        a = self.arena
+        return a.view(a.master, n), a.view(a.shadow, n), a.view(a.grad, n)
+
+    def _bind(self) -> None:
+        tr = self.lm.transformer
+        self.wte = self._views(tr.wte.weight)
+        self.wpe = self._views(tr.wpe.weight)
+        self.ctrl_w = self._views(self.ctrl.control_embeds.weight) if self.ctrl is not None else (None,) * 3
+        self.lnf_w = self._views(tr.ln_f.weight)
+        self.lnf_b = self._views(getattr(tr.ln_f, "bias", None))
+        self.layers = []
+        for blk in tr.h:
+            L = dict(
+                ln1_w=self._views(blk.ln_1.weight), ln1_b=self._views(getattr(blk.ln_1, "bias", None)),
+                ln2_w=self._views(blk.ln_2.weight), ln2_b=self._views(getattr(blk.ln_2, "bias", None)),
+                qkv_w=self._views(blk.attn.c_attn.weight), qkv_b=self._views(blk.attn.c_attn.bias),
+                o_w=self._views(blk.attn.c_proj.weight), o_b=self._views(blk.attn.c_proj.bias),
+                moe=isinstance(blk.mlp, MoEMLP), block=blk)
+            if not L["moe"]:
+                L.update(fc_w=self._views(blk.mlp.c_fc.weight), fc_b=self._views(blk.mlp.c_fc.bias),
+                         pr_w=self._views(blk.mlp.c_proj.weight), pr_b=self._views(blk.mlp.c_proj.bias))
+            self.layers.append(L)
+        if self.reg is not None:
+            self.wv = self._views(self.reg.value_head[0].weight)
+            self.bv = self._views(self.reg.value_head[0].bias)
+            self.wt = self._views(self.reg.time_head[0].weight)
+            self.bt = self._views(self.reg.time_head[0].bias)
+
+    # -------------------------------------------------------------- buffers
+    def _buffers(self, B: int, T: int, train: bool) -> dict:
+        key = (B, T, train)
+        if key in self._bufs:
+            return self._bufs[key]
+        cfg, dev = self.cfg, self.device
+        M, d, F, V = B * T, cfg.n_embd, cfg.ffn_dim, cfg.vocab_size
+        bf, f32, i32 = torch.bfloat16, torch.float32, torch.int32
+        e = lambda *s, dt=bf: torch.empty(*s, dtype=dt, device=dev)
+        buf = dict(
+            ids=e(M, dt=i32), pos=e(M, dt=i32), labels=e(M, dt=i32), vlab=e(M, dt=f32),
+            tlab=e(M, dt=f32), h=e(M, d), meanf=e(M, dt=f32), rstdf=e(M, dt=f32),
+            logits=e(M, V), value=e(M, dt=f32), time=e(M, dt=f32), dv=e(M, dt=f32), dt=e(M, dt=f32),
+        )
+        nl = cfg.n_layer
+        if train:
+            # every layer keeps what its backward needs
+            buf["x"] = [e(M, d, dt=f32) for _ in range(nl + 1)]
+            buf["xmid"] = [e(M, d, dt=f32) for _ in range(nl)]
+            for name, width in (("ln1", d), ("qkv", 3 * d), ("attn", d), ("ln2", d), ("pre", F), ("act", F)):
+                buf[name] = [e(M, width) for _ in range(nl)]
+            for name in ("mean1", "rstd1", "mean2", "rstd2"):
+                buf[name] = [e(M, dt=f32) for _ in range(nl)]
+            buf["lse"] = [e(B, cfg.n_head, T, dt=f32) for _ in range(nl)]
+            buf["dx"] = e(M, d, dt=f32)
+            buf["dyb"] = e(M, d)
+            buf["dpre"] = e(M, F)
+            buf["dqkv"] = e(M, 3 * d)
+            buf["dsmall"] = e(M, d)
+        else:
+            # inference: two ping-pong residual buffers and one set of scratch activations
+            x0, x1 = e(M, d, dt=f32), e(M, d, dt=f32)
+            buf["x"] = [x0 if i % 2 == 0 else x1 for i in range(nl + 1)]
+            xm = e(M, d, dt=f32)
+            buf["xmid"] = [xm] * nl
+            shared = {n: e(M, w) for n, w in (("ln1", d), ("qkv", 3 * d), ("attn", d), ("ln2", d), ("pre", F), ("act", F))}
+            for n, t in shared.items():
+                buf[n] = [t] * nl
+            for name in ("mean1", "rstd1", "mean2", "rstd2"):
+                t = e(M, dt=f32)
+                buf[name] = [t] * nl
+            lse = e(B, cfg.n_head, T, dt=f32)
+            buf["lse"] = [lse] * nl
+        self._bufs[key] = buf
+        return buf
+
+    # ------------------------------------------------------------ attention
+    def _attention_fwd(self, qkv, out, lse, B, T, p_drop, seed, stream_id):
+        from ..ops.attention import attention_fwd
+
+        attention_fwd(qkv, out, lse, B, T, self.cfg.n_head, self.cfg.head_dim, p_drop, seed, stream_id)
+
+    def _attention_bwd(self, qkv, out, lse, dout, dqkv, B, T, p_drop, seed, stream_id):
+        from ..ops.attention import attention_bwd
+
+        attention_bwd(qkv, out, lse, dout, dqkv, B, T, self.cfg.n_head, self.cfg.head_dim, p_drop,
+                      seed, stream_id)
+
+    # -------------------------------------------------------------- forward
+    def _drop(self, train: bool):
+        cfg = self.cfg
+        if not train:
+            return 0.0, 0.0, 0.0
+        return cfg.embd_pdrop, cfg.resid_pdrop, cfg.attn_pdrop
+
+    def forward(self, B: int, T: int, train: bool, seed: int, compute_loss: bool,
+                write_grad: bool) -> dict:
+        """Runs the forward schedule on the ids / labels already placed in the buffers."""
+        cfg = self.cfg
+        buf = self._buffers(B, T, train)
+        d, V, eps = cfg.n_embd, cfg.vocab_size, cfg.layer_norm_epsilon
+        p_emb, p_res, p_att = self._drop(train)
+        x = buf["x"]
+        K.embed_fwd(buf["ids"], buf["pos"], self.wte[0], self.wpe[0], self.ctrl_w[0], x[0], V, seed, 0, p_emb)
+        for l, L in enumerate(self.layers):
+            K.layernorm_fwd(x[l], L["ln1_w"][0], L["ln1_b"][0], buf["ln1"][l], buf["mean1"][l],
+                            buf["rstd1"][l], eps, self.rms)
+            gemm(buf["ln1"][l], L["qkv_w"][1], b_mn=True, out=buf["qkv"][l], bias=L["qkv_b"][0])
+            self._attention_fwd(buf["qkv"][l], buf["attn"][l], buf["lse"][l], B, T, p_att, seed, 3 + 3 * l)
+            gemm(buf["attn"][l], L["o_w"][1], b_mn=True, out=buf["xmid"][l], bias=L["o_b"][0],
+                 resid=x[l], drop_p=p_res, drop_seed=seed, drop_stream=1 + 3 * l)
+            K.layernorm_fwd(buf["xmid"][l], L["ln2_w"][0], L["ln2_b"][0], buf["ln2"][l], buf["mean2"][l],
+                            buf["rstd2"][l], eps, self.rms)
+            if L["moe"]:
+                raise NotImplementedError("MoE layers run through allie_b200.parallel.moe")
+            gemm(buf["ln2"][l], L["fc_w"][1], b_mn=True, out=buf["act"][l], bias=L["fc_b"][0], act=1,
+                 aux=buf["pre"][l])
+            gemm(buf["act"][l], L["pr_w"][1], b_mn=True, out=x[l + 1], bias=L["pr_b"][0],
+                 resid=buf["xmid"][l], drop_p=p_res, drop_seed=seed, drop_stream=2 + 3 * l)
+        nl = cfg.n_layer
+        K.layernorm_fwd(x[nl], self.lnf_w[0], self.lnf_b[0], buf["h"], buf["meanf"], buf["rstdf"], eps, self.rms)
+        gemm(buf["h"], self.wte[1], b_mn=False, out=buf["logits"])
+        if compute_loss:
+            self.loss_acc.zero_()
+            lm_coef = self.reg.lm_loss_coef if self.reg is not None else 1.0
+            K.ce_fwd_bwd(buf["logits"], buf["labels"], self.counts[0:1], lm_coef, self.loss_acc[0:1], write_grad)
+        if self.reg is not None:
+            vc = self.reg.value_loss_coef
+            K.heads_fwd(buf["h"], self.wv[0], self.bv[0], self.wt[0], self.bt[0],
+                        buf["vlab"] if compute_loss else None, buf["tlab"] if compute_loss else None,
+                        self.counts, vc, vc, buf["value"], buf["time"], buf["dv"], buf["dt"],
+                        self.loss_acc if compute_loss else None)
+        if compute_loss:
+            lm_coef = self.reg.lm_loss_coef if self.reg is not None else 1.0
+            vc = self.reg.value_loss_coef if self.reg is not None else 0.0
+            K.loss_finalize(self.loss_acc, self.counts, lm_coef, vc, vc, self.loss_out)
+        return buf
+
+    # ------------------------------------------------------------- backward
+    def backward(self, B: int, T: int, seed: int) -> None:
+        cfg = self.cfg
+        buf = self._buffers(B, T, True)
+        d, V = cfg.n_embd, cfg.vocab_size
+        p_emb, p_res, p_att = self._drop(True)
+        nl = cfg.n_layer
+        dx, dyb, dsmall = buf["dx"], buf["dyb"], buf["dsmall"]
+        dpre, dqkv = buf["dpre"], buf["dqkv"]
+        F = cfg.ffn_dim
+        dlogits = buf["logits"]
+        # lm head: d h = dlogits @ wte ; d wte += dlogits^T @ h
+        gemm(dlogits, self.wte[1], b_mn=True, out=dsmall)
+        gemm(dlogits, buf["h"], a_mn=True, b_mn=True, out=self.wte[2], accumulate=True)
+        s0 = w0 = s1 = w1 = None
+        if self.reg is not None:
+            K.heads_bwd_w(buf["h"], buf["dv"], buf["dt"], self.wv[2].view(-1), self.bv[2],
+                          self.wt[2].view(-1), self.bt[2])
+            s0, w0, s1, w1 = buf["dv"], self.wv[0].view(-1), buf["dt"], self.wt[0].view(-1)
+        K.layernorm_bwd(dsmall, buf["x"][nl], buf["meanf"], buf["rstdf"], self.lnf_w[0], None, dx, dyb,
+                        self.lnf_w[2], self.lnf_b[2], s0=s0, w0=w0, s1=s1, w1=w1, rms=self.rms,
+                        drop_seed=seed, drop_stream=2 + 3 * (nl - 1), drop_p=p_res)
+        for l in range(nl - 1, -1, -1):
+            L = self.layers[l]
+            # ---- MLP
+            gemm(buf["act"][l], dyb, a_mn=True, b_mn=True, out=L["pr_w"][2], accumulate=True)
+            K.colsum_bf16(dyb, L["pr_b"][2])
+            gemm(dyb, L["pr_w"][1], b_mn=False, out=dpre, act=2, aux=buf["pre"][l])
+            gemm(buf["ln2"][l], dpre, a_mn=True, b_mn=True, out=L["fc_w"][2], accumulate=True)
+            K.colsum_bf16(dpre, L["fc_b"][2])
+            gemm(dpre, L["fc_w"][1], b_mn=False, out=dsmall)
+            K.layernorm_bwd(dsmall, buf["xmid"][l], buf["mean2"][l], buf["rstd2"][l], L["ln2_w"][0], dx, dx,
+                            dyb, L["ln2_w"][2], L["ln2_b"][2], rms=self.rms, drop_seed=seed,
+                            drop_stream=1 + 3 * l, drop_p=p_res)
+            # ---- attention
+            gemm(buf["attn"][l], dyb, a_mn=True, b_mn=True, out=L["o_w"][2], accumulate=True)
+            K.colsum_bf16(dyb, L["o_b"][2])
+            gemm(dyb, L["o_w"][1], b_mn=False, out=dsmall)
+            self._attention_bwd(buf["qkv"][l], buf["attn"][l], buf["lse"][l], dsmall, dqkv, B, T, p_att,
+                                seed, 3 + 3 * l)
+            gemm(buf["ln1"][l], dqkv, a_mn=True, b_mn=True, out=L["qkv_w"][2], accumulate=True)
+            K.colsum_bf16(dqkv, L["qkv_b"][2])
+            gemm(dqkv, L["qkv_w"][1], b_mn=False, out=dsmall)
+            K.layernorm_bwd(dsmall, buf["x"][l], buf["mean1"][l], buf["rstd1"][l], L["ln1_w"][0], dx, dx,
+                            dyb if l > 0 else None, L["ln1_w"][2], L["ln1_b"][2], rms=self.rms,
+                            drop_seed=seed, drop_stream=max(0, 2 + 3 * (l - 1)), drop_p=p_res if l > 0 else 0.0)
+        K.embed_bwd(buf["ids"], buf["pos"], dx, self.wte[2], self.wpe[2], self.ctrl_w[2], V, seed, 0, p_emb)
+
+    # ------------------------------------------------------------- public API
+    def load_window(self, words: torch.Tensor) -> tuple[int, int]:
+        """words: uint32/int32 [B, T] raw training words already on the device."""
+        B, T = words.shape
+        buf = self._buffers(B, T, True)
+        tok_pad = self.cfg.pad_token_id if self.cfg.pad_token_id is not None else -1
+        K.unpack_window(words, self.cfg.vocab_size, tok_pad, TIME_MEAN, TIME_STDEV, buf["ids"], buf["pos"],
+                        buf["labels"], buf["vlab"], buf["tlab"], self.counts)
+        return B, T
+
+    def load_batch(self, batch: dict, train: bool) -> tuple[int, int]:
+        """Collated batch (input_ids / position_ids / labels / value_labels / time_labels)."""
+        ids = batch["input_ids"]
+        B, T = ids.shape
+        buf = self._buffers(B, T, train)
+        dev = self.device
+        buf["ids"].copy_(ids.reshape(-1).to(dev, non_blocking=True))
+        if "position_ids" in batch and batch["position_ids"] is not None:
+            buf["pos"].copy_(batch["position_ids"].reshape(-1).to(dev, non_blocking=True))
+        else:
+            buf["pos"].copy_(torch.arange(T, device=dev, dtype=torch.int32).repeat(B))
+        if batch.get("labels") is not None:
+            lab = batch["labels"].to(dev)
+            shifted = torch.full_like(lab, -100)
+            shifted[:, :-1] = lab[:, 1:]
+            buf["labels"].copy_(shifted.reshape(-1))
+            vl = batch.get("value_labels")
+            tl = batch.get("time_labels")
+            buf["vlab"].copy_((vl if vl is not None else torch.full((B, T), -100.0)).reshape(-1).to(dev))
+            buf["tlab"].copy_((tl if tl is not None else torch.full((B, T), -100.0)).reshape(-1).to(dev))
+            self.counts[0] = (buf["labels"] >= 0).sum()
+            self.counts[1] = (buf["vlab"] != -100).sum()
+            self.counts[2] = (buf["tlab"] != -100).sum()
+        return B, T
+
+    def _next_seed(self) -> int:
+        self.fwd_count += 1
+        return (self.seed * 0x9E3779B97F4A7C15 + self.fwd_count * 0xD1B54A32D192ED03) & ((1 << 64) - 1)
+
+    def micro_step(self, words: torch.Tensor) -> torch.Tensor:
+        """Forward + backward of one micro-batch of raw words; gradients accumulate.  Returns the
+        device tensor [loss, lm_loss, value_loss, time_loss] (no host sync)."""
+        B, T = self.load_window(words)
+        seed = self._next_seed()
+        self.forward(B, T, True, seed, True, True)
+        self.backward(B, T, seed)
+        return self.loss_out
+
+    def micro_step_batch(self, batch: dict) -> torch.Tensor:
+        B, T = self.load_batch(batch, True)
+        seed = self._next_seed()
+        self.forward(B, T, True, seed, True, True)
+        self.backward(B, T, seed)
+        return self.loss_out
+
+    @torch.no_grad()
+    def evaluate_batch(self, batch: dict, with_loss: bool = True) -> dict:
+        """Inference forward (no dropout).  Returns logits [B,T,V] bf16, value/time logits and, if
+        the batch has labels, the four losses."""
+        B, T = self.load_batch(batch, False)
+        has_labels = with_loss and batch.get("labels") is not None
+        buf = self.forward(B, T, False, 0, has_labels, False)
+        V = self.cfg.vocab_size
+        out = {"logits": buf["logits"].view(B, T, V), "hidden_states": (buf["h"].view(B, T, -1),)}
+        if self.reg is not None:
+            out["value_logits"] = buf["value"].view(B, T)
+            out["time_logits"] = buf["time"].view(B, T)
+        if has_labels:
+            lo = self.loss_out.clone()
+            out.update(loss=lo[0], lm_loss=lo[1], value_loss=lo[2], time_loss=lo[3])
+        return out
+
+    def zero_grad(self) -> None:
+        self.arena.grad.zero_()
+
+    def optimizer_step(self, lr: float, betas=(0.9, 0.95), eps: float = 1e-8, weight_decay: float = 0.0,
+                       grad_clip: float = 0.0, grad_scale: float = 1.0) -> None:
+        a = self.arena
+        a.ensure_state()
+        self.step_count += 1
+        gn = None
+        if grad_clip > 0:
+            self.gnorm_sq.zero_()
+            K.sumsq(a.grad, self.gnorm_sq)
+            gn = self.gnorm_sq
+        e = a.decay_end
+        if e > 0:
+            K.adamw(a.master[:e], a.grad[:e], a.exp_avg[:e], a.exp_avg_sq[:e], a.shadow[:e], lr, betas[0],
+                    betas[1], eps, weight_decay, self.step_count, gn, grad_clip, grad_scale)
+        if a.total > e:
+            K.adamw(a.master[e:], a.grad[e:], a.exp_avg[e:], a.exp_avg_sq[e:], a.shadow[e:], lr, betas[0],
+                    betas[1], eps, 0.0, self.step_count, gn, grad_clip, grad_scale)

@@ -1,0 +1,34 @@
+"""Causal self-attention over the packed QKV activation.
+
+``qkv`` is the [B*T, 3*d] bf16 output of the QKV GEMM (q | k | v, head h in columns
+h*hd .. (h+1)*hd of each third); ``out`` is [B*T, d] bf16 in the layout the output projection GEMM
+reads.  ``lse`` [B, H, T] keeps the log-sum-exp of each row for the backward pass.
+"""
+from __future__ import annotations
+
+from ctypes import c_float, c_int, c_uint, c_ulonglong
+
+import torch
+
+from . import _lib
+from ._lib import ptr, stream_ptr
+
+
+def attention_fwd(qkv, out, lse, B: int, T: int, H: int, hd: int, p_drop: float, seed: int,
+                  stream_id: int) -> None:
+    rc = _lib.cuda().ab_attn_fwd(ptr(qkv), ptr(out), ptr(lse), c_int(B), c_int(T), c_int(H), c_int(hd),
+                                 c_float(1.0 / hd ** 0.5), c_ulonglong(seed), c_uint(stream_id),
+                                 c_uint(_lib.dropout_thr16(p_drop)), ptr(_lib.status_word()),
+                                 stream_ptr())
+    if rc != 0:
+        raise RuntimeError(f"ab_attn_fwd failed with code {rc} (B={B} T={T} H={H} hd={hd})")
+
+
+def attention_bwd(qkv, out, lse, dout, dqkv, B: int, T: int, H: int, hd: int, p_drop: float,
+                  seed: int, stream_id: int) -> None:
+    rc = _lib.cuda().ab_attn_bwd(ptr(qkv), ptr(out), ptr(lse), ptr(dout), ptr(dqkv), c_int(B), c_int(T),
+                                 c_int(H), c_int(hd), c_float(1.0 / hd ** 0.5), c_ulonglong(seed),
+                                 c_uint(stream_id), c_uint(_lib.dropout_thr16(p_drop)),
+                                 ptr(_lib.status_word()), stream_ptr())
+    if rc != 0:
+        raise RuntimeError(f"ab_attn_bwd failed with code {rc} (B={B} T={T} H={H} hd={hd})")

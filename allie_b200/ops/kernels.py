@@ -1,0 +1,117 @@
+"""Python entries to the non-GEMM sm_100a kernels (norms, embedding, loss heads, optimizer).
+
+Every function launches on the current CUDA stream, allocates nothing unless an output argument is
+omitted, and never synchronises with the host.
+"""
+from __future__ import annotations
+
+from ctypes import c_float, c_int, c_longlong, c_uint, c_ulonglong
+
+import torch
+
+from . import _lib
+from ._lib import ptr, stream_ptr
+
+
+def _ck(rc: int, name: str) -> None:
+    if rc != 0:
+        raise RuntimeError(f"{name} failed with code {rc}")
+
+
+# ------------------------------------------------------------------ norms ---
+def layernorm_fwd(x, gamma, beta, y, mean, rstd, eps: float, rms: bool = False) -> None:
+    M, d = x.shape
+    _ck(_lib.cuda().ab_layernorm_fwd(ptr(x), ptr(gamma), ptr(beta), ptr(y), ptr(mean), ptr(rstd),
+                                     c_int(M), c_int(d), c_float(eps), c_int(int(rms)), stream_ptr()),
+        "ab_layernorm_fwd")
+
+
+def layernorm_bwd(dy, x, mean, rstd, gamma, dres_in, dx, dbranch, dgamma, dbeta, *, s0=None, w0=None,
+                  s1=None, w1=None, rms: bool = False, drop_seed: int = 0, drop_stream: int = 0,
+                  drop_p: float = 0.0) -> None:
+    M, d = x.shape
+    _ck(_lib.cuda().ab_layernorm_bwd(
+        ptr(dy), ptr(x), ptr(mean), ptr(rstd), ptr(gamma), ptr(dres_in), ptr(dx), ptr(dbranch),
+        ptr(dgamma), ptr(dbeta), ptr(s0), ptr(w0), ptr(s1), ptr(w1), c_int(M), c_int(d),
+        c_int(int(rms)), c_ulonglong(drop_seed), c_uint(drop_stream),
+        c_uint(_lib.dropout_thr16(drop_p)), stream_ptr()), "ab_layernorm_bwd")
+
+
+# -------------------------------------------------------------- embedding ---
+def unpack_window(words, vocab: int, pad_id: int, time_mean: float, time_std: float, ids, pos,
+                  lm_labels, value_labels, time_labels, counts) -> None:
+    B, T = words.shape
+    _ck(_lib.cuda().ab_unpack_window(ptr(words), c_int(B), c_int(T), c_int(vocab), c_int(pad_id),
+                                     c_float(time_mean), c_float(time_std), ptr(ids), ptr(pos),
+                                     ptr(lm_labels), ptr(value_labels), ptr(time_labels), ptr(counts),
+                                     stream_ptr()), "ab_unpack_window")
+
+
+def embed_fwd(ids, pos, wte, wpe, ctrl, x, vocab: int, drop_seed: int, drop_stream: int,
+              drop_p: float) -> None:
+    M, d = x.shape
+    _ck(_lib.cuda().ab_embed_fwd(ptr(ids), ptr(pos), ptr(wte), ptr(wpe), ptr(ctrl), ptr(x), c_int(M),
+                                 c_int(d), c_int(vocab), c_ulonglong(drop_seed), c_uint(drop_stream),
+                                 c_uint(_lib.dropout_thr16(drop_p)), stream_ptr()), "ab_embed_fwd")
+
+
+def embed_bwd(ids, pos, dx, dwte, dwpe, dctrl, vocab: int, drop_seed: int, drop_stream: int,
+              drop_p: float) -> None:
+    M, d = dx.shape
+    _ck(_lib.cuda().ab_embed_bwd(ptr(ids), ptr(pos), ptr(dx), ptr(dwte), ptr(dwpe), ptr(dctrl),
+                                 c_int(M), c_int(d), c_int(vocab), c_ulonglong(drop_seed),
+                                 c_uint(drop_stream), c_uint(_lib.dropout_thr16(drop_p)),
+                                 stream_ptr()), "ab_embed_bwd")
+
+
+# ------------------------------------------------------------------ losses ---
+def ce_fwd_bwd(logits, labels, n_valid, coef: float, loss_acc, write_grad: bool = True) -> None:
+    M, V = logits.shape
+    _ck(_lib.cuda().ab_ce_fwd_bwd(ptr(logits), ptr(labels), ptr(n_valid), c_float(coef), c_int(M),
+                                  c_int(V), c_longlong(logits.stride(0)), ptr(loss_acc),
+                                  c_int(int(write_grad)), stream_ptr()), "ab_ce_fwd_bwd")
+
+
+def heads_fwd(h, wv, bv, wt, bt, value_labels, time_labels, counts, value_coef: float,
+              time_coef: float, value_out, time_out, dv, dt, acc) -> None:
+    M, d = h.shape
+    _ck(_lib.cuda().ab_heads_fwd(ptr(h), ptr(wv), ptr(bv), ptr(wt), ptr(bt), ptr(value_labels),
+                                 ptr(time_labels), ptr(counts), c_float(value_coef),
+                                 c_float(time_coef), ptr(value_out), ptr(time_out), ptr(dv), ptr(dt),
+                                 ptr(acc), c_int(M), c_int(d), stream_ptr()), "ab_heads_fwd")
+
+
+def heads_bwd_w(h, dv, dt, dwv, dbv, dwt, dbt) -> None:
+    M, d = h.shape
+    _ck(_lib.cuda().ab_heads_bwd_w(ptr(h), ptr(dv), ptr(dt), ptr(dwv), ptr(dbv), ptr(dwt), ptr(dbt),
+                                   c_int(M), c_int(d), stream_ptr()), "ab_heads_bwd_w")
+
+
+def loss_finalize(acc, counts, lm_coef: float, value_coef: float, time_coef: float, out) -> None:
+    _ck(_lib.cuda().ab_loss_finalize(ptr(acc), ptr(counts), c_float(lm_coef), c_float(value_coef),
+                                     c_float(time_coef), ptr(out), stream_ptr()), "ab_loss_finalize")
+
+
+# --------------------------------------------------------------- optimizer ---
+def sumsq(g, out) -> None:
+    _ck(_lib.cuda().ab_sumsq(ptr(g), c_longlong(g.numel()), ptr(out), stream_ptr()), "ab_sumsq")
+
+
+def adamw(p, g, m, v, p_bf16, lr: float, beta1: float, beta2: float, eps: float, wd: float,
+          step: int, gnorm_sq=None, max_norm: float = 0.0, grad_scale: float = 1.0) -> None:
+    _ck(_lib.cuda().ab_adamw(ptr(p), ptr(g), ptr(m), ptr(v), ptr(p_bf16), c_longlong(p.numel()),
+                             c_float(lr), c_float(beta1), c_float(beta2), c_float(eps), c_float(wd),
+                             c_int(step), ptr(gnorm_sq), c_float(max_norm), c_float(grad_scale),
+                             stream_ptr()), "ab_adamw")
+
+
+def cast_bf16(src, dst) -> None:
+    _ck(_lib.cuda().ab_cast_bf16(ptr(src), ptr(dst), c_longlong(src.numel()), stream_ptr()),
+        "ab_cast_bf16")
+
+
+def colsum_bf16(x, out) -> None:
+    """out[n] += sum over rows of the bf16 matrix x (bias gradients)."""
+    M, N = x.shape
+    _ck(_lib.cuda().ab_colsum_bf16(ptr(x), c_longlong(x.stride(0)), c_int(M), c_int(N), ptr(out),
+                                   stream_ptr()), "ab_colsum_bf16")
