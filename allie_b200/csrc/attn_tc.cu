@@ -1,0 +1,673 @@
+// Causal flash attention on tcgen05 (forward; the backward kernels follow further down).
+//
+// One CTA owns one 128-row query tile of one (batch, head).  Per 128-row key/value tile:
+//   warp 5 (one thread) : S = Q K^T          -> TMEM (128 lanes = query rows, 128 fp32 columns)
+//   warps 0-3           : tcgen05.ld S, online softmax (row = thread), dropout, P -> smem (bf16,
+//                         128B-swizzled panels = the UMMA K-major A layout)
+//   warp 5              : PV = P V           -> TMEM (fresh, not accumulated)
+//   warps 0-3           : O = O * alpha + PV in registers
+//   warp 4 (one thread) : TMA loads of Q once and K/V tiles through a 2-stage ring
+// Q, K and V are read straight out of the packed [B*T, 3*d] QKV activation with 2-D TMA boxes
+// (64 columns x 128 rows), and O is written in the [B*T, d] layout the projection GEMM reads.
+// V is consumed MN-major (rows = keys), so no transposes exist anywhere.
+#include "ptx.cuh"
+
+namespace ab {
+
+constexpr int AT_BM = 128;   // query rows per CTA
+constexpr int AT_BN = 128;   // keys per inner tile
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct AttnArgs {
+  int B, T, H, hd;
+  float scale;              // 1/sqrt(hd)
+  unsigned long long seed;
+  unsigned int stream_id, thr16;
+  __nv_bfloat16* out;       // [B*T, H*hd]
+  float* lse;               // [B, H, T]
+  int* status;
+};
+
+// byte offset of the 16-byte chunk holding columns [8*c16, 8*c16+8) of row r inside a
+// 128-row x 64-column bf16 panel with 128-byte swizzle (what TMA SWIZZLE_128B writes)
+__device__ __forceinline__ uint32_t sw128_chunk(int r, int c16) {
+  return static_cast<uint32_t>(r * 128 + ((c16 ^ (r & 7)) << 4));
+}
+
+template <int HD>
+__global__ void __launch_bounds__(192)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnArgs a) {
+  constexpr int PANELS = HD / 64;               // 64-column panels per Q/K/V tile
+  constexpr int TILE_BYTES = 128 * HD * 2;      // one Q / K / V tile
+  constexpr int P_BYTES = 128 * 128 * 2;
+  constexpr int TMEM_COLS = (128 + HD) <= 256 ? 256 : 512;
+  constexpr uint32_t IDESC_S = make_idesc_bf16(128, 128, 0, 0);
+  constexpr uint32_t IDESC_PV = make_idesc_bf16(128, HD, 0, 1);
+
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  if (smem_u32(smem) & 1023) {  // swizzled tiles need a 1024-byte aligned base
+    if (threadIdx.x == 0) atomicCAS(a.status, 0, ST_BAD_ARGUMENT);
+    return;
+  }
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + TILE_BYTES;            // 2 stages
+  uint8_t* sV = sK + 2 * TILE_BYTES;        // 2 stages
+  uint8_t* sP = sV + 2 * TILE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + P_BYTES);
+  uint64_t* q_full = bars;                  // 1
+  uint64_t* k_full = bars + 1;              // 2
+  uint64_t* v_full = bars + 3;              // 2
+  uint64_t* k_empty = bars + 5;             // 2
+  uint64_t* v_empty = bars + 7;             // 2
+  uint64_t* s_full = bars + 9;
+  uint64_t* s_empty = bars + 10;
+  uint64_t* p_full = bars + 11;
+  uint64_t* pv_full = bars + 12;
+  uint64_t* pv_empty = bars + 13;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nqt = (a.T + AT_BM - 1) / AT_BM;
+  const int qt = nqt - 1 - blockIdx.x;      // heaviest tiles first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int nkv = qt + 1;                   // causal: key tiles 0..qt
+  const int d_model = a.H * HD;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1); mbar_init(&v_full[i], 1);
+      mbar_init(&k_empty[i], 1); mbar_init(&v_empty[i], 1);
+    }
+    mbar_init(s_full, 1); mbar_init(s_empty, 128);
+    mbar_init(p_full, 128); mbar_init(pv_full, 1); mbar_init(pv_empty, 128);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmQKV);
+  }
+  if (warp == 5) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base, tPV = tmem_base + 128;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      const int row_q = b * a.T + qt * AT_BM;
+      mbar_expect_tx(q_full, TILE_BYTES);
+#pragma unroll
+      for (int p = 0; p < PANELS; ++p)
+        tma_load_2d(sQ + p * 16384, &tmQKV, q_full, h * HD + p * 64, row_q);
+      for (int j = 0; j < nkv; ++j) {
+        const int st = j & 1;
+        const uint32_t par = ((j >> 1) & 1) ^ 1;
+        const int row_k = b * a.T + j * AT_BN;
+        if (!mbar_wait(&k_empty[st], par, abort_flag)) { *abort_flag = ST_TIMEOUT_EMPTY; atomicCAS(a.status, 0, ST_TIMEOUT_EMPTY); break; }
+        mbar_expect_tx(&k_full[st], TILE_BYTES);
+#pragma unroll
+        for (int p = 0; p < PANELS; ++p)
+          tma_load_2d(sK + st * TILE_BYTES + p * 16384, &tmQKV, &k_full[st],
+                      d_model + h * HD + p * 64, row_k);
+        if (!mbar_wait(&v_empty[st], par, abort_flag)) { *abort_flag = ST_TIMEOUT_EMPTY; atomicCAS(a.status, 0, ST_TIMEOUT_EMPTY); break; }
+        mbar_expect_tx(&v_full[st], TILE_BYTES);
+#pragma unroll
+        for (int p = 0; p < PANELS; ++p)
+          tma_load_2d(sV + st * TILE_BYTES + p * 16384, &tmQKV, &v_full[st],
+                      2 * d_model + h * HD + p * 64, row_k);
+      }
+    }
+  } else if (warp == 5) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      bool ok = mbar_wait(q_full, 0, abort_flag);
+      auto issue_qk = [&](int j) {
+        const int st = j & 1;
+        if (!mbar_wait(&k_full[st], (j >> 1) & 1, abort_flag)) return false;
+        if (j > 0 && !mbar_wait(s_empty, (j - 1) & 1, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t q0 = smem_u32(sQ), k0 = smem_u32(sK + st * TILE_BYTES);
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) {
+          const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
+          umma_bf16(tS, make_sdesc_sw128(q0 + off, 16, 1024), make_sdesc_sw128(k0 + off, 16, 1024),
+                    IDESC_S, k > 0);
+        }
+        umma_commit(&k_empty[st]);
+        umma_commit(s_full);
+        return true;
+      };
+      if (ok) ok = issue_qk(0);
+      for (int j = 0; j < nkv && ok; ++j) {
+        const int st = j & 1;
+        if (j + 1 < nkv) { ok = issue_qk(j + 1); if (!ok) break; }
+        if (!mbar_wait(&v_full[st], (j >> 1) & 1, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(p_full, j & 1, abort_flag)) { ok = false; break; }
+        if (j > 0 && !mbar_wait(pv_empty, (j - 1) & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t p0 = smem_u32(sP), v0 = smem_u32(sV + st * TILE_BYTES);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {  // 128 keys = 8 UMMA_K steps
+          const uint64_t adesc = make_sdesc_sw128(p0 + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024);
+          const uint64_t bdesc = make_sdesc_sw128(v0 + k * 2048, 16384, 1024);
+          umma_bf16(tPV, adesc, bdesc, IDESC_PV, k > 0);
+        }
+        umma_commit(&v_empty[st]);
+        umma_commit(pv_full);
+      }
+      if (!ok) { *abort_flag = ST_TIMEOUT_FULL; atomicCAS(a.status, 0, ST_TIMEOUT_FULL); }
+    }
+  } else {
+    // ---------------------------------------------------- softmax / output warps
+    const int r = threadIdx.x;                    // query row inside the tile = TMEM lane
+    const int q_idx = qt * AT_BM + r;
+    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    const float sl2 = a.scale * LOG2E;
+    float m_run = -INFINITY, l_run = 0.f;
+    float o[HD];
+#pragma unroll
+    for (int i = 0; i < HD; ++i) o[i] = 0.f;
+    const float dscale = dropout_scale(a.thr16);
+    const uint64_t row_elem0 = (static_cast<uint64_t>(b * a.H + h) * a.T + q_idx) * a.T;
+    bool ok = true;
+    for (int j = 0; j < nkv && ok; ++j) {
+      if (!mbar_wait(s_full, j & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const bool diag = (j == qt);
+      // pass 1: row maximum
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld32(tS + lane_addr + c * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float s = __uint_as_float(v[i]);
+          if (!diag || (c * 32 + i) <= r) mx = fmaxf(mx, s);
+        }
+      }
+      const float m_new = fmaxf(m_run, mx);       // finite: the diagonal always has column 0..r
+      const float alpha = ex2_fast((m_run - m_new) * sl2);
+      const float mb = m_new * sl2;
+      float rs = 0.f;
+      // pass 2: probabilities -> smem (bf16), row sum
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld32(tS + lane_addr + c * 32, v);
+        tmem_ld_wait();
+        float p[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float e = ex2_fast(__uint_as_float(v[i]) * sl2 - mb);
+          p[i] = (!diag || (c * 32 + i) <= r) ? e : 0.f;
+          rs += p[i];
+        }
+        if (a.thr16) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const uint64_t e0 = row_elem0 + j * AT_BN + c * 32 + g * 8;
+            const uint32_t keep = dropout_keep8(a.seed, a.stream_id, e0 >> 3, a.thr16);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) p[g * 8 + i] = ((keep >> i) & 1u) ? p[g * 8 + i] * dscale : 0.f;
+          }
+        }
+        uint8_t* panel = sP + (c >> 1) * 16384;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 w;
+          w.x = pack_bf16x2(p[g * 8 + 0], p[g * 8 + 1]); w.y = pack_bf16x2(p[g * 8 + 2], p[g * 8 + 3]);
+          w.z = pack_bf16x2(p[g * 8 + 4], p[g * 8 + 5]); w.w = pack_bf16x2(p[g * 8 + 6], p[g * 8 + 7]);
+          *reinterpret_cast<uint4*>(panel + sw128_chunk(r, (c & 1) * 4 + g)) = w;
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(s_empty);              // S may be overwritten by the next QK^T
+      fence_proxy_async_smem();          // P visible to the tensor core's async proxy
+      mbar_arrive(p_full);
+      l_run = l_run * alpha + rs;
+      m_run = m_new;
+      // fold in this tile's PV
+      if (!mbar_wait(pv_full, j & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld32(tPV + lane_addr + c * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * alpha + __uint_as_float(v[i]);
+      }
+      tc_fence_before();
+      mbar_arrive(pv_empty);
+    }
+    if (!ok) { *abort_flag = ST_TIMEOUT_TMEM_FULL; atomicCAS(a.status, 0, ST_TIMEOUT_TMEM_FULL); }
+    if (ok && q_idx < a.T) {
+      const float inv = 1.f / l_run;
+      __nv_bfloat16* orow = a.out + (static_cast<long long>(b) * a.T + q_idx) * d_model + h * HD;
+#pragma unroll
+      for (int g = 0; g < HD / 8; ++g) {
+        uint4 w;
+        w.x = pack_bf16x2(o[g * 8 + 0] * inv, o[g * 8 + 1] * inv);
+        w.y = pack_bf16x2(o[g * 8 + 2] * inv, o[g * 8 + 3] * inv);
+        w.z = pack_bf16x2(o[g * 8 + 4] * inv, o[g * 8 + 5] * inv);
+        w.w = pack_bf16x2(o[g * 8 + 6] * inv, o[g * 8 + 7] * inv);
+        *reinterpret_cast<uint4*>(orow + g * 8) = w;
+      }
+      if (a.lse) a.lse[(static_cast<long long>(b) * a.H + h) * a.T + q_idx] = m_run * a.scale + logf(l_run);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
+}
+
+}  // namespace ab
+
+// =================================================================================================
+// Backward.  Two launches of one templated kernel, both with threads = query rows:
+//   MODE 0 (key/value-stationary): CTA owns key tile j, streams query tiles i >= j, accumulates
+//           dV_j += P^T dO_i and dK_j += dS^T Q_i in TMEM.
+//   MODE 1 (query-stationary)    : CTA owns query tile i, streams key tiles j <= i, accumulates
+//           dQ_i += dS K_j in TMEM.
+// Both recompute S = Q K^T and dP = dO V^T per tile pair, so no atomics and no fp32 dQ buffer
+// are needed.  P and dS are written once to shared memory as [query row][key] bf16 panels; that
+// one layout is the K-major A operand of dS*K and the MN-major A operand of P^T*dO / dS^T*Q.
+// delta[b,h,t] = sum_c dO*O is produced by a small pre-kernel.
+namespace ab {
+
+struct AttnBwdArgs {
+  int B, T, H, hd;
+  float scale;
+  unsigned long long seed;
+  unsigned int stream_id, thr16;
+  const float* lse;          // [B,H,T]
+  const float* delta;        // [B,H,T]
+  __nv_bfloat16* dqkv;       // [B*T, 3*H*hd]
+  int* status;
+};
+
+__global__ void __launch_bounds__(256)
+attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
+                  float* __restrict__ delta, int B, int T, int H, int hd) {
+  const long long idx = blockIdx.x * 256ll + threadIdx.x;   // (row, head)
+  if (idx >= static_cast<long long>(B) * T * H) return;
+  const int hh = static_cast<int>(idx % H);
+  const long long row = idx / H;
+  const uint4* po = reinterpret_cast<const uint4*>(o + (row * H + hh) * hd);
+  const uint4* pd = reinterpret_cast<const uint4*>(dout + (row * H + hh) * hd);
+  float s = 0.f;
+  for (int c = 0; c < hd / 8; ++c) {
+    const uint4 x = po[c], y = pd[c];
+    s += bf16_lo(x.x) * bf16_lo(y.x) + bf16_hi(x.x) * bf16_hi(y.x);
+    s += bf16_lo(x.y) * bf16_lo(y.y) + bf16_hi(x.y) * bf16_hi(y.y);
+    s += bf16_lo(x.z) * bf16_lo(y.z) + bf16_hi(x.z) * bf16_hi(y.z);
+    s += bf16_lo(x.w) * bf16_lo(y.w) + bf16_hi(x.w) * bf16_hi(y.w);
+  }
+  const int bb = static_cast<int>(row / T), t = static_cast<int>(row % T);
+  delta[(static_cast<long long>(bb) * H + hh) * T + t] = s;
+}
+
+template <int HD, int MODE>
+__global__ void __launch_bounds__(192)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmDO,
+                const AttnBwdArgs a) {
+  constexpr int STAGES = HD <= 64 ? 2 : 1;
+  constexpr int PANELS = HD / 64;
+  constexpr int TILE_BYTES = 128 * HD * 2;
+  constexpr int P_BYTES = 128 * 128 * 2;
+  constexpr uint32_t IDESC_S = make_idesc_bf16(128, 128, 0, 0);     // Q K^T and dO V^T
+  constexpr uint32_t IDESC_T = make_idesc_bf16(128, HD, 1, 1);      // P^T dO, dS^T Q (both MN-major)
+  constexpr uint32_t IDESC_DQ = make_idesc_bf16(128, HD, 0, 1);     // dS K
+
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  if (smem_u32(smem) & 1023) {
+    if (threadIdx.x == 0) atomicCAS(a.status, 0, ST_BAD_ARGUMENT);
+    return;
+  }
+  uint8_t* sStatA = smem;                                  // MODE 0: K_j   MODE 1: Q_i
+  uint8_t* sStatB = sStatA + TILE_BYTES;                   // MODE 0: V_j   MODE 1: dO_i
+  uint8_t* sStrX = sStatB + TILE_BYTES;                    // MODE 0: Q_i   MODE 1: K_j   (STAGES)
+  uint8_t* sStrY = sStrX + STAGES * TILE_BYTES;            // MODE 0: dO_i  MODE 1: V_j   (STAGES)
+  uint8_t* sP = sStrY + STAGES * TILE_BYTES;
+  uint8_t* sDS = sP + P_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + P_BYTES);
+  uint64_t* stat_full = bars;
+  uint64_t* full = bars + 1;        // STAGES
+  uint64_t* empty = bars + 3;       // STAGES
+  uint64_t* sdp_full = bars + 5;
+  uint64_t* sdp_empty = bars + 6;
+  uint64_t* pds_full = bars + 7;
+  uint64_t* pds_empty = bars + 8;
+  uint64_t* acc_full = bars + 9;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nt = (a.T + 127) / 128;
+  const int h = blockIdx.y, b = blockIdx.z;
+  // MODE 0: own key tile `own`, iterate query tiles own..nt-1 (heaviest = small own first)
+  // MODE 1: own query tile `own`, iterate key tiles 0..own (heaviest = large own first)
+  const int own = MODE == 0 ? static_cast<int>(blockIdx.x) : nt - 1 - static_cast<int>(blockIdx.x);
+  const int n_iter = MODE == 0 ? nt - own : own + 1;
+  const int d_model = a.H * HD;
+
+  if (threadIdx.x == 0) {
+    mbar_init(stat_full, 1);
+    for (int i = 0; i < STAGES; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
+    mbar_init(sdp_full, 1); mbar_init(sdp_empty, 128);
+    mbar_init(pds_full, 128); mbar_init(pds_empty, 1); mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmQKV);
+    tma_prefetch_desc(&tmDO);
+  }
+  if (warp == 5) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base, tDP = tmem_base + 128, tAcc0 = tmem_base + 256,
+                 tAcc1 = tmem_base + 256 + HD;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      const int row_own = b * a.T + own * 128;
+      mbar_expect_tx(stat_full, 2 * TILE_BYTES);
+#pragma unroll
+      for (int p = 0; p < PANELS; ++p) {
+        if (MODE == 0) {
+          tma_load_2d(sStatA + p * 16384, &tmQKV, stat_full, d_model + h * HD + p * 64, row_own);
+          tma_load_2d(sStatB + p * 16384, &tmQKV, stat_full, 2 * d_model + h * HD + p * 64, row_own);
+        } else {
+          tma_load_2d(sStatA + p * 16384, &tmQKV, stat_full, h * HD + p * 64, row_own);
+          tma_load_2d(sStatB + p * 16384, &tmDO, stat_full, h * HD + p * 64, row_own);
+        }
+      }
+      for (int it = 0; it < n_iter; ++it) {
+        const int st = it % STAGES;
+        const uint32_t use = it / STAGES;
+        const int tile = MODE == 0 ? own + it : it;
+        const int row = b * a.T + tile * 128;
+        if (!mbar_wait(&empty[st], (use & 1) ^ 1, abort_flag)) {
+          *abort_flag = ST_TIMEOUT_EMPTY; atomicCAS(a.status, 0, ST_TIMEOUT_EMPTY); break;
+        }
+        mbar_expect_tx(&full[st], 2 * TILE_BYTES);
+#pragma unroll
+        for (int p = 0; p < PANELS; ++p) {
+          if (MODE == 0) {
+            tma_load_2d(sStrX + st * TILE_BYTES + p * 16384, &tmQKV, &full[st], h * HD + p * 64, row);
+            tma_load_2d(sStrY + st * TILE_BYTES + p * 16384, &tmDO, &full[st], h * HD + p * 64, row);
+          } else {
+            tma_load_2d(sStrX + st * TILE_BYTES + p * 16384, &tmQKV, &full[st],
+                        d_model + h * HD + p * 64, row);
+            tma_load_2d(sStrY + st * TILE_BYTES + p * 16384, &tmQKV, &full[st],
+                        2 * d_model + h * HD + p * 64, row);
+          }
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      bool ok = mbar_wait(stat_full, 0, abort_flag);
+      // group 1: S = Q K^T, dP = dO V^T
+      auto issue_sdp = [&](int it) {
+        const int st = it % STAGES;
+        if (!mbar_wait(&full[st], (it / STAGES) & 1, abort_flag)) return false;
+        if (it > 0 && !mbar_wait(sdp_empty, (it - 1) & 1, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t x = smem_u32(sStrX + st * TILE_BYTES), y = smem_u32(sStrY + st * TILE_BYTES);
+        const uint32_t sa = smem_u32(sStatA), sb = smem_u32(sStatB);
+        const uint32_t q = MODE == 0 ? x : sa, kk = MODE == 0 ? sa : x;
+        const uint32_t dO = MODE == 0 ? y : sb, vv = MODE == 0 ? sb : y;
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) {
+          const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
+          umma_bf16(tS, make_sdesc_sw128(q + off, 16, 1024), make_sdesc_sw128(kk + off, 16, 1024),
+                    IDESC_S, k > 0);
+        }
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) {
+          const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
+          umma_bf16(tDP, make_sdesc_sw128(dO + off, 16, 1024), make_sdesc_sw128(vv + off, 16, 1024),
+                    IDESC_S, k > 0);
+        }
+        umma_commit(sdp_full);
+        return true;
+      };
+      // group 2: the accumulating products
+      auto issue_acc = [&](int it) {
+        const int st = it % STAGES;
+        if (!mbar_wait(pds_full, it & 1, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t x = smem_u32(sStrX + st * TILE_BYTES), y = smem_u32(sStrY + st * TILE_BYTES);
+        const uint32_t p0 = smem_u32(sP), ds0 = smem_u32(sDS);
+        if (MODE == 0) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {   // contraction over 128 query rows
+            umma_bf16(tAcc0, make_sdesc_sw128(p0 + k * 2048, 16384, 1024),
+                      make_sdesc_sw128(y + k * 2048, 16384, 1024), IDESC_T, (it > 0 || k > 0));
+          }
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            umma_bf16(tAcc1, make_sdesc_sw128(ds0 + k * 2048, 16384, 1024),
+                      make_sdesc_sw128(x + k * 2048, 16384, 1024), IDESC_T, (it > 0 || k > 0));
+          }
+        } else {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {   // contraction over 128 keys
+            umma_bf16(tAcc0, make_sdesc_sw128(ds0 + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024),
+                      make_sdesc_sw128(x + k * 2048, 16384, 1024), IDESC_DQ, (it > 0 || k > 0));
+          }
+        }
+        umma_commit(&empty[st]);
+        umma_commit(pds_empty);
+        return true;
+      };
+      if (ok) ok = issue_sdp(0);
+      for (int it = 0; it < n_iter && ok; ++it) {
+        if (STAGES > 1 && it + 1 < n_iter) { ok = issue_sdp(it + 1); if (!ok) break; }
+        ok = issue_acc(it);
+        if (!ok) break;
+        if (STAGES == 1 && it + 1 < n_iter) ok = issue_sdp(it + 1);
+      }
+      if (ok) umma_commit(acc_full);
+      else { *abort_flag = ST_TIMEOUT_FULL; atomicCAS(a.status, 0, ST_TIMEOUT_FULL); }
+    }
+  } else {
+    // ------------------------------------------------------------ math warps
+    const int r = threadIdx.x;
+    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    const float sl2 = a.scale * LOG2E;
+    const float dscale = dropout_scale(a.thr16);
+    const long long bh = static_cast<long long>(b) * a.H + h;
+    bool ok = true;
+    for (int it = 0; it < n_iter && ok; ++it) {
+      const int qi = MODE == 0 ? own + it : own;     // query tile
+      const int kj = MODE == 0 ? own : it;           // key tile
+      const int q_idx = qi * 128 + r;
+      const bool q_ok = q_idx < a.T;
+      const float lse_l2 = q_ok ? a.lse[bh * a.T + q_idx] * LOG2E : 0.f;
+      const float dlt = q_ok ? a.delta[bh * a.T + q_idx] : 0.f;
+      const bool diag = (qi == kj);
+      const uint64_t row_elem0 = (static_cast<uint64_t>(bh) * a.T + q_idx) * a.T + kj * 128;
+      if (!mbar_wait(sdp_full, it & 1, abort_flag)) { ok = false; break; }
+      if (it > 0 && !mbar_wait(pds_empty, (it - 1) & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t sv[32], dv[32];
+        tmem_ld32(tS + lane_addr + c * 32, sv);
+        tmem_ld32(tDP + lane_addr + c * 32, dv);
+        tmem_ld_wait();
+        float p[32], ds[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const bool live = q_ok && (!diag || (c * 32 + i) <= r);
+          p[i] = live ? ex2_fast(__uint_as_float(sv[i]) * sl2 - lse_l2) : 0.f;
+          ds[i] = __uint_as_float(dv[i]);
+        }
+        if (a.thr16) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const uint64_t e0 = row_elem0 + c * 32 + g * 8;
+            const uint32_t keep = dropout_keep8(a.seed, a.stream_id, e0 >> 3, a.thr16);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const bool kp = (keep >> i) & 1u;
+              const float pd = kp ? p[g * 8 + i] * dscale : 0.f;          // dropped P (for dV)
+              const float dpe = kp ? ds[g * 8 + i] * dscale : 0.f;        // grad wrt softmax prob
+              ds[g * 8 + i] = p[g * 8 + i] * (dpe - dlt) * a.scale;
+              p[g * 8 + i] = pd;
+            }
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) ds[i] = p[i] * (ds[i] - dlt) * a.scale;
+        }
+        const uint32_t poff = (c >> 1) * 16384;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const uint32_t off = poff + sw128_chunk(r, (c & 1) * 4 + g);
+          uint4 w;
+          if (MODE == 0) {
+            w.x = pack_bf16x2(p[g * 8 + 0], p[g * 8 + 1]); w.y = pack_bf16x2(p[g * 8 + 2], p[g * 8 + 3]);
+            w.z = pack_bf16x2(p[g * 8 + 4], p[g * 8 + 5]); w.w = pack_bf16x2(p[g * 8 + 6], p[g * 8 + 7]);
+            *reinterpret_cast<uint4*>(sP + off) = w;
+          }
+          w.x = pack_bf16x2(ds[g * 8 + 0], ds[g * 8 + 1]); w.y = pack_bf16x2(ds[g * 8 + 2], ds[g * 8 + 3]);
+          w.z = pack_bf16x2(ds[g * 8 + 4], ds[g * 8 + 5]); w.w = pack_bf16x2(ds[g * 8 + 6], ds[g * 8 + 7]);
+          *reinterpret_cast<uint4*>(sDS + off) = w;
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(sdp_empty);
+      fence_proxy_async_smem();
+      mbar_arrive(pds_full);
+    }
+    if (ok && !mbar_wait(acc_full, 0, abort_flag)) ok = false;
+    if (!ok) { *abort_flag = ST_TIMEOUT_TMEM_FULL; atomicCAS(a.status, 0, ST_TIMEOUT_TMEM_FULL); }
+    if (ok) {
+      tc_fence_after();
+      const int t_idx = own * 128 + r;   // row of the owned tile (key row in MODE 0, query row in MODE 1)
+      __nv_bfloat16* base = a.dqkv + (static_cast<long long>(b) * a.T + t_idx) * (3 * d_model) + h * HD;
+      constexpr int NACC = MODE == 0 ? 2 : 1;
+#pragma unroll
+      for (int which = 0; which < NACC; ++which) {
+        // MODE 0: acc0 = dV -> third block, acc1 = dK -> second block.  MODE 1: acc0 = dQ -> first.
+        const uint32_t tacc = which == 0 ? tAcc0 : tAcc1;
+        __nv_bfloat16* dst = base + (MODE == 0 ? (which == 0 ? 2 * d_model : d_model) : 0);
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld32(tacc + lane_addr + c * 32, v);
+          tmem_ld_wait();
+          if (t_idx < a.T) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              uint4 w;
+              w.x = pack_bf16x2(__uint_as_float(v[g * 8 + 0]), __uint_as_float(v[g * 8 + 1]));
+              w.y = pack_bf16x2(__uint_as_float(v[g * 8 + 2]), __uint_as_float(v[g * 8 + 3]));
+              w.z = pack_bf16x2(__uint_as_float(v[g * 8 + 4]), __uint_as_float(v[g * 8 + 5]));
+              w.w = pack_bf16x2(__uint_as_float(v[g * 8 + 6]), __uint_as_float(v[g * 8 + 7]));
+              *reinterpret_cast<uint4*>(dst + c * 32 + g * 8) = w;
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+}
+
+}  // namespace ab
+
+// ------------------------------------------------------------------------------------ host side
+namespace ab {
+template <int HD>
+static int launch_attn_fwd(const CUtensorMap& tm, const AttnArgs& a, cudaStream_t stream) {
+  constexpr int SMEM = 5 * 128 * HD * 2 + 128 * 128 * 2 + 256;
+  auto kern = attn_fwd_kernel<HD>;
+  static bool attr = false;
+  if (!attr) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (e != cudaSuccess) return (int)e;
+    attr = true;
+  }
+  dim3 grid((a.T + 127) / 128, a.H, a.B);
+  kern<<<grid, 192, SMEM, stream>>>(tm, a);
+  return (int)cudaGetLastError();
+}
+
+template <int HD, int MODE>
+static int launch_attn_bwd(const CUtensorMap& tq, const CUtensorMap& td, const AttnBwdArgs& a,
+                           cudaStream_t stream) {
+  constexpr int STAGES = HD <= 64 ? 2 : 1;
+  constexpr int SMEM = (2 + 2 * STAGES) * 128 * HD * 2 + 2 * 128 * 128 * 2 + 256;
+  auto kern = attn_bwd_kernel<HD, MODE>;
+  static bool attr = false;
+  if (!attr) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (e != cudaSuccess) return (int)e;
+    attr = true;
+  }
+  dim3 grid((a.T + 127) / 128, a.H, a.B);
+  kern<<<grid, 192, SMEM, stream>>>(tq, td, a);
+  return (int)cudaGetLastError();
+}
+}  // namespace ab
+
+extern "C" {
+
+// qkv: bf16 [B*T, 3*H*hd]; out: bf16 [B*T, H*hd]; lse: fp32 [B,H,T] (may be null).
+// hd must be 64 or 128.  With dropout (thr16 > 0) T must be a multiple of 8.
+int ab_attn_fwd(const void* qkv, void* out, float* lse, int B, int T, int H, int hd, float scale,
+                unsigned long long seed, unsigned int stream_id, unsigned int thr16, int* status,
+                cudaStream_t stream) {
+  using namespace ab;
+  if ((hd != 64 && hd != 128) || B <= 0 || T <= 0 || (thr16 && (T & 7))) return -1;
+  CUtensorMap tm;
+  int rc = make_tmap_2d(&tm, qkv, (uint64_t)B * T, 3ull * H * hd, 3ull * H * hd, 128, 64, 2, true);
+  if (rc) return rc;
+  AttnArgs a;
+  a.B = B; a.T = T; a.H = H; a.hd = hd; a.scale = scale; a.seed = seed; a.stream_id = stream_id;
+  a.thr16 = thr16; a.out = (__nv_bfloat16*)out; a.lse = lse; a.status = status;
+  return hd == 64 ? launch_attn_fwd<64>(tm, a, stream) : launch_attn_fwd<128>(tm, a, stream);
+}
+
+// delta: fp32 scratch [B,H,T] owned by the caller.
+int ab_attn_bwd(const void* qkv, const void* out, const float* lse, const void* dout, void* dqkv,
+                float* delta, int B, int T, int H, int hd, float scale, unsigned long long seed,
+                unsigned int stream_id, unsigned int thr16, int* status, cudaStream_t stream) {
+  using namespace ab;
+  if ((hd != 64 && hd != 128) || B <= 0 || T <= 0 || (thr16 && (T & 7))) return -1;
+  CUtensorMap tq, td;
+  int rc = make_tmap_2d(&tq, qkv, (uint64_t)B * T, 3ull * H * hd, 3ull * H * hd, 128, 64, 2, true);
+  if (rc) return rc;
+  rc = make_tmap_2d(&td, dout, (uint64_t)B * T, (uint64_t)H * hd, (uint64_t)H * hd, 128, 64, 2, true);
+  if (rc) return rc;
+  const long long n = (long long)B * T * H;
+  attn_delta_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(
+      (const __nv_bfloat16*)out, (const __nv_bfloat16*)dout, delta, B, T, H, hd);
+  AttnBwdArgs a;
+  a.B = B; a.T = T; a.H = H; a.hd = hd; a.scale = scale; a.seed = seed; a.stream_id = stream_id;
+  a.thr16 = thr16; a.lse = lse; a.delta = delta; a.dqkv = (__nv_bfloat16*)dqkv; a.status = status;
+  if (hd == 64) {
+    rc = launch_attn_bwd<64, 0>(tq, td, a, stream);
+    if (rc) return rc;
+    return launch_attn_bwd<64, 1>(tq, td, a, stream);
+  }
+  rc = launch_attn_bwd<128, 0>(tq, td, a, stream);
+  if (rc) return rc;
+  return launch_attn_bwd<128, 1>(tq, td, a, stream);
+}
+}

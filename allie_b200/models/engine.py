@@ -104,16 +104,6 @@ class ParamArena:
         K.cast_bf16(self.master, self.shadow)
 
 
-@dataclass
-class LayerRefs:
-    ln1_w: torch.Tensor; ln1_b: torch.Tensor | None
-    ln2_w: torch.Tensor; ln2_b: torch.Tensor | None
-    qkv_w: torch.Tensor; qkv_b: torch.Tensor
-    o_w: torch.Tensor; o_b: torch.Tensor
-    fc_w: torch.Tensor | None = None; fc_b: torch.Tensor | None = None
-    pr_w: torch.Tensor | None = None; pr_b: torch.Tensor | None = None
-
-
 class B200Engine:
     def __init__(self, model: nn.Module, device: str | torch.device = "cuda", seed: int = 1234):
         self.device = torch.device(device)
@@ -203,6 +193,7 @@ class B200Engine:
                 buf[name] = [e(M, dt=f32) for _ in range(nl)]
             buf["lse"] = [e(B, cfg.n_head, T, dt=f32) for _ in range(nl)]
             buf["dx"] = e(M, d, dt=f32)
+            buf["delta"] = e(B, cfg.n_head, T, dt=f32)
             buf["dyb"] = e(M, d)
             buf["dpre"] = e(M, F)
             buf["dqkv"] = e(M, 3 * d)
@@ -233,7 +224,8 @@ class B200Engine:
     def _attention_bwd(self, qkv, out, lse, dout, dqkv, B, T, p_drop, seed, stream_id):
         from ..ops.attention import attention_bwd
 
-        attention_bwd(qkv, out, lse, dout, dqkv, B, T, self.cfg.n_head, self.cfg.head_dim, p_drop,
+        delta = self._buffers(B, T, True)["delta"]
+        attention_bwd(qkv, out, lse, dout, dqkv, delta, B, T, self.cfg.n_head, self.cfg.head_dim, p_drop,
                       seed, stream_id)
 
     # -------------------------------------------------------------- forward

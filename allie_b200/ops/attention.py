@@ -24,9 +24,10 @@ def attention_fwd(qkv, out, lse, B: int, T: int, H: int, hd: int, p_drop: float,
         raise RuntimeError(f"ab_attn_fwd failed with code {rc} (B={B} T={T} H={H} hd={hd})")
 
 
-def attention_bwd(qkv, out, lse, dout, dqkv, B: int, T: int, H: int, hd: int, p_drop: float,
+def attention_bwd(qkv, out, lse, dout, dqkv, delta, B: int, T: int, H: int, hd: int, p_drop: float,
                   seed: int, stream_id: int) -> None:
-    rc = _lib.cuda().ab_attn_bwd(ptr(qkv), ptr(out), ptr(lse), ptr(dout), ptr(dqkv), c_int(B), c_int(T),
+    """``delta`` is fp32 scratch [B, H, T] (row sums of dO*O, filled here)."""
+    rc = _lib.cuda().ab_attn_bwd(ptr(qkv), ptr(out), ptr(lse), ptr(dout), ptr(dqkv), ptr(delta), c_int(B), c_int(T),
                                  c_int(H), c_int(hd), c_float(1.0 / hd ** 0.5), c_ulonglong(seed),
                                  c_uint(stream_id), c_uint(_lib.dropout_thr16(p_drop)),
                                  ptr(_lib.status_word()), stream_ptr())
