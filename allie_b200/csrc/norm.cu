@@ -84,12 +84,6 @@ __global__ void __launch_bounds__(LN_WARPS * 32)
 ln_bwd_kernel(const LnBwdArgs a) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int d = a.d, nv = d >> 7;
-  float4 dg[NV_MAX], db[NV_MAX];
-#pragma unroll
-  for (int i = 0; i < NV_MAX; ++i) {
-    dg[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-    db[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-  }
   const float dscale = dropout_scale(a.drop_thr16);
   for (int row = blockIdx.x * LN_WARPS + warp; row < a.M; row += gridDim.x * LN_WARPS) {
     const float mean = a.rms ? 0.f : a.mean[row];
@@ -120,9 +114,6 @@ ln_bwd_kernel(const LnBwdArgs a) {
         const float4 g = __ldg(reinterpret_cast<const float4*>(a.gamma) + c4);
         xh[i] = make_float4((xv.x - mean) * rstd, (xv.y - mean) * rstd, (xv.z - mean) * rstd,
                             (xv.w - mean) * rstd);
-        dg[i].x += dyv.x * xh[i].x; dg[i].y += dyv.y * xh[i].y;
-        dg[i].z += dyv.z * xh[i].z; dg[i].w += dyv.w * xh[i].w;
-        db[i].x += dyv.x; db[i].y += dyv.y; db[i].z += dyv.z; db[i].w += dyv.w;
         gy[i] = make_float4(dyv.x * g.x, dyv.y * g.y, dyv.z * g.z, dyv.w * g.w);
         s1 += gy[i].x + gy[i].y + gy[i].z + gy[i].w;
         s2 += gy[i].x * xh[i].x + gy[i].y * xh[i].y + gy[i].z * xh[i].z + gy[i].w * xh[i].w;
@@ -169,32 +160,43 @@ ln_bwd_kernel(const LnBwdArgs a) {
         }
       }
   }
-  // block-level reduction of dgamma / dbeta, then one atomic per column
-  __shared__ float4 red[LN_WARPS][32];
-  for (int pass = 0; pass < 2; ++pass) {
-    float* dst = pass == 0 ? a.dgamma : a.dbeta;
-    if (!dst) continue;
-#pragma unroll
-    for (int i = 0; i < NV_MAX; ++i) {
-      if (i < nv) {  // uniform across the block
-        __syncthreads();
-        red[warp][lane] = pass == 0 ? dg[i] : db[i];
-        __syncthreads();
-        if (warp == 0) {
-          float4 t = red[0][lane];
-#pragma unroll
-          for (int w = 1; w < LN_WARPS; ++w) {
-            t.x += red[w][lane].x; t.y += red[w][lane].y;
-            t.z += red[w][lane].z; t.w += red[w][lane].w;
-          }
-          float* p = dst + (lane + 32 * i) * 4;
-          asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(t.x),
-                       "f"(t.y), "f"(t.z), "f"(t.w)
-                       : "memory");
-        }
-      }
+}
+
+// dgamma[c] += sum_m dy[m,c] * xhat[m,c], dbeta[c] += sum_m dy[m,c].  Column-parallel: a block
+// covers 1024 columns (warp w -> columns 128w.., lane -> one float4) and a chunk of rows, so every
+// row read is one contiguous 4 KB segment; partial sums stay in registers and finish with one
+// vector atomic per thread.
+__global__ void __launch_bounds__(256)
+ln_bwd_params_kernel(const LnBwdArgs a, int rows_per_blk) {
+  const int c = (blockIdx.y * 256 + threadIdx.x) * 4;
+  if (c >= a.d) return;
+  const int r0 = blockIdx.x * rows_per_blk;
+  const int r1 = min(a.M, r0 + rows_per_blk);
+  float4 dg = make_float4(0.f, 0.f, 0.f, 0.f), db = dg;
+  float4 w0 = dg, w1 = dg;
+  if (a.s0) w0 = __ldg(reinterpret_cast<const float4*>(a.w0 + c));
+  if (a.s1) w1 = __ldg(reinterpret_cast<const float4*>(a.w1 + c));
+#pragma unroll 4
+  for (int r = r0; r < r1; ++r) {
+    const float4 xv = *reinterpret_cast<const float4*>(a.x + (long long)r * a.d + c);
+    float4 dyv = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (a.dy) {
+      const uint2 p = *reinterpret_cast<const uint2*>(a.dy + (long long)r * a.d + c);
+      dyv = make_float4(bf16_lo(p.x), bf16_hi(p.x), bf16_lo(p.y), bf16_hi(p.y));
     }
+    if (a.s0) { const float s = a.s0[r]; dyv.x += s * w0.x; dyv.y += s * w0.y; dyv.z += s * w0.z; dyv.w += s * w0.w; }
+    if (a.s1) { const float s = a.s1[r]; dyv.x += s * w1.x; dyv.y += s * w1.y; dyv.z += s * w1.z; dyv.w += s * w1.w; }
+    const float mean = a.rms ? 0.f : a.mean[r];
+    const float rstd = a.rstd[r];
+    dg.x += dyv.x * (xv.x - mean) * rstd; dg.y += dyv.y * (xv.y - mean) * rstd;
+    dg.z += dyv.z * (xv.z - mean) * rstd; dg.w += dyv.w * (xv.w - mean) * rstd;
+    db.x += dyv.x; db.y += dyv.y; db.z += dyv.z; db.w += dyv.w;
   }
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(a.dgamma + c), "f"(dg.x),
+               "f"(dg.y), "f"(dg.z), "f"(dg.w) : "memory");
+  if (a.dbeta)
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(a.dbeta + c), "f"(db.x),
+                 "f"(db.y), "f"(db.z), "f"(db.w) : "memory");
 }
 
 }  // namespace ab
@@ -231,9 +233,15 @@ int ab_layernorm_bwd(const void* dy, const float* x, const float* mean, const fl
   a.dbeta = dbeta; a.s0 = s0; a.w0 = w0; a.s1 = s1; a.w1 = w1; a.M = M; a.d = d; a.rms = rms;
   a.drop_seed = drop_seed; a.drop_stream = drop_stream; a.drop_thr16 = drop_thr16;
   int grid = (M + LN_WARPS - 1) / LN_WARPS;
-  if (grid > 148 * 2) grid = 148 * 2;
+  if (grid > 148 * 16) grid = 148 * 16;
   if (d <= 1024) ln_bwd_kernel<8><<<grid, LN_WARPS * 32, 0, stream>>>(a);
   else           ln_bwd_kernel<16><<<grid, LN_WARPS * 32, 0, stream>>>(a);
+  if (dgamma) {
+    int rows_per_blk = (M + 148 * 4 - 1) / (148 * 4);
+    if (rows_per_blk < 8) rows_per_blk = 8;
+    dim3 g2((M + rows_per_blk - 1) / rows_per_blk, (d + 1023) / 1024);
+    ln_bwd_params_kernel<<<g2, 256, 0, stream>>>(a, rows_per_blk);
+  }
   return (int)cudaGetLastError();
 }
 }

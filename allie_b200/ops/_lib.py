@@ -14,6 +14,12 @@ import torch
 _LIB_DIR = Path(__file__).resolve().parent.parent / "lib"
 _cuda_lib = None
 _host_lib = None
+LAUNCHES = 0   # kernels of this package launched so far (counted by the Python entry points)
+
+
+def count_launches(n: int = 1) -> None:
+    global LAUNCHES
+    LAUNCHES += n
 
 
 class NativeLibraryMissing(RuntimeError):

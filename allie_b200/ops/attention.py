@@ -22,6 +22,7 @@ def attention_fwd(qkv, out, lse, B: int, T: int, H: int, hd: int, p_drop: float,
                                  stream_ptr())
     if rc != 0:
         raise RuntimeError(f"ab_attn_fwd failed with code {rc} (B={B} T={T} H={H} hd={hd})")
+    _lib.count_launches(1)
 
 
 def attention_bwd(qkv, out, lse, dout, dqkv, delta, B: int, T: int, H: int, hd: int, p_drop: float,
@@ -33,3 +34,4 @@ def attention_bwd(qkv, out, lse, dout, dqkv, delta, B: int, T: int, H: int, hd: 
                                  ptr(_lib.status_word()), stream_ptr())
     if rc != 0:
         raise RuntimeError(f"ab_attn_bwd failed with code {rc} (B={B} T={T} H={H} hd={hd})")
+    _lib.count_launches(3)  # delta + key/value-stationary + query-stationary kernels

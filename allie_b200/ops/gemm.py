@@ -108,4 +108,5 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         _lib.ptr(_lib.status_word()), _lib.stream_ptr())
     if rc != 0:
         raise RuntimeError(f"ab_gemm_bf16 failed with code {rc} for M={M} N={N} K={K}")
+    _lib.count_launches(1)
     return out

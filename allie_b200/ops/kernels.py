@@ -16,6 +16,7 @@ from ._lib import ptr, stream_ptr
 def _ck(rc: int, name: str) -> None:
     if rc != 0:
         raise RuntimeError(f"{name} failed with code {rc}")
+    _lib.count_launches(1)
 
 
 # ------------------------------------------------------------------ norms ---

@@ -1,0 +1,356 @@
+"""Distributed trainer with the reference's public surface (``src/modeling/trainer.py:37-409``):
+``Trainer(config, **trainer_config)`` then ``save_config / setup_dataloaders / setup_model / train /
+test / cleanup`` plus ``load_ckpt / save_ckpt / get_lr / evaluate / validate``.  Same YAML keys, same
+log lines, same checkpoint files.
+
+What differs is everything underneath.  On a CUDA device the model runs through
+:class:`allie_b200.models.engine.B200Engine` (hand-scheduled sm_100a kernels, flat parameter
+arenas, device-side loss accumulation), the training window crosses PCIe as raw ``uint32`` words
+from pinned memory and is unpacked on the GPU, gradients of the data-parallel ranks are combined
+by :class:`allie_b200.parallel.ddp.GradSync`, and the loss is read back asynchronously instead of
+a ``loss.item()`` every step.  On CPU the same class drives the plain-PyTorch oracle model with
+``torch.optim.AdamW`` (gloo for multi-process runs), which is what the CPU tests exercise.
+
+Semantics kept on purpose: micro-step gradients are summed, not averaged over
+``gradient_accumulation_steps`` (``trainer.py:270-280``); gradients are averaged over ranks (the
+synchronous data parallelism the reference intends); only rank 0 validates, logs and checkpoints.
+``torch_compile`` is accepted and ignored.
+"""
+from __future__ import annotations
+
+import logging
+import math
+import os
+import time
+from collections import defaultdict, deque
+from os.path import join
+from typing import Any, Iterable, Optional
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from ..config import Config, save_config as _save_config
+from ..data import Batch, UCITokenizer, json_to_game
+from ..utils.logging import setup_logging
+from ..utils.metrics import MetricsSink
+
+logger = logging.getLogger(__name__)
+
+
+def to_device(batch: Batch, device: str, blocking: bool = False) -> Batch:
+    if str(device).startswith("cuda"):
+        return {k: v.pin_memory().to(device, non_blocking=not blocking) for k, v in batch.items()}
+    return batch
+
+
+def count_params(model: torch.nn.Module) -> int:
+    return sum(p.numel() for p in model.parameters())
+
+
+class WindowSampler:
+    """Random fixed-length windows out of the flat token stream (``trainer.py:159-167``), gathered
+    straight into a pinned ``int32`` staging buffer (the words are < 2^31 only in their low 31 bits,
+    so they are carried bit-exact as int32)."""
+
+    def __init__(self, data: np.ndarray, batch_size: int, seq_len: int, pin: bool, depth: int = 4):
+        self.data, self.B, self.T = data, batch_size, seq_len
+        self.n = len(data) - seq_len
+        assert self.n > 0, "training stream shorter than one window"
+        self.bufs = [torch.empty((batch_size, seq_len), dtype=torch.int32, pin_memory=pin)
+                     for _ in range(depth)]
+        self.i = 0
+        self.rng = np.random.default_rng(int.from_bytes(os.urandom(8), "little"))
+        self.offs = np.arange(seq_len, dtype=np.int64)[None, :]
+
+    def next(self) -> torch.Tensor:
+        buf = self.bufs[self.i % len(self.bufs)]
+        self.i += 1
+        starts = self.rng.integers(0, self.n, size=(self.B, 1))
+        win = self.data[(starts + self.offs).reshape(-1)]
+        buf.numpy().view(np.uint32)[...] = np.asarray(win, dtype=np.uint32).reshape(self.B, self.T)
+        return buf
+
+
+class Trainer:
+    def __init__(self, config: Config | dict | None = None, output_dir: str = "output/debug",
+                 seed: int = 42, backend: str = "nccl", device: str = "cuda", dtype: str = "bfloat16",
+                 torch_compile: bool = True, wandb_run_name: Optional[str] = None,
+                 wandb_run_id: Optional[str] = None, gradient_accumulation_steps: int = 1,
+                 batch_size: int = 16, lr: float = 6e-4, min_lr: float = 6e-5, decay_lr: bool = True,
+                 weight_decay: float = 1e-1, beta1: float = 0.9, beta2: float = 0.95,
+                 grad_clip: float = 1.0, warmup_iters: int = 2000, decay_iters: int = 200000,
+                 max_iters: int = 600000, eval_interval: int = 2000, log_interval: int = 10,
+                 save_interval: int = 500,
+                 # extensions (absent from the reference schema, all optional)
+                 shard_optimizer: bool = False, grad_sync: str = "auto", use_wandb: bool = True):
+        self.config = config
+        self.output_dir = output_dir
+        self.backend = backend
+        self.dtype = dtype
+        self.torch_compile = torch_compile
+        self.gradient_accumulation_steps = gradient_accumulation_steps
+        self.batch_size = batch_size
+        self.ddp = int(os.environ.get("RANK", -1)) != -1
+        if self.ddp:
+            use_cuda = str(device).startswith("cuda") and torch.cuda.is_available()
+            if not dist.is_initialized():
+                dist.init_process_group(backend=backend if use_cuda else "gloo")
+            self.ddp_rank = int(os.environ["RANK"])
+            self.ddp_world_size = int(os.environ["WORLD_SIZE"])
+            self.ddp_local_rank = int(os.environ.get("LOCAL_RANK", 0))
+            if use_cuda:
+                self.device = f"cuda:{self.ddp_local_rank}"
+                torch.cuda.set_device(self.device)
+            else:
+                self.device = "cpu"
+            self.master_process = self.ddp_rank == 0
+            seed += self.ddp_rank
+        else:
+            self.device = device if (device == "cpu" or torch.cuda.is_available()) else "cpu"
+            self.ddp_rank, self.ddp_world_size, self.ddp_local_rank = 0, 1, 0
+            self.master_process = True
+        self.device_type = "cuda" if "cuda" in str(self.device) else "cpu"
+        self.metrics = MetricsSink(enabled=self.master_process and use_wandb, project="chess-lm",
+                                   name=wandb_run_name, run_id=wandb_run_id,
+                                   config=config.to_container() if isinstance(config, Config) else config)
+        if self.master_process:
+            os.makedirs(output_dir, exist_ok=True)
+            setup_logging(output_dir, file=True)
+        self.seed = seed
+        self.lr, self.min_lr, self.decay_lr = lr, min_lr, decay_lr
+        self.weight_decay = weight_decay
+        self.betas = (beta1, beta2)
+        self.grad_clip = grad_clip
+        self.warmup_iters, self.decay_iters, self.max_iters = warmup_iters, decay_iters, max_iters
+        self.eval_interval, self.log_interval, self.save_interval = eval_interval, log_interval, save_interval
+        self.shard_optimizer = shard_optimizer
+        self.grad_sync_mode = grad_sync
+        self.iter_num = 0
+        self.best_val_loss = float("inf")
+        self.engine = None
+        self.optimizer = None
+        self.grad_sync = None
+
+    # ------------------------------------------------------------------ setup
+    def save_config(self, config: Config | dict) -> None:
+        logger.info("saving experiment configuration")
+        if self.master_process:
+            _save_config(config, join(self.output_dir, "config.yaml"))
+
+    def setup_dataloaders(self, tokenizer: UCITokenizer, train_dataset, val_dataset: Iterable,
+                          test_dataset: Iterable) -> None:
+        self.tokenizer = tokenizer
+        self.train_dataset, self.val_dataset, self.test_dataset = train_dataset, val_dataset, test_dataset
+        self.sampler = WindowSampler(train_dataset, self.batch_size, tokenizer.max_length,
+                                     pin=self.device_type == "cuda")
+
+    def _eval_batches(self, dataset):
+        rows = list(dataset)
+        for i in range(0, len(rows), self.batch_size):
+            games = [json_to_game(d) for d in rows[i:i + self.batch_size]]
+            yield self.tokenizer.pad_and_collate(games)
+
+    def setup_model(self, model: torch.nn.Module) -> None:
+        from ..models.engine import partition_parameter_names
+        from ..parallel.ddp import GradSync, broadcast_parameters
+
+        self.model = model
+        logger.info(f"model parameters: {count_params(model)/1e9:.2f}B")
+        if self.device_type == "cuda":
+            from ..models.engine import B200Engine
+
+            self.engine = B200Engine(model, self.device, seed=self.seed)
+            logger.info("using the fused sm_100a AdamW over flat parameter arenas")
+        else:
+            model.to(self.device)
+            decay, no_decay = partition_parameter_names(model)
+            params = dict(model.named_parameters())
+            self.optimizer = torch.optim.AdamW(
+                [{"params": [params[n] for n in decay], "weight_decay": self.weight_decay},
+                 {"params": [params[n] for n in no_decay], "weight_decay": 0.0}],
+                lr=self.lr, betas=self.betas)
+        logger.info("optimizer initialized")
+        if self.ddp:
+            broadcast_parameters(model, self.engine)
+            self.grad_sync = GradSync(model, self.engine, mode=self.grad_sync_mode)
+        self.load_ckpt("last")
+
+    # --------------------------------------------------------------- training
+    def get_lr(self) -> float:
+        it = self.iter_num
+        if not self.decay_lr:
+            return self.lr
+        assert self.lr >= self.min_lr
+        if it < self.warmup_iters:
+            return self.lr * it / self.warmup_iters
+        if it > self.decay_iters:
+            return self.min_lr
+        ratio = (it - self.warmup_iters) / (self.decay_iters - self.warmup_iters)
+        assert 0 <= ratio <= 1
+        return self.min_lr + 0.5 * (1.0 + math.cos(math.pi * ratio)) * (self.lr - self.min_lr)
+
+    def train_step(self, windows: list[torch.Tensor] | None = None) -> torch.Tensor:
+        """One optimizer step = ``gradient_accumulation_steps`` micro-batches, gradient
+        synchronisation across ranks, clip, AdamW.  ``windows``: one [B, T] tensor of raw words per
+        micro-step (host tensors are copied to the device here); drawn from the sampler when
+        omitted.  Returns the loss of the last micro-batch as a 0-dim tensor without
+        synchronising."""
+        lr = self.get_lr()
+        ga = self.gradient_accumulation_steps
+        if self.engine is not None:
+            eng = self.engine
+            loss = None
+            for ms in range(ga):
+                w = windows[ms] if windows is not None else self.sampler.next()
+                if not w.is_cuda:
+                    w = w.to(eng.device, non_blocking=True)
+                loss = eng.micro_step(w)
+            world = self.ddp_world_size
+            if self.grad_sync is not None and self.grad_sync.fused:
+                # reduce-scatter + clip + AdamW + all-gather in the NVLink kernels
+                self.grad_sync.fused_step(lr, self.betas, 1e-8, self.weight_decay, self.grad_clip)
+            else:
+                if self.grad_sync is not None:
+                    self.grad_sync.all_reduce_sum()
+                eng.optimizer_step(lr, self.betas, 1e-8, self.weight_decay, self.grad_clip,
+                                   grad_scale=1.0 / world)
+            eng.zero_grad()
+            return loss[0]
+        # CPU oracle path
+        for g in self.optimizer.param_groups:
+            g["lr"] = lr
+        self.model.train()
+        loss = None
+        for ms in range(ga):
+            w = windows[ms] if windows is not None else self.sampler.next()
+            batch = self.tokenizer.unpack(w.to(torch.int64) & 0xFFFFFFFF)
+            loss = self.model(**batch)["loss"]
+            loss.backward()
+        if self.grad_sync is not None:
+            self.grad_sync.all_reduce_mean_torch()
+        if self.grad_clip > 0.0:
+            torch.nn.utils.clip_grad_norm_(self.model.parameters(), self.grad_clip)
+        self.optimizer.step()
+        self.optimizer.zero_grad(set_to_none=True)
+        return loss.detach()
+
+    def train(self) -> None:
+        t_start = t0 = time.time()
+        losses: deque = deque(maxlen=100)
+        pending: deque = deque()          # (device loss tensor, event) not yet read back
+        tokens_per_step = (self.batch_size * self.tokenizer.max_length *
+                           self.gradient_accumulation_steps * self.ddp_world_size)
+        while True:
+            lr = self.get_lr()
+            if self.eval_interval > 0 and self.iter_num % self.eval_interval == 0 and self.master_process:
+                self._drain(pending, losses, all_=True)
+                val_log = self.validate()
+                self.metrics.log({"iter": self.iter_num, "lr": lr,
+                                  "train/loss": sum(losses) / len(losses) if losses else None} | val_log)
+            if self.save_interval > 0 and self.iter_num % self.save_interval == 0 and self.master_process:
+                self.save_ckpt("last")
+            loss = self.train_step()
+            if loss.is_cuda:
+                host = torch.empty((), dtype=torch.float32, pin_memory=True)
+                host.copy_(loss, non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record()
+                pending.append((host, ev))
+                self._drain(pending, losses, all_=False)
+            else:
+                losses.append(float(loss))
+            if self.log_interval >= 0 and self.iter_num % self.log_interval == 0:
+                self._drain(pending, losses, all_=True)
+                t1 = time.time()
+                dt, t0 = t1 - t0, t1
+                loss_mean = sum(losses) / max(1, len(losses))
+                steps = max(1, self.log_interval) if self.iter_num > 0 else 1
+                logger.info(f"train - iter {self.iter_num}: loss {loss_mean:.4f}, time {dt:.2f}s")
+                logger.debug(f"throughput {tokens_per_step * steps / max(dt, 1e-9):.0f} tokens/s")
+            self.iter_num += 1
+            if self.iter_num > self.max_iters:
+                break
+        self._drain(pending, losses, all_=True)
+        logger.info(f"training complete! total time {time.time() - t_start:.2f}s")
+
+    @staticmethod
+    def _drain(pending: deque, losses: deque, all_: bool) -> None:
+        while pending and (all_ or pending[0][1].query()):
+            host, ev = pending.popleft()
+            ev.synchronize()
+            losses.append(float(host))
+
+    # ------------------------------------------------------------- evaluation
+    @torch.no_grad()
+    def evaluate(self, dataset) -> dict[str, float]:
+        assert self.master_process
+        t0 = time.time()
+        losses = defaultdict(list)
+        keys = ["lm_loss", "value_loss", "time_loss", "loss"]
+        if self.engine is None:
+            self.model.eval()
+        for batch in self._eval_batches(dataset):
+            if self.engine is not None:
+                out = self.engine.evaluate_batch(batch)
+            else:
+                out = self.model(**batch)
+            assert "loss" in out
+            for k in keys:
+                if k in out:
+                    losses[k].append(float(out[k]))
+        if self.engine is None:
+            self.model.train()
+        return {k: sum(v) / len(v) for k, v in losses.items()} | {"time": time.time() - t0}
+
+    def generate_log_string(self, eval_data: dict[str, float]) -> str:
+        keys = ["lm_loss", "value_loss", "time_loss", "loss"]
+        return ", ".join([f"{k} {eval_data[k]:.4f}" for k in keys if k in eval_data] +
+                         [f"time {eval_data['time']:.2f}s"])
+
+    def validate(self) -> dict[str, float]:
+        out = self.evaluate(self.val_dataset)
+        if "loss" not in out:
+            logger.info(f"val - iter {self.iter_num}: no validation data")
+            return {}
+        logger.info(f"val - iter {self.iter_num}: {self.generate_log_string(out)}")
+        if out["loss"] < self.best_val_loss:
+            logger.info(f"new best val loss {out['loss']:.4f}")
+            self.best_val_loss = out["loss"]
+            self.save_ckpt("best")
+        return {f"val/{k}": v for k, v in out.items() if k.endswith("loss")}
+
+    def test(self) -> None:
+        self.load_ckpt("best")
+        if self.master_process:
+            out = self.evaluate(self.test_dataset)
+            if "loss" in out:
+                logger.info(f"test: loss {out['loss']:.4f}, time {out['time']:.2f}s")
+                self.metrics.log({"iter": self.iter_num, "test/loss": out["loss"]})
+
+    def cleanup(self) -> None:
+        if self.ddp and dist.is_initialized():
+            dist.destroy_process_group()
+        self.metrics.finish()
+        logger.info("all done! exiting gracefully...")
+
+    # ------------------------------------------------------------ checkpoints
+    def load_ckpt(self, ckpt_type: str) -> None:
+        from .checkpoint import load_checkpoint
+
+        path = join(self.output_dir, f"{ckpt_type}.pt")
+        if os.path.exists(path):
+            meta = load_checkpoint(path, self.model, self.engine, self.optimizer, self.device)
+            self.iter_num, self.best_val_loss = meta["iter_num"], meta["best_val_loss"]
+            logger.info(f"loading {ckpt_type} checkpoint from iter {self.iter_num}: "
+                        f"best_val_loss {self.best_val_loss}")
+        else:
+            logger.info(f"no {ckpt_type} checkpoint found, start training from scratch")
+
+    def save_ckpt(self, ckpt_type: str) -> None:
+        from .checkpoint import save_checkpoint
+
+        path = join(self.output_dir, f"{ckpt_type}.pt")
+        save_checkpoint(path, self.model, self.engine, self.optimizer, self.iter_num, self.best_val_loss,
+                        lr=self.lr, betas=self.betas, weight_decay=self.weight_decay)
+        logger.info(f"saved checkpoint to {path}")

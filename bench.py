@@ -1,0 +1,368 @@
+"""Headline benchmark: training throughput (tokens/s) of the GPT-2-medium-shaped Allie model.
+
+Config (fixed): 24 layers, d_model 1024, 16 heads, MLP 4096, context 512, vocab 2048, policy +
+value + think-time losses, dropout 0.1 as the reference trains, bf16 tensor-core math with fp32
+residual stream / master weights, global batch 512 sequences per optimizer step (micro-batch 64 per
+GPU, gradient accumulation 8 / n_gpus: strong scaling), AdamW with global-norm clipping.
+Synthetic uniform-random move tokens with two leading ELO tokens per window, random-init weights.
+
+    python bench.py --gpus N --steps K --warmup W            # this framework
+    python bench.py --impl reference --gpus N ...             # the unmodified reference trainer
+
+For N > 1 launch under ``python -m torch.distributed.run --nproc-per-node N``.  Rank 0 prints one
+JSON line.  ``value`` is timed on the device with CUDA events around exactly K optimizer steps,
+max over ranks, inputs already resident on the GPU; ``e2e`` times the same K steps through
+``Trainer.train_step`` with the per-step host->device copy of the raw windows from pinned memory
+and a device->host read of the loss.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+MODEL = dict(n_layer=24, n_embd=1024, n_head=16, n_positions=1024)
+SEQ_LEN, VOCAB_MULT, GLOBAL_BATCH, MICRO_BATCH = 512, 128, 512, 64
+BASELINE_TOKENS_PER_S = 2.17e5   # derived from the reference README: 8x RTX A6000, ~2 weeks
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.rows: list[list[str]] = []
+        self.proc = None
+        self.idx = gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 9:
+                continue
+            try:
+                sm.append(float(r[1])); mx = float(r[2])
+            except ValueError:
+                continue
+            for name, val in zip(names, r[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def synthetic_stream(n_words: int, vocab: int, seq_len: int, seed: int):
+    """Uniform random move tokens with think times and outcomes packed like real data; every
+    ``seq_len`` words start with two ELO pseudo-tokens and a time-control token."""
+    import numpy as np
+
+    rng = np.random.default_rng(seed)
+    ids = rng.integers(0, 1968, size=n_words, dtype=np.uint32)
+    secs = rng.integers(0, 30, size=n_words, dtype=np.uint32)
+    words = ids | ((secs + 1) << 16)
+    starts = np.arange(0, n_words - 3, seq_len)
+    outcome = rng.integers(0, 3, size=len(starts), dtype=np.uint32) << 14
+    words = words.reshape(-1)
+    words[starts] = (vocab + rng.integers(800, 2600, size=len(starts))).astype(np.uint32)
+    words[starts + 1] = (vocab + rng.integers(800, 2600, size=len(starts))).astype(np.uint32)
+    words[starts + 2] = rng.integers(1968, 1992, size=len(starts)).astype(np.uint32)
+    for k in range(seq_len):
+        sl = starts + k
+        sl = sl[sl < n_words]
+        words[sl] |= outcome[: len(sl)]
+    return words
+
+
+def dist_info():
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    return rank, world, local
+
+
+def max_over_ranks(x: float, world: int) -> float:
+    import torch
+    import torch.distributed as dist
+
+    if world == 1:
+        return x
+    t = torch.tensor([x], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def barrier_sync(world: int):
+    import torch
+    import torch.distributed as dist
+
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def run_ours(args) -> dict:
+    import numpy as np
+    import torch
+
+    from allie_b200.config import Config
+    from allie_b200.data import UCITokenizer
+    from allie_b200.models import initialize_model
+    from allie_b200.ops import _lib
+    from allie_b200.train.trainer import Trainer
+
+    rank, world, local = dist_info()
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+    assert 8 % world == 0
+    ga = GLOBAL_BATCH // (MICRO_BATCH * world)
+    os.environ.setdefault("ALLIE_NO_WANDB", "1")
+    out_dir = tempfile.mkdtemp(prefix="allie_bench_")
+    cfg = Config({"trainer_config": {}, "data_config": {}, "model_config": {}})
+    trainer = Trainer(cfg, output_dir=out_dir, batch_size=MICRO_BATCH, gradient_accumulation_steps=ga,
+                      lr=6e-4, min_lr=1e-5, weight_decay=1e-2, grad_clip=1.0, warmup_iters=2000,
+                      decay_iters=2_000_000, max_iters=2_000_000, eval_interval=0, log_interval=-1,
+                      save_interval=0, use_wandb=False)
+    tok = UCITokenizer(max_length=SEQ_LEN, vocab_size_multiple_of=VOCAB_MULT)
+    torch.manual_seed(1234)
+    model = initialize_model(tok, "gpt2-medium", use_control_token=True, use_regression_head=True,
+                             use_pretrained=False, **MODEL)
+    stream = synthetic_stream(64 * 1024 * SEQ_LEN // 8, len(tok), SEQ_LEN, seed=7 + rank)
+    trainer.setup_dataloaders(tok, stream, [], [])
+    trainer.setup_model(model)
+    trainer.iter_num = 1000     # mid-warmup learning rate, nonzero updates
+    dev = trainer.engine.device
+
+    # windows larger than L2 in aggregate: K*ga distinct [64, 512] windows per rank, pre-staged
+    n_win = (args.steps + args.warmup) * ga
+    host_windows = [trainer.sampler.next().clone().pin_memory() for _ in range(min(n_win, 64))]
+    dev_windows = [w.to(dev) for w in host_windows]
+
+    def step_device(i):
+        ws = [dev_windows[(i * ga + m) % len(dev_windows)] for m in range(ga)]
+        return trainer.train_step(ws)
+
+    def step_e2e(i, sink):
+        ws = [host_windows[(i * ga + m) % len(host_windows)] for m in range(ga)]
+        loss = trainer.train_step(ws)
+        sink.copy_(loss, non_blocking=True)
+
+    for i in range(args.warmup):
+        step_device(i)
+    torch.cuda.synchronize()
+    _lib.check_status()
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    barrier_sync(world)
+    launches0 = _lib.LAUNCHES
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        loss = step_device(args.warmup + i)
+    e1.record()
+    barrier_sync(world)
+    launches = _lib.LAUNCHES - launches0
+    clocks = sampler.stop()
+    ms = max_over_ranks(e0.elapsed_time(e1), world)
+    final_loss = float(loss)
+    _lib.check_status()
+
+    # end-to-end: pinned host windows -> H2D every micro-step, loss -> host every step
+    sink = torch.zeros((), dtype=torch.float32, pin_memory=True)
+    step_e2e(0, sink)
+    barrier_sync(world)
+    t0 = time.perf_counter()
+    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    g0.record()
+    for i in range(args.steps):
+        step_e2e(i, sink)
+        torch.cuda.current_stream().synchronize()   # the loss value is on the host here
+        _ = float(sink)
+    g1.record()
+    barrier_sync(world)
+    wall_ms = (time.perf_counter() - t0) * 1e3
+    e2e_ms = max_over_ranks(max(g0.elapsed_time(g1), wall_ms), world)
+
+    tokens_per_step = GLOBAL_BATCH * SEQ_LEN
+    value = tokens_per_step * args.steps / (ms / 1e3)
+    e2e_value = tokens_per_step * args.steps / (e2e_ms / 1e3)
+    n_params = sum(p.numel() for p in model.parameters())
+    flops_per_token = 6 * (n_params - 2048 * 1024 - 1024 * 1024) + 6 * 2048 * 1024 + 12 * 24 * 1024 * SEQ_LEN
+    result = {
+        "metric": "train tokens/sec (medium config)", "value": value, "unit": "tokens/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": value / BASELINE_TOKENS_PER_S, "dtype": "bf16", "data": "synthetic",
+        "impl": "allie_b200",
+        "config": {"model": "gpt2-medium-like 24L d1024 16H mlp4096 ctx512 vocab2048 + control token "
+                            "+ value/time heads, dropout 0.1",
+                   "global_batch": GLOBAL_BATCH, "seq_len": SEQ_LEN, "micro_batch": MICRO_BATCH,
+                   "grad_accum": ga, "parallelism": f"dp{world}",
+                   "l2_policy": "inputs larger than L2: each micro-step streams >1 GB of activations "
+                                "and 1.2 GB of fp32 weights+grads, distinct windows per micro-step",
+                   "grad_sync": "fused-nvlink" if (trainer.grad_sync and trainer.grad_sync.fused)
+                                else ("all_reduce" if world > 1 else "none")},
+        "clocks": clocks,
+        "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
+                "h2d_bytes_per_step": ga * MICRO_BATCH * SEQ_LEN * 4, "d2h_bytes_per_step": 4},
+        "gpu_launches": launches,
+        "final_loss": final_loss,
+        "model_tflops_per_gpu": value * flops_per_token / world / 1e12,
+    }
+    trainer.cleanup()
+    return result
+
+
+def run_reference(args) -> dict:
+    """The unmodified reference package (installed with ``pip --target baseline/_ref --no-deps``),
+    driven through its own ``Trainer`` / ``initialize_model`` / ``UCITokenizer`` and its stock
+    ``train()`` loop (bf16 autocast, ``torch.compile``, DDP, fused AdamW).  Third-party modules that are
+    not installed here (omegaconf, python-chess, optimum) are satisfied by import stand-ins in
+    ``baseline/shims``; the GPT-2-medium shape comes from a local ``config.json`` instead of the hub.
+    Timing hooks are attached from outside through ``optimizer.register_step_post_hook``."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "modeling")):
+        return {"impl": "reference", "unavailable": "baseline/_ref is missing (pip install --target was not run)"}
+    sys.path.insert(0, os.path.join(ROOT, "baseline", "shims"))
+    sys.path.insert(0, ref_dir)
+    os.environ.setdefault("WANDB_MODE", "disabled")
+    os.environ.setdefault("WANDB_SILENT", "true")
+    os.environ.setdefault("TOKENIZERS_PARALLELISM", "false")
+    try:
+        import numpy as np
+        import torch
+        import torch.distributed as dist
+        from modeling.data import UCITokenizer
+        from modeling.model import initialize_model
+        from modeling.trainer import Trainer
+        from omegaconf import OmegaConf
+    except Exception as e:
+        return {"impl": "reference", "unavailable": f"reference import failed: {type(e).__name__}: {e}"[:300]}
+
+    rank, world, local = dist_info()
+    assert world == args.gpus
+    ga = GLOBAL_BATCH // (MICRO_BATCH * world)
+    W, K = args.warmup, args.steps
+    out_dir = tempfile.mkdtemp(prefix="allie_ref_")
+    cfg = OmegaConf.create({"trainer_config": {}, "data_config": {}, "model_config": {}})
+    trainer = Trainer(cfg, output_dir=out_dir, dtype="bfloat16", torch_compile=True, batch_size=MICRO_BATCH,
+                      gradient_accumulation_steps=ga, lr=6e-4, min_lr=1e-5, weight_decay=1e-2,
+                      warmup_iters=2000, decay_iters=2_000_000, max_iters=W + K - 1, eval_interval=0,
+                      log_interval=10**9, save_interval=0)
+    tok = UCITokenizer(max_length=SEQ_LEN, vocab_size_multiple_of=VOCAB_MULT)
+    torch.manual_seed(1234)
+    model = initialize_model(tok, os.path.join(ROOT, "baseline", "gpt2-medium"), use_control_token=True,
+                             use_regression_head=True, use_pretrained=False)
+    stream = synthetic_stream(64 * 1024 * SEQ_LEN // 8, len(tok), SEQ_LEN, seed=7 + rank)
+    trainer.setup_dataloaders(tok, stream, [], [])
+    trainer.setup_model(model)
+    trainer.iter_num = 1000
+    trainer.max_iters = 1000 + W + K - 1
+
+    state = {"n": 0, "ms": None, "clocks": None, "wall0": None}
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(local)
+
+    def hook(optimizer, a, kw):
+        state["n"] += 1
+        if state["n"] == W:
+            sampler.start()
+            barrier_sync(world)
+            state["wall0"] = time.perf_counter()
+            e0.record()
+        elif state["n"] == W + K:
+            e1.record()
+            barrier_sync(world)
+            state["wall_ms"] = (time.perf_counter() - state["wall0"]) * 1e3
+            state["clocks"] = sampler.stop()
+            state["ms"] = e0.elapsed_time(e1)
+
+    trainer.optimizer.register_step_post_hook(hook)
+    trainer.train()
+    if state["ms"] is None:
+        return {"impl": "reference", "unavailable": "reference train() ended before the timed steps completed"}
+    ms = max_over_ranks(state["ms"], world)
+    tokens_per_step = GLOBAL_BATCH * SEQ_LEN
+    value = tokens_per_step * K / (ms / 1e3)
+    result = {
+        "metric": "train tokens/sec (medium config)", "value": value, "unit": "tokens/s",
+        "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms / K, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": value / BASELINE_TOKENS_PER_S, "dtype": "bf16",
+        "data": "synthetic", "impl": "reference",
+        "config": {"model": "gpt2-medium 24L d1024 16H ctx512 vocab2048 + control token + value/time heads",
+                   "global_batch": GLOBAL_BATCH, "seq_len": SEQ_LEN, "micro_batch": MICRO_BATCH,
+                   "grad_accum": ga, "parallelism": f"dp{world}",
+                   "stack": "reference Trainer.train(): autocast bf16 + torch.compile + DDP + fused AdamW",
+                   "note": "the reference loop times its own host data pipeline, H2D copies and "
+                           "loss.item() every step, so value == e2e for this arm"},
+        "clocks": state["clocks"],
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": ga * MICRO_BATCH * SEQ_LEN * (8 * 3 + 4 * 3),
+                "d2h_bytes_per_step": 4},
+        "gpu_launches": 0,
+    }
+    trainer.cleanup()
+    return result
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    rank, world, _ = dist_info()
+    if args.gpus > 1 and world == 1:
+        # convenience: re-launch under torchrun when started as a plain process
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", os.environ.get("MASTER_PORT", "29517"),
+               os.path.abspath(__file__), *sys.argv[1:]]
+        sys.exit(subprocess.call(cmd))
+    if args.impl == "reference":
+        try:
+            res = run_reference(args)
+        except Exception as e:  # the reference arm must never take the bench down
+            import traceback
+
+            traceback.print_exc(file=sys.stderr)
+            res = {"impl": "reference", "unavailable": f"{type(e).__name__}: {e}"[:300]}
+    else:
+        res = run_ours(args)
+    if rank == 0:
+        print(json.dumps(res), flush=True)
+
+
+if __name__ == "__main__":
+    main()
