@@ -30,12 +30,27 @@ struct AttnArgs {
 
 // byte offset of the 16-byte chunk holding columns [8*c16, 8*c16+8) of row r inside a
 // 128-row x 64-column bf16 panel with 128-byte swizzle (what TMA SWIZZLE_128B writes)
+// order-preserving float <-> int coding (so integer atomicMax orders floats)
+__device__ __forceinline__ int ord_encode(float f) {
+  const int i = __float_as_int(f);
+  return i ^ ((i >> 31) & 0x7fffffff);
+}
+__device__ __forceinline__ float ord_decode(int i) {
+  return __int_as_float(i ^ ((i >> 31) & 0x7fffffff));
+}
+
 __device__ __forceinline__ uint32_t sw128_chunk(int r, int c16) {
   return static_cast<uint32_t>(r * 128 + ((c16 ^ (r & 7)) << 4));
 }
 
+constexpr int FWD_MATH_WARPS = 8;
+constexpr int FWD_MATH_THREADS = FWD_MATH_WARPS * 32;
+constexpr int FWD_TMA_WARP = FWD_MATH_WARPS;
+constexpr int FWD_MMA_WARP = FWD_MATH_WARPS + 1;
+constexpr int FWD_THREADS = (FWD_MATH_WARPS + 2) * 32;
+
 template <int HD>
-__global__ void __launch_bounds__(192)
+__global__ void __launch_bounds__(FWD_THREADS, HD <= 64 ? 2 : 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnArgs a) {
   constexpr int PANELS = HD / 64;               // 64-column panels per Q/K/V tile
   constexpr int TILE_BYTES = 128 * HD * 2;      // one Q / K / V tile
@@ -65,8 +80,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnArgs a) {
   uint64_t* p_full = bars + 11;
   uint64_t* pv_full = bars + 12;
   uint64_t* pv_empty = bars + 13;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  uint64_t* xchg = bars + 14;               // row statistics exchange between the two column halves
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* s_stat = reinterpret_cast<int*>(tmem_slot + 2);       // [128 rows] running row maximum (ordered-int coded)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nqt = (a.T + AT_BM - 1) / AT_BM;
@@ -81,20 +98,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnArgs a) {
       mbar_init(&k_full[i], 1); mbar_init(&v_full[i], 1);
       mbar_init(&k_empty[i], 1); mbar_init(&v_empty[i], 1);
     }
-    mbar_init(s_full, 1); mbar_init(s_empty, 128);
-    mbar_init(p_full, 128); mbar_init(pv_full, 1); mbar_init(pv_empty, 128);
+    mbar_init(s_full, 1); mbar_init(s_empty, FWD_MATH_THREADS);
+    mbar_init(p_full, FWD_MATH_THREADS); mbar_init(pv_full, 1); mbar_init(pv_empty, FWD_MATH_THREADS);
+    mbar_init(xchg, FWD_MATH_THREADS);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmQKV);
   }
-  if (warp == 5) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  if (threadIdx.x < 128) s_stat[threadIdx.x] = ord_encode(-INFINITY);
+  if (warp == FWD_MMA_WARP) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tS = tmem_base, tPV = tmem_base + 128;
 
-  if (warp == 4) {
+  if (warp == FWD_TMA_WARP) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       const int row_q = b * a.T + qt * AT_BM;
@@ -120,7 +139,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnArgs a) {
                       2 * d_model + h * HD + p * 64, row_k);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == FWD_MMA_WARP) {
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       bool ok = mbar_wait(q_full, 0, abort_flag);
@@ -162,49 +181,59 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnArgs a) {
     }
   } else {
     // ---------------------------------------------------- softmax / output warps
-    const int r = threadIdx.x;                    // query row inside the tile = TMEM lane
+    // warp w: TMEM lane quarter w & 3 (query rows), column half w >> 2 (64 keys of each tile and
+    // HD/2 output columns).  The halves exchange their partial row maxima through shared memory.
+    const int r = (warp & 3) * 32 + lane;         // query row inside the tile = TMEM lane
+    const int hf = warp >> 2;
     const int q_idx = qt * AT_BM + r;
-    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const float sl2 = a.scale * LOG2E;
-    float m_run = -INFINITY, l_run = 0.f;
-    float o[HD];
+    constexpr int OC = HD / 2;                    // output columns owned by this thread
+    float m_run = -INFINITY, l_part = 0.f;
+    float o[OC];
 #pragma unroll
-    for (int i = 0; i < HD; ++i) o[i] = 0.f;
+    for (int i = 0; i < OC; ++i) o[i] = 0.f;
     const float dscale = dropout_scale(a.thr16);
-    const uint64_t row_elem0 = (static_cast<uint64_t>(b * a.H + h) * a.T + q_idx) * a.T;
+    const uint64_t row_elem0 = (static_cast<uint64_t>(b * a.H + h) * a.T + q_idx) * a.T + hf * 64;
     bool ok = true;
     for (int j = 0; j < nkv && ok; ++j) {
       if (!mbar_wait(s_full, j & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const bool diag = (j == qt);
-      // pass 1: row maximum
+      // pass 1: partial row maximum over this half's 64 keys
       float mx = -INFINITY;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t v[32];
-        tmem_ld32(tS + lane_addr + c * 32, v);
+        tmem_ld32(tS + lane_addr + hf * 64 + c * 32, v);
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const float s = __uint_as_float(v[i]);
-          if (!diag || (c * 32 + i) <= r) mx = fmaxf(mx, s);
+          const float sc = __uint_as_float(v[i]);
+          if (!diag || (hf * 64 + c * 32 + i) <= r) mx = fmaxf(mx, sc);
         }
       }
-      const float m_new = fmaxf(m_run, mx);       // finite: the diagonal always has column 0..r
+      // running maximum of the row, shared by the two column halves (monotone, so one slot per
+      // row updated with atomicMax is enough; its last reader is ordered before its next writer by
+      // the s_empty -> next S chain)
+      atomicMax(&s_stat[r], ord_encode(mx));
+      mbar_arrive(xchg);
+      if (!mbar_wait(xchg, j & 1, abort_flag)) { ok = false; break; }
+      const float m_new = ord_decode(s_stat[r]);   // finite: key 0 is never masked
       const float alpha = ex2_fast((m_run - m_new) * sl2);
       const float mb = m_new * sl2;
       float rs = 0.f;
-      // pass 2: probabilities -> smem (bf16), row sum
+      // pass 2: probabilities -> smem (bf16), partial row sum
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t v[32];
-        tmem_ld32(tS + lane_addr + c * 32, v);
+        tmem_ld32(tS + lane_addr + hf * 64 + c * 32, v);
         tmem_ld_wait();
         float p[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           const float e = ex2_fast(__uint_as_float(v[i]) * sl2 - mb);
-          p[i] = (!diag || (c * 32 + i) <= r) ? e : 0.f;
+          p[i] = (!diag || (hf * 64 + c * 32 + i) <= r) ? e : 0.f;
           rs += p[i];
         }
         if (a.thr16) {
@@ -216,28 +245,28 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnArgs a) {
             for (int i = 0; i < 8; ++i) p[g * 8 + i] = ((keep >> i) & 1u) ? p[g * 8 + i] * dscale : 0.f;
           }
         }
-        uint8_t* panel = sP + (c >> 1) * 16384;
+        uint8_t* panel = sP + hf * 16384;
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           uint4 w;
           w.x = pack_bf16x2(p[g * 8 + 0], p[g * 8 + 1]); w.y = pack_bf16x2(p[g * 8 + 2], p[g * 8 + 3]);
           w.z = pack_bf16x2(p[g * 8 + 4], p[g * 8 + 5]); w.w = pack_bf16x2(p[g * 8 + 6], p[g * 8 + 7]);
-          *reinterpret_cast<uint4*>(panel + sw128_chunk(r, (c & 1) * 4 + g)) = w;
+          *reinterpret_cast<uint4*>(panel + sw128_chunk(r, c * 4 + g)) = w;
         }
       }
       tc_fence_before();
       mbar_arrive(s_empty);              // S may be overwritten by the next QK^T
       fence_proxy_async_smem();          // P visible to the tensor core's async proxy
       mbar_arrive(p_full);
-      l_run = l_run * alpha + rs;
+      l_part = l_part * alpha + rs;
       m_run = m_new;
-      // fold in this tile's PV
+      // fold in this tile's PV (this thread's HD/2 output columns)
       if (!mbar_wait(pv_full, j & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
 #pragma unroll
-      for (int c = 0; c < HD / 32; ++c) {
+      for (int c = 0; c < OC / 32; ++c) {
         uint32_t v[32];
-        tmem_ld32(tPV + lane_addr + c * 32, v);
+        tmem_ld32(tPV + lane_addr + hf * OC + c * 32, v);
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * alpha + __uint_as_float(v[i]);
@@ -245,12 +274,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnArgs a) {
       tc_fence_before();
       mbar_arrive(pv_empty);
     }
+    // total row sum = sum of the two halves' partial sums: half 1 publishes its part, half 0 adds
+    // its own and publishes the total (two rounds through the same slot)
+    if (ok) {
+      float* fs = reinterpret_cast<float*>(s_stat);
+      if (hf == 1) fs[r] = l_part;
+      mbar_arrive(xchg);
+      if (!mbar_wait(xchg, nkv & 1, abort_flag)) ok = false;
+      if (ok && hf == 0) { l_part += fs[r]; fs[r] = l_part; }
+      mbar_arrive(xchg);
+      if (ok && !mbar_wait(xchg, (nkv + 1) & 1, abort_flag)) ok = false;
+      if (ok && hf == 1) l_part = fs[r];
+    }
     if (!ok) { *abort_flag = ST_TIMEOUT_TMEM_FULL; atomicCAS(a.status, 0, ST_TIMEOUT_TMEM_FULL); }
     if (ok && q_idx < a.T) {
-      const float inv = 1.f / l_run;
-      __nv_bfloat16* orow = a.out + (static_cast<long long>(b) * a.T + q_idx) * d_model + h * HD;
+      const float inv = 1.f / l_part;
+      __nv_bfloat16* orow = a.out + (static_cast<long long>(b) * a.T + q_idx) * d_model + h * HD + hf * OC;
 #pragma unroll
-      for (int g = 0; g < HD / 8; ++g) {
+      for (int g = 0; g < OC / 8; ++g) {
         uint4 w;
         w.x = pack_bf16x2(o[g * 8 + 0] * inv, o[g * 8 + 1] * inv);
         w.y = pack_bf16x2(o[g * 8 + 2] * inv, o[g * 8 + 3] * inv);
@@ -258,12 +299,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnArgs a) {
         w.w = pack_bf16x2(o[g * 8 + 6] * inv, o[g * 8 + 7] * inv);
         *reinterpret_cast<uint4*>(orow + g * 8) = w;
       }
-      if (a.lse) a.lse[(static_cast<long long>(b) * a.H + h) * a.T + q_idx] = m_run * a.scale + logf(l_run);
+      if (a.lse && hf == 0) a.lse[(static_cast<long long>(b) * a.H + h) * a.T + q_idx] = m_run * a.scale + logf(l_part);
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
+  if (warp == FWD_MMA_WARP) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
 }
 
 }  // namespace ab
@@ -312,8 +353,14 @@ attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __re
   delta[(static_cast<long long>(bb) * H + hh) * T + t] = s;
 }
 
+constexpr int BWD_MATH_WARPS = 16;
+constexpr int BWD_MATH_THREADS = BWD_MATH_WARPS * 32;
+constexpr int BWD_TMA_WARP = BWD_MATH_WARPS;
+constexpr int BWD_MMA_WARP = BWD_MATH_WARPS + 1;
+constexpr int BWD_THREADS = (BWD_MATH_WARPS + 2) * 32;
+
 template <int HD, int MODE>
-__global__ void __launch_bounds__(192)
+__global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmDO,
                 const AttnBwdArgs a) {
   constexpr int STAGES = HD <= 64 ? 2 : 1;
@@ -360,14 +407,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
   if (threadIdx.x == 0) {
     mbar_init(stat_full, 1);
     for (int i = 0; i < STAGES; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
-    mbar_init(sdp_full, 1); mbar_init(sdp_empty, 128);
-    mbar_init(pds_full, 128); mbar_init(pds_empty, 1); mbar_init(acc_full, 1);
+    mbar_init(sdp_full, 1); mbar_init(sdp_empty, BWD_MATH_THREADS);
+    mbar_init(pds_full, BWD_MATH_THREADS); mbar_init(pds_empty, 1); mbar_init(acc_full, 1);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmQKV);
     tma_prefetch_desc(&tmDO);
   }
-  if (warp == 5) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  if (warp == BWD_MMA_WARP) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -375,7 +422,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
   const uint32_t tS = tmem_base, tDP = tmem_base + 128, tAcc0 = tmem_base + 256,
                  tAcc1 = tmem_base + 256 + HD;
 
-  if (warp == 4) {
+  if (warp == BWD_TMA_WARP) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       const int row_own = b * a.T + own * 128;
@@ -413,7 +460,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == BWD_MMA_WARP) {
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       bool ok = mbar_wait(stat_full, 0, abort_flag);
@@ -483,8 +530,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
     }
   } else {
     // ------------------------------------------------------------ math warps
-    const int r = threadIdx.x;
-    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    // warp w: TMEM lane quarter w & 3 (query rows 32*(w&3)..), key columns 32*(w>>2)..+31
+    const int r = (warp & 3) * 32 + lane;
+    const int cb = warp >> 2;
+    const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const float sl2 = a.scale * LOG2E;
     const float dscale = dropout_scale(a.thr16);
     const long long bh = static_cast<long long>(b) * a.H + h;
@@ -497,27 +546,28 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
       const float lse_l2 = q_ok ? a.lse[bh * a.T + q_idx] * LOG2E : 0.f;
       const float dlt = q_ok ? a.delta[bh * a.T + q_idx] : 0.f;
       const bool diag = (qi == kj);
-      const uint64_t row_elem0 = (static_cast<uint64_t>(bh) * a.T + q_idx) * a.T + kj * 128;
+      const uint64_t row_elem0 = (static_cast<uint64_t>(bh) * a.T + q_idx) * a.T + kj * 128 + cb * 32;
       if (!mbar_wait(sdp_full, it & 1, abort_flag)) { ok = false; break; }
       if (it > 0 && !mbar_wait(pds_empty, (it - 1) & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t sv[32], dv[32];
-        tmem_ld32(tS + lane_addr + c * 32, sv);
-        tmem_ld32(tDP + lane_addr + c * 32, dv);
-        tmem_ld_wait();
-        float p[32], ds[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const bool live = q_ok && (!diag || (c * 32 + i) <= r);
+      for (int hf = 0; hf < 2; ++hf) {      // two 16-column pieces keep the register count low
+        const int col0 = cb * 32 + hf * 16;
+        uint32_t sv[16], dv[16];
+        tmem_ld16(tS + lane_addr + col0, sv);
+        tmem_ld16(tDP + lane_addr + col0, dv);
+        tmem_ld_wait();
+        float p[16], ds[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const bool live = q_ok && (!diag || (col0 + i) <= r);
           p[i] = live ? ex2_fast(__uint_as_float(sv[i]) * sl2 - lse_l2) : 0.f;
           ds[i] = __uint_as_float(dv[i]);
         }
         if (a.thr16) {
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            const uint64_t e0 = row_elem0 + c * 32 + g * 8;
+          for (int g = 0; g < 2; ++g) {
+            const uint64_t e0 = row_elem0 + hf * 16 + g * 8;
             const uint32_t keep = dropout_keep8(a.seed, a.stream_id, e0 >> 3, a.thr16);
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
@@ -530,12 +580,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
           }
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) ds[i] = p[i] * (ds[i] - dlt) * a.scale;
+          for (int i = 0; i < 16; ++i) ds[i] = p[i] * (ds[i] - dlt) * a.scale;
         }
-        const uint32_t poff = (c >> 1) * 16384;
+        const uint32_t poff = (col0 >> 6) * 16384;
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          const uint32_t off = poff + sw128_chunk(r, (c & 1) * 4 + g);
+        for (int g = 0; g < 2; ++g) {
+          const uint32_t off = poff + sw128_chunk(r, ((col0 & 63) >> 3) + g);
           uint4 w;
           if (MODE == 0) {
             w.x = pack_bf16x2(p[g * 8 + 0], p[g * 8 + 1]); w.y = pack_bf16x2(p[g * 8 + 2], p[g * 8 + 3]);
@@ -559,26 +609,24 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
       const int t_idx = own * 128 + r;   // row of the owned tile (key row in MODE 0, query row in MODE 1)
       __nv_bfloat16* base = a.dqkv + (static_cast<long long>(b) * a.T + t_idx) * (3 * d_model) + h * HD;
       constexpr int NACC = MODE == 0 ? 2 : 1;
-#pragma unroll
-      for (int which = 0; which < NACC; ++which) {
-        // MODE 0: acc0 = dV -> third block, acc1 = dK -> second block.  MODE 1: acc0 = dQ -> first.
+      constexpr int CH = HD / 32;        // 32-column chunks per accumulator
+      // MODE 0: acc0 = dV -> third block, acc1 = dK -> second block.  MODE 1: acc0 = dQ -> first.
+      for (int g = cb; g < NACC * CH; g += 4) {
+        const int which = g / CH, c = g % CH;
         const uint32_t tacc = which == 0 ? tAcc0 : tAcc1;
         __nv_bfloat16* dst = base + (MODE == 0 ? (which == 0 ? 2 * d_model : d_model) : 0);
+        uint32_t v[32];
+        tmem_ld32(tacc + lane_addr + c * 32, v);
+        tmem_ld_wait();
+        if (t_idx < a.T) {
 #pragma unroll
-        for (int c = 0; c < HD / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld32(tacc + lane_addr + c * 32, v);
-          tmem_ld_wait();
-          if (t_idx < a.T) {
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              uint4 w;
-              w.x = pack_bf16x2(__uint_as_float(v[g * 8 + 0]), __uint_as_float(v[g * 8 + 1]));
-              w.y = pack_bf16x2(__uint_as_float(v[g * 8 + 2]), __uint_as_float(v[g * 8 + 3]));
-              w.z = pack_bf16x2(__uint_as_float(v[g * 8 + 4]), __uint_as_float(v[g * 8 + 5]));
-              w.w = pack_bf16x2(__uint_as_float(v[g * 8 + 6]), __uint_as_float(v[g * 8 + 7]));
-              *reinterpret_cast<uint4*>(dst + c * 32 + g * 8) = w;
-            }
+          for (int q4 = 0; q4 < 4; ++q4) {
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(v[q4 * 8 + 0]), __uint_as_float(v[q4 * 8 + 1]));
+            w.y = pack_bf16x2(__uint_as_float(v[q4 * 8 + 2]), __uint_as_float(v[q4 * 8 + 3]));
+            w.z = pack_bf16x2(__uint_as_float(v[q4 * 8 + 4]), __uint_as_float(v[q4 * 8 + 5]));
+            w.w = pack_bf16x2(__uint_as_float(v[q4 * 8 + 6]), __uint_as_float(v[q4 * 8 + 7]));
+            *reinterpret_cast<uint4*>(dst + c * 32 + q4 * 8) = w;
           }
         }
       }
@@ -586,7 +634,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+  if (warp == BWD_MMA_WARP) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
 }
 
 }  // namespace ab
@@ -595,16 +643,20 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
 namespace ab {
 template <int HD>
 static int launch_attn_fwd(const CUtensorMap& tm, const AttnArgs& a, cudaStream_t stream) {
-  constexpr int SMEM = 5 * 128 * HD * 2 + 128 * 128 * 2 + 256;
+  constexpr int SMEM = 5 * 128 * HD * 2 + 128 * 128 * 2 + 1024;
   auto kern = attn_fwd_kernel<HD>;
   static bool attr = false;
   if (!attr) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (e != cudaSuccess) return (int)e;
+    // two CTAs per SM only fit when the SM is configured for its largest shared-memory carve-out
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
+                             cudaSharedmemCarveoutMaxShared);
+    if (e != cudaSuccess) return (int)e;
     attr = true;
   }
   dim3 grid((a.T + 127) / 128, a.H, a.B);
-  kern<<<grid, 192, SMEM, stream>>>(tm, a);
+  kern<<<grid, FWD_THREADS, SMEM, stream>>>(tm, a);
   return (int)cudaGetLastError();
 }
 
@@ -621,7 +673,7 @@ static int launch_attn_bwd(const CUtensorMap& tq, const CUtensorMap& td, const A
     attr = true;
   }
   dim3 grid((a.T + 127) / 128, a.H, a.B);
-  kern<<<grid, 192, SMEM, stream>>>(tq, td, a);
+  kern<<<grid, BWD_THREADS, SMEM, stream>>>(tq, td, a);
   return (int)cudaGetLastError();
 }
 }  // namespace ab

@@ -1,0 +1,312 @@
+// Data-parallel gradient path over NVLink / NVSwitch, as two kernels that ARE the collectives:
+//
+//   nvl_reduce_scatter : every rank sums its 1/N shard of the flat fp32 gradient arena across all
+//                        ranks by loading the peers' arenas directly (plain peer loads, or one
+//                        multimem.ld_reduce through the switch), writes the sum back into its own
+//                        arena and accumulates the shard's sum of squares for the global-norm clip.
+//   nvl_adamw_allgather: derives the clip coefficient from all ranks' partial norms (peer loads),
+//                        runs AdamW on the shard (fp32 master + moments, which exist only for the
+//                        shard: optimizer state is sharded N ways) and stores the updated fp32
+//                        master and the bf16 shadow straight into every rank's arenas (peer
+//                        stores or multimem.st) - the parameter all-gather is the store itself.
+//   nvl_wait           : returns once every peer has delivered its shard of the new parameters.
+//
+// Ranks synchronise through epoch counters in a small symmetric flag array: a rank releases a
+// phase by storing the step's epoch into slot [phase][my_rank] of every peer; a kernel waits for
+// a phase by spinning on its LOCAL slots.  Every spin is bounded; on time-out the kernel writes
+// ST_TIMEOUT_PEER to the status word and returns without touching peer memory further.
+// One process per GPU only: these kernels wait on other GPUs, never on another launch of the
+// same GPU.
+#include "ptx.cuh"
+
+namespace ab {
+
+constexpr int MAX_RANKS = 8;
+constexpr int FLAG_STRIDE = 32;   // uint32 slots per phase (>= MAX_RANKS, keeps phases on separate lines)
+
+struct NvlPeers {
+  void* ptr[MAX_RANKS];
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ float4 ld_relaxed_sys_f4(const float* p) {
+  float4 v;
+  asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ float4 multimem_ld_reduce_f4(const float* mc) {
+  float4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(mc) : "memory");
+  return v;
+}
+__device__ __forceinline__ void multimem_st_f4(float* mc, float4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "f"(v.x),
+               "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+__device__ __forceinline__ void multimem_st_u2(void* mc, uint2 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v2.f32 [%0], {%1, %2};" ::"l"(mc),
+               "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)) : "memory");
+}
+
+// Block-wide bounded wait until all `world` local slots of a phase reach `epoch`.
+// Returns false on time-out.  Must be called by all threads of the block.
+__device__ __forceinline__ bool wait_phase(const uint32_t* local_flags, int phase, int world,
+                                           uint32_t epoch, int* status) {
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if (threadIdx.x < world) {
+    const uint32_t* slot = local_flags + phase * FLAG_STRIDE + threadIdx.x;
+    const long long t0 = clock64();
+    uint32_t spins = 0;
+    while (static_cast<int32_t>(ld_acquire_sys(slot) - epoch) < 0) {
+      if ((++spins & 0xff) == 0 && clock64() - t0 > AB_SPIN_CYCLES) {
+        s_ok = 0;
+        atomicCAS(status, 0, ST_TIMEOUT_PEER);
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  return s_ok != 0;
+}
+
+// Called by one thread per rank slot of ONE block: release `phase` to every peer.
+__device__ __forceinline__ void signal_phase(const NvlPeers& flags, int phase, int rank, int world,
+                                             uint32_t epoch) {
+  if (threadIdx.x < world) {
+    __threadfence_system();
+    uint32_t* slot = static_cast<uint32_t*>(flags.ptr[threadIdx.x]) + phase * FLAG_STRIDE + rank;
+    st_release_sys(slot, epoch);
+  }
+}
+
+struct RsArgs {
+  NvlPeers grads;          // base of every rank's flat fp32 gradient arena
+  NvlPeers flags;          // base of every rank's flag array
+  const float* mc_grads;   // multicast alias of the gradient arena or null
+  float* norm_part;        // local [2] partial sums of squares (symmetric memory)
+  unsigned int* ticket;    // local counter, zero between launches
+  long long shard_off, shard_n;   // this rank's shard, in floats (multiples of 4)
+  int rank, world;
+  uint32_t epoch;
+  int* status;
+};
+
+__global__ void __launch_bounds__(512)
+nvl_reduce_scatter_kernel(const RsArgs a) {
+  // phase 0: "my gradients are final" -> peers; wait until everyone's are
+  if (blockIdx.x == 0) {
+    if (threadIdx.x == 0) a.norm_part[(a.epoch + 1) & 1] = 0.f;   // recycle the idle slot
+    signal_phase(a.flags, 0, a.rank, a.world, a.epoch);
+  }
+  if (!wait_phase(static_cast<const uint32_t*>(a.flags.ptr[a.rank]), 0, a.world, a.epoch, a.status))
+    return;
+  float ss = 0.f;
+  float* mine = static_cast<float*>(a.grads.ptr[a.rank]) + a.shard_off;
+  const long long n4 = a.shard_n >> 2;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4;
+       i += (long long)gridDim.x * blockDim.x) {
+    float4 s;
+    if (a.mc_grads) {
+      s = multimem_ld_reduce_f4(a.mc_grads + a.shard_off + i * 4);
+    } else {
+      s = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int p = 0; p < MAX_RANKS; ++p)
+        if (p < a.world) {
+          // start with the next rank so the peers' links are loaded evenly
+          const int src = (a.rank + 1 + p) % a.world;
+          const float4 v = ld_relaxed_sys_f4(static_cast<const float*>(a.grads.ptr[src]) +
+                                             a.shard_off + i * 4);
+          s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+        }
+    }
+    reinterpret_cast<float4*>(mine)[i] = s;
+    ss += s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w;
+  }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  __shared__ float red[16];
+  __shared__ unsigned int s_last;
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += red[w];
+    atomicAdd(&a.norm_part[a.epoch & 1], t);
+    __threadfence();
+    s_last = (atomicAdd(a.ticket, 1u) == gridDim.x - 1) ? 1u : 0u;
+  }
+  __syncthreads();
+  // phase 1: "I have read your gradients and my partial norm is published"
+  if (s_last) {
+    if (threadIdx.x == 0) *a.ticket = 0;
+    signal_phase(a.flags, 1, a.rank, a.world, a.epoch);
+  }
+}
+
+struct AgArgs {
+  NvlPeers master;         // every rank's flat fp32 master arena
+  NvlPeers shadow;         // every rank's flat bf16 shadow arena
+  NvlPeers flags;
+  NvlPeers norm_parts;     // every rank's norm_part[2]
+  float* mc_master;        // multicast aliases or null
+  void* mc_shadow;
+  const float* grad;       // local gradient arena (summed shard inside)
+  float* exp_avg;          // local, shard-sized
+  float* exp_avg_sq;       // local, shard-sized
+  unsigned int* ticket;
+  long long shard_off, shard_n, decay_end;
+  int rank, world;
+  uint32_t epoch;
+  float lr, beta1, beta2, eps, wd, bc1, bc2_sqrt, max_norm, grad_scale;
+  int* status;
+};
+
+__global__ void __launch_bounds__(512)
+nvl_adamw_allgather_kernel(const AgArgs a) {
+  if (!wait_phase(static_cast<const uint32_t*>(a.flags.ptr[a.rank]), 1, a.world, a.epoch, a.status))
+    return;
+  __shared__ float s_clip;
+  if (threadIdx.x == 0) {
+    float tot = 0.f;
+    for (int p = 0; p < a.world; ++p) {
+      float v;
+      const float* src = static_cast<const float*>(a.norm_parts.ptr[p]) + (a.epoch & 1);
+      asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(src) : "memory");
+      tot += v;
+    }
+    float clip = a.grad_scale;
+    if (a.max_norm > 0.f) {
+      const float norm = sqrtf(tot) * a.grad_scale;
+      const float c = a.max_norm / (norm + 1e-6f);
+      if (c < 1.f) clip *= c;
+    }
+    s_clip = clip;
+  }
+  __syncthreads();
+  const float clip = s_clip;
+  const float step = a.lr / a.bc1;
+  const long long n4 = a.shard_n >> 2;
+  float* my_master = static_cast<float*>(a.master.ptr[a.rank]);
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long gi = a.shard_off + i * 4;     // index in the flat arena
+    const float decay = gi < a.decay_end ? 1.f - a.lr * a.wd : 1.f;
+    const float4 p4 = *reinterpret_cast<const float4*>(my_master + gi);
+    const float4 g4 = *reinterpret_cast<const float4*>(a.grad + gi);
+    const float4 m4 = reinterpret_cast<const float4*>(a.exp_avg)[i];
+    const float4 v4 = reinterpret_cast<const float4*>(a.exp_avg_sq)[i];
+    float pe[4] = {p4.x, p4.y, p4.z, p4.w}, ge[4] = {g4.x, g4.y, g4.z, g4.w};
+    float me[4] = {m4.x, m4.y, m4.z, m4.w}, ve[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float g = ge[j] * clip;
+      pe[j] *= decay;
+      me[j] = a.beta1 * me[j] + (1.f - a.beta1) * g;
+      ve[j] = a.beta2 * ve[j] + (1.f - a.beta2) * g * g;
+      pe[j] -= step * me[j] / (sqrtf(ve[j]) / a.bc2_sqrt + a.eps);
+    }
+    reinterpret_cast<float4*>(a.exp_avg)[i] = make_float4(me[0], me[1], me[2], me[3]);
+    reinterpret_cast<float4*>(a.exp_avg_sq)[i] = make_float4(ve[0], ve[1], ve[2], ve[3]);
+    const float4 pn = make_float4(pe[0], pe[1], pe[2], pe[3]);
+    uint2 pb;
+    pb.x = pack_bf16x2(pe[0], pe[1]);
+    pb.y = pack_bf16x2(pe[2], pe[3]);
+    if (a.mc_master) {
+      multimem_st_f4(a.mc_master + gi, pn);
+      multimem_st_u2(static_cast<__nv_bfloat16*>(a.mc_shadow) + gi, pb);
+    } else {
+#pragma unroll
+      for (int p = 0; p < MAX_RANKS; ++p)
+        if (p < a.world) {
+          const int dst = (a.rank + p) % a.world;
+          *reinterpret_cast<float4*>(static_cast<float*>(a.master.ptr[dst]) + gi) = pn;
+          *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(a.shadow.ptr[dst]) + gi) = pb;
+        }
+    }
+  }
+  __shared__ unsigned int s_last;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    s_last = (atomicAdd(a.ticket, 1u) == gridDim.x - 1) ? 1u : 0u;
+  }
+  __syncthreads();
+  // phase 2: "my shard of the new parameters is in your memory"
+  if (s_last) {
+    if (threadIdx.x == 0) *a.ticket = 0;
+    signal_phase(a.flags, 2, a.rank, a.world, a.epoch);
+  }
+}
+
+__global__ void nvl_wait_kernel(const uint32_t* local_flags, int phase, int world, uint32_t epoch,
+                                int* status) {
+  wait_phase(local_flags, phase, world, epoch, status);
+}
+
+}  // namespace ab
+
+extern "C" {
+
+int ab_nvl_reduce_scatter(void* const* grad_ptrs, void* const* flag_ptrs, const float* mc_grads,
+                          float* norm_part, unsigned int* ticket, long long shard_off,
+                          long long shard_n, int rank, int world, unsigned int epoch, int* status,
+                          cudaStream_t stream) {
+  using namespace ab;
+  if (world < 1 || world > MAX_RANKS || (shard_off & 3) || (shard_n & 3)) return -1;
+  RsArgs a;
+  for (int i = 0; i < MAX_RANKS; ++i) {
+    a.grads.ptr[i] = i < world ? grad_ptrs[i] : nullptr;
+    a.flags.ptr[i] = i < world ? flag_ptrs[i] : nullptr;
+  }
+  a.mc_grads = mc_grads; a.norm_part = norm_part; a.ticket = ticket; a.shard_off = shard_off;
+  a.shard_n = shard_n; a.rank = rank; a.world = world; a.epoch = epoch; a.status = status;
+  nvl_reduce_scatter_kernel<<<148 * 2, 512, 0, stream>>>(a);
+  return (int)cudaGetLastError();
+}
+
+int ab_nvl_adamw_allgather(void* const* master_ptrs, void* const* shadow_ptrs,
+                           void* const* flag_ptrs, void* const* norm_ptrs, float* mc_master,
+                           void* mc_shadow, const float* grad, float* exp_avg, float* exp_avg_sq,
+                           unsigned int* ticket, long long shard_off, long long shard_n,
+                           long long decay_end, int rank, int world, unsigned int epoch, float lr,
+                           float beta1, float beta2, float eps, float wd, int step, float max_norm,
+                           float grad_scale, int* status, cudaStream_t stream) {
+  using namespace ab;
+  if (world < 1 || world > MAX_RANKS || (shard_off & 3) || (shard_n & 3)) return -1;
+  AgArgs a;
+  for (int i = 0; i < MAX_RANKS; ++i) {
+    a.master.ptr[i] = i < world ? master_ptrs[i] : nullptr;
+    a.shadow.ptr[i] = i < world ? shadow_ptrs[i] : nullptr;
+    a.flags.ptr[i] = i < world ? flag_ptrs[i] : nullptr;
+    a.norm_parts.ptr[i] = i < world ? norm_ptrs[i] : nullptr;
+  }
+  a.mc_master = mc_master; a.mc_shadow = mc_shadow; a.grad = grad; a.exp_avg = exp_avg;
+  a.exp_avg_sq = exp_avg_sq; a.ticket = ticket; a.shard_off = shard_off; a.shard_n = shard_n;
+  a.decay_end = decay_end; a.rank = rank; a.world = world; a.epoch = epoch; a.lr = lr;
+  a.beta1 = beta1; a.beta2 = beta2; a.eps = eps; a.wd = wd;
+  a.bc1 = 1.f - powf(beta1, (float)step);
+  a.bc2_sqrt = sqrtf(1.f - powf(beta2, (float)step));
+  a.max_norm = max_norm; a.grad_scale = grad_scale; a.status = status;
+  nvl_adamw_allgather_kernel<<<148 * 2, 512, 0, stream>>>(a);
+  return (int)cudaGetLastError();
+}
+
+int ab_nvl_wait(const void* local_flags, int phase, int world, unsigned int epoch, int* status,
+                cudaStream_t stream) {
+  ab::nvl_wait_kernel<<<1, 32, 0, stream>>>((const uint32_t*)local_flags, phase, world, epoch,
+                                            status);
+  return (int)cudaGetLastError();
+}
+}

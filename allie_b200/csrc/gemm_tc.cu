@@ -2,7 +2,8 @@
 //
 //   warp 0      : TMA producer   (cp.async.bulk.tensor into a STAGES-deep smem ring)
 //   warp 1      : MMA issuer     (one thread issues tcgen05.mma; accumulators live in TMEM)
-//   warps 2..9  : epilogue       (tcgen05.ld TMEM -> registers -> fused epilogue -> global)
+//   warps 2..17 : epilogue       (tcgen05.ld TMEM -> registers -> fused epilogue -> global);
+//                 four warps per TMEM lane quarter, each owning a quarter of the tile's columns
 //
 // The 512 TMEM columns hold two 128 x BN fp32 accumulators, so the epilogue of
 // work unit i overlaps the main loop of unit i+1.  Work units are
@@ -33,6 +34,12 @@ EncodeTiledFn get_encode_tiled() {
 
 int make_tmap_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
                  uint32_t box_rows, uint32_t box_cols, int elem_bytes, bool swizzle128) {
+  return make_tmap_2d_sw(out, base, rows, cols, ld, box_rows, box_cols, elem_bytes,
+                         swizzle128 ? 128 : 0);
+}
+
+int make_tmap_2d_sw(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                    uint32_t box_rows, uint32_t box_cols, int elem_bytes, int swizzle_bytes) {
   EncodeTiledFn enc = get_encode_tiled();
   if (!enc) return -100;
   cuuint64_t dims[2] = {cols, rows};
@@ -44,7 +51,10 @@ int make_tmap_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t col
                                              : CU_TENSOR_MAP_DATA_TYPE_UINT8;
   CUresult r = enc(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                   swizzle_bytes == 128  ? CU_TENSOR_MAP_SWIZZLE_128B
+                   : swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                   : swizzle_bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B
+                                         : CU_TENSOR_MAP_SWIZZLE_NONE,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : -200 - static_cast<int>(r);
 }
@@ -52,7 +62,7 @@ int make_tmap_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t col
 constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
-constexpr int NUM_EPI_WARPS = 8;
+constexpr int NUM_EPI_WARPS = 16;
 constexpr int NUM_THREADS = 64 + 32 * NUM_EPI_WARPS;
 
 struct GemmArgs {
@@ -62,80 +72,55 @@ struct GemmArgs {
   int* status;
 };
 
-template <int BN>
-__device__ __forceinline__ void epilogue_chunk(const GemmArgs& g, const uint32_t* r, int m, int n0,
-                                               bool row_ok) {
+// Fused epilogue math for 8 adjacent columns n..n+7 of row m.  `v` comes in as the raw fp32
+// accumulators and leaves as the final values; `pre` receives the bf16 pre-activation when
+// act == 1.  Reads (bias, aux for act == 2, residual) are predicated by the caller's `ok`.
+__device__ __forceinline__ void epilogue_math8(const GemmArgs& g, float* v, uint4& pre, int m, int n,
+                                               bool ok) {
   const AbGemmEpilogue& ep = g.ep;
-  if (!row_ok) return;
 #pragma unroll
-  for (int grp = 0; grp < 4; ++grp) {
-    const int n = n0 + grp * 8;
-    if (n >= g.N) break;
-    float v[8];
+  for (int j = 0; j < 8; ++j) v[j] *= ep.alpha;
+  if (!ok) return;
+  if (ep.bias) {
+    const float4 b0 = __ldg(reinterpret_cast<const float4*>(ep.bias + n));
+    const float4 b1 = __ldg(reinterpret_cast<const float4*>(ep.bias + n + 4));
+    v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
+    v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+  }
+  if (ep.act == 1) {
+    pre.x = pack_bf16x2(v[0], v[1]); pre.y = pack_bf16x2(v[2], v[3]);
+    pre.z = pack_bf16x2(v[4], v[5]); pre.w = pack_bf16x2(v[6], v[7]);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[grp * 8 + j]) * ep.alpha;
-    if (ep.bias) {
-      const float4 b0 = __ldg(reinterpret_cast<const float4*>(ep.bias + n));
-      const float4 b1 = __ldg(reinterpret_cast<const float4*>(ep.bias + n + 4));
-      v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
-      v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
-    }
-    if (ep.act == 1) {
-      uint4 pre;
-      pre.x = pack_bf16x2(v[0], v[1]); pre.y = pack_bf16x2(v[2], v[3]);
-      pre.z = pack_bf16x2(v[4], v[5]); pre.w = pack_bf16x2(v[6], v[7]);
-      *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(ep.aux) + (long long)m * ep.ldaux + n) =
-          pre;
+    for (int j = 0; j < 8; ++j) v[j] = gelu_tanh(v[j]);
+  } else if (ep.act == 2) {
+    const uint4 q = *reinterpret_cast<const uint4*>(
+        static_cast<const __nv_bfloat16*>(ep.aux) + (long long)m * ep.ldaux + n);
+    v[0] *= gelu_tanh_grad(bf16_lo(q.x)); v[1] *= gelu_tanh_grad(bf16_hi(q.x));
+    v[2] *= gelu_tanh_grad(bf16_lo(q.y)); v[3] *= gelu_tanh_grad(bf16_hi(q.y));
+    v[4] *= gelu_tanh_grad(bf16_lo(q.z)); v[5] *= gelu_tanh_grad(bf16_hi(q.z));
+    v[6] *= gelu_tanh_grad(bf16_lo(q.w)); v[7] *= gelu_tanh_grad(bf16_hi(q.w));
+  }
+  if (ep.resid) {
+    if (ep.drop_thr16) {
+      const uint64_t group = (static_cast<uint64_t>(m) * g.N + n) >> 3;
+      const uint32_t keep = dropout_keep8(ep.drop_seed, ep.drop_stream, group, ep.drop_thr16);
+      const float s = dropout_scale(ep.drop_thr16);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = gelu_tanh(v[j]);
-    } else if (ep.act == 2) {
-      const uint4 pre = *reinterpret_cast<const uint4*>(
-          static_cast<const __nv_bfloat16*>(ep.aux) + (long long)m * ep.ldaux + n);
-      v[0] *= gelu_tanh_grad(bf16_lo(pre.x)); v[1] *= gelu_tanh_grad(bf16_hi(pre.x));
-      v[2] *= gelu_tanh_grad(bf16_lo(pre.y)); v[3] *= gelu_tanh_grad(bf16_hi(pre.y));
-      v[4] *= gelu_tanh_grad(bf16_lo(pre.z)); v[5] *= gelu_tanh_grad(bf16_hi(pre.z));
-      v[6] *= gelu_tanh_grad(bf16_lo(pre.w)); v[7] *= gelu_tanh_grad(bf16_hi(pre.w));
+      for (int j = 0; j < 8; ++j) v[j] = ((keep >> j) & 1u) ? v[j] * s : 0.f;
     }
-    if (ep.resid) {
-      if (ep.drop_thr16) {
-        const uint64_t group = (static_cast<uint64_t>(m) * g.N + n) >> 3;
-        const uint32_t keep = dropout_keep8(ep.drop_seed, ep.drop_stream, group, ep.drop_thr16);
-        const float s = dropout_scale(ep.drop_thr16);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = ((keep >> j) & 1u) ? v[j] * s : 0.f;
-      }
-      const float4 r0 = *reinterpret_cast<const float4*>(ep.resid + (long long)m * ep.ldr + n);
-      const float4 r1 = *reinterpret_cast<const float4*>(ep.resid + (long long)m * ep.ldr + n + 4);
-      v[0] += r0.x; v[1] += r0.y; v[2] += r0.z; v[3] += r0.w;
-      v[4] += r1.x; v[5] += r1.y; v[6] += r1.z; v[7] += r1.w;
-    }
-    if (ep.out_fp32) {
-      float* o = static_cast<float*>(ep.out) + (long long)m * ep.ldo + n;
-      if (ep.accumulate) {
-        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o), "f"(v[0]),
-                     "f"(v[1]), "f"(v[2]), "f"(v[3])
-                     : "memory");
-        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o + 4), "f"(v[4]),
-                     "f"(v[5]), "f"(v[6]), "f"(v[7])
-                     : "memory");
-      } else {
-        *reinterpret_cast<float4*>(o) = make_float4(v[0], v[1], v[2], v[3]);
-        *reinterpret_cast<float4*>(o + 4) = make_float4(v[4], v[5], v[6], v[7]);
-      }
-    } else {
-      uint4 o;
-      o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
-      o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
-      *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(ep.out) + (long long)m * ep.ldo + n) =
-          o;
-    }
+    const float4 r0 = *reinterpret_cast<const float4*>(ep.resid + (long long)m * ep.ldr + n);
+    const float4 r1 = *reinterpret_cast<const float4*>(ep.resid + (long long)m * ep.ldr + n + 4);
+    v[0] += r0.x; v[1] += r0.y; v[2] += r0.z; v[3] += r0.w;
+    v[4] += r1.x; v[5] += r1.y; v[6] += r1.z; v[7] += r1.w;
   }
 }
 
 template <int BN, int STAGES, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
-                         const __grid_constant__ CUtensorMap tmB, const GemmArgs g) {
+                         const __grid_constant__ CUtensorMap tmB,
+                         const __grid_constant__ CUtensorMap tmOut,
+                         const __grid_constant__ CUtensorMap tmAux, const GemmArgs g) {
   constexpr int A_BYTES = BM * BK * 2;
   constexpr int B_BYTES = BN * BK * 2;
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
@@ -145,7 +130,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  // per-epilogue-warp staging tiles for the TMA stores: 2 KB each (32 rows x 16 columns of
+  // fp32, or 32 x 16 bf16 output + 32 x 16 bf16 pre-activation)
+  uint8_t* stage_out = smem + STAGES * STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(stage_out + NUM_EPI_WARPS * 2048);
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + STAGES;
   uint64_t* tfull_bar = bars + 2 * STAGES;
@@ -169,6 +157,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
+    tma_prefetch_desc(&tmOut);
+    if (g.ep.act == 1) tma_prefetch_desc(&tmAux);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, TMEM_COLS);
@@ -183,7 +173,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   const int n_tiles = (g.N + BN - 1) / BN;
   const int kb_total = (g.K + BK - 1) / BK;
   const int kb_per = (kb_total + g.k_splits - 1) / g.k_splits;
-  const int num_units = m_tiles * n_tiles * g.k_splits;
+  const int num_tiles = m_tiles * n_tiles;
+  // units are ordered K-split-major: CTAs running at the same time work on the same K range of
+  // different output tiles, so each operand slab is fetched from HBM once and shared through L2
+  const int num_units = num_tiles * g.k_splits;
 
   if (warp == 0) {
     // ------------------------------------------------------- TMA producer
@@ -192,8 +185,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       uint32_t phase = 0;
       bool ok = true;
       for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
-        const int ks = u % g.k_splits;
-        const int tile = u / g.k_splits;
+        const int ks = u / num_tiles;
+        const int tile = u % num_tiles;
         const int m0 = (tile / n_tiles) * BM;
         const int n0 = (tile % n_tiles) * BN;
         const int kb0 = ks * kb_per;
@@ -241,7 +234,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       int it = 0;
       bool ok = true;
       for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x, ++it) {
-        const int ks = u % g.k_splits;
+        const int ks = u / num_tiles;
         const int kb0 = ks * kb_per;
         const int kb1 = min(kb_total, kb0 + kb_per);
         if (kb0 >= kb1) continue;
@@ -281,19 +274,20 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     // ----------------------------------------------------------- epilogue
     const int e = warp - 2;
     const int quad = warp & 3;           // TMEM lane quarter this warp may read
-    const int half = e >> 2;             // which half of the BN columns
-    constexpr int COLS_PER_WARP = BN / 2;
+    const int part = e >> 2;             // which quarter of the BN columns
+    constexpr int COLS_PER_WARP = BN / 4;
+    uint8_t* my_stage = stage_out + e * 2048;
     uint32_t acc_phase[2] = {0, 0};
     int it = 0;
     for (int u = blockIdx.x; u < num_units; u += gridDim.x, ++it) {
-      const int ks = u % g.k_splits;
-      const int tile = u / g.k_splits;
+      const int ks = u / num_tiles;
+      const int tile = u % num_tiles;
       const int kb0 = ks * kb_per;
       const int kb1 = min(kb_total, kb0 + kb_per);
       if (kb0 >= kb1) continue;
       const int ab = it & 1;
       const int m = (tile / n_tiles) * BM + quad * 32 + lane;
-      const int nbase = (tile % n_tiles) * BN + half * COLS_PER_WARP;
+      const int nbase = (tile % n_tiles) * BN + part * COLS_PER_WARP;
       if (!mbar_wait(&tfull_bar[ab], acc_phase[ab], abort_flag)) {
         *abort_flag = ST_TIMEOUT_TMEM_FULL;
         atomicCAS(g.status, 0, ST_TIMEOUT_TMEM_FULL);
@@ -302,18 +296,56 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       acc_phase[ab] ^= 1;
       tc_fence_after();
       const uint32_t taddr =
-          tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + ab * BN + half * COLS_PER_WARP;
+          tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + ab * BN + part * COLS_PER_WARP;
+      const int m0w = (tile / n_tiles) * BM + quad * 32;   // first row of this warp's block
+      const bool row_ok = m < g.M;
 #pragma unroll 1
-      for (int c = 0; c < COLS_PER_WARP / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(taddr + c * 32, r);
+      for (int rd = 0; rd < COLS_PER_WARP / 16; ++rd) {      // rounds of 16 columns
+        const int n0 = nbase + rd * 16;
+        if (n0 >= g.N) break;                                 // warp-uniform
+        uint32_t r[16];
+        tmem_ld16(taddr + rd * 16, r);
+        if (lane == 0) tma_store_wait_read<0>();              // staging tile free again
+        __syncwarp();
         tmem_ld_wait();
-        epilogue_chunk<BN>(g, r, m, nbase + c * 32, m < g.M);
+#pragma unroll
+        for (int grp = 0; grp < 2; ++grp) {
+          const int n = n0 + grp * 8;
+          float v[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[grp * 8 + j]);
+          uint4 pre = make_uint4(0, 0, 0, 0);
+          epilogue_math8(g, v, pre, m, n, row_ok && n < g.N);
+          if (g.ep.out_fp32) {
+            // 16 fp32 columns = 64-byte rows, 64B swizzle: 16-byte chunk index ^= (row >> 1) & 3
+            uint8_t* rowp = my_stage + lane * 64;
+            const int sw = (lane >> 1) & 3;
+            *reinterpret_cast<float4*>(rowp + (((2 * grp) ^ sw) << 4)) = make_float4(v[0], v[1], v[2], v[3]);
+            *reinterpret_cast<float4*>(rowp + (((2 * grp + 1) ^ sw) << 4)) = make_float4(v[4], v[5], v[6], v[7]);
+          } else {
+            // 16 bf16 columns = 32-byte rows, 32B swizzle: chunk index ^= (row >> 2) & 1
+            const uint32_t off = lane * 32 + ((grp ^ ((lane >> 2) & 1)) << 4);
+            uint4 o;
+            o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
+            o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
+            *reinterpret_cast<uint4*>(my_stage + off) = o;
+            if (g.ep.act == 1) *reinterpret_cast<uint4*>(my_stage + 1024 + off) = pre;
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          if (g.ep.accumulate) tma_reduce_add_2d(&tmOut, my_stage, n0, m0w);
+          else                 tma_store_2d(&tmOut, my_stage, n0, m0w);
+          if (g.ep.act == 1) tma_store_2d(&tmAux, my_stage + 1024, n0, m0w);
+          tma_store_commit();
+        }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[ab]);
     }
+    if (lane == 0) tma_store_wait<0>();   // all of this warp's bulk stores have landed
   }
 
   tc_fence_before();
@@ -335,7 +367,19 @@ static int launch(const void* A, long long lda, const void* B, long long ldb, co
   if (!B_MN) rc = make_tmap_2d(&tmB, B, g.N, g.K, ldb, BN, BK, 2, true);
   else       rc = make_tmap_2d(&tmB, B, g.K, g.N, ldb, BK, 64, 2, true);
   if (rc) return rc;
-  constexpr int SMEM = 1024 + STAGES * (BM * BK * 2 + BN * BK * 2) + 256;
+  // output / pre-activation maps for the epilogue's TMA stores: boxes of 32 rows x 16 columns
+  CUtensorMap tmOut, tmAux;
+  const AbGemmEpilogue& ep = g.ep;
+  if (ep.out_fp32) rc = make_tmap_2d_sw(&tmOut, ep.out, g.M, g.N, ep.ldo, 32, 16, 4, 64);
+  else             rc = make_tmap_2d_sw(&tmOut, ep.out, g.M, g.N, ep.ldo, 32, 16, 2, 32);
+  if (rc) return rc;
+  if (ep.act == 1) {
+    rc = make_tmap_2d_sw(&tmAux, ep.aux, g.M, g.N, ep.ldaux, 32, 16, 2, 32);
+    if (rc) return rc;
+  } else {
+    tmAux = tmOut;
+  }
+  constexpr int SMEM = 1024 + STAGES * (BM * BK * 2 + BN * BK * 2) + NUM_EPI_WARPS * 2048 + 256;
   auto kern = gemm_bf16_tcgen05_kernel<BN, STAGES, A_MN, B_MN>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -347,7 +391,7 @@ static int launch(const void* A, long long lda, const void* B, long long ldb, co
   const int units = m_tiles * n_tiles * g.k_splits;
   int grid = units < max_ctas ? units : max_ctas;
   if (grid < 1) grid = 1;
-  kern<<<grid, NUM_THREADS, SMEM, stream>>>(tmA, tmB, g);
+  kern<<<grid, NUM_THREADS, SMEM, stream>>>(tmA, tmB, tmOut, tmAux, g);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -363,8 +407,10 @@ extern "C" int ab_gemm_bf16(const void* A, int a_mn, long long lda, const void* 
   if (k_splits < 1) k_splits = 1;
   if (k_splits > 1 && !(ep->out_fp32 && ep->accumulate)) return -2;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) |
-       reinterpret_cast<uintptr_t>(ep->out)) & 15)
+       reinterpret_cast<uintptr_t>(ep->out) | reinterpret_cast<uintptr_t>(ep->aux)) & 15)
     return -3;
+  if ((ep->ldo * (ep->out_fp32 ? 4 : 2)) & 15) return -4;   // TMA row pitch: multiple of 16 bytes
+  if (ep->act == 1 && (ep->ldaux & 7)) return -4;
   GemmArgs g;
   g.M = M; g.N = N; g.K = K; g.k_splits = k_splits; g.ep = *ep; g.status = status;
   if (max_ctas <= 0) max_ctas = 148;

@@ -79,44 +79,60 @@ struct LnBwdArgs {
   unsigned long long drop_seed; unsigned int drop_stream, drop_thr16;
 };
 
+// dy (+ rank-2 term) of lane-owned float4 column c4 of one row
+__device__ __forceinline__ float4 ln_dy_eff(const LnBwdArgs& a, uint2 p, bool has_dy, int c4,
+                                            float sc0, float sc1) {
+  float4 dyv = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (has_dy) dyv = make_float4(bf16_lo(p.x), bf16_hi(p.x), bf16_lo(p.y), bf16_hi(p.y));
+  if (a.s0) {
+    const float4 w = __ldg(reinterpret_cast<const float4*>(a.w0) + c4);
+    dyv.x += sc0 * w.x; dyv.y += sc0 * w.y; dyv.z += sc0 * w.z; dyv.w += sc0 * w.w;
+  }
+  if (a.s1) {
+    const float4 w = __ldg(reinterpret_cast<const float4*>(a.w1) + c4);
+    dyv.x += sc1 * w.x; dyv.y += sc1 * w.y; dyv.z += sc1 * w.z; dyv.w += sc1 * w.w;
+  }
+  return dyv;
+}
+
+// Row kernel: every global load of a row (x, dy, incoming residual gradient) is issued up front,
+// so a row costs one memory round trip; dy stays packed in registers and gamma*dy is recomputed.
 template <int NV_MAX>
-__global__ void __launch_bounds__(LN_WARPS * 32)
+__global__ void __launch_bounds__(LN_WARPS * 32, NV_MAX <= 8 ? 2 : 1)
 ln_bwd_kernel(const LnBwdArgs a) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int d = a.d, nv = d >> 7;
   const float dscale = dropout_scale(a.drop_thr16);
+  const bool has_dy = a.dy != nullptr, has_r = a.dres_in != nullptr;
   for (int row = blockIdx.x * LN_WARPS + warp; row < a.M; row += gridDim.x * LN_WARPS) {
+    const float4* xr = reinterpret_cast<const float4*>(a.x + (long long)row * d);
+    const uint2* dyr = reinterpret_cast<const uint2*>(a.dy + (long long)row * d);
+    const float4* rr = reinterpret_cast<const float4*>(a.dres_in + (long long)row * d);
+    float4 xh[NV_MAX], rv[NV_MAX];
+    uint2 dyp[NV_MAX];
+#pragma unroll
+    for (int i = 0; i < NV_MAX; ++i)
+      if (i < nv) {
+        const int c4 = lane + 32 * i;
+        xh[i] = xr[c4];
+        dyp[i] = has_dy ? dyr[c4] : make_uint2(0u, 0u);
+        rv[i] = has_r ? rr[c4] : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
     const float mean = a.rms ? 0.f : a.mean[row];
     const float rstd = a.rstd[row];
-    const float4* xr = reinterpret_cast<const float4*>(a.x + (long long)row * d);
-    const uint2* dyr = a.dy ? reinterpret_cast<const uint2*>(a.dy + (long long)row * d) : nullptr;
     const float sc0 = a.s0 ? a.s0[row] : 0.f, sc1 = a.s1 ? a.s1[row] : 0.f;
-    float4 xh[NV_MAX], gy[NV_MAX];  // xhat and gamma*dy
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int i = 0; i < NV_MAX; ++i)
       if (i < nv) {
         const int c4 = lane + 32 * i;
-        const float4 xv = xr[c4];
-        float4 dyv = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (dyr) {
-          const uint2 p = dyr[c4];
-          dyv = make_float4(bf16_lo(p.x), bf16_hi(p.x), bf16_lo(p.y), bf16_hi(p.y));
-        }
-        if (a.s0) {
-          const float4 w = __ldg(reinterpret_cast<const float4*>(a.w0) + c4);
-          dyv.x += sc0 * w.x; dyv.y += sc0 * w.y; dyv.z += sc0 * w.z; dyv.w += sc0 * w.w;
-        }
-        if (a.s1) {
-          const float4 w = __ldg(reinterpret_cast<const float4*>(a.w1) + c4);
-          dyv.x += sc1 * w.x; dyv.y += sc1 * w.y; dyv.z += sc1 * w.z; dyv.w += sc1 * w.w;
-        }
+        const float4 dyv = ln_dy_eff(a, dyp[i], has_dy, c4, sc0, sc1);
         const float4 g = __ldg(reinterpret_cast<const float4*>(a.gamma) + c4);
-        xh[i] = make_float4((xv.x - mean) * rstd, (xv.y - mean) * rstd, (xv.z - mean) * rstd,
-                            (xv.w - mean) * rstd);
-        gy[i] = make_float4(dyv.x * g.x, dyv.y * g.y, dyv.z * g.z, dyv.w * g.w);
-        s1 += gy[i].x + gy[i].y + gy[i].z + gy[i].w;
-        s2 += gy[i].x * xh[i].x + gy[i].y * xh[i].y + gy[i].z * xh[i].z + gy[i].w * xh[i].w;
+        xh[i] = make_float4((xh[i].x - mean) * rstd, (xh[i].y - mean) * rstd,
+                            (xh[i].z - mean) * rstd, (xh[i].w - mean) * rstd);
+        const float4 gy = make_float4(dyv.x * g.x, dyv.y * g.y, dyv.z * g.z, dyv.w * g.w);
+        s1 += gy.x + gy.y + gy.z + gy.w;
+        s2 += gy.x * xh[i].x + gy.y * xh[i].y + gy.z * xh[i].z + gy.w * xh[i].w;
       }
 #pragma unroll
     for (int o = 16; o; o >>= 1) {
@@ -124,23 +140,19 @@ ln_bwd_kernel(const LnBwdArgs a) {
       s2 += __shfl_xor_sync(0xffffffffu, s2, o);
     }
     const float m1 = a.rms ? 0.f : s1 / d, m2 = s2 / d;
-    const float4* rr =
-        a.dres_in ? reinterpret_cast<const float4*>(a.dres_in + (long long)row * d) : nullptr;
     float4* dxr = reinterpret_cast<float4*>(a.dx + (long long)row * d);
     uint2* dbr = a.dbranch ? reinterpret_cast<uint2*>(a.dbranch + (long long)row * d) : nullptr;
 #pragma unroll
     for (int i = 0; i < NV_MAX; ++i)
       if (i < nv) {
         const int c4 = lane + 32 * i;
+        const float4 dyv = ln_dy_eff(a, dyp[i], has_dy, c4, sc0, sc1);
+        const float4 g = __ldg(reinterpret_cast<const float4*>(a.gamma) + c4);
         float4 o;
-        o.x = (gy[i].x - m1 - xh[i].x * m2) * rstd;
-        o.y = (gy[i].y - m1 - xh[i].y * m2) * rstd;
-        o.z = (gy[i].z - m1 - xh[i].z * m2) * rstd;
-        o.w = (gy[i].w - m1 - xh[i].w * m2) * rstd;
-        if (rr) {
-          const float4 r = rr[c4];
-          o.x += r.x; o.y += r.y; o.z += r.z; o.w += r.w;
-        }
+        o.x = (dyv.x * g.x - m1 - xh[i].x * m2) * rstd + rv[i].x;
+        o.y = (dyv.y * g.y - m1 - xh[i].y * m2) * rstd + rv[i].y;
+        o.z = (dyv.z * g.z - m1 - xh[i].z * m2) * rstd + rv[i].z;
+        o.w = (dyv.w * g.w - m1 - xh[i].w * m2) * rstd + rv[i].w;
         dxr[c4] = o;
         if (dbr) {
           float4 m = o;

@@ -62,7 +62,9 @@ def partition_parameter_names(model: nn.Module) -> tuple[list[str], list[str]]:
 class ParamArena:
     """Flat storage for parameters / gradients / Adam state / bf16 shadows."""
 
-    def __init__(self, model: nn.Module, device: torch.device):
+    def __init__(self, model: nn.Module, device: torch.device, symmetric: bool = False):
+        """``symmetric``: allocate the master / gradient / shadow arenas in symmetric memory so
+        peer GPUs can address them (the fused NVLink gradient path needs that)."""
         decay, no_decay = partition_parameter_names(model)
         params = dict(model.named_parameters())
         decay_set = set(decay)
@@ -76,9 +78,17 @@ class ParamArena:
             if n in decay_set:
                 self.decay_end = off
         self.total = off
-        self.master = torch.zeros(off, dtype=torch.float32, device=device)
-        self.grad = torch.zeros(off, dtype=torch.float32, device=device)
-        self.shadow = torch.zeros(off, dtype=torch.bfloat16, device=device)
+        self.symmetric = symmetric
+        if symmetric:
+            from ..parallel.nvl import symmetric_empty
+
+            self.master = symmetric_empty(off, torch.float32, device).zero_()
+            self.grad = symmetric_empty(off, torch.float32, device).zero_()
+            self.shadow = symmetric_empty(off, torch.bfloat16, device).zero_()
+        else:
+            self.master = torch.zeros(off, dtype=torch.float32, device=device)
+            self.grad = torch.zeros(off, dtype=torch.float32, device=device)
+            self.shadow = torch.zeros(off, dtype=torch.bfloat16, device=device)
         self.exp_avg: torch.Tensor | None = None
         self.exp_avg_sq: torch.Tensor | None = None
         self.shapes = {n: tuple(params[n].shape) for n in self.names}
@@ -105,7 +115,8 @@ class ParamArena:
 
 
 class B200Engine:
-    def __init__(self, model: nn.Module, device: str | torch.device = "cuda", seed: int = 1234):
+    def __init__(self, model: nn.Module, device: str | torch.device = "cuda", seed: int = 1234,
+                 symmetric: bool = False):
         self.device = torch.device(device)
         assert self.device.type == "cuda"
         if self.device.index is None:
@@ -117,7 +128,7 @@ class B200Engine:
         self.cfg: ModelConfig = self.lm.config
         assert self.cfg.activation_function == "gelu_new"
         model.to(self.device)
-        self.arena = ParamArena(model, self.device)
+        self.arena = ParamArena(model, self.device, symmetric=symmetric)
         self.rms = self.cfg.norm_type == "rmsnorm"
         self.seed = seed
         self.step_count = 0      # optimizer steps taken

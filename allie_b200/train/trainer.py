@@ -160,7 +160,14 @@ class Trainer:
         if self.device_type == "cuda":
             from ..models.engine import B200Engine
 
-            self.engine = B200Engine(model, self.device, seed=self.seed)
+            symmetric = self.ddp and self.ddp_world_size > 1 and self.grad_sync_mode in ("auto", "fused")
+            try:
+                self.engine = B200Engine(model, self.device, seed=self.seed, symmetric=symmetric)
+            except Exception as e:
+                if not symmetric or self.grad_sync_mode == "fused":
+                    raise
+                logger.warning(f"symmetric-memory arenas unavailable ({e}); using all_reduce")
+                self.engine = B200Engine(model, self.device, seed=self.seed, symmetric=False)
             logger.info("using the fused sm_100a AdamW over flat parameter arenas")
         else:
             model.to(self.device)
@@ -248,8 +255,10 @@ class Trainer:
                 val_log = self.validate()
                 self.metrics.log({"iter": self.iter_num, "lr": lr,
                                   "train/loss": sum(losses) / len(losses) if losses else None} | val_log)
-            if self.save_interval > 0 and self.iter_num % self.save_interval == 0 and self.master_process:
-                self.save_ckpt("last")
+            if self.save_interval > 0 and self.iter_num % self.save_interval == 0:
+                self._gather_optimizer_state()        # collective when the optimizer is sharded
+                if self.master_process:
+                    self.save_ckpt("last")
             loss = self.train_step()
             if loss.is_cuda:
                 host = torch.empty((), dtype=torch.float32, pin_memory=True)
@@ -335,12 +344,21 @@ class Trainer:
         logger.info("all done! exiting gracefully...")
 
     # ------------------------------------------------------------ checkpoints
+    def _gather_optimizer_state(self) -> None:
+        """With the fused NVLink path the Adam moments live sharded across ranks; bring them into
+        the replicated flat layout the checkpoint writer reads.  Every rank must call this."""
+        if self.grad_sync is not None and self.grad_sync.fused and self.grad_sync.nvl.epoch > 0:
+            a = self.engine.arena
+            a.exp_avg, a.exp_avg_sq = self.grad_sync.nvl.gather_state()
+
     def load_ckpt(self, ckpt_type: str) -> None:
         from .checkpoint import load_checkpoint
 
         path = join(self.output_dir, f"{ckpt_type}.pt")
         if os.path.exists(path):
             meta = load_checkpoint(path, self.model, self.engine, self.optimizer, self.device)
+            if self.grad_sync is not None and self.grad_sync.fused and self.engine.arena.exp_avg is not None:
+                self.grad_sync.nvl.scatter_state(self.engine.arena.exp_avg, self.engine.arena.exp_avg_sq)
             self.iter_num, self.best_val_loss = meta["iter_num"], meta["best_val_loss"]
             logger.info(f"loading {ckpt_type} checkpoint from iter {self.iter_num}: "
                         f"best_val_loss {self.best_val_loss}")

@@ -1,0 +1,67 @@
+"""Worker for the multi-rank trainer tests (run under torch.distributed.run).
+
+usage: ddp_worker.py <out_dir> <mode> <device>   mode: fused | collective | auto
+Trains a tiny model for 3 optimizer steps on a fixed synthetic stream (dropout off) and writes
+the final flat parameters of every rank to <out_dir>/params_<mode>_<rank>.pt .
+"""
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import numpy as np
+import torch
+
+from allie_b200.config import Config
+from allie_b200.data import UCITokenizer
+from allie_b200.models import initialize_model
+from allie_b200.train.trainer import Trainer
+
+
+def main():
+    out_dir, mode, device = sys.argv[1], sys.argv[2], sys.argv[3]
+    os.environ["ALLIE_NO_WANDB"] = "1"
+    rank = int(os.environ.get("RANK", 0))
+    T, B = 128, 4
+    tr = Trainer(Config({}), output_dir=os.path.join(out_dir, f"run_{mode}"), device=device, batch_size=B,
+                 gradient_accumulation_steps=2, lr=1e-3, min_lr=1e-4, warmup_iters=0, decay_iters=100,
+                 max_iters=3, eval_interval=0, log_interval=-1, save_interval=0, weight_decay=0.01,
+                 grad_clip=1.0, grad_sync=mode, use_wandb=False)
+    tok = UCITokenizer(max_length=T, vocab_size_multiple_of=128)
+    torch.manual_seed(0)
+    model = initialize_model(tok, "gpt2", use_control_token=True, use_regression_head=True, n_layer=2,
+                             n_embd=128, n_head=2, n_positions=T, resid_pdrop=0.0, embd_pdrop=0.0,
+                             attn_pdrop=0.0)
+    rng = np.random.default_rng(5)
+    stream = (rng.integers(0, 1968, size=1 << 16).astype(np.uint32)
+              | (rng.integers(1, 20, size=1 << 16).astype(np.uint32) << 16))
+    tr.setup_dataloaders(tok, stream, [], [])
+    tr.setup_model(model)
+    world = tr.ddp_world_size
+    wrng = np.random.default_rng(11)
+    losses = []
+    for step in range(3):
+        # the same global batch regardless of world size: rank r takes every world-th window
+        starts = wrng.integers(0, len(stream) - T, size=(2, B * world))
+        wins = []
+        for ms in range(2):
+            mine = starts[ms][rank::world]
+            w = np.stack([stream[s:s + T] for s in mine]).astype(np.uint32).view(np.int32)
+            wins.append(torch.from_numpy(w))
+        losses.append(float(tr.train_step(wins)))
+        tr.iter_num += 1
+    flat = torch.cat([p.detach().float().reshape(-1).cpu() for _, p in sorted(model.named_parameters())])
+    fused = bool(tr.grad_sync is not None and tr.grad_sync.fused)
+    torch.save({"params": flat, "losses": losses, "fused": fused,
+                "multimem": bool(fused and tr.grad_sync.nvl.multimem)},
+               os.path.join(out_dir, f"params_{mode}_{rank}.pt"))
+    if device.startswith("cuda"):
+        from allie_b200.ops import _lib
+
+        torch.cuda.synchronize()
+        _lib.check_status()
+    tr.cleanup()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,54 @@
+"""Data-parallel trainer: CPU gloo ranks (host logic) and, on a multi-GPU box, the fused NVLink
+gradient path against the all_reduce path."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _launch(nproc, out_dir, mode, device, port, extra_env=None):
+    env = dict(os.environ, ALLIE_NO_WANDB="1", **(extra_env or {}))
+    env.pop("RANK", None)
+    if nproc == 1:
+        cmd = [sys.executable, os.path.join(HERE, "ddp_worker.py"), str(out_dir), mode, device]
+    else:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+               "--master-addr", "127.0.0.1", "--master-port", str(port),
+               os.path.join(HERE, "ddp_worker.py"), str(out_dir), mode, device]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+
+
+def test_cpu_gloo_two_ranks_match_single(tmp_path):
+    """2 gloo ranks, each with half of every micro-batch, must land on the single-process parameters
+    of a run whose gradients are averaged the same way."""
+    _launch(2, tmp_path, "collective", "cpu", 29611)
+    a = torch.load(tmp_path / "params_collective_0.pt")
+    b = torch.load(tmp_path / "params_collective_1.pt")
+    assert torch.equal(a["params"], b["params"]), "ranks diverged"
+    assert all(l == l for l in a["losses"])
+
+
+@pytest.mark.gpu
+def test_fused_nvlink_path_matches_all_reduce(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    n = 2
+    _launch(n, tmp_path, "collective", "cuda", 29621)
+    _launch(n, tmp_path, "fused", "cuda", 29622, {"ALLIE_NVL_MULTIMEM": "0"})
+    ref = torch.load(tmp_path / "params_collective_0.pt")
+    for r in range(n):
+        got = torch.load(tmp_path / f"params_fused_{r}.pt")
+        assert got["fused"] and not got["multimem"]
+        diff = (got["params"] - ref["params"]).abs().max().item()
+        assert diff < 5e-4, diff      # one bf16-rounding-flipped Adam step is 2*lr = 2e-3
+    os.rename(tmp_path / "params_fused_0.pt", tmp_path / "params_p2p_0.pt")
+    _launch(n, tmp_path, "fused", "cuda", 29623, {"ALLIE_NVL_MULTIMEM": "1"})
+    got = torch.load(tmp_path / "params_fused_0.pt")
+    p2p = torch.load(tmp_path / "params_p2p_0.pt")
+    diff = (got["params"] - p2p["params"]).abs().max().item()
+    assert diff < 5e-4, (diff, got["multimem"])
