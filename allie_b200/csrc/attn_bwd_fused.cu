@@ -1,0 +1,395 @@
+// Single-kernel attention backward for head_dim 64 (the medium / large configurations).
+//
+// A CTA owns one 128-row key/value tile j of one (batch, head) and streams the query tiles
+// i >= j.  Per pair (i, j) the tensor core runs five products, S and dP into TMEM, then
+// dV += P^T dO, dK += dS^T Q (accumulated over i in TMEM) and dQ_ij = dS K_j (fresh each time,
+// double-buffered).  The 16 math warps turn S/dP into P/dS exactly once per pair - half the
+// exponentials and dropout work of the two-kernel scheme - and push each dQ_ij tile to an fp32
+// accumulator in global memory with TMA reduce-add, one 32x16 box per warp, so no atomics are
+// issued by threads.  A trailing kernel converts the fp32 dQ to bf16 into the packed dQKV
+// activation and clears the accumulator for the next layer.
+//
+// TMEM columns (512): S 0-127 | dP 128-255 | dV 256-319 | dK 320-383 | dQ 384-447, 448-511.
+#include "attn_common.cuh"
+
+namespace ab {
+
+#ifdef AB_ATTN_PROFILE
+// development aid: per-CTA cycle stamps (enabled only in private profiling builds)
+__device__ long long* g_attn_dbg = nullptr;
+#define AB_STAMP(k) do { if (g_attn_dbg && threadIdx.x == 0) \
+    g_attn_dbg[((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 16 + (k)] = clock64(); } while (0)
+#else
+#define AB_STAMP(k) do { } while (0)
+#endif
+
+constexpr int FB_MATH_WARPS = 16;
+constexpr int FB_MATH_THREADS = FB_MATH_WARPS * 32;
+constexpr int FB_TMA_WARP = FB_MATH_WARPS;
+constexpr int FB_MMA_WARP = FB_MATH_WARPS + 1;
+constexpr int FB_THREADS = (FB_MATH_WARPS + 2) * 32;
+constexpr int FB_TILE = 128 * 64 * 2;       // one 128 x 64 bf16 tile
+constexpr int FB_P = 128 * 128 * 2;
+
+template <bool DIAG, bool DROP>
+__device__ __forceinline__ void fb_math16(const uint32_t* sv, const uint32_t* dv, float* p, float* ds,
+                                          int r, int col0, bool q_ok, float sl2, float lse_l2,
+                                          float dlt, float scale, float dscale, uint32_t keep16) {
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const bool live = q_ok && (!DIAG || (col0 + i) <= r);
+    const float pi = live ? ex2_fast(__uint_as_float(sv[i]) * sl2 - lse_l2) : 0.f;
+    float dpe = __uint_as_float(dv[i]);
+    if (DROP) {
+      const bool kp = (keep16 >> i) & 1u;
+      dpe = kp ? dpe * dscale : 0.f;
+      p[i] = kp ? pi * dscale : 0.f;
+    } else {
+      p[i] = pi;
+    }
+    ds[i] = pi * (dpe - dlt) * scale;
+  }
+}
+
+__global__ void __launch_bounds__(FB_THREADS, 1)
+attn_bwd_fused64_kernel(const __grid_constant__ CUtensorMap tmQKV,
+                        const __grid_constant__ CUtensorMap tmDO,
+                        const __grid_constant__ CUtensorMap tmDQ, const AttnBwdArgs a) {
+  constexpr int HD = 64;
+  constexpr uint32_t IDESC_S = make_idesc_bf16(128, 128, 0, 0);
+  constexpr uint32_t IDESC_T = make_idesc_bf16(128, HD, 1, 1);
+  constexpr uint32_t IDESC_DQ = make_idesc_bf16(128, HD, 0, 1);
+
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  if (smem_u32(smem) & 1023) {
+    if (threadIdx.x == 0) atomicCAS(a.status, 0, ST_BAD_ARGUMENT);
+    return;
+  }
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + FB_TILE;
+  uint8_t* sQ = sV + FB_TILE;            // 2 stages
+  uint8_t* sDO = sQ + 2 * FB_TILE;       // 2 stages
+  uint8_t* sP = sDO + 2 * FB_TILE;
+  uint8_t* sDS = sP + FB_P;
+  uint8_t* sDQ = sDS + FB_P;             // 16 warps x 2 KB staging for the dQ reduce-adds
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sDQ + FB_MATH_WARPS * 2048);
+  uint64_t* stat_full = bars;
+  uint64_t* full = bars + 1;       // 2
+  uint64_t* empty = bars + 3;      // 2
+  uint64_t* sdp_full = bars + 5;
+  uint64_t* sdp_empty = bars + 6;
+  uint64_t* pds_full = bars + 7;
+  uint64_t* pds_empty = bars + 8;
+  uint64_t* dq_full = bars + 9;    // 2
+  uint64_t* dq_empty = bars + 11;  // 2
+  uint64_t* acc_full = bars + 13;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  AB_STAMP(0);
+#ifdef AB_ATTN_PROFILE
+  if (g_attn_dbg && threadIdx.x == 0) {
+    unsigned smid;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+    g_attn_dbg[((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 16 + 15] = smid;
+  }
+#endif
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nt = (a.T + 127) / 128;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int own = static_cast<int>(blockIdx.x);     // key tile; small index = most query tiles first
+  const int n_iter = nt - own;
+  const int d_model = a.H * HD;
+
+  if (threadIdx.x == 0) {
+    mbar_init(stat_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&full[i], 1); mbar_init(&empty[i], 1);
+      mbar_init(&dq_full[i], 1); mbar_init(&dq_empty[i], FB_MATH_WARPS);
+    }
+    mbar_init(sdp_full, 1); mbar_init(sdp_empty, FB_MATH_WARPS);
+    mbar_init(pds_full, FB_MATH_WARPS); mbar_init(pds_empty, 1); mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmQKV);
+    tma_prefetch_desc(&tmDO);
+    tma_prefetch_desc(&tmDQ);
+  }
+  if (warp == FB_MMA_WARP) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base, tDP = tmem_base + 128, tDV = tmem_base + 256, tDK = tmem_base + 320,
+                 tDQ = tmem_base + 384;
+  AB_STAMP(1);
+
+  if (warp == FB_TMA_WARP) {
+    if (lane == 0) {
+      const int row_own = b * a.T + own * 128;
+      mbar_expect_tx(stat_full, 2 * FB_TILE);
+      tma_load_2d(sK, &tmQKV, stat_full, d_model + h * HD, row_own);
+      tma_load_2d(sV, &tmQKV, stat_full, 2 * d_model + h * HD, row_own);
+      for (int it = 0; it < n_iter; ++it) {
+        const int st = it & 1;
+        const int row = b * a.T + (own + it) * 128;
+        if (!mbar_wait(&empty[st], ((it >> 1) & 1) ^ 1, abort_flag)) {
+          *abort_flag = ST_TIMEOUT_EMPTY; atomicCAS(a.status, 0, ST_TIMEOUT_EMPTY); break;
+        }
+        mbar_expect_tx(&full[st], 2 * FB_TILE);
+        tma_load_2d(sQ + st * FB_TILE, &tmQKV, &full[st], h * HD, row);
+        tma_load_2d(sDO + st * FB_TILE, &tmDO, &full[st], h * HD, row);
+      }
+    }
+  } else if (warp == FB_MMA_WARP) {
+    if (lane == 0) {
+      bool ok = mbar_wait(stat_full, 0, abort_flag);
+      const uint32_t k0 = smem_u32(sK), v0 = smem_u32(sV), p0 = smem_u32(sP), ds0 = smem_u32(sDS);
+      auto issue_sdp = [&](int it) {
+        const int st = it & 1;
+        if (!mbar_wait(&full[st], (it >> 1) & 1, abort_flag)) return false;
+        if (it > 0 && !mbar_wait(sdp_empty, (it - 1) & 1, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t q = smem_u32(sQ + st * FB_TILE), dO = smem_u32(sDO + st * FB_TILE);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          umma_bf16(tS, make_sdesc_sw128(q + k * 32, 16, 1024), make_sdesc_sw128(k0 + k * 32, 16, 1024),
+                    IDESC_S, k > 0);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          umma_bf16(tDP, make_sdesc_sw128(dO + k * 32, 16, 1024), make_sdesc_sw128(v0 + k * 32, 16, 1024),
+                    IDESC_S, k > 0);
+        umma_commit(sdp_full);
+        return true;
+      };
+      auto issue_acc = [&](int it) {
+        const int st = it & 1;
+        if (!mbar_wait(pds_full, it & 1, abort_flag)) return false;
+        if (it >= 2 && !mbar_wait(&dq_empty[it & 1], ((it - 2) >> 1) & 1, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t q = smem_u32(sQ + st * FB_TILE), dO = smem_u32(sDO + st * FB_TILE);
+        // dQ_ij = dS K_j first: its consumers (the math warps) can start draining it earliest
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          umma_bf16(tDQ + (it & 1) * 64, make_sdesc_sw128(ds0 + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024),
+                    make_sdesc_sw128(k0 + k * 2048, 16384, 1024), IDESC_DQ, k > 0);
+        umma_commit(&dq_full[it & 1]);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          umma_bf16(tDV, make_sdesc_sw128(p0 + k * 2048, 16384, 1024),
+                    make_sdesc_sw128(dO + k * 2048, 16384, 1024), IDESC_T, (it > 0 || k > 0));
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          umma_bf16(tDK, make_sdesc_sw128(ds0 + k * 2048, 16384, 1024),
+                    make_sdesc_sw128(q + k * 2048, 16384, 1024), IDESC_T, (it > 0 || k > 0));
+        umma_commit(&empty[st]);
+        umma_commit(pds_empty);
+        return true;
+      };
+      if (ok) ok = issue_sdp(0);
+      for (int it = 0; it < n_iter && ok; ++it) {
+        if (it + 1 < n_iter) { ok = issue_sdp(it + 1); if (!ok) break; }
+        ok = issue_acc(it);
+      }
+      if (ok) umma_commit(acc_full);
+      else { *abort_flag = ST_TIMEOUT_FULL; atomicCAS(a.status, 0, ST_TIMEOUT_FULL); }
+    }
+  } else {
+    // ------------------------------------------------------------ math warps
+    const int quad = warp & 3, cb = warp >> 2;
+    const int r = quad * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    const float sl2 = a.scale * LOG2E;
+    const float dscale = dropout_scale(a.thr16);
+    const long long bh = static_cast<long long>(b) * a.H + h;
+    uint8_t* my_dq = sDQ + warp * 2048;
+    bool ok = true;
+
+    // drains dQ tile `it` (rows of query tile own+it, this warp's 16 columns) into the global
+    // fp32 accumulator with one TMA reduce-add
+    auto drain_dq = [&](int it) {
+      if (!mbar_wait(&dq_full[it & 1], (it >> 1) & 1, abort_flag)) return false;
+      tc_fence_after();
+      uint32_t v[16];
+      tmem_ld16(tDQ + (it & 1) * 64 + lane_addr + cb * 16, v);
+      if (lane == 0) tma_store_wait_read<0>();
+      __syncwarp();
+      tmem_ld_wait();
+      tc_fence_before();
+      // 16 fp32 columns = 64-byte rows, 64B swizzle
+      uint8_t* rowp = my_dq + lane * 64;
+      const int sw = (lane >> 1) & 3;
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        *reinterpret_cast<float4*>(rowp + ((c ^ sw) << 4)) =
+            make_float4(__uint_as_float(v[c * 4 + 0]), __uint_as_float(v[c * 4 + 1]),
+                        __uint_as_float(v[c * 4 + 2]), __uint_as_float(v[c * 4 + 3]));
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&dq_empty[it & 1]);
+        tma_reduce_add_2d(&tmDQ, my_dq, h * HD + cb * 16, b * a.T + (own + it) * 128 + quad * 32);
+        tma_store_commit();
+      }
+      return true;
+    };
+
+    for (int it = 0; it < n_iter && ok; ++it) {
+      const int qi = own + it;
+      const int q_idx = qi * 128 + r;
+      const bool q_ok = q_idx < a.T;
+      const float lse_l2 = q_ok ? a.lse[bh * a.T + q_idx] * LOG2E : 0.f;
+      const float dlt = q_ok ? a.delta[bh * a.T + q_idx] : 0.f;
+      const bool diag = it == 0;
+      const uint64_t row_elem0 = (static_cast<uint64_t>(bh) * a.T + q_idx) * a.T + own * 128 + cb * 32;
+      uint32_t keep32 = 0xffffffffu;
+      if (a.thr16) {
+        if (a.drop_mask) {
+          keep32 = q_ok ? a.drop_mask[row_elem0 >> 5] : 0u;
+        } else {
+          keep32 = 0;
+#pragma unroll
+          for (int g = 0; g < 4; ++g)
+            keep32 |= dropout_keep8(a.seed, a.stream_id, (row_elem0 >> 3) + g, a.thr16) << (8 * g);
+        }
+      }
+      if (!mbar_wait(sdp_full, it & 1, abort_flag)) { ok = false; break; }
+      AB_STAMP(2 + 2 * it);
+      if (it > 0 && !mbar_wait(pds_empty, (it - 1) & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        const int col0 = cb * 32 + hf * 16;
+        uint32_t sv[16], dv[16];
+        tmem_ld16(tS + lane_addr + col0, sv);
+        tmem_ld16(tDP + lane_addr + col0, dv);
+        tmem_ld_wait();
+        float p[16], ds[16];
+        const uint32_t k16 = keep32 >> (hf * 16);
+        if (a.thr16) {
+          if (diag) fb_math16<true, true>(sv, dv, p, ds, r, col0, q_ok, sl2, lse_l2, dlt, a.scale, dscale, k16);
+          else      fb_math16<false, true>(sv, dv, p, ds, r, col0, q_ok, sl2, lse_l2, dlt, a.scale, dscale, k16);
+        } else {
+          if (diag) fb_math16<true, false>(sv, dv, p, ds, r, col0, q_ok, sl2, lse_l2, dlt, a.scale, dscale, k16);
+          else      fb_math16<false, false>(sv, dv, p, ds, r, col0, q_ok, sl2, lse_l2, dlt, a.scale, dscale, k16);
+        }
+        const uint32_t poff = (col0 >> 6) * 16384;
+#pragma unroll
+        for (int g = 0; g < 2; ++g) {
+          const uint32_t off = poff + sw128_chunk(r, ((col0 & 63) >> 3) + g);
+          uint4 w;
+          w.x = pack_bf16x2(p[g * 8 + 0], p[g * 8 + 1]); w.y = pack_bf16x2(p[g * 8 + 2], p[g * 8 + 3]);
+          w.z = pack_bf16x2(p[g * 8 + 4], p[g * 8 + 5]); w.w = pack_bf16x2(p[g * 8 + 6], p[g * 8 + 7]);
+          *reinterpret_cast<uint4*>(sP + off) = w;
+          w.x = pack_bf16x2(ds[g * 8 + 0], ds[g * 8 + 1]); w.y = pack_bf16x2(ds[g * 8 + 2], ds[g * 8 + 3]);
+          w.z = pack_bf16x2(ds[g * 8 + 4], ds[g * 8 + 5]); w.w = pack_bf16x2(ds[g * 8 + 6], ds[g * 8 + 7]);
+          *reinterpret_cast<uint4*>(sDS + off) = w;
+        }
+      }
+      // one arrival per warp: hundreds of threads arriving on one mbarrier serialise on it
+      tc_fence_before();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) { mbar_arrive(sdp_empty); mbar_arrive(pds_full); }
+      AB_STAMP(3 + 2 * it);
+      // the previous pair's dQ tile finished long ago: drain it while the tensor core works
+      if (it > 0) ok = drain_dq(it - 1);
+    }
+    if (ok) ok = drain_dq(n_iter - 1);
+    AB_STAMP(10);
+    if (ok && !mbar_wait(acc_full, 0, abort_flag)) ok = false;
+    AB_STAMP(11);
+    if (!ok) { *abort_flag = ST_TIMEOUT_TMEM_FULL; atomicCAS(a.status, 0, ST_TIMEOUT_TMEM_FULL); }
+    if (ok) {
+      tc_fence_after();
+      const int t_idx = own * 128 + r;
+      __nv_bfloat16* base = a.dqkv + (static_cast<long long>(b) * a.T + t_idx) * (3 * d_model) + h * HD;
+      // 4 chunks of 32 columns: dV chunks 0,1 then dK chunks 0,1; warp group cb takes chunk cb
+      const uint32_t tacc = (cb < 2 ? tDV : tDK) + (cb & 1) * 32;
+      __nv_bfloat16* dst = base + (cb < 2 ? 2 * d_model : d_model) + (cb & 1) * 32;
+      uint32_t v[32];
+      tmem_ld32(tacc + lane_addr, v);
+      tmem_ld_wait();
+      if (t_idx < a.T) {
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint4 w;
+          w.x = pack_bf16x2(__uint_as_float(v[q4 * 8 + 0]), __uint_as_float(v[q4 * 8 + 1]));
+          w.y = pack_bf16x2(__uint_as_float(v[q4 * 8 + 2]), __uint_as_float(v[q4 * 8 + 3]));
+          w.z = pack_bf16x2(__uint_as_float(v[q4 * 8 + 4]), __uint_as_float(v[q4 * 8 + 5]));
+          w.w = pack_bf16x2(__uint_as_float(v[q4 * 8 + 6]), __uint_as_float(v[q4 * 8 + 7]));
+          *reinterpret_cast<uint4*>(dst + q4 * 8) = w;
+        }
+      }
+    }
+    AB_STAMP(12);
+    if (lane == 0) tma_store_wait<0>();
+    AB_STAMP(13);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == FB_MMA_WARP) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+  AB_STAMP(14);
+}
+
+#ifdef AB_ATTN_PROFILE
+extern "C" int ab_attn_set_dbg(long long* p) {
+  return (int)cudaMemcpyToSymbol(g_attn_dbg, &p, sizeof(p));
+}
+#endif
+
+// dqkv[:, 0:d] = bf16(dq_acc).  A block walks whole rows (thread = one float4 column group), so
+// every access is a contiguous row segment.  The accumulator is cleared by a separate memset:
+// overwriting each element right after loading it in the same kernel measured ten times slower
+// on B200 than the read-only conversion plus a memset.
+__global__ void __launch_bounds__(256)
+attn_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dqkv, int rows, int d) {
+  const int d4 = d >> 2;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float4* src = reinterpret_cast<const float4*>(acc + static_cast<long long>(row) * d);
+    uint2* dst = reinterpret_cast<uint2*>(dqkv + static_cast<long long>(row) * 3 * d);
+    for (int c4 = threadIdx.x; c4 < d4; c4 += 256) {
+      const float4 v = src[c4];
+      uint2 o;
+      o.x = pack_bf16x2(v.x, v.y);
+      o.y = pack_bf16x2(v.z, v.w);
+      dst[c4] = o;
+    }
+  }
+}
+
+int launch_attn_bwd_fused64(const CUtensorMap& tq, const CUtensorMap& td, const AttnBwdArgs& a,
+                            cudaStream_t stream) {
+  CUtensorMap tdq;
+  const long long rows = static_cast<long long>(a.B) * a.T;
+  const int d = a.H * 64;
+  int rc = make_tmap_2d_sw(&tdq, a.dq_acc, rows, d, d, 32, 16, 4, 64);
+  if (rc) return rc;
+  constexpr int SMEM = 6 * FB_TILE + 2 * FB_P + FB_MATH_WARPS * 2048 + 256;
+  static bool attr = false;
+  if (!attr) {
+    cudaError_t e = cudaFuncSetAttribute(attn_bwd_fused64_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (e != cudaSuccess) return (int)e;
+    attr = true;
+  }
+  dim3 grid((a.T + 127) / 128, a.H, a.B);
+  attn_bwd_fused64_kernel<<<grid, FB_THREADS, SMEM, stream>>>(tq, td, tdq, a);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
+  attn_dq_convert_kernel<<<148 * 16, 256, 0, stream>>>(a.dq_acc, a.dqkv, (int)rows, d);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
+  return (int)cudaMemsetAsync(a.dq_acc, 0, sizeof(float) * rows * d, stream);
+}
+
+}  // namespace ab
+
+// Stand-alone entry to the dQ conversion (bf16 copy into the packed dQKV activation, then clear).
+extern "C" int ab_attn_dq_convert(float* acc, void* dqkv, int rows, int d, cudaStream_t stream) {
+  ab::attn_dq_convert_kernel<<<148 * 16, 256, 0, stream>>>(acc, (__nv_bfloat16*)dqkv, rows, d);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
+  return (int)cudaMemsetAsync(acc, 0, sizeof(float) * (size_t)rows * d, stream);
+}

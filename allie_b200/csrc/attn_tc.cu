@@ -10,38 +10,9 @@
 // Q, K and V are read straight out of the packed [B*T, 3*d] QKV activation with 2-D TMA boxes
 // (64 columns x 128 rows), and O is written in the [B*T, d] layout the projection GEMM reads.
 // V is consumed MN-major (rows = keys), so no transposes exist anywhere.
-#include "ptx.cuh"
+#include "attn_common.cuh"
 
 namespace ab {
-
-constexpr int AT_BM = 128;   // query rows per CTA
-constexpr int AT_BN = 128;   // keys per inner tile
-constexpr float LOG2E = 1.4426950408889634f;
-
-struct AttnArgs {
-  int B, T, H, hd;
-  float scale;              // 1/sqrt(hd)
-  unsigned long long seed;
-  unsigned int stream_id, thr16;
-  __nv_bfloat16* out;       // [B*T, H*hd]
-  float* lse;               // [B, H, T]
-  int* status;
-};
-
-// byte offset of the 16-byte chunk holding columns [8*c16, 8*c16+8) of row r inside a
-// 128-row x 64-column bf16 panel with 128-byte swizzle (what TMA SWIZZLE_128B writes)
-// order-preserving float <-> int coding (so integer atomicMax orders floats)
-__device__ __forceinline__ int ord_encode(float f) {
-  const int i = __float_as_int(f);
-  return i ^ ((i >> 31) & 0x7fffffff);
-}
-__device__ __forceinline__ float ord_decode(int i) {
-  return __int_as_float(i ^ ((i >> 31) & 0x7fffffff));
-}
-
-__device__ __forceinline__ uint32_t sw128_chunk(int r, int c16) {
-  return static_cast<uint32_t>(r * 128 + ((c16 ^ (r & 7)) << 4));
-}
 
 constexpr int FWD_MATH_WARPS = 8;
 constexpr int FWD_MATH_THREADS = FWD_MATH_WARPS * 32;
@@ -98,9 +69,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnArgs a) {
       mbar_init(&k_full[i], 1); mbar_init(&v_full[i], 1);
       mbar_init(&k_empty[i], 1); mbar_init(&v_empty[i], 1);
     }
-    mbar_init(s_full, 1); mbar_init(s_empty, FWD_MATH_THREADS);
-    mbar_init(p_full, FWD_MATH_THREADS); mbar_init(pv_full, 1); mbar_init(pv_empty, FWD_MATH_THREADS);
-    mbar_init(xchg, FWD_MATH_THREADS);
+    mbar_init(s_full, 1); mbar_init(s_empty, FWD_MATH_WARPS);
+    mbar_init(p_full, FWD_MATH_WARPS); mbar_init(pv_full, 1); mbar_init(pv_empty, FWD_MATH_WARPS);
+    mbar_init(xchg, FWD_MATH_WARPS);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmQKV);
@@ -217,7 +188,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnArgs a) {
       // row updated with atomicMax is enough; its last reader is ordered before its next writer by
       // the s_empty -> next S chain)
       atomicMax(&s_stat[r], ord_encode(mx));
-      mbar_arrive(xchg);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(xchg);     // one arrival per warp (see below)
       if (!mbar_wait(xchg, j & 1, abort_flag)) { ok = false; break; }
       const float m_new = ord_decode(s_stat[r]);   // finite: key 0 is never masked
       const float alpha = ex2_fast((m_run - m_new) * sl2);
@@ -237,13 +209,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnArgs a) {
           rs += p[i];
         }
         if (a.thr16) {
+          uint32_t word = 0;
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             const uint64_t e0 = row_elem0 + j * AT_BN + c * 32 + g * 8;
             const uint32_t keep = dropout_keep8(a.seed, a.stream_id, e0 >> 3, a.thr16);
+            word |= keep << (8 * g);
 #pragma unroll
             for (int i = 0; i < 8; ++i) p[g * 8 + i] = ((keep >> i) & 1u) ? p[g * 8 + i] * dscale : 0.f;
           }
+          // keep bits of these 32 keys, for the backward pass (so it never re-runs the generator)
+          if (a.drop_mask && q_idx < a.T)
+            a.drop_mask[(row_elem0 + j * AT_BN + c * 32) >> 5] = word;
         }
         uint8_t* panel = sP + hf * 16384;
 #pragma unroll
@@ -254,10 +231,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnArgs a) {
           *reinterpret_cast<uint4*>(panel + sw128_chunk(r, c * 4 + g)) = w;
         }
       }
+      // one arrival per warp: hundreds of threads arriving on one mbarrier serialise on it
       tc_fence_before();
-      mbar_arrive(s_empty);              // S may be overwritten by the next QK^T
       fence_proxy_async_smem();          // P visible to the tensor core's async proxy
-      mbar_arrive(p_full);
+      __syncwarp();
+      if (lane == 0) { mbar_arrive(s_empty); mbar_arrive(p_full); }   // S reusable, P ready
       l_part = l_part * alpha + rs;
       m_run = m_new;
       // fold in this tile's PV (this thread's HD/2 output columns)
@@ -272,17 +250,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnArgs a) {
         for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * alpha + __uint_as_float(v[i]);
       }
       tc_fence_before();
-      mbar_arrive(pv_empty);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pv_empty);
     }
     // total row sum = sum of the two halves' partial sums: half 1 publishes its part, half 0 adds
     // its own and publishes the total (two rounds through the same slot)
     if (ok) {
       float* fs = reinterpret_cast<float*>(s_stat);
       if (hf == 1) fs[r] = l_part;
-      mbar_arrive(xchg);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(xchg);
       if (!mbar_wait(xchg, nkv & 1, abort_flag)) ok = false;
       if (ok && hf == 0) { l_part += fs[r]; fs[r] = l_part; }
-      mbar_arrive(xchg);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(xchg);
       if (ok && !mbar_wait(xchg, (nkv + 1) & 1, abort_flag)) ok = false;
       if (ok && hf == 1) l_part = fs[r];
     }
@@ -321,16 +302,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnArgs a) {
 // delta[b,h,t] = sum_c dO*O is produced by a small pre-kernel.
 namespace ab {
 
-struct AttnBwdArgs {
-  int B, T, H, hd;
-  float scale;
-  unsigned long long seed;
-  unsigned int stream_id, thr16;
-  const float* lse;          // [B,H,T]
-  const float* delta;        // [B,H,T]
-  __nv_bfloat16* dqkv;       // [B*T, 3*H*hd]
-  int* status;
-};
 
 __global__ void __launch_bounds__(256)
 attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
@@ -407,8 +378,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
   if (threadIdx.x == 0) {
     mbar_init(stat_full, 1);
     for (int i = 0; i < STAGES; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
-    mbar_init(sdp_full, 1); mbar_init(sdp_empty, BWD_MATH_THREADS);
-    mbar_init(pds_full, BWD_MATH_THREADS); mbar_init(pds_empty, 1); mbar_init(acc_full, 1);
+    mbar_init(sdp_full, 1); mbar_init(sdp_empty, BWD_MATH_WARPS);
+    mbar_init(pds_full, BWD_MATH_WARPS); mbar_init(pds_empty, 1); mbar_init(acc_full, 1);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmQKV);
@@ -568,7 +539,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
 #pragma unroll
           for (int g = 0; g < 2; ++g) {
             const uint64_t e0 = row_elem0 + hf * 16 + g * 8;
-            const uint32_t keep = dropout_keep8(a.seed, a.stream_id, e0 >> 3, a.thr16);
+            const uint32_t keep = a.drop_mask
+                ? (q_ok ? (a.drop_mask[e0 >> 5] >> (e0 & 31)) & 0xffu : 0u)
+                : dropout_keep8(a.seed, a.stream_id, e0 >> 3, a.thr16);
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               const bool kp = (keep >> i) & 1u;
@@ -597,10 +570,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
           *reinterpret_cast<uint4*>(sDS + off) = w;
         }
       }
+      // one arrival per warp: hundreds of threads arriving on one mbarrier serialise on it
       tc_fence_before();
-      mbar_arrive(sdp_empty);
       fence_proxy_async_smem();
-      mbar_arrive(pds_full);
+      __syncwarp();
+      if (lane == 0) { mbar_arrive(sdp_empty); mbar_arrive(pds_full); }
     }
     if (ok && !mbar_wait(acc_full, 0, abort_flag)) ok = false;
     if (!ok) { *abort_flag = ST_TIMEOUT_TMEM_FULL; atomicCAS(a.status, 0, ST_TIMEOUT_TMEM_FULL); }
@@ -641,6 +615,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
 
 // ------------------------------------------------------------------------------------ host side
 namespace ab {
+int launch_attn_bwd_fused64(const CUtensorMap& tq, const CUtensorMap& td, const AttnBwdArgs& a,
+                            cudaStream_t stream);   // attn_bwd_fused.cu
+
 template <int HD>
 static int launch_attn_fwd(const CUtensorMap& tm, const AttnArgs& a, cudaStream_t stream) {
   constexpr int SMEM = 5 * 128 * HD * 2 + 128 * 128 * 2 + 1024;
@@ -682,26 +659,33 @@ extern "C" {
 
 // qkv: bf16 [B*T, 3*H*hd]; out: bf16 [B*T, H*hd]; lse: fp32 [B,H,T] (may be null).
 // hd must be 64 or 128.  With dropout (thr16 > 0) T must be a multiple of 8.
-int ab_attn_fwd(const void* qkv, void* out, float* lse, int B, int T, int H, int hd, float scale,
-                unsigned long long seed, unsigned int stream_id, unsigned int thr16, int* status,
-                cudaStream_t stream) {
+// drop_mask (optional): uint32 [B,H,T,T/32], receives the dropout keep bits (needs T % 32 == 0).
+int ab_attn_fwd(const void* qkv, void* out, float* lse, unsigned int* drop_mask, int B, int T, int H,
+                int hd, float scale, unsigned long long seed, unsigned int stream_id,
+                unsigned int thr16, int* status, cudaStream_t stream) {
   using namespace ab;
   if ((hd != 64 && hd != 128) || B <= 0 || T <= 0 || (thr16 && (T & 7))) return -1;
+  if (drop_mask && (T & 31)) return -1;
   CUtensorMap tm;
   int rc = make_tmap_2d(&tm, qkv, (uint64_t)B * T, 3ull * H * hd, 3ull * H * hd, 128, 64, 2, true);
   if (rc) return rc;
   AttnArgs a;
   a.B = B; a.T = T; a.H = H; a.hd = hd; a.scale = scale; a.seed = seed; a.stream_id = stream_id;
   a.thr16 = thr16; a.out = (__nv_bfloat16*)out; a.lse = lse; a.status = status;
+  a.drop_mask = drop_mask;
   return hd == 64 ? launch_attn_fwd<64>(tm, a, stream) : launch_attn_fwd<128>(tm, a, stream);
 }
 
-// delta: fp32 scratch [B,H,T] owned by the caller.
+// delta: fp32 scratch [B,H,T] owned by the caller.  drop_mask (optional): the keep bits the forward
+// pass wrote.  dq_acc (optional, hd == 64): fp32 [B*T, H*hd] accumulator that must be all zero on
+// entry and is all zero again on return; when given, the single-kernel backward runs.
 int ab_attn_bwd(const void* qkv, const void* out, const float* lse, const void* dout, void* dqkv,
-                float* delta, int B, int T, int H, int hd, float scale, unsigned long long seed,
-                unsigned int stream_id, unsigned int thr16, int* status, cudaStream_t stream) {
+                float* delta, const unsigned int* drop_mask, float* dq_acc, int B, int T, int H, int hd,
+                float scale, unsigned long long seed, unsigned int stream_id, unsigned int thr16,
+                int* status, cudaStream_t stream) {
   using namespace ab;
   if ((hd != 64 && hd != 128) || B <= 0 || T <= 0 || (thr16 && (T & 7))) return -1;
+  if (drop_mask && (T & 31)) return -1;
   CUtensorMap tq, td;
   int rc = make_tmap_2d(&tq, qkv, (uint64_t)B * T, 3ull * H * hd, 3ull * H * hd, 128, 64, 2, true);
   if (rc) return rc;
@@ -713,6 +697,8 @@ int ab_attn_bwd(const void* qkv, const void* out, const float* lse, const void* 
   AttnBwdArgs a;
   a.B = B; a.T = T; a.H = H; a.hd = hd; a.scale = scale; a.seed = seed; a.stream_id = stream_id;
   a.thr16 = thr16; a.lse = lse; a.delta = delta; a.dqkv = (__nv_bfloat16*)dqkv; a.status = status;
+  a.drop_mask = drop_mask; a.dq_acc = dq_acc;
+  if (hd == 64 && dq_acc) return launch_attn_bwd_fused64(tq, td, a, stream);
   if (hd == 64) {
     rc = launch_attn_bwd<64, 0>(tq, td, a, stream);
     if (rc) return rc;

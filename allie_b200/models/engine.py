@@ -205,6 +205,10 @@ class B200Engine:
             buf["lse"] = [e(B, cfg.n_head, T, dt=f32) for _ in range(nl)]
             buf["dx"] = e(M, d, dt=f32)
             buf["delta"] = e(B, cfg.n_head, T, dt=f32)
+            if cfg.head_dim == 64:
+                buf["dq_acc"] = torch.zeros(M, d, dtype=f32, device=dev)   # kept all-zero between uses
+            if T % 32 == 0 and cfg.attn_pdrop > 0:
+                buf["dmask"] = [e(B, cfg.n_head, T, T // 32, dt=i32) for _ in range(nl)]
             buf["dyb"] = e(M, d)
             buf["dpre"] = e(M, F)
             buf["dqkv"] = e(M, 3 * d)
@@ -227,17 +231,18 @@ class B200Engine:
         return buf
 
     # ------------------------------------------------------------ attention
-    def _attention_fwd(self, qkv, out, lse, B, T, p_drop, seed, stream_id):
+    def _attention_fwd(self, qkv, out, lse, B, T, p_drop, seed, stream_id, drop_mask=None):
         from ..ops.attention import attention_fwd
 
-        attention_fwd(qkv, out, lse, B, T, self.cfg.n_head, self.cfg.head_dim, p_drop, seed, stream_id)
+        attention_fwd(qkv, out, lse, B, T, self.cfg.n_head, self.cfg.head_dim, p_drop, seed, stream_id,
+                      drop_mask if p_drop > 0 else None)
 
-    def _attention_bwd(self, qkv, out, lse, dout, dqkv, B, T, p_drop, seed, stream_id):
+    def _attention_bwd(self, qkv, out, lse, dout, dqkv, B, T, p_drop, seed, stream_id, drop_mask=None):
         from ..ops.attention import attention_bwd
 
-        delta = self._buffers(B, T, True)["delta"]
-        attention_bwd(qkv, out, lse, dout, dqkv, delta, B, T, self.cfg.n_head, self.cfg.head_dim, p_drop,
-                      seed, stream_id)
+        buf = self._buffers(B, T, True)
+        attention_bwd(qkv, out, lse, dout, dqkv, buf["delta"], B, T, self.cfg.n_head, self.cfg.head_dim,
+                      p_drop, seed, stream_id, drop_mask if p_drop > 0 else None, buf.get("dq_acc"))
 
     # -------------------------------------------------------------- forward
     def _drop(self, train: bool):
@@ -259,7 +264,8 @@ class B200Engine:
             K.layernorm_fwd(x[l], L["ln1_w"][0], L["ln1_b"][0], buf["ln1"][l], buf["mean1"][l],
                             buf["rstd1"][l], eps, self.rms)
             gemm(buf["ln1"][l], L["qkv_w"][1], b_mn=True, out=buf["qkv"][l], bias=L["qkv_b"][0])
-            self._attention_fwd(buf["qkv"][l], buf["attn"][l], buf["lse"][l], B, T, p_att, seed, 3 + 3 * l)
+            self._attention_fwd(buf["qkv"][l], buf["attn"][l], buf["lse"][l], B, T, p_att, seed, 3 + 3 * l,
+                                buf["dmask"][l] if "dmask" in buf else None)
             gemm(buf["attn"][l], L["o_w"][1], b_mn=True, out=buf["xmid"][l], bias=L["o_b"][0],
                  resid=x[l], drop_p=p_res, drop_seed=seed, drop_stream=1 + 3 * l)
             K.layernorm_fwd(buf["xmid"][l], L["ln2_w"][0], L["ln2_b"][0], buf["ln2"][l], buf["mean2"][l],
@@ -328,7 +334,7 @@ class B200Engine:
             K.colsum_bf16(dyb, L["o_b"][2])
             gemm(dyb, L["o_w"][1], b_mn=False, out=dsmall)
             self._attention_bwd(buf["qkv"][l], buf["attn"][l], buf["lse"][l], dsmall, dqkv, B, T, p_att,
-                                seed, 3 + 3 * l)
+                                seed, 3 + 3 * l, buf["dmask"][l] if "dmask" in buf else None)
             gemm(buf["ln1"][l], dqkv, a_mn=True, b_mn=True, out=L["qkv_w"][2], accumulate=True)
             K.colsum_bf16(dqkv, L["qkv_b"][2])
             gemm(dqkv, L["qkv_w"][1], b_mn=False, out=dsmall)

@@ -15,8 +15,10 @@ from ._lib import ptr, stream_ptr
 
 
 def attention_fwd(qkv, out, lse, B: int, T: int, H: int, hd: int, p_drop: float, seed: int,
-                  stream_id: int) -> None:
-    rc = _lib.cuda().ab_attn_fwd(ptr(qkv), ptr(out), ptr(lse), c_int(B), c_int(T), c_int(H), c_int(hd),
+                  stream_id: int, drop_mask=None) -> None:
+    """``drop_mask``: optional int32 [B, H, T, T//32] that receives the dropout keep bits so the
+    backward pass can read them back instead of re-running the generator."""
+    rc = _lib.cuda().ab_attn_fwd(ptr(qkv), ptr(out), ptr(lse), ptr(drop_mask), c_int(B), c_int(T), c_int(H), c_int(hd),
                                  c_float(1.0 / hd ** 0.5), c_ulonglong(seed), c_uint(stream_id),
                                  c_uint(_lib.dropout_thr16(p_drop)), ptr(_lib.status_word()),
                                  stream_ptr())
@@ -26,12 +28,15 @@ def attention_fwd(qkv, out, lse, B: int, T: int, H: int, hd: int, p_drop: float,
 
 
 def attention_bwd(qkv, out, lse, dout, dqkv, delta, B: int, T: int, H: int, hd: int, p_drop: float,
-                  seed: int, stream_id: int) -> None:
-    """``delta`` is fp32 scratch [B, H, T] (row sums of dO*O, filled here)."""
-    rc = _lib.cuda().ab_attn_bwd(ptr(qkv), ptr(out), ptr(lse), ptr(dout), ptr(dqkv), ptr(delta), c_int(B), c_int(T),
+                  seed: int, stream_id: int, drop_mask=None, dq_acc=None) -> None:
+    """``delta`` is fp32 scratch [B, H, T] (row sums of dO*O, filled here).  ``dq_acc``: optional
+    all-zero fp32 [B*T, H*hd] accumulator (head_dim 64 only) that selects the single-kernel
+    backward; it is handed back all zero."""
+    rc = _lib.cuda().ab_attn_bwd(ptr(qkv), ptr(out), ptr(lse), ptr(dout), ptr(dqkv), ptr(delta),
+                                 ptr(drop_mask), ptr(dq_acc), c_int(B), c_int(T),
                                  c_int(H), c_int(hd), c_float(1.0 / hd ** 0.5), c_ulonglong(seed),
                                  c_uint(stream_id), c_uint(_lib.dropout_thr16(p_drop)),
                                  ptr(_lib.status_word()), stream_ptr())
     if rc != 0:
         raise RuntimeError(f"ab_attn_bwd failed with code {rc} (B={B} T={T} H={H} hd={hd})")
-    _lib.count_launches(3)  # delta + key/value-stationary + query-stationary kernels
+    _lib.count_launches(3)  # delta + (two backward kernels | fused backward + dQ conversion)

@@ -41,19 +41,24 @@ def test_attention_fwd_bwd_no_dropout(B, T, H, hd):
     assert torch.allclose(out.float(), o_ref, rtol=2e-2, atol=2e-2), (out.float() - o_ref).abs().max()
     assert torch.allclose(lse, lse_ref, rtol=1e-3, atol=1e-2)
     dout = (torch.randn(B * T, d, device=dev) * 0.5).bfloat16()
-    dqkv = torch.zeros(B * T, 3 * d, device=dev, dtype=torch.bfloat16)
     delta = torch.zeros(B, H, T, device=dev)
-    attention_bwd(qkv, out, lse, dout, dqkv, delta, B, T, H, hd, 0.0, 0, 0)
-    torch.cuda.synchronize()
-    _lib.check_status()
     o_ref.backward(dout.float())
     g = leaf.grad
-    err = (dqkv.float() - g).abs().max().item()
-    assert err < 3e-2 * max(1.0, g.abs().max().item()), err
-    for i, name in enumerate("qkv"):
-        a, b_ = dqkv.float()[:, i * d:(i + 1) * d], g[:, i * d:(i + 1) * d]
-        rel = (a - b_).norm() / (b_.norm() + 1e-9)
-        assert rel < 2e-2, (name, rel.item())
+    # two-kernel backward, and for head_dim 64 also the single-kernel one with its fp32 dQ accumulator
+    variants = [None] + ([torch.zeros(B * T, d, device=dev)] if hd == 64 else [])
+    for dq_acc in variants:
+        dqkv = torch.zeros(B * T, 3 * d, device=dev, dtype=torch.bfloat16)
+        attention_bwd(qkv, out, lse, dout, dqkv, delta, B, T, H, hd, 0.0, 0, 0, None, dq_acc)
+        torch.cuda.synchronize()
+        _lib.check_status()
+        err = (dqkv.float() - g).abs().max().item()
+        assert err < 3e-2 * max(1.0, g.abs().max().item()), err
+        for i, name in enumerate("qkv"):
+            a, b_ = dqkv.float()[:, i * d:(i + 1) * d], g[:, i * d:(i + 1) * d]
+            rel = (a - b_).norm() / (b_.norm() + 1e-9)
+            assert rel < 2e-2, (name, rel.item(), dq_acc is not None)
+        if dq_acc is not None:
+            assert float(dq_acc.abs().max()) == 0.0     # handed back cleared
 
 
 def test_attention_dropout_mask_consistency():
@@ -91,14 +96,22 @@ def test_attention_dropout_mask_consistency():
     leaf = qkv.float().requires_grad_(True)
     o_ref, _ = _ref(leaf, B, T, H, hd, mask.float(), scale_keep)
     out = torch.zeros(B * T, d, device=dev, dtype=torch.bfloat16)
-    attention_fwd(qkv, out, lse, B, T, H, hd, p, seed, stream)
+    bits = torch.zeros(B, H, T, T // 32, device=dev, dtype=torch.int32)
+    attention_fwd(qkv, out, lse, B, T, H, hd, p, seed, stream, bits)
     assert torch.allclose(out.float(), o_ref, rtol=3e-2, atol=3e-2)
+    # the stored keep bits are the mask recovered above
+    unpacked = ((bits.unsqueeze(-1) >> torch.arange(32, device=dev)) & 1).view(B, H, T, T).bool()
+    assert torch.equal(unpacked & causal, mask & causal)
     dout = (torch.randn(B * T, d, device=dev) * 0.5).bfloat16()
-    dqkv = torch.zeros(B * T, 3 * d, device=dev, dtype=torch.bfloat16)
     delta = torch.zeros(B, H, T, device=dev)
-    attention_bwd(qkv, out, lse, dout, dqkv, delta, B, T, H, hd, p, seed, stream)
-    torch.cuda.synchronize()
-    _lib.check_status()
     o_ref.backward(dout.float())
-    rel = (dqkv.float() - leaf.grad).norm() / leaf.grad.norm()
-    assert rel < 3e-2, rel.item()
+    # regenerate the mask / read the stored bits; two-kernel / single-kernel backward
+    for use_bits, fused in ((False, False), (True, False), (False, True), (True, True)):
+        dqkv = torch.zeros(B * T, 3 * d, device=dev, dtype=torch.bfloat16)
+        dq_acc = torch.zeros(B * T, d, device=dev) if fused else None
+        attention_bwd(qkv, out, lse, dout, dqkv, delta, B, T, H, hd, p, seed, stream,
+                      bits if use_bits else None, dq_acc)
+        torch.cuda.synchronize()
+        _lib.check_status()
+        rel = (dqkv.float() - leaf.grad).norm() / leaf.grad.norm()
+        assert rel < 3e-2, (rel.item(), use_bits, fused)
