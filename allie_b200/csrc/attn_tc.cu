@@ -709,3 +709,37 @@ int ab_attn_bwd(const void* qkv, const void* out, const float* lse, const void* 
   return launch_attn_bwd<128, 1>(tq, td, a, stream);
 }
 }
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free variant (see attn_static.cuh for who needs it and why).
+#include "attn_static.cuh"
+
+namespace ab {
+// Scratch for `delta`.  In host code this name is only a handle; the device address is looked up
+// per device below.
+static __device__ __align__(256) float g_attn_static_delta[AB_ATTN_STATIC_MAX_ROWS];
+static float* g_attn_static_ptr[64] = {nullptr};
+}  // namespace ab
+
+extern "C" int ab_attn_bwd_static(const void* qkv, const void* out, const float* lse,
+                                  const void* dout, void* dqkv, const unsigned int* drop_mask, int B,
+                                  int T, int H, int hd, float scale, unsigned long long seed,
+                                  unsigned int stream_id, unsigned int thr16, int* status,
+                                  cudaStream_t stream) {
+  using namespace ab;
+  if (B <= 0 || T <= 0 || H <= 0) return -1;
+  if (static_cast<long long>(B) * H * T > AB_ATTN_STATIC_MAX_ROWS) return -10;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= 64) return -11;
+  if (!g_attn_static_ptr[dev]) {
+    // once per device, with that device current: turn the symbol into a device pointer
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_attn_static_delta);
+    if (e != cudaSuccess) return (int)e;
+    g_attn_static_ptr[dev] = static_cast<float*>(p);
+  }
+  return ab_attn_bwd(qkv, out, lse, dout, dqkv, g_attn_static_ptr[dev], drop_mask, nullptr, B, T, H, hd,
+                     scale, seed, stream_id, thr16, status, stream);
+}
