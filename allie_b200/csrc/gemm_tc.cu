@@ -414,7 +414,8 @@ extern "C" int ab_gemm_bf16(const void* A, int a_mn, long long lda, const void* 
   GemmArgs g;
   g.M = M; g.N = N; g.K = K; g.k_splits = k_splits; g.ep = *ep; g.status = status;
   if (max_ctas <= 0) max_ctas = 148;
-  const bool narrow = (N <= 128);
+  // narrow tiles also for skinny problems (decode steps with a few hundred rows): twice the CTAs
+  const bool narrow = (N <= 128) || (M <= 256);
   if (narrow) {
     if (!a_mn && !b_mn) return launch<128, 6, false, false>(A, lda, B, ldb, g, max_ctas, stream);
     if (!a_mn && b_mn) return launch<128, 6, false, true>(A, lda, B, ldb, g, max_ctas, stream);

@@ -252,8 +252,10 @@ class B200Engine:
         return cfg.embd_pdrop, cfg.resid_pdrop, cfg.attn_pdrop
 
     def forward(self, B: int, T: int, train: bool, seed: int, compute_loss: bool,
-                write_grad: bool) -> dict:
-        """Runs the forward schedule on the ids / labels already placed in the buffers."""
+                write_grad: bool, kv_hook=None) -> dict:
+        """Runs the forward schedule on the ids / labels already placed in the buffers.
+        ``kv_hook(layer, qkv)`` is called right after each layer's QKV GEMM (the KV-cache prefill
+        uses it to copy keys/values out of the shared inference scratch)."""
         cfg = self.cfg
         buf = self._buffers(B, T, train)
         d, V, eps = cfg.n_embd, cfg.vocab_size, cfg.layer_norm_epsilon
@@ -264,6 +266,8 @@ class B200Engine:
             K.layernorm_fwd(x[l], L["ln1_w"][0], L["ln1_b"][0], buf["ln1"][l], buf["mean1"][l],
                             buf["rstd1"][l], eps, self.rms)
             gemm(buf["ln1"][l], L["qkv_w"][1], b_mn=True, out=buf["qkv"][l], bias=L["qkv_b"][0])
+            if kv_hook is not None:
+                kv_hook(l, buf["qkv"][l])
             self._attention_fwd(buf["qkv"][l], buf["attn"][l], buf["lse"][l], B, T, p_att, seed, 3 + 3 * l,
                                 buf["dmask"][l] if "dmask" in buf else None)
             gemm(buf["attn"][l], L["o_w"][1], b_mn=True, out=buf["xmid"][l], bias=L["o_b"][0],

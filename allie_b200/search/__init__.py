@@ -1,0 +1,7 @@
+"""Decode / search runtime: strategies, model runners, the batched C++ MCTS and its KV-cached
+GPU leaf evaluator."""
+from .strategies import (DECODE_STRATEGIES, ActionValue, AdaptiveMCTS, DecodeResult, DecodeStrategy, MCTS,
+                         MCTSNode, Policy, ScoreResult, kl_regularized_policy)
+
+__all__ = ["DECODE_STRATEGIES", "ActionValue", "AdaptiveMCTS", "DecodeResult", "DecodeStrategy", "MCTS",
+           "MCTSNode", "Policy", "ScoreResult", "kl_regularized_policy"]

@@ -1,0 +1,118 @@
+"""MCTS leaf-evaluation throughput (positions per second) of the medium model.
+
+Workload: `--trees` concurrent search trees (default 256) with `--sims` simulations each (default
+400) on one GPU, random-init GPT-2-medium-shaped Allie model in bf16, root positions = random legal
+games whose prompts are 1-300 tokens long.  Every leaf evaluation is one KV-cached decode step
+(softmax policy over the leaf's legal moves, value, think time).
+
+    python bench_mcts.py                       # batched C++ search + KV-cached sm_100a evaluator
+    python bench_mcts.py --impl sequential     # the reference algorithm: one tree at a time, every
+                                               # leaf re-encodes its whole game at batch 1
+Prints one JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+def random_games(n, tok, rng, max_tokens=300):
+    from allie_b200.data import Game
+
+    games = []
+    for i in range(n):
+        target = int(rng.integers(0, max_tokens - 3))
+        g = Game("180+0", int(rng.integers(800, 2600)), int(rng.integers(800, 2600)), None, False, [], [])
+        while len(g.moves) < target:
+            legal = g.legal_moves
+            if not legal or g.board.is_game_over():
+                break
+            nxt = g.make_move(legal[int(rng.integers(0, len(legal)))])
+            if nxt.board.is_game_over():
+                break
+            g = nxt
+        games.append(g)
+    return games
+
+
+def main():
+    import numpy as np
+    import torch
+
+    from allie_b200.data import UCITokenizer
+    from allie_b200.models import initialize_model
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--trees", type=int, default=256)
+    ap.add_argument("--sims", type=int, default=400)
+    ap.add_argument("--impl", default="batched", choices=["batched", "sequential"])
+    ap.add_argument("--small", action="store_true", help="tiny model (smoke test)")
+    ap.add_argument("--seq-positions", type=int, default=4, help="root positions for --impl sequential")
+    args = ap.parse_args()
+    torch.manual_seed(0)
+    tok = UCITokenizer(max_length=512, vocab_size_multiple_of=128)
+    shape = dict(n_layer=2, n_embd=256, n_head=4) if args.small else dict(n_layer=24, n_embd=1024, n_head=16)
+    model = initialize_model(tok, "gpt2-medium", use_control_token=True, use_regression_head=True,
+                             n_positions=1024, **shape)
+    rng = np.random.default_rng(0)
+    out = {"metric": "MCTS leaf-eval positions/sec", "unit": "positions/s", "impl": args.impl,
+           "dtype": "bf16", "data": "synthetic random legal games, prompts of 1-300 tokens",
+           "config": {"model": "tiny" if args.small else "gpt2-medium-like 24L d1024 16H", "trees": args.trees,
+                      "sims": args.sims}}
+    if args.impl == "batched":
+        from allie_b200.models.engine import B200Engine
+        from allie_b200.ops import _lib
+        from allie_b200.search.batched import BatchedMCTS, KVStepEvaluator
+
+        eng = B200Engine(model, "cuda")
+        games = random_games(args.trees, tok, rng)
+        ev = KVStepEvaluator(eng, tok, args.trees, anc_max=128, legal_max=224, max_prefix=320,
+                             max_nodes=args.sims + 8)
+        bm = BatchedMCTS(tok, ev, n_trees=args.trees, n_sims=args.sims)
+        bm.search(games[: args.trees], n_sims=8)           # warm-up (graph capture, first launches)
+        torch.cuda.synchronize()
+        ev.positions = 0
+        l0 = _lib.LAUNCHES
+        t0 = time.perf_counter()
+        res = bm.search(games)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        _lib.check_status()
+        out.update(value=ev.positions / dt, seconds=dt, positions=ev.positions, steps=ev.kv.steps,
+                   moves_per_s=len(games) / dt, latency_per_move_batch_s=dt, gpu_launches=_lib.LAUNCHES - l0,
+                   sims_done=int(sum(r.n_sims for r in res)))
+    else:
+        from allie_b200.search import MCTS
+
+        dev = "cuda" if torch.cuda.is_available() else "cpu"
+        model.to(dev).eval()
+        from allie_b200.search.runner import TorchRunner
+
+        runner = TorchRunner(model, tok, dev)
+        games = random_games(args.seq_positions, tok, rng)
+        m = MCTS(model, tok, device=dev, runner=runner, n_sims=args.sims)
+        m.score_full(games[0], games[0].legal_moves)
+        if dev == "cuda":
+            torch.cuda.synchronize()
+        c0 = runner.calls
+        t0 = time.perf_counter()
+        for g in games:
+            m.score_full(g, g.legal_moves)
+        if dev == "cuda":
+            torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        out.update(value=(runner.calls - c0) / dt, seconds=dt, positions=runner.calls - c0,
+                   p50_move_latency_s=dt / len(games),
+                   note="sequential PUCT, batch-1 full re-encode per leaf, fp32 PyTorch model "
+                        "(the reference's decode path, src/evaluation/decode.py:336-467)")
+    print(json.dumps(out), flush=True)
+
+
+if __name__ == "__main__":
+    main()
