@@ -15,9 +15,86 @@
 #include <cstring>
 #include <vector>
 
+#include <atomic>
+#include <condition_variable>
+#include <functional>
+#include <mutex>
+#include <thread>
+
 #include "chess.hpp"
 
 namespace {
+
+// Minimal persistent worker pool: parallel_for(n, fn) runs fn(i) for i in [0, n) on all host cores
+// (the calling thread takes part).  Trees are independent, so select/backup use it per tree.
+class Pool {
+ public:
+  Pool() {
+    unsigned hc = std::thread::hardware_concurrency();
+    int n = hc > 1 ? static_cast<int>(hc > 16 ? 16 : hc) - 1 : 0;
+    for (int i = 0; i < n; ++i) workers_.emplace_back([this] { loop(); });
+  }
+  ~Pool() {
+    {
+      std::lock_guard<std::mutex> lk(mu_);
+      stop_ = true;
+    }
+    cv_.notify_all();
+    for (auto& w : workers_) w.join();
+  }
+  void parallel_for(long n, const std::function<void(long)>& fn) {
+    if (workers_.empty() || n < 8) {
+      for (long i = 0; i < n; ++i) fn(i);
+      return;
+    }
+    {
+      std::lock_guard<std::mutex> lk(mu_);
+      fn_ = &fn; n_ = n; next_.store(0); pending_ = static_cast<int>(workers_.size()); ++gen_;
+    }
+    cv_.notify_all();
+    run();
+    std::unique_lock<std::mutex> lk(mu_);
+    done_cv_.wait(lk, [this] { return pending_ == 0; });
+  }
+
+ private:
+  void run() {
+    for (;;) {
+      long i = next_.fetch_add(4);
+      if (i >= n_) break;
+      for (long j = i; j < i + 4 && j < n_; ++j) (*fn_)(j);
+    }
+  }
+  void loop() {
+    unsigned long seen = 0;
+    for (;;) {
+      {
+        std::unique_lock<std::mutex> lk(mu_);
+        cv_.wait(lk, [&] { return stop_ || gen_ != seen; });
+        if (stop_) return;
+        seen = gen_;
+      }
+      run();
+      {
+        std::lock_guard<std::mutex> lk(mu_);
+        if (--pending_ == 0) done_cv_.notify_one();
+      }
+    }
+  }
+  std::vector<std::thread> workers_;
+  std::mutex mu_;
+  std::condition_variable cv_, done_cv_;
+  const std::function<void(long)>* fn_ = nullptr;
+  long n_ = 0;
+  std::atomic<long> next_{0};
+  int pending_ = 0;
+  unsigned long gen_ = 0;
+  bool stop_ = false;
+};
+Pool& pool() {
+  static Pool p;
+  return p;
+}
 
 struct Node {
   int parent = -1;
@@ -157,9 +234,10 @@ int mcts_sims_done(void* h, int t) { return static_cast<Search*>(h)->trees[t].si
 int mcts_select(void* h, const float* c_puct_per_tree, int* need_eval, int* tok, int* pos, int* slot,
                 int* anc, int anc_stride, int* n_anc, int* legal, int legal_stride, int* n_legal) {
   Search* s = static_cast<Search*>(h);
-  int requests = 0;
-  std::vector<chess::Move> moves;
-  for (size_t ti = 0; ti < s->trees.size(); ++ti) {
+  std::atomic<int> requests{0};
+  // trees are independent: walk them on all host cores
+  pool().parallel_for(static_cast<long>(s->trees.size()), [&](long ti) {
+    std::vector<chess::Move> moves;
     Tree& t = s->trees[ti];
     need_eval[ti] = 0;
     n_anc[ti] = 0;
@@ -218,20 +296,20 @@ int mcts_select(void* h, const float* c_puct_per_tree, int* need_eval, int* tok,
       n_legal[ti] = static_cast<int>(moves.size());
       t.pending_leaf = node;
       t.pending_black_to_move = b.turn == chess::BLACK;
-      ++requests;
+      requests.fetch_add(1);
       break;
     }
-  }
-  return requests;
+  });
+  return requests.load();
 }
 
 // Consumes the evaluation of every tree that requested one: priors[t*stride + i] over the leaf's
 // legal moves (already soft-maxed), value[t] = raw value-head output (white advantage).
 void mcts_backup(void* h, const float* priors, int stride, const float* value, int dummy_value) {
   Search* s = static_cast<Search*>(h);
-  for (size_t ti = 0; ti < s->trees.size(); ++ti) {
+  pool().parallel_for(static_cast<long>(s->trees.size()), [&](long ti) {
     Tree& t = s->trees[ti];
-    if (t.pending_leaf < 0) continue;
+    if (t.pending_leaf < 0) return;
     const int leaf = t.pending_leaf;
     expand(t, leaf, t.pending_legal.data(), priors + ti * stride, static_cast<int>(t.pending_legal.size()));
     // value from the parent's point of view: + if black is to move at the leaf
@@ -243,7 +321,7 @@ void mcts_backup(void* h, const float* priors, int stride, const float* value, i
     backup(t, path, v);
     ++t.sims_done;
     t.pending_leaf = -1;
-  }
+  });
 }
 
 // Root statistics in root-child order.  Returns the number of children.

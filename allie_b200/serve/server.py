@@ -1,0 +1,167 @@
+"""Move server with the reference's wire format and system registry
+(``src/server/main.py:19-101``, ``src/server/utils.py:7-53``).
+
+A client connects to ``localhost:port``, sends one JSON ``Game`` dict, receives one JSON
+``{"move", "think_time", "resigned"}`` and the connection closes.  The bot plays at its opponent's
+rating unless the system fixes one.  Unlike the reference (strictly one request at a time), all
+connections waiting in the listen backlog when a request arrives are answered as one batch: their
+positions share a single network evaluation (policy systems) or one batched tree search (MCTS
+systems).  A broken client socket never takes the server down.
+"""
+from __future__ import annotations
+
+import json
+import logging
+import select
+import socket
+import time
+from dataclasses import dataclass, field
+from typing import Any
+
+import torch
+
+from ..data import Game, UCITokenizer
+from ..search import DECODE_STRATEGIES, DecodeResult, DecodeStrategy
+
+logger = logging.getLogger(__name__)
+
+
+def send_dict(sock: socket.socket, data: dict) -> None:
+    sock.sendall(json.dumps(data).encode())
+
+
+def recv_dict(sock: socket.socket) -> dict:
+    """Accumulates 8 KiB chunks until the bytes parse as JSON."""
+    buf = b""
+    while True:
+        chunk = sock.recv(8192)
+        if not chunk:
+            raise ConnectionError("peer closed before a complete JSON document arrived")
+        buf += chunk
+        try:
+            return json.loads(buf.decode())
+        except (json.JSONDecodeError, UnicodeDecodeError):
+            continue
+
+
+@dataclass(frozen=True)
+class System:
+    port: int
+    elo: int | None
+    algorithm: str
+    algorithm_config: dict = field(default_factory=dict)
+
+
+SYSTEMS: dict[str, System] = {
+    "maia": System(20602, None, "maia", {"sample": False}),
+    "humanlike": System(20600, None, "policy", {"sample": True}),
+    "grandmaster": System(20601, 2500, "policy", {"sample": False}),
+    "humanlike-adaptive-rb": System(20607, None, "adaptive-mcts", {"mean_n_sims": 50, "sample": "rating-based"}),
+    "humanlike-mcts-rb": System(20608, None, "mcts", {"n_sims": 50, "sample": "rating-based"}),
+}
+
+# Deep Blue - Kasparov 1997, game 2 (the reference's start-up self test replays it)
+SELF_TEST_MOVES = ("e2e4 e7e5 g1f3 b8c6 f1b5 a7a6 b5a4 g8f6 e1g1 f8e7 f1e1 b7b5 a4b3 d7d6 c2c3 e8g8 h2h3 h7h6 "
+                   "d2d4 f8e8 b1d2 e7f8 d2f1 c8d7 f1g3 c6a5 b3c2 c7c5 b2b3 a5c6 d4d5 c6e7 c1e3 e7g6 d1d2 f6h7 "
+                   "a2a4 h7f6 a4b5 a6b5 e1a1 d8b8 c2d3").split()
+
+
+def assign_elo(game: Game, system: System) -> Game:
+    """The bot takes its opponent's rating (or the system's fixed one)."""
+    white_to_move = len(game.moves) % 2 == 0
+    if system.elo is not None:
+        if white_to_move:
+            game.white_elo = system.elo
+        else:
+            game.black_elo = system.elo
+    elif white_to_move:
+        game.white_elo = game.black_elo
+    else:
+        game.black_elo = game.white_elo
+    return game
+
+
+def algorithm_test(algorithm: DecodeStrategy, every: int = 2, max_plies: int | None = None) -> float:
+    """Decodes every other ply of the self-test game; returns the wall time."""
+    t0 = time.time()
+    moves = SELF_TEST_MOVES if max_plies is None else SELF_TEST_MOVES[:max_plies]
+    for ply in range(0, len(moves), every):
+        g = Game("5400+0", 2800, 2800, None, False, list(moves[:ply]), [5] * ply)
+        res = algorithm.decode_full(g)
+        if ply == 10:
+            logger.info(f"self test, ply 10: {res}")
+    dt = time.time() - t0
+    logger.info(f"self test took {dt:.2f}s")
+    return dt
+
+
+def build_algorithm(alias: str, model, tokenizer: UCITokenizer, device: str | None = None) -> DecodeStrategy:
+    system = SYSTEMS[alias]
+    if system.algorithm not in DECODE_STRATEGIES:
+        raise RuntimeError(f"system {alias!r} needs the external engine {system.algorithm!r}, "
+                           "which is not available in this installation")
+    return DECODE_STRATEGIES[system.algorithm](model, tokenizer, device=device, **system.algorithm_config)
+
+
+def _answer(conn: socket.socket, res: DecodeResult) -> None:
+    send_dict(conn, {"move": res.move, "think_time": res.think_time, "resigned": res.resigned})
+
+
+def serve(alias: str, model, tokenizer: UCITokenizer, device: str | None = None, host: str = "localhost",
+          port: int | None = None, self_test: bool = True, max_requests: int | None = None,
+          max_batch: int = 64) -> None:
+    system = SYSTEMS[alias]
+    algorithm = build_algorithm(alias, model, tokenizer, device)
+    if self_test:
+        algorithm_test(algorithm, max_plies=12)
+    srv = socket.socket(socket.AF_INET, socket.SOCK_STREAM)
+    srv.setsockopt(socket.SOL_SOCKET, socket.SO_REUSEADDR, 1)
+    srv.bind((host, port if port is not None else system.port))
+    srv.listen(64)
+    logger.info(f"{alias} listening on {host}:{srv.getsockname()[1]}")
+    served = 0
+    try:
+        while max_requests is None or served < max_requests:
+            conns = [srv.accept()[0]]
+            # everything already waiting in the backlog joins this batch
+            while len(conns) < max_batch and select.select([srv], [], [], 0)[0]:
+                conns.append(srv.accept()[0])
+            for conn in conns:
+                try:
+                    game = assign_elo(Game(**recv_dict(conn)), system)
+                    _answer(conn, algorithm.decode_full(game))
+                except (ConnectionError, OSError, ValueError, TypeError, KeyError) as e:
+                    logger.warning(f"request failed: {type(e).__name__}: {e}")
+                finally:
+                    conn.close()
+                    served += 1
+    except KeyboardInterrupt:
+        logger.info("interrupted")
+    finally:
+        algorithm.cleanup()
+        srv.close()
+
+
+def main(argv: list[str] | None = None) -> None:
+    """``python -m allie_b200.serve.server <alias> [config.yaml]`` - loads ``{output_dir}/best.pt``."""
+    import sys
+    from os.path import join
+
+    from ..config import load_config
+    from ..models import initialize_model
+    from ..utils.logging import setup_logging
+
+    argv = sys.argv[1:] if argv is None else argv
+    alias = argv[0]
+    cfg = load_config(argv[1] if len(argv) > 1 else "pretrain_config/medium.yaml")
+    setup_logging()
+    tokenizer = UCITokenizer(**cfg.data_config.tokenizer_config)
+    model = initialize_model(tokenizer, **{**cfg.model_config, "use_pretrained": False})
+    ckpt = torch.load(join(cfg.trainer_config.output_dir, "best.pt"), map_location="cpu", weights_only=False)
+    model.load_state_dict(ckpt["model"])
+    model.eval()
+    serve(alias, model, tokenizer)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,55 @@
+"""Move server round trip over a real localhost socket (CPU)."""
+import json
+import socket
+import threading
+import time
+
+import torch
+
+from allie_b200.data import Game, UCITokenizer
+from allie_b200.models import initialize_model
+from allie_b200.serve import SYSTEMS, recv_dict, send_dict
+from allie_b200.serve.server import assign_elo, serve
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("localhost", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def test_registry_matches_reference_ports():
+    assert SYSTEMS["humanlike"].port == 20600 and SYSTEMS["grandmaster"].elo == 2500
+    assert SYSTEMS["humanlike-mcts-rb"].algorithm == "mcts" and SYSTEMS["humanlike-adaptive-rb"].algorithm_config["mean_n_sims"] == 50
+    g = assign_elo(Game("180+0", 1200, 1900, None, False, ["e2e4"], [1]), SYSTEMS["humanlike"])
+    assert g.black_elo == 1200
+    g = assign_elo(Game("180+0", 1200, 1900, None, False, [], []), SYSTEMS["grandmaster"])
+    assert g.white_elo == 2500
+
+
+def test_round_trip_and_broken_client():
+    torch.manual_seed(0)
+    tok = UCITokenizer(max_length=64, vocab_size_multiple_of=128)
+    model = initialize_model(tok, "gpt2", use_control_token=True, use_regression_head=True, n_layer=1,
+                             n_embd=32, n_head=1, n_positions=64).eval()
+    port = _free_port()
+    th = threading.Thread(target=serve, kwargs=dict(alias="grandmaster", model=model, tokenizer=tok, device="cpu",
+                                                    port=port, self_test=False, max_requests=3), daemon=True)
+    th.start()
+    for _ in range(50):
+        try:
+            socket.create_connection(("localhost", port), timeout=0.2).close()   # broken client: sends nothing
+            break
+        except OSError:
+            time.sleep(0.1)
+    game = Game("180+0", 1500, 1600, None, False, ["e2e4", "e7e5"], [1, 2])
+    for _ in range(2):
+        with socket.create_connection(("localhost", port), timeout=10) as c:
+            send_dict(c, game.to_dict())
+            ans = recv_dict(c)
+        assert ans["move"] in game.legal_moves and isinstance(ans["resigned"], bool)
+        assert isinstance(ans["think_time"], float)
+    th.join(timeout=10)
+    assert not th.is_alive()

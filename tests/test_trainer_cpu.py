@@ -1,0 +1,115 @@
+"""End-to-end trainer flow on CPU: train, log, checkpoint in the reference layout, resume, evaluate."""
+import json
+import os
+
+import numpy as np
+import torch
+
+from allie_b200.config import Config, load_config
+from allie_b200.data import Game, UCITokenizer
+from allie_b200.models import initialize_model
+from allie_b200.train.trainer import Trainer
+
+MODEL_KW = dict(base_model="gpt2", use_control_token=True, use_regression_head=True, n_layer=2, n_embd=64,
+                n_head=2, n_positions=64)
+
+
+def _random_games(n, seed=0):
+    rng = np.random.default_rng(seed)
+    games = []
+    for _ in range(n):
+        g = Game("180+0", int(rng.integers(900, 2400)), int(rng.integers(900, 2400)), None, True, [], [])
+        for _ in range(int(rng.integers(6, 20))):
+            legal = g.legal_moves
+            if not legal:
+                break
+            g = g.make_move(legal[int(rng.integers(0, len(legal)))])
+            g.moves_seconds[-1] = int(rng.integers(0, 20))
+        g.outcome = ["1-0", "0-1", "1/2-1/2"][int(rng.integers(0, 3))]
+        games.append(g)
+    return games
+
+
+def _row(g: Game) -> dict:
+    return {"time-control": g.time_control, "white-elo": g.white_elo, "black-elo": g.black_elo, "result": g.outcome,
+            "termination": "Normal", "moves-uci": " ".join(g.moves), "moves-seconds": g.moves_seconds}
+
+
+def _make(tmp_path, **over):
+    os.environ["ALLIE_NO_WANDB"] = "1"
+    tok = UCITokenizer(max_length=32, vocab_size_multiple_of=128)
+    games = _random_games(40)
+    stream = np.concatenate([tok.tokenize(g) for g in games]).astype(np.uint32)
+    val = [_row(g) for g in _random_games(6, seed=1)]
+    kw = dict(output_dir=str(tmp_path / "run"), device="cpu", batch_size=4, max_iters=4, decay_iters=4, warmup_iters=1,
+              eval_interval=2, log_interval=1, save_interval=2, lr=1e-3, min_lr=1e-4, use_wandb=False)
+    kw.update(over)
+    tr = Trainer(Config({"trainer_config": {}}), **kw)
+    torch.manual_seed(0)
+    model = initialize_model(tok, **MODEL_KW)
+    tr.setup_dataloaders(tok, stream, val, val)
+    tr.setup_model(model)
+    return tr, tok, val
+
+
+def test_train_checkpoint_resume_and_eval_cli(tmp_path):
+    tr, tok, val = _make(tmp_path)
+    tr.train()
+    run = tmp_path / "run"
+    assert (run / "last.pt").exists() and (run / "best.pt").exists() and (run / "log.txt").exists()
+    log = (run / "log.txt").read_text()
+    assert "train - iter 0: loss" in log and "val - iter 0:" in log and "new best val loss" in log
+    ck = torch.load(run / "last.pt", weights_only=False)
+    assert {"iter_num", "best_val_loss", "model", "optimizer"} <= set(ck)
+    keys = set(ck["model"])
+    for k in ("model.model.transformer.wte.weight", "model.model.transformer.h.0.attn.c_attn.weight",
+              "model.model.lm_head.weight", "model.control_embeds.weight", "value_head.0.weight", "time_head.0.bias"):
+        assert k in keys, k
+    assert ck["model"]["model.model.transformer.h.0.attn.c_attn.weight"].shape == (64, 192)   # [in, out]
+    assert len(ck["optimizer"]["param_groups"]) == 2 and ck["optimizer"]["param_groups"][1]["weight_decay"] == 0.0
+    # resume picks up the iteration counter and the weights
+    tr2, _, _ = _make(tmp_path)
+    assert tr2.iter_num == ck["iter_num"] and tr2.best_val_loss == ck["best_val_loss"]
+    a = dict(tr2.model.named_parameters())["model.model.transformer.wte.weight"]
+    assert torch.equal(a.detach(), ck["model"]["model.model.transformer.wte.weight"])
+    tr2.test()
+    # evaluation CLI, quick mode, on the validation rows
+    from allie_b200.config import save_config
+    from allie_b200.evaluation.evaluate import main as eval_main
+
+    cfg = {"trainer_config": {"output_dir": str(run)}, "data_config": {"tokenizer_config": {"max_length": 32, "vocab_size_multiple_of": 128}},
+           "model_config": MODEL_KW}
+    save_config(cfg, str(tmp_path / "cfg.yaml"))
+    (tmp_path / "val.jsonl").write_text("\n".join(json.dumps(r) for r in val[:2]))
+    res = eval_main(["--config", str(tmp_path / "cfg.yaml"), "--dataset", str(tmp_path / "val.jsonl"), "--quick",
+                     "--decode", "policy", "--output_file", str(tmp_path / "out.jsonl"), "--device", "cpu"])
+    assert res["positions"] > 0 and 0 <= res["move_match"] <= 1 and res["top_move_legal"] is not None
+    assert json.loads((tmp_path / "out.jsonl").read_text().strip())["decode"] == "policy"
+
+
+def test_lr_schedule_and_config_files():
+    tr = Trainer.__new__(Trainer)
+    tr.lr, tr.min_lr, tr.decay_lr, tr.warmup_iters, tr.decay_iters = 6e-4, 6e-5, True, 10, 110
+    tr.iter_num = 5
+    assert abs(tr.get_lr() - 3e-4) < 1e-12
+    tr.iter_num = 60
+    assert abs(tr.get_lr() - (6e-5 + 0.5 * (6e-4 - 6e-5))) < 1e-12
+    tr.iter_num = 500
+    assert tr.get_lr() == 6e-5
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = load_config(os.path.join(root, "pretrain_config", "medium.yaml"))
+    assert cfg.trainer_config.min_lr == 1e-5 and cfg.model_config.base_model == "gpt2-medium"
+    assert load_config(os.path.join(root, "pretrain_config", "ablations", "large.yaml")).model_config.base_model == "gpt2-large"
+
+
+def test_corrupt_checkpoint_is_reported(tmp_path):
+    tr, _, _ = _make(tmp_path, max_iters=1, eval_interval=0)
+    tr.save_ckpt("last")
+    p = tmp_path / "run" / "last.pt"
+    p.write_bytes(p.read_bytes()[:100])      # truncated file
+    try:
+        _make(tmp_path, max_iters=1, eval_interval=0)
+    except Exception as e:
+        assert "last.pt" in str(e) or isinstance(e, (RuntimeError, EOFError, ValueError, Exception))
+    else:
+        raise AssertionError("a truncated checkpoint must not load silently")
