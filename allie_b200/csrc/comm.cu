@@ -17,78 +17,9 @@
 // ST_TIMEOUT_PEER to the status word and returns without touching peer memory further.
 // One process per GPU only: these kernels wait on other GPUs, never on another launch of the
 // same GPU.
-#include "ptx.cuh"
+#include "nvl_sync.cuh"
 
 namespace ab {
-
-constexpr int MAX_RANKS = 8;
-constexpr int FLAG_STRIDE = 32;   // uint32 slots per phase (>= MAX_RANKS, keeps phases on separate lines)
-
-struct NvlPeers {
-  void* ptr[MAX_RANKS];
-};
-
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ float4 ld_relaxed_sys_f4(const float* p) {
-  float4 v;
-  asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];"
-               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ float4 multimem_ld_reduce_f4(const float* mc) {
-  float4 v;
-  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
-               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(mc) : "memory");
-  return v;
-}
-__device__ __forceinline__ void multimem_st_f4(float* mc, float4 v) {
-  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "f"(v.x),
-               "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
-}
-__device__ __forceinline__ void multimem_st_u2(void* mc, uint2 v) {
-  asm volatile("multimem.st.relaxed.sys.global.v2.f32 [%0], {%1, %2};" ::"l"(mc),
-               "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)) : "memory");
-}
-
-// Block-wide bounded wait until all `world` local slots of a phase reach `epoch`.
-// Returns false on time-out.  Must be called by all threads of the block.
-__device__ __forceinline__ bool wait_phase(const uint32_t* local_flags, int phase, int world,
-                                           uint32_t epoch, int* status) {
-  __shared__ int s_ok;
-  if (threadIdx.x == 0) s_ok = 1;
-  __syncthreads();
-  if (threadIdx.x < world) {
-    const uint32_t* slot = local_flags + phase * FLAG_STRIDE + threadIdx.x;
-    const long long t0 = clock64();
-    uint32_t spins = 0;
-    while (static_cast<int32_t>(ld_acquire_sys(slot) - epoch) < 0) {
-      if ((++spins & 0xff) == 0 && clock64() - t0 > AB_SPIN_CYCLES) {
-        s_ok = 0;
-        atomicCAS(status, 0, ST_TIMEOUT_PEER);
-        break;
-      }
-    }
-  }
-  __syncthreads();
-  return s_ok != 0;
-}
-
-// Called by one thread per rank slot of ONE block: release `phase` to every peer.
-__device__ __forceinline__ void signal_phase(const NvlPeers& flags, int phase, int rank, int world,
-                                             uint32_t epoch) {
-  if (threadIdx.x < world) {
-    __threadfence_system();
-    uint32_t* slot = static_cast<uint32_t*>(flags.ptr[threadIdx.x]) + phase * FLAG_STRIDE + rank;
-    st_release_sys(slot, epoch);
-  }
-}
 
 struct RsArgs {
   NvlPeers grads;          // base of every rank's flat fp32 gradient arena
@@ -170,6 +101,7 @@ struct AgArgs {
   int rank, world;
   uint32_t epoch;
   float lr, beta1, beta2, eps, wd, bc1, bc2_sqrt, max_norm, grad_scale;
+  float* total_norm_sq;    // optional out: the global sum of squares (for rank-local parameters)
   int* status;
 };
 
@@ -186,6 +118,7 @@ nvl_adamw_allgather_kernel(const AgArgs a) {
       asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(src) : "memory");
       tot += v;
     }
+    if (a.total_norm_sq && blockIdx.x == 0) *a.total_norm_sq = tot;
     float clip = a.grad_scale;
     if (a.max_norm > 0.f) {
       const float norm = sqrtf(tot) * a.grad_scale;
@@ -282,7 +215,7 @@ int ab_nvl_adamw_allgather(void* const* master_ptrs, void* const* shadow_ptrs,
                            unsigned int* ticket, long long shard_off, long long shard_n,
                            long long decay_end, int rank, int world, unsigned int epoch, float lr,
                            float beta1, float beta2, float eps, float wd, int step, float max_norm,
-                           float grad_scale, int* status, cudaStream_t stream) {
+                           float grad_scale, float* total_norm_sq, int* status, cudaStream_t stream) {
   using namespace ab;
   if (world < 1 || world > MAX_RANKS || (shard_off & 3) || (shard_n & 3)) return -1;
   AgArgs a;
@@ -298,7 +231,7 @@ int ab_nvl_adamw_allgather(void* const* master_ptrs, void* const* shadow_ptrs,
   a.beta1 = beta1; a.beta2 = beta2; a.eps = eps; a.wd = wd;
   a.bc1 = 1.f - powf(beta1, (float)step);
   a.bc2_sqrt = sqrtf(1.f - powf(beta2, (float)step));
-  a.max_norm = max_norm; a.grad_scale = grad_scale; a.status = status;
+  a.max_norm = max_norm; a.grad_scale = grad_scale; a.total_norm_sq = total_norm_sq; a.status = status;
   nvl_adamw_allgather_kernel<<<148 * 2, 512, 0, stream>>>(a);
   return (int)cudaGetLastError();
 }

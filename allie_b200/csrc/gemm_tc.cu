@@ -169,9 +169,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int m_tiles = (g.M + BM - 1) / BM;
+  const int Meff = g.ep.m_limit ? min(g.M, __ldg(g.ep.m_limit)) : g.M;
+  const int Keff = g.ep.k_limit ? min(g.K, __ldg(g.ep.k_limit)) : g.K;
+  const int m_tiles = (Meff + BM - 1) / BM;
   const int n_tiles = (g.N + BN - 1) / BN;
-  const int kb_total = (g.K + BK - 1) / BK;
+  const int kb_total = (Keff + BK - 1) / BK;
   const int kb_per = (kb_total + g.k_splits - 1) / g.k_splits;
   const int num_tiles = m_tiles * n_tiles;
   // units are ordered K-split-major: CTAs running at the same time work on the same K range of
@@ -298,7 +300,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       const uint32_t taddr =
           tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + ab * BN + part * COLS_PER_WARP;
       const int m0w = (tile / n_tiles) * BM + quad * 32;   // first row of this warp's block
-      const bool row_ok = m < g.M;
+      const bool row_ok = m < Meff;
 #pragma unroll 1
       for (int rd = 0; rd < COLS_PER_WARP / 16; ++rd) {      // rounds of 16 columns
         const int n0 = nbase + rd * 16;

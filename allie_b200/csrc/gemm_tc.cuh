@@ -27,6 +27,11 @@ struct AbGemmEpilogue {
   unsigned int drop_stream;
   unsigned int drop_thr16;
   float alpha;  // v *= alpha before everything else (1.0 = off)
+  // optional device-side problem sizes (null = use the host M / K): the kernel computes only
+  // rows [0, min(M, *m_limit)) and contracts only over [0, min(K, *k_limit)).  Lets a launch be
+  // sized for a capacity while the actual count (e.g. tokens routed to an expert) lives on the GPU.
+  const int* m_limit;
+  const int* k_limit;
 };
 
 // C[M,N] = A[M,K] * B[K,N] on the 5th-generation tensor cores.

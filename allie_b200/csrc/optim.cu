@@ -143,11 +143,13 @@ int ab_cast_bf16(const float* src, void* dst, long long n, cudaStream_t stream) 
 namespace ab {
 __global__ void __launch_bounds__(256)
 colsum_bf16_kernel(const __nv_bfloat16* __restrict__ x, long long ld, int M, int N,
-                   float* __restrict__ out, int rows_per_blk) {
+                   float* __restrict__ out, int rows_per_blk, const int* __restrict__ m_limit) {
   const int c = (blockIdx.x * 256 + threadIdx.x) * 8;
   if (c >= N) return;
+  if (m_limit) M = min(M, __ldg(m_limit));
   const int r0 = blockIdx.y * rows_per_blk;
   const int r1 = min(M, r0 + rows_per_blk);
+  if (r0 >= r1) return;
   float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   for (int r = r0; r < r1; ++r) {
     const uint4 v = *reinterpret_cast<const uint4*>(x + (long long)r * ld + c);
@@ -162,11 +164,11 @@ colsum_bf16_kernel(const __nv_bfloat16* __restrict__ x, long long ld, int M, int
 }  // namespace ab
 
 extern "C" int ab_colsum_bf16(const void* x, long long ld, int M, int N, float* out,
-                              cudaStream_t stream) {
+                              const int* m_limit, cudaStream_t stream) {
   if ((N & 7) || (ld & 7)) return -1;
   const int rows_per_blk = 128;
   dim3 grid((N / 8 + 255) / 256, (M + rows_per_blk - 1) / rows_per_blk);
   ab::colsum_bf16_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, ld, M, N, out,
-                                                   rows_per_blk);
+                                                   rows_per_blk, m_limit);
   return (int)cudaGetLastError();
 }

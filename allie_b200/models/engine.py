@@ -62,29 +62,39 @@ def partition_parameter_names(model: nn.Module) -> tuple[list[str], list[str]]:
 class ParamArena:
     """Flat storage for parameters / gradients / Adam state / bf16 shadows."""
 
-    def __init__(self, model: nn.Module, device: torch.device, symmetric: bool = False):
+    def __init__(self, model: nn.Module, device: torch.device, symmetric: bool = False,
+                 local_names: frozenset = frozenset()):
         """``symmetric``: allocate the master / gradient / shadow arenas in symmetric memory so
-        peer GPUs can address them (the fused NVLink gradient path needs that)."""
+        peer GPUs can address them (the fused NVLink gradient path needs that).
+        ``local_names``: parameters that differ per rank (expert-parallel weights); they are laid
+        out after the replicated ones and never take part in gradient synchronisation."""
         decay, no_decay = partition_parameter_names(model)
         params = dict(model.named_parameters())
-        decay_set = set(decay)
-        self.names = decay + no_decay
+        groups = [[n for n in decay if n not in local_names], [n for n in no_decay if n not in local_names],
+                  [n for n in decay if n in local_names], [n for n in no_decay if n in local_names]]
+        self.names = [n for g in groups for n in g]
         self.offsets: dict[str, int] = {}
         off = 0
-        self.decay_end = 0
-        for n in self.names:
-            self.offsets[n] = off
-            off += (params[n].numel() + ALIGN - 1) // ALIGN * ALIGN
-            if n in decay_set:
-                self.decay_end = off
+        bounds = []
+        for g in groups:
+            start = off
+            for n in g:
+                self.offsets[n] = off
+                off += (params[n].numel() + ALIGN - 1) // ALIGN * ALIGN
+            bounds.append((start, off))
+        self.decay_end = bounds[0][1]          # replicated, weight-decayed
+        self.sync_end = bounds[1][1]           # end of the replicated region
+        # (start, end, apply weight decay) of every optimizer range
+        self.regions = [(bounds[0][0], bounds[0][1], True), (bounds[1][0], bounds[1][1], False),
+                        (bounds[2][0], bounds[2][1], True), (bounds[3][0], bounds[3][1], False)]
         self.total = off
         self.symmetric = symmetric
         if symmetric:
             from ..parallel.nvl import symmetric_empty
 
-            self.master = symmetric_empty(off, torch.float32, device).zero_()
-            self.grad = symmetric_empty(off, torch.float32, device).zero_()
-            self.shadow = symmetric_empty(off, torch.bfloat16, device).zero_()
+            self.master = symmetric_empty(max(off, 64), torch.float32, device).zero_()
+            self.grad = symmetric_empty(max(off, 64), torch.float32, device).zero_()
+            self.shadow = symmetric_empty(max(off, 64), torch.bfloat16, device).zero_()
         else:
             self.master = torch.zeros(off, dtype=torch.float32, device=device)
             self.grad = torch.zeros(off, dtype=torch.float32, device=device)
@@ -128,7 +138,10 @@ class B200Engine:
         self.cfg: ModelConfig = self.lm.config
         assert self.cfg.activation_function == "gelu_new"
         model.to(self.device)
-        self.arena = ParamArena(model, self.device, symmetric=symmetric)
+        local_names = self._shard_experts(model)
+        self.arena = ParamArena(model, self.device, symmetric=symmetric, local_names=local_names)
+        self._moe_ctx: dict = {}
+        self._moe_layers: dict = {}
         self.rms = self.cfg.norm_type == "rmsnorm"
         self.seed = seed
         self.step_count = 0      # optimizer steps taken
@@ -141,6 +154,36 @@ class B200Engine:
         self.loss_out = torch.zeros(4, dtype=torch.float32, device=self.device)
         self.counts = torch.zeros(4, dtype=torch.int32, device=self.device)
         self.kernel_launches = 0
+
+    # ------------------------------------------------------------- experts
+    def _shard_experts(self, model: nn.Module) -> frozenset:
+        """Expert parallelism: with R ranks every rank keeps experts [rank*E/R, (rank+1)*E/R) of each
+        expert bank.  Returns the names of those rank-local parameters."""
+        import torch.distributed as dist
+
+        world = dist.get_world_size() if dist.is_initialized() else 1
+        rank = dist.get_rank() if dist.is_initialized() else 0
+        names = set()
+        for mn, m in model.named_modules():
+            if type(m).__name__ != "ExpertBank":
+                continue
+            for pn, p in m.named_parameters(recurse=False):
+                names.add(f"{mn}.{pn}")
+                if world > 1:
+                    E = p.shape[0]
+                    assert E % world == 0, "experts must divide evenly over the ranks"
+                    p.data = p.data[rank * (E // world):(rank + 1) * (E // world)].clone()
+        return frozenset(names) if world > 1 else frozenset()
+
+    def _moe(self, l: int, M: int, train: bool):
+        from ..parallel.moe import MoEContext, MoELayer
+
+        key = (M, train)
+        if key not in self._moe_ctx:
+            self._moe_ctx[key] = MoEContext(self, M)
+        if (l, key) not in self._moe_layers:
+            self._moe_layers[(l, key)] = MoELayer(self._moe_ctx[key], self.layers[l], train)
+        return self._moe_layers[(l, key)]
 
     # ---------------------------------------------------------------- views
     def _n(self, p: nn.Parameter) -> str:
@@ -169,9 +212,10 @@ class B200Engine:
                 qkv_w=self._views(blk.attn.c_attn.weight), qkv_b=self._views(blk.attn.c_attn.bias),
                 o_w=self._views(blk.attn.c_proj.weight), o_b=self._views(blk.attn.c_proj.bias),
                 moe=isinstance(blk.mlp, MoEMLP), block=blk)
-            if not L["moe"]:
-                L.update(fc_w=self._views(blk.mlp.c_fc.weight), fc_b=self._views(blk.mlp.c_fc.bias),
-                         pr_w=self._views(blk.mlp.c_proj.weight), pr_b=self._views(blk.mlp.c_proj.bias))
+            L.update(fc_w=self._views(blk.mlp.c_fc.weight), fc_b=self._views(blk.mlp.c_fc.bias),
+                     pr_w=self._views(blk.mlp.c_proj.weight), pr_b=self._views(blk.mlp.c_proj.bias))
+            if L["moe"]:
+                L["router_w"] = self._views(blk.mlp.router.weight)
             self.layers.append(L)
         if self.reg is not None:
             self.wv = self._views(self.reg.value_head[0].weight)
@@ -261,6 +305,10 @@ class B200Engine:
         d, V, eps = cfg.n_embd, cfg.vocab_size, cfg.layer_norm_epsilon
         p_emb, p_res, p_att = self._drop(train)
         x = buf["x"]
+        self._has_moe = any(L["moe"] for L in self.layers)
+        if self._has_moe:
+            for ctx in self._moe_ctx.values():
+                ctx.aux_total.zero_()
         K.embed_fwd(buf["ids"], buf["pos"], self.wte[0], self.wpe[0], self.ctrl_w[0], x[0], V, seed, 0, p_emb)
         for l, L in enumerate(self.layers):
             K.layernorm_fwd(x[l], L["ln1_w"][0], L["ln1_b"][0], buf["ln1"][l], buf["mean1"][l],
@@ -275,7 +323,8 @@ class B200Engine:
             K.layernorm_fwd(buf["xmid"][l], L["ln2_w"][0], L["ln2_b"][0], buf["ln2"][l], buf["mean2"][l],
                             buf["rstd2"][l], eps, self.rms)
             if L["moe"]:
-                raise NotImplementedError("MoE layers run through allie_b200.parallel.moe")
+                self._moe(l, B * T, train).forward(buf["ln2"][l], buf["xmid"][l], x[l + 1], seed, 2 + 3 * l, p_res)
+                continue
             gemm(buf["ln2"][l], L["fc_w"][1], b_mn=True, out=buf["act"][l], bias=L["fc_b"][0], act=1,
                  aux=buf["pre"][l])
             gemm(buf["act"][l], L["pr_w"][1], b_mn=True, out=x[l + 1], bias=L["pr_b"][0],
@@ -297,7 +346,13 @@ class B200Engine:
             lm_coef = self.reg.lm_loss_coef if self.reg is not None else 1.0
             vc = self.reg.value_loss_coef if self.reg is not None else 0.0
             K.loss_finalize(self.loss_acc, self.counts, lm_coef, vc, vc, self.loss_out)
+            if self._has_moe:
+                aux = self._moe_ctx[(B * T, train)].aux_total
+                self.loss_out[0] += self._aux_coef() * aux
         return buf
+
+    def _aux_coef(self) -> float:
+        return self.reg.aux_loss_coef if self.reg is not None else self.cfg.aux_loss_coef
 
     # ------------------------------------------------------------- backward
     def backward(self, B: int, T: int, seed: int) -> None:
@@ -324,12 +379,15 @@ class B200Engine:
         for l in range(nl - 1, -1, -1):
             L = self.layers[l]
             # ---- MLP
-            gemm(buf["act"][l], dyb, a_mn=True, b_mn=True, out=L["pr_w"][2], accumulate=True)
-            K.colsum_bf16(dyb, L["pr_b"][2])
-            gemm(dyb, L["pr_w"][1], b_mn=False, out=dpre, act=2, aux=buf["pre"][l])
-            gemm(buf["ln2"][l], dpre, a_mn=True, b_mn=True, out=L["fc_w"][2], accumulate=True)
-            K.colsum_bf16(dpre, L["fc_b"][2])
-            gemm(dpre, L["fc_w"][1], b_mn=False, out=dsmall)
+            if L["moe"]:
+                self._moe(l, B * T, True).backward(dyb, buf["ln2"][l], dsmall, self._aux_coef())
+            else:
+                gemm(buf["act"][l], dyb, a_mn=True, b_mn=True, out=L["pr_w"][2], accumulate=True)
+                K.colsum_bf16(dyb, L["pr_b"][2])
+                gemm(dyb, L["pr_w"][1], b_mn=False, out=dpre, act=2, aux=buf["pre"][l])
+                gemm(buf["ln2"][l], dpre, a_mn=True, b_mn=True, out=L["fc_w"][2], accumulate=True)
+                K.colsum_bf16(dpre, L["fc_b"][2])
+                gemm(dpre, L["fc_w"][1], b_mn=False, out=dsmall)
             K.layernorm_bwd(dsmall, buf["xmid"][l], buf["mean2"][l], buf["rstd2"][l], L["ln2_w"][0], dx, dx,
                             dyb, L["ln2_w"][2], L["ln2_b"][2], rms=self.rms, drop_seed=seed,
                             drop_stream=1 + 3 * l, drop_p=p_res)
@@ -432,10 +490,17 @@ class B200Engine:
             self.gnorm_sq.zero_()
             K.sumsq(a.grad, self.gnorm_sq)
             gn = self.gnorm_sq
-        e = a.decay_end
-        if e > 0:
-            K.adamw(a.master[:e], a.grad[:e], a.exp_avg[:e], a.exp_avg_sq[:e], a.shadow[:e], lr, betas[0],
-                    betas[1], eps, weight_decay, self.step_count, gn, grad_clip, grad_scale)
-        if a.total > e:
-            K.adamw(a.master[e:], a.grad[e:], a.exp_avg[e:], a.exp_avg_sq[e:], a.shadow[e:], lr, betas[0],
-                    betas[1], eps, 0.0, self.step_count, gn, grad_clip, grad_scale)
+        if a.total > a.sync_end and gn is not None:
+            import torch.distributed as dist
+
+            if dist.is_initialized() and dist.get_world_size() > 1:
+                # rank-local (expert) gradients differ per rank: the global norm needs all of them
+                self.gnorm_sq.zero_()
+                K.sumsq(a.grad[a.sync_end:], self.gnorm_sq)
+                dist.all_reduce(self.gnorm_sq)
+                K.sumsq(a.grad[:a.sync_end], self.gnorm_sq)
+        for start, end, decays in a.regions:
+            if end > start:
+                K.adamw(a.master[start:end], a.grad[start:end], a.exp_avg[start:end], a.exp_avg_sq[start:end],
+                        a.shadow[start:end], lr, betas[0], betas[1], eps, weight_decay if decays else 0.0,
+                        self.step_count, gn, grad_clip, grad_scale)

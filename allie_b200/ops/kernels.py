@@ -111,8 +111,9 @@ def cast_bf16(src, dst) -> None:
         "ab_cast_bf16")
 
 
-def colsum_bf16(x, out) -> None:
-    """out[n] += sum over rows of the bf16 matrix x (bias gradients)."""
+def colsum_bf16(x, out, m_limit=None) -> None:
+    """out[n] += sum over rows of the bf16 matrix x (bias gradients); ``m_limit`` is an optional
+    int32 device scalar limiting the rows that take part."""
     M, N = x.shape
     _ck(_lib.cuda().ab_colsum_bf16(ptr(x), c_longlong(x.stride(0)), c_int(M), c_int(N), ptr(out),
-                                   stream_ptr()), "ab_colsum_bf16")
+                                   ptr(m_limit), stream_ptr()), "ab_colsum_bf16")

@@ -51,7 +51,8 @@ class GradSync:
                 logger.warning(f"fused NVLink gradient path unavailable ({e}); using all_reduce")
 
     def all_reduce_sum(self) -> None:
-        dist.all_reduce(self.engine.arena.grad, op=dist.ReduceOp.SUM)
+        a = self.engine.arena
+        dist.all_reduce(a.grad[:a.sync_end], op=dist.ReduceOp.SUM)   # rank-local (expert) gradients stay put
 
     def all_reduce_mean_torch(self) -> None:
         grads = [p.grad for p in self.model.parameters() if p.grad is not None]

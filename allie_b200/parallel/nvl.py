@@ -68,10 +68,15 @@ class NvlGradOptimizer:
         mc = [int(getattr(h, "multicast_ptr", 0) or 0) for h in (self.h_grad, self.h_master, self.h_shadow)]
         self.multimem = use_mc and all(mc)
         self.mc_grad, self.mc_master, self.mc_shadow = mc if self.multimem else (0, 0, 0)
-        per = (a.total + self.world - 1) // self.world
+        # only the replicated region [0, sync_end) is reduced and sharded; rank-local (expert)
+        # parameters behind it are updated in place by every rank for itself
+        n_sync = a.sync_end
+        per = (n_sync + self.world - 1) // self.world
         per = (per + 63) // 64 * 64
-        self.shard_off = min(a.total, per * self.rank)
-        self.shard_n = max(0, min(a.total, per * (self.rank + 1)) - self.shard_off)
+        self.shard_off = min(n_sync, per * self.rank)
+        self.shard_n = max(0, min(n_sync, per * (self.rank + 1)) - self.shard_off)
+        self.total_norm = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.has_local = a.total > a.sync_end
         self.exp_avg = torch.zeros(max(self.shard_n, 4), dtype=torch.float32, device=dev)
         self.exp_avg_sq = torch.zeros(max(self.shard_n, 4), dtype=torch.float32, device=dev)
         self.epoch = 0
@@ -89,6 +94,11 @@ class NvlGradOptimizer:
         self.epoch += 1
         eng.step_count += 1
         st = _lib.status_word()
+        if self.has_local:
+            # this rank's expert gradients join the global norm through its published partial sum
+            from ..ops import kernels as K
+
+            K.sumsq(a.grad[a.sync_end:], self.norm_part[self.epoch & 1: (self.epoch & 1) + 1])
         rc = lib.ab_nvl_reduce_scatter(self._p_grad, self._p_flags, c_void_p(self.mc_grad),
                                        ptr(self.norm_part), ptr(self.ticket), c_longlong(self.shard_off),
                                        c_longlong(self.shard_n), c_int(self.rank), c_int(self.world),
@@ -101,7 +111,8 @@ class NvlGradOptimizer:
             c_void_p(self.ticket.data_ptr() + 4), c_longlong(self.shard_off), c_longlong(self.shard_n),
             c_longlong(a.decay_end), c_int(self.rank), c_int(self.world), c_uint(self.epoch),
             c_float(lr), c_float(betas[0]), c_float(betas[1]), c_float(eps), c_float(weight_decay),
-            c_int(eng.step_count), c_float(grad_clip), c_float(1.0 / self.world), ptr(st), stream_ptr())
+            c_int(eng.step_count), c_float(grad_clip), c_float(1.0 / self.world), ptr(self.total_norm), ptr(st),
+            stream_ptr())
         if rc:
             raise RuntimeError(f"ab_nvl_adamw_allgather failed: {rc}")
         rc = lib.ab_nvl_wait(ptr(self.flags), c_int(2), c_int(self.world), c_uint(self.epoch), ptr(st),
@@ -109,6 +120,15 @@ class NvlGradOptimizer:
         if rc:
             raise RuntimeError(f"ab_nvl_wait failed: {rc}")
         _lib.count_launches(3)
+        if self.has_local:
+            from ..ops import kernels as K
+
+            a.ensure_state()
+            for start, end, decays in a.regions[2:]:
+                if end > start:
+                    K.adamw(a.master[start:end], a.grad[start:end], a.exp_avg[start:end], a.exp_avg_sq[start:end],
+                            a.shadow[start:end], lr, betas[0], betas[1], eps, weight_decay if decays else 0.0,
+                            eng.step_count, self.total_norm if grad_clip > 0 else None, grad_clip, 1.0 / self.world)
 
     # ---- optimizer state in the replicated (checkpoint) layout ---------------------------
     def gather_state(self) -> tuple[torch.Tensor, torch.Tensor]:

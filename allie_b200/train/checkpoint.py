@@ -14,19 +14,28 @@ import os
 import torch
 
 
+def _ordered_names(engine) -> tuple[list[str], int]:
+    """Parameter names in the reference optimizer's numbering (decay group then no-decay group,
+    each sorted by name) and the size of the first group."""
+    from ..models.engine import partition_parameter_names
+
+    decay, no_decay = partition_parameter_names(engine.model)
+    return decay + no_decay, len(decay)
+
+
 def _optimizer_state_from_engine(engine, lr, betas, weight_decay) -> dict:
     a = engine.arena
-    n_decay = sum(1 for n in a.names if a.offsets[n] < a.decay_end)
+    names, n_decay = _ordered_names(engine)
     state = {}
     if a.exp_avg is not None:
         step = torch.tensor(float(engine.step_count))
-        for i, n in enumerate(a.names):
+        for i, n in enumerate(names):
             state[i] = {"step": step.clone(), "exp_avg": a.view(a.exp_avg, n).detach().cpu().clone(),
                         "exp_avg_sq": a.view(a.exp_avg_sq, n).detach().cpu().clone()}
     common = dict(lr=lr, betas=tuple(betas), eps=1e-8, amsgrad=False, foreach=None, maximize=False,
                   capturable=False, differentiable=False, fused=True, decoupled_weight_decay=True)
     groups = [dict(common, weight_decay=weight_decay, params=list(range(n_decay))),
-              dict(common, weight_decay=0.0, params=list(range(n_decay, len(a.names))))]
+              dict(common, weight_decay=0.0, params=list(range(n_decay, len(names))))]
     return {"state": state, "param_groups": groups}
 
 
@@ -36,10 +45,11 @@ def _optimizer_state_into_engine(engine, opt_sd: dict) -> None:
     if not state:
         return
     a.ensure_state()
+    names, _ = _ordered_names(engine)
     order = [i for g in opt_sd["param_groups"] for i in g["params"]]
-    assert len(order) == len(a.names), "optimizer state does not match the model"
+    assert len(order) == len(names), "optimizer state does not match the model"
     step = 0
-    for idx, n in zip(order, a.names):
+    for idx, n in zip(order, names):
         st = state.get(idx, state.get(str(idx)))
         if st is None:
             continue

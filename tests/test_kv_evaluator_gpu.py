@@ -21,7 +21,7 @@ def test_kv_cached_leaf_matches_full_reencode():
     # make the heads and logits less degenerate than a fresh init
     with torch.no_grad():
         for p in model.parameters():
-            p.mul_(2.0)
+            p.mul_(1.5)
     eng = B200Engine(model, "cuda")
     model._b200_engine = eng
     games = [Game("180+0", 1500, 1600, None, False, mv, [1] * len(mv)) for mv in
@@ -57,8 +57,11 @@ def test_kv_cached_leaf_matches_full_reencode():
             torch.cuda.synchronize()
             _lib.check_status()
             # two different bf16 kernel paths (flash prefill vs cached decode): noise grows with depth
-            assert np.allclose(pa, pb, atol=1e-2, rtol=0.15), (depth, np.abs(pa - pb).max())
-            assert np.allclose(vva, vvb, atol=5e-2), (depth, np.abs(vva - vvb).max())
+            for t in range(n):
+                nl = int(req["n_legal"][t])
+                la_, lb_ = np.log(pa[t, :nl] + 1e-9), np.log(pb[t, :nl] + 1e-9)
+                assert np.abs(la_ - lb_).max() < 0.1, (depth, t, np.abs(la_ - lb_).max())
+            assert np.allclose(vva, vvb, atol=4e-2), (depth, np.abs(vva - vvb).max())
     # whole searches run and respect their budgets
     bm = BatchedMCTS(tok, KVStepEvaluator(eng, tok, n, 64, 224, 64, 128), n_trees=n, n_sims=40, anc_max=64)
     res = bm.search(games)
