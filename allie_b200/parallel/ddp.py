@@ -26,7 +26,8 @@ logger = logging.getLogger(__name__)
 def broadcast_parameters(model: torch.nn.Module, engine=None, src: int = 0) -> None:
     """Rank 0's initial weights to every rank (what the DDP constructor does)."""
     if engine is not None:
-        dist.broadcast(engine.arena.master, src)
+        a = engine.arena
+        dist.broadcast(a.master[:a.sync_end], src)     # rank-local (expert) parameters are not replicated
         engine.arena.refresh_shadow()
     else:
         for p in model.parameters():

@@ -1,6 +1,6 @@
 """Worker for the multi-rank trainer tests (run under torch.distributed.run).
 
-usage: ddp_worker.py <out_dir> <mode> <device>   mode: fused | collective | auto
+usage: ddp_worker.py <out_dir> <mode> <device> [moe]   mode: fused | collective | auto
 Trains a tiny model for 3 optimizer steps on a fixed synthetic stream (dropout off) and writes
 the final flat parameters of every rank to <out_dir>/params_<mode>_<rank>.pt .
 """
@@ -20,6 +20,7 @@ from allie_b200.train.trainer import Trainer
 
 def main():
     out_dir, mode, device = sys.argv[1], sys.argv[2], sys.argv[3]
+    moe = len(sys.argv) > 4 and sys.argv[4] == "moe"
     os.environ["ALLIE_NO_WANDB"] = "1"
     rank = int(os.environ.get("RANK", 0))
     T, B = 128, 4
@@ -31,7 +32,13 @@ def main():
     torch.manual_seed(0)
     model = initialize_model(tok, "gpt2", use_control_token=True, use_regression_head=True, n_layer=2,
                              n_embd=128, n_head=2, n_positions=T, resid_pdrop=0.0, embd_pdrop=0.0,
-                             attn_pdrop=0.0)
+                             attn_pdrop=0.0, **(dict(num_experts=8, moe_ffn=256, moe_layer_freq=2, capacity_factor=8.0,
+                                                      aux_loss_coef=0.0) if moe else {}))
+    if moe:
+        with torch.no_grad():
+            for n_, p_ in model.named_parameters():
+                if "router" in n_:
+                    p_.mul_(20.0)
     rng = np.random.default_rng(5)
     stream = (rng.integers(0, 1968, size=1 << 16).astype(np.uint32)
               | (rng.integers(1, 20, size=1 << 16).astype(np.uint32) << 16))
@@ -42,7 +49,7 @@ def main():
     losses = []
     for step in range(3):
         # the same global batch regardless of world size: rank r takes every world-th window
-        starts = wrng.integers(0, len(stream) - T, size=(2, B * world))
+        starts = wrng.integers(0, len(stream) - T, size=(2, 8))     # 8 windows per micro-step in total
         wins = []
         for ms in range(2):
             mine = starts[ms][rank::world]
@@ -52,7 +59,8 @@ def main():
         tr.iter_num += 1
     flat = torch.cat([p.detach().float().reshape(-1).cpu() for _, p in sorted(model.named_parameters())])
     fused = bool(tr.grad_sync is not None and tr.grad_sync.fused)
-    torch.save({"params": flat, "losses": losses, "fused": fused,
+    named = {n: p.detach().float().cpu() for n, p in model.named_parameters()}
+    torch.save({"params": flat, "named": named, "rank": rank, "world": world, "losses": losses, "fused": fused,
                 "multimem": bool(fused and tr.grad_sync.nvl.multimem)},
                os.path.join(out_dir, f"params_{mode}_{rank}.pt"))
     if device.startswith("cuda"):

@@ -10,15 +10,15 @@ import torch
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def _launch(nproc, out_dir, mode, device, port, extra_env=None):
+def _launch(nproc, out_dir, mode, device, port, extra_env=None, extra_args=()):
     env = dict(os.environ, ALLIE_NO_WANDB="1", **(extra_env or {}))
     env.pop("RANK", None)
     if nproc == 1:
-        cmd = [sys.executable, os.path.join(HERE, "ddp_worker.py"), str(out_dir), mode, device]
+        cmd = [sys.executable, os.path.join(HERE, "ddp_worker.py"), str(out_dir), mode, device, *extra_args]
     else:
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
                "--master-addr", "127.0.0.1", "--master-port", str(port),
-               os.path.join(HERE, "ddp_worker.py"), str(out_dir), mode, device]
+               os.path.join(HERE, "ddp_worker.py"), str(out_dir), mode, device, *extra_args]
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
 
@@ -53,3 +53,27 @@ def test_fused_nvlink_path_matches_all_reduce(tmp_path):
     p2p = torch.load(tmp_path / "params_p2p_0.pt")
     d = (got["params"] - p2p["params"]).abs()
     assert d.max().item() < 3 * 2e-3 and d.mean().item() < 2e-5, (d.max().item(), d.mean().item(), got["multimem"])
+
+
+@pytest.mark.gpu
+def test_expert_parallel_two_ranks_match_single_rank(tmp_path):
+    """MoE model: 2 ranks (each owning half of the experts, tokens exchanged through the peer-memory
+    dispatch/combine kernels, dense gradients through the fused NVLink path) must land on the
+    parameters of a single-rank run over the same global batch."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    one, two = tmp_path / "one", tmp_path / "two"
+    one.mkdir(); two.mkdir()
+    _launch(1, one, "collective", "cuda", 29631, extra_args=("moe",))
+    _launch(2, two, "fused", "cuda", 29632, {"ALLIE_NVL_MULTIMEM": "0"}, extra_args=("moe",))
+    ref = torch.load(one / "params_collective_0.pt")["named"]
+    for r in range(2):
+        got = torch.load(two / f"params_fused_{r}.pt")
+        assert got["fused"]
+        for name, p in got["named"].items():
+            want = ref[name]
+            if p.shape != want.shape:          # rank-local expert shard
+                El = p.shape[0]
+                want = want[r * El:(r + 1) * El]
+            d = (p - want).abs()
+            assert d.max().item() < 3 * 2e-3 and d.mean().item() < 2e-4, (name, r, d.max().item(), d.mean().item())
