@@ -99,6 +99,9 @@ class ModelConfig:
     moe_layer_freq: int = 3               # every k-th block is MoE (block index % k == k-1)
     aux_loss_coef: float = 0.01
     capacity_factor: float = 2.0
+    # expert parallelism at construction time: build only experts [ep_rank*E/ep_world, ...) per rank
+    ep_world: int = 1
+    ep_rank: int = 0
     extra: dict = field(default_factory=dict)
 
     @property

@@ -1,0 +1,125 @@
+"""JSONL -> training stream and friends (reference ``src/data/sample-lichess.py``,
+``create-np-dataset.py``, ``concat-np-memmaps.py``, ``compute-elo-stats.py``, ``random-games.py``).
+
+    python -m allie_b200.etl.dataset sample  in.jsonl out_prefix      # ELO-balanced, val/test split
+    python -m allie_b200.etl.dataset tokenize train.jsonl train.bin   # flat uint32 memmap
+    python -m allie_b200.etl.dataset concat a.bin b.bin out.bin
+    python -m allie_b200.etl.dataset elo-stats in.jsonl
+    python -m allie_b200.etl.dataset random-games out.jsonl --n 1000
+"""
+from __future__ import annotations
+
+import argparse
+import collections
+import json
+import random
+
+import numpy as np
+
+from ..data import Game, UCITokenizer, json_to_game
+
+
+def keep_probability(elo: int, counts: dict[int, int], target: int) -> float:
+    """Per-100-ELO-bin keep probability that flattens the rating histogram to ``target`` games."""
+    return min(1.0, target / max(1, counts.get(elo // 100, 1)))
+
+
+def sample(src: str, prefix: str, target_per_bin: int = 100_000, seed: int = 0) -> None:
+    rng = random.Random(seed)
+    counts: dict[int, int] = collections.Counter()
+    with open(src) as f:
+        for line in f:
+            counts[int(json.loads(line)["white-elo"]) // 100] += 1
+    outs = {k: open(f"{prefix}-{k}.jsonl", "w") for k in ("train", "val", "test")}
+    with open(src) as f:
+        for line in f:
+            row = json.loads(line)
+            if rng.random() > keep_probability(int(row["white-elo"]), counts, target_per_bin):
+                continue
+            u = rng.random()
+            outs["val" if u < 1e-4 else "test" if u < 3e-4 else "train"].write(line)
+    for o in outs.values():
+        o.close()
+
+
+def tokenize(src: str, dst: str, seed: int = 0, tokenizer: UCITokenizer | None = None) -> int:
+    """5 % of the games lose their ELO tokens (BOS instead) and 5 % their time control (UNK), games
+    are shuffled and concatenated into one ``uint32`` stream."""
+    tok = tokenizer or UCITokenizer(max_length=512)
+    rng = random.Random(seed)
+    chunks = []
+    with open(src) as f:
+        for line in f:
+            g = json_to_game(json.loads(line))
+            u = rng.random()
+            chunks.append(tok.tokenize(g, add_elo=not u < 0.05, add_time_control=not 0.05 <= u < 0.10))
+    rng.shuffle(chunks)
+    flat = np.concatenate(chunks).astype(np.uint32)
+    mm = np.memmap(dst, dtype=np.uint32, mode="w+", shape=flat.shape)
+    mm[:] = flat
+    mm.flush()
+    return int(flat.size)
+
+
+def concat(parts: list[str], dst: str) -> int:
+    arrays = [np.memmap(p, dtype=np.uint32, mode="r") for p in parts]
+    total = sum(a.size for a in arrays)
+    mm = np.memmap(dst, dtype=np.uint32, mode="w+", shape=(total,))
+    o = 0
+    for a in arrays:
+        mm[o:o + a.size] = a
+        o += a.size
+    mm.flush()
+    return total
+
+
+def elo_stats(src: str) -> dict:
+    elos = []
+    with open(src) as f:
+        for line in f:
+            r = json.loads(line)
+            elos += [int(r["white-elo"]), int(r["black-elo"])]
+    a = np.array(elos)
+    return {"n": int(a.size), "mean": float(a.mean()), "std": float(a.std()), "min": int(a.min()), "max": int(a.max())}
+
+
+def random_games(dst: str, n: int = 1000, max_plies: int = 120, seed: int = 0) -> None:
+    rng = random.Random(seed)
+    with open(dst, "w") as f:
+        for _ in range(n):
+            g = Game("180+0", rng.randint(800, 2600), rng.randint(800, 2600), None, True, [], [])
+            for _ in range(rng.randint(10, max_plies)):
+                legal = g.legal_moves
+                if not legal or g.board.is_game_over():
+                    break
+                g = g.make_move(rng.choice(legal))
+            out = g.board.outcome()
+            result = "1/2-1/2" if out is None or out.winner is None else ("1-0" if out.winner else "0-1")
+            f.write(json.dumps({"time-control": g.time_control, "white-elo": g.white_elo, "black-elo": g.black_elo,
+                                "result": result, "termination": "Normal", "moves-uci": " ".join(g.moves),
+                                "moves-seconds": [rng.randint(0, 20) for _ in g.moves]}) + "\n")
+
+
+def main(argv=None) -> None:
+    ap = argparse.ArgumentParser()
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    s = sub.add_parser("sample"); s.add_argument("src"); s.add_argument("prefix"); s.add_argument("--target", type=int, default=100_000)
+    s = sub.add_parser("tokenize"); s.add_argument("src"); s.add_argument("dst")
+    s = sub.add_parser("concat"); s.add_argument("parts", nargs="+"); s.add_argument("dst")
+    s = sub.add_parser("elo-stats"); s.add_argument("src")
+    s = sub.add_parser("random-games"); s.add_argument("dst"); s.add_argument("--n", type=int, default=1000)
+    a = ap.parse_args(argv)
+    if a.cmd == "sample":
+        sample(a.src, a.prefix, a.target)
+    elif a.cmd == "tokenize":
+        print(tokenize(a.src, a.dst), "tokens")
+    elif a.cmd == "concat":
+        print(concat(a.parts, a.dst), "tokens")
+    elif a.cmd == "elo-stats":
+        print(json.dumps(elo_stats(a.src)))
+    else:
+        random_games(a.dst, a.n)
+
+
+if __name__ == "__main__":
+    main()

@@ -169,7 +169,7 @@ class B200Engine:
                 continue
             for pn, p in m.named_parameters(recurse=False):
                 names.add(f"{mn}.{pn}")
-                if world > 1:
+                if world > 1 and self.cfg.ep_world == 1:     # built with all experts: keep this rank's slice
                     E = p.shape[0]
                     assert E % world == 0, "experts must divide evenly over the ranks"
                     p.data = p.data[rank * (E // world):(rank + 1) * (E // world)].clone()

@@ -82,6 +82,12 @@ class Attention(nn.Module):
             k = torch.cat([past[0], k], dim=2)
             v = torch.cat([past[1], v], dim=2)
         Tk = k.size(2)
+        if getattr(self, "use_sdpa", False) and past is None and key_mask is None:
+            # library attention (used by the plain-PyTorch baselines, not by the oracle tests)
+            y = F.scaled_dot_product_attention(q, k, v, is_causal=True,
+                                               dropout_p=self.attn_pdrop if self.training else 0.0)
+            y = y.transpose(1, 2).reshape(B, T, d)
+            return F.dropout(self.c_proj(y), self.resid_pdrop, self.training), (k, v)
         att = (q @ k.transpose(-1, -2)) / math.sqrt(self.head_dim)
         causal = torch.ones(Tk, Tk, dtype=torch.bool, device=x.device).tril()[Tk - T:]
         att = att.masked_fill(~causal, float("-inf"))
@@ -125,8 +131,10 @@ class MoEMLP(nn.Module):
         self.top_k = cfg.moe_top_k
         self.router = nn.Linear(d, E, bias=False)
         nn.init.normal_(self.router.weight, std=0.02)
-        self.c_fc = ExpertBank(E, d, Fe)
-        self.c_proj = ExpertBank(E, Fe, d)
+        assert E % cfg.ep_world == 0
+        n_local = E // cfg.ep_world          # all experts unless built for one expert-parallel rank
+        self.c_fc = ExpertBank(n_local, d, Fe)
+        self.c_proj = ExpertBank(n_local, Fe, d)
         self.resid_pdrop = cfg.resid_pdrop
         self.aux_loss: torch.Tensor | None = None
 

@@ -3,5 +3,7 @@ GPU leaf evaluator."""
 from .strategies import (DECODE_STRATEGIES, ActionValue, AdaptiveMCTS, DecodeResult, DecodeStrategy, MCTS,
                          MCTSNode, Policy, ScoreResult, kl_regularized_policy)
 
+from . import external  # noqa: F401,E402  (registers the external baselines)
+
 __all__ = ["DECODE_STRATEGIES", "ActionValue", "AdaptiveMCTS", "DecodeResult", "DecodeStrategy", "MCTS",
            "MCTSNode", "Policy", "ScoreResult", "kl_regularized_policy"]

@@ -1,0 +1,142 @@
+"""Training throughput of the mixture-of-experts configuration (tokens/s).
+
+Config: 24 layers, d_model 2048, 16 heads of 128, every third block routes top-2 over 64 experts
+of FFN 4096 (dense FFN 4096 elsewhere; about 9.3 B parameters), context 512, vocab 2048, softmax
+router with load-balance loss, expert parallelism over all ranks, global batch 512 sequences
+(micro-batch 8 per GPU), dropout 0.1, bf16 tensor-core math.  Synthetic tokens, random init.
+
+    torchrun --nproc-per-node 8 bench_moe.py --gpus 8              # this framework
+    torchrun --nproc-per-node 8 bench_moe.py --gpus 8 --impl torch # plain-PyTorch EP baseline
+``--layers`` / ``--experts`` shrink the model for smoke runs on fewer GPUs (the full model only
+fits when its experts are spread over 8 GPUs).  Rank 0 prints one JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import tempfile
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+from bench import ClockSampler, barrier_sync, dist_info, max_over_ranks, synthetic_stream  # noqa: E402
+
+SEQ_LEN, GLOBAL_BATCH, MICRO_BATCH = 512, 512, 8
+
+
+def main():
+    import numpy as np
+    import torch
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "torch"])
+    ap.add_argument("--layers", type=int, default=24)
+    ap.add_argument("--experts", type=int, default=64)
+    ap.add_argument("--global-batch", type=int, default=GLOBAL_BATCH)
+    args = ap.parse_args()
+    rank, world, local = dist_info()
+    assert world == args.gpus
+    os.environ.setdefault("ALLIE_NO_WANDB", "1")
+    from allie_b200.config import Config
+    from allie_b200.data import UCITokenizer
+    from allie_b200.models import initialize_model
+
+    ga = max(1, args.global_batch // (MICRO_BATCH * world))
+    tok = UCITokenizer(max_length=SEQ_LEN, vocab_size_multiple_of=128)
+    shape = dict(n_layer=args.layers, n_embd=2048, n_head=16, n_inner=4096, n_positions=1024,
+                 num_experts=args.experts, moe_top_k=2, moe_ffn=4096, moe_layer_freq=3, aux_loss_coef=0.01,
+                 capacity_factor=2.0, ep_world=world, ep_rank=rank)
+    torch.manual_seed(1234)
+    stream = synthetic_stream(1 << 22, len(tok), SEQ_LEN, seed=7 + rank)
+    tokens_per_step = ga * MICRO_BATCH * world * SEQ_LEN
+    if args.impl == "ours":
+        from allie_b200.ops import _lib
+        from allie_b200.train.trainer import Trainer
+
+        trainer = Trainer(Config({}), output_dir=tempfile.mkdtemp(prefix="allie_moe_"), batch_size=MICRO_BATCH,
+                          gradient_accumulation_steps=ga, lr=3e-4, min_lr=1e-5, weight_decay=1e-2, grad_clip=1.0,
+                          warmup_iters=2000, decay_iters=2_000_000, max_iters=2_000_000, eval_interval=0,
+                          log_interval=-1, save_interval=0, use_wandb=False)
+        model = initialize_model(tok, "gpt2-medium", use_control_token=True, use_regression_head=True, **shape)
+        trainer.setup_dataloaders(tok, stream, [], [])
+        trainer.setup_model(model)
+        trainer.iter_num = 100
+        dev = trainer.engine.device
+        wins = [trainer.sampler.next().clone().to(dev) for _ in range(max(ga, 4))]
+        step = lambda i: trainer.train_step([wins[(i * ga + m) % len(wins)] for m in range(ga)])
+        counter = lambda: _lib.LAUNCHES
+        check = _lib.check_status
+    else:
+        sys.path.insert(0, os.path.join(ROOT, "baseline"))
+        import torch.distributed as dist
+        from moe_torch import patch_model_for_baseline
+
+        if world > 1:
+            dist.init_process_group("nccl")
+        torch.cuda.set_device(local)
+        dev = torch.device("cuda", local)
+        model = initialize_model(tok, "gpt2-medium", use_control_token=True, use_regression_head=True, **shape)
+        patch_model_for_baseline(model)
+        model.to(dev).train()
+        local_params = {id(p) for m in model.modules() if type(m).__name__ == "ExpertBank" for p in m.parameters()}
+        dense = [p for p in model.parameters() if id(p) not in local_params]
+        opt = torch.optim.AdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=1e-2, fused=True)
+        wins = []
+        for _ in range(max(ga, 4)):
+            s = np.random.default_rng(len(wins) + rank).integers(0, len(stream) - SEQ_LEN, size=MICRO_BATCH)
+            w = np.stack([stream[i:i + SEQ_LEN] for i in s]).astype(np.int64)
+            wins.append({k: v.to(dev) for k, v in tok.pad_and_collate(list(w.astype(np.uint32))).items()})
+
+        def step(i):
+            for m in range(ga):
+                with torch.autocast("cuda", dtype=torch.bfloat16):
+                    loss = model(**wins[(i * ga + m) % len(wins)])["loss"]
+                loss.backward()
+            if world > 1:
+                flat = torch.cat([p.grad.reshape(-1) for p in dense])
+                dist.all_reduce(flat)
+                flat /= world
+                o = 0
+                for p in dense:
+                    p.grad.copy_(flat[o:o + p.numel()].view_as(p)); o += p.numel()
+            torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
+            opt.step(); opt.zero_grad(set_to_none=True)
+            return loss.detach()
+        counter = lambda: 0
+        check = lambda: None
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize()
+    check()
+    sampler = ClockSampler(local)
+    sampler.start()
+    barrier_sync(world)
+    l0 = counter()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        loss = step(args.warmup + i)
+    e1.record()
+    barrier_sync(world)
+    clocks = sampler.stop()
+    ms = max_over_ranks(e0.elapsed_time(e1), world)
+    check()
+    n_params = sum(p.numel() for p in model.parameters())
+    res = {"metric": "train tokens/sec (MoE config)", "value": tokens_per_step * args.steps / (ms / 1e3),
+           "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+           "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "dtype": "bf16",
+           "data": "synthetic", "impl": "allie_b200" if args.impl == "ours" else "plain-pytorch-ep",
+           "config": {"model": f"{args.layers}L d2048 16H hd128, MoE every 3rd layer: {args.experts} experts x FFN 4096, top-2",
+                      "global_batch": ga * MICRO_BATCH * world, "seq_len": SEQ_LEN, "micro_batch": MICRO_BATCH,
+                      "grad_accum": ga, "parallelism": f"dp{world}+ep{world}", "params_per_rank": n_params},
+           "clocks": clocks, "gpu_launches": counter() - l0, "final_loss": float(loss if loss.dim() == 0 else loss[0])}
+    if rank == 0:
+        print(json.dumps(res), flush=True)
+
+
+if __name__ == "__main__":
+    main()

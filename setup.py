@@ -1,0 +1,11 @@
+from setuptools import find_packages, setup
+
+setup(
+    name="allie-b200",
+    version="0.1.0",
+    description="Blackwell-native framework with the capabilities of y0mingzhang/allie",
+    packages=find_packages(include=["allie_b200", "allie_b200.*"]) + ["modeling", "evaluation", "server"],
+    package_dir={"modeling": "src/modeling", "evaluation": "src/evaluation", "server": "src/server"},
+    package_data={"allie_b200": ["lib/*.so", "csrc/*"]},
+    python_requires=">=3.10",
+)

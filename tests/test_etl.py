@@ -1,0 +1,45 @@
+"""Data preparation: SAN resolution, PGN rows, tokenised stream (CPU)."""
+import json
+
+import numpy as np
+
+from allie_b200.chess import Board
+from allie_b200.data import UCITokenizer
+from allie_b200.etl.dataset import concat, elo_stats, random_games, tokenize
+from allie_b200.etl.pgn import parse_game, san_to_uci
+
+PGN = '''[Event "Rated Blitz game"]
+[White "a"]
+[Black "b"]
+[Result "1-0"]
+[WhiteElo "1500"]
+[BlackElo "1600"]
+[TimeControl "180+2"]
+[Termination "Normal"]
+
+1. e4 { [%clk 0:03:00] } 1... e5 { [%clk 0:03:00] } 2. Nf3 { [%clk 0:02:58] } 2... Nc6 { [%clk 0:02:59] } 3. Bc4 { [%clk 0:02:55] } 3... Nf6 { [%clk 0:02:50] } 4. O-O { [%clk 0:02:50] } 4... Bc5 { [%clk 0:02:45] } 5. d3 { [%clk 0:02:45] } 5... d6 { [%clk 0:02:40] } 1-0
+'''
+
+
+def test_san_resolution():
+    b = Board()
+    assert san_to_uci(b, "e4") == "e2e4" and san_to_uci(b, "Nf3") == "g1f3"
+    b = Board("8/P6k/8/8/8/8/8/K7 w - - 0 1")
+    assert san_to_uci(b, "a8=Q+") == "a7a8q"
+    b = Board("r3k2r/8/8/8/8/8/8/R3K2R w KQkq - 0 1")
+    assert san_to_uci(b, "O-O-O") == "e1c1" and san_to_uci(b, "Rad1") == "a1d1"
+
+
+def test_parse_game_and_stream(tmp_path):
+    row = parse_game(PGN)
+    assert row["moves-uci"].split()[:4] == ["e2e4", "e7e5", "g1f3", "b8c6"] and row["moves-uci"].split()[6] == "e1g1"
+    assert row["moves-seconds"][0] == 2 and row["moves-seconds"][2] == 4 and len(row["moves-seconds"]) == 10
+    assert parse_game(PGN.replace("Blitz", "Bullet")) is None
+    random_games(str(tmp_path / "g.jsonl"), n=20, max_plies=30)
+    rows = [json.loads(l) for l in open(tmp_path / "g.jsonl")]
+    assert len(rows) == 20 and all(len(r["moves-uci"].split()) == len(r["moves-seconds"]) for r in rows)
+    tok = UCITokenizer(max_length=64)
+    n = tokenize(str(tmp_path / "g.jsonl"), str(tmp_path / "a.bin"), tokenizer=tok)
+    assert n == np.memmap(tmp_path / "a.bin", dtype=np.uint32, mode="r").size
+    assert concat([str(tmp_path / "a.bin"), str(tmp_path / "a.bin")], str(tmp_path / "c.bin")) == 2 * n
+    assert elo_stats(str(tmp_path / "g.jsonl"))["n"] == 40
