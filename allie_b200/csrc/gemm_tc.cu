@@ -14,6 +14,7 @@
 // transposed copies.  No TMA multicast is used anywhere.
 #include "gemm_tc.cuh"
 #include "ptx.cuh"
+#include <cstdlib>
 
 namespace ab {
 
@@ -112,6 +113,57 @@ __device__ __forceinline__ void epilogue_math8(const GemmArgs& g, float* v, uint
     const float4 r1 = *reinterpret_cast<const float4*>(ep.resid + (long long)m * ep.ldr + n + 4);
     v[0] += r0.x; v[1] += r0.y; v[2] += r0.z; v[3] += r0.w;
     v[4] += r1.x; v[5] += r1.y; v[6] += r1.z; v[7] += r1.w;
+  }
+}
+
+// One epilogue warp drains its 32 rows x COLS columns of a finished accumulator: TMEM -> registers
+// -> fused math -> swizzled staging tile -> TMA store (or reduce-add), 16 columns per round.
+template <int COLS>
+__device__ __forceinline__ void epilogue_drain(const GemmArgs& g, const CUtensorMap& tmOut,
+                                               const CUtensorMap& tmAux, uint32_t taddr, int m,
+                                               int m0w, int nbase, bool row_ok, uint8_t* my_stage,
+                                               int lane) {
+#pragma unroll 1
+  for (int rd = 0; rd < COLS / 16; ++rd) {      // rounds of 16 columns
+    const int n0 = nbase + rd * 16;
+    if (n0 >= g.N) break;                                 // warp-uniform
+    uint32_t r[16];
+    tmem_ld16(taddr + rd * 16, r);
+    if (lane == 0) tma_store_wait_read<0>();              // staging tile free again
+    __syncwarp();
+    tmem_ld_wait();
+#pragma unroll
+    for (int grp = 0; grp < 2; ++grp) {
+      const int n = n0 + grp * 8;
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[grp * 8 + j]);
+      uint4 pre = make_uint4(0, 0, 0, 0);
+      epilogue_math8(g, v, pre, m, n, row_ok && n < g.N);
+      if (g.ep.out_fp32) {
+        // 16 fp32 columns = 64-byte rows, 64B swizzle: 16-byte chunk index ^= (row >> 1) & 3
+        uint8_t* rowp = my_stage + lane * 64;
+        const int sw = (lane >> 1) & 3;
+        *reinterpret_cast<float4*>(rowp + (((2 * grp) ^ sw) << 4)) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(rowp + (((2 * grp + 1) ^ sw) << 4)) = make_float4(v[4], v[5], v[6], v[7]);
+      } else {
+        // 16 bf16 columns = 32-byte rows, 32B swizzle: chunk index ^= (row >> 2) & 1
+        const uint32_t off = lane * 32 + ((grp ^ ((lane >> 2) & 1)) << 4);
+        uint4 o;
+        o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
+        o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
+        *reinterpret_cast<uint4*>(my_stage + off) = o;
+        if (g.ep.act == 1) *reinterpret_cast<uint4*>(my_stage + 1024 + off) = pre;
+      }
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      if (g.ep.accumulate) tma_reduce_add_2d(&tmOut, my_stage, n0, m0w);
+      else                 tma_store_2d(&tmOut, my_stage, n0, m0w);
+      if (g.ep.act == 1) tma_store_2d(&tmAux, my_stage + 1024, n0, m0w);
+      tma_store_commit();
+    }
   }
 }
 
@@ -301,48 +353,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + ab * BN + part * COLS_PER_WARP;
       const int m0w = (tile / n_tiles) * BM + quad * 32;   // first row of this warp's block
       const bool row_ok = m < Meff;
-#pragma unroll 1
-      for (int rd = 0; rd < COLS_PER_WARP / 16; ++rd) {      // rounds of 16 columns
-        const int n0 = nbase + rd * 16;
-        if (n0 >= g.N) break;                                 // warp-uniform
-        uint32_t r[16];
-        tmem_ld16(taddr + rd * 16, r);
-        if (lane == 0) tma_store_wait_read<0>();              // staging tile free again
-        __syncwarp();
-        tmem_ld_wait();
-#pragma unroll
-        for (int grp = 0; grp < 2; ++grp) {
-          const int n = n0 + grp * 8;
-          float v[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[grp * 8 + j]);
-          uint4 pre = make_uint4(0, 0, 0, 0);
-          epilogue_math8(g, v, pre, m, n, row_ok && n < g.N);
-          if (g.ep.out_fp32) {
-            // 16 fp32 columns = 64-byte rows, 64B swizzle: 16-byte chunk index ^= (row >> 1) & 3
-            uint8_t* rowp = my_stage + lane * 64;
-            const int sw = (lane >> 1) & 3;
-            *reinterpret_cast<float4*>(rowp + (((2 * grp) ^ sw) << 4)) = make_float4(v[0], v[1], v[2], v[3]);
-            *reinterpret_cast<float4*>(rowp + (((2 * grp + 1) ^ sw) << 4)) = make_float4(v[4], v[5], v[6], v[7]);
-          } else {
-            // 16 bf16 columns = 32-byte rows, 32B swizzle: chunk index ^= (row >> 2) & 1
-            const uint32_t off = lane * 32 + ((grp ^ ((lane >> 2) & 1)) << 4);
-            uint4 o;
-            o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
-            o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
-            *reinterpret_cast<uint4*>(my_stage + off) = o;
-            if (g.ep.act == 1) *reinterpret_cast<uint4*>(my_stage + 1024 + off) = pre;
-          }
-        }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          if (g.ep.accumulate) tma_reduce_add_2d(&tmOut, my_stage, n0, m0w);
-          else                 tma_store_2d(&tmOut, my_stage, n0, m0w);
-          if (g.ep.act == 1) tma_store_2d(&tmAux, my_stage + 1024, n0, m0w);
-          tma_store_commit();
-        }
-      }
+      epilogue_drain<COLS_PER_WARP>(g, tmOut, tmAux, taddr, m, m0w, nbase, row_ok, my_stage, lane);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[ab]);
@@ -356,6 +367,273 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
+}
+
+// ------------------------------------------------------------------------------------------
+// CTA-pair variant: a cluster of two CTAs computes a 256 x 256 output tile with
+// tcgen05.mma.cta_group::2 (instruction shape 256 x 256 x 16).  CTA r of the pair stages rows
+// [r*128, r*128+128) of the A tile and columns [r*128, r*128+128) of the B tile in its own shared
+// memory (32 KB per stage instead of 48 KB, so the ring is PAIR_STAGES deep and each B byte is
+// fetched by one SM instead of two) and owns accumulator rows [r*128, r*128+128) in its own TMEM.
+// Only the leader (rank 0) issues MMAs.  Barrier protocol:
+//   full[s]    leader only, 1 arrival (leader producer's expect_tx) + the bytes of both CTAs' loads
+//   empty[s]   one per CTA, 1 arrival: the leader commits to its own and to the partner's
+//   tfull[b]   one per CTA, 1 arrival: committed by the leader to both
+//   tempty[b]  leader only, 2 x NUM_EPI_WARPS arrivals: the epilogue warps of both CTAs
+// Loads are plain unicast TMA loads whose completion is counted on the leader's barrier.
+constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_BN = 256;      // instruction N; each CTA stages PAIR_BN / 2 columns of B
+
+template <bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA,
+                              const __grid_constant__ CUtensorMap tmB,
+                              const __grid_constant__ CUtensorMap tmOut,
+                              const __grid_constant__ CUtensorMap tmAux, const GemmArgs g) {
+  constexpr int STAGES = PAIR_STAGES;
+  constexpr int BN = PAIR_BN;
+  constexpr int HALF_N = BN / 2;
+  constexpr int A_BYTES = BM * BK * 2;
+  constexpr int B_BYTES = HALF_N * BK * 2;
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int TMEM_COLS = 2 * BN;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* stage_out = smem + STAGES * STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(stage_out + NUM_EPI_WARPS * 2048);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + STAGES;
+  uint64_t* tfull_bar = bars + 2 * STAGES;
+  uint64_t* tempty_bar = bars + 2 * STAGES + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tfull_bar[i], 1);
+      mbar_init(&tempty_bar[i], 2 * NUM_EPI_WARPS);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    tma_prefetch_desc(&tmOut);
+    if (g.ep.act == 1) tma_prefetch_desc(&tmAux);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();     // both CTAs' barriers are initialised before either signals the other
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int m_tiles = (g.M + 2 * BM - 1) / (2 * BM);
+  const int n_tiles = (g.N + BN - 1) / BN;
+  const int kb_total = (g.K + BK - 1) / BK;
+  const int kb_per = (kb_total + g.k_splits - 1) / g.k_splits;
+  const int num_tiles = m_tiles * n_tiles;
+  const int num_units = num_tiles * g.k_splits;
+  const int pair_id = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  if (warp == 0) {
+    // ------------------------------------------------------- TMA producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int u = pair_id; u < num_units && ok; u += num_pairs) {
+        const int ks = u / num_tiles;
+        const int tile = u % num_tiles;
+        const int m0 = (tile / n_tiles) * (2 * BM) + rank * BM;
+        const int n0 = (tile % n_tiles) * BN + rank * HALF_N;
+        const int kb0 = ks * kb_per;
+        const int kb1 = min(kb_total, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
+            *abort_flag = ST_TIMEOUT_EMPTY;
+            atomicCAS(g.status, 0, ST_TIMEOUT_EMPTY);
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * STAGE_BYTES;
+          uint8_t* sb = sa + A_BYTES;
+          const uint32_t fb = mapa_shared(smem_u32(&full_bar[stage]), 0);
+          if (leader) mbar_expect_tx(&full_bar[stage], 2 * STAGE_BYTES);
+          const int k0 = kb * BK;
+          if constexpr (!A_MN) {
+            tma_load_2d_pair(sa, &tmA, fb, k0, m0);
+          } else {
+#pragma unroll
+            for (int i = 0; i < BM / 64; ++i)
+              tma_load_2d_pair(sa + i * (BK * 128), &tmA, fb, m0 + i * 64, k0);
+          }
+          if constexpr (!B_MN) {
+            tma_load_2d_pair(sb, &tmB, fb, k0, n0);
+          } else {
+#pragma unroll
+            for (int i = 0; i < HALF_N / 64; ++i)
+              tma_load_2d_pair(sb + i * (BK * 128), &tmB, fb, n0 + i * 64, k0);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // --------------------------------------------------------- MMA issuer (leader only)
+    if (leader && lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(2 * BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      constexpr uint32_t A_LBO = A_MN ? BK * 128 : 16;
+      constexpr uint32_t B_LBO = B_MN ? BK * 128 : 16;
+      constexpr uint32_t A_KADV = A_MN ? UMMA_K * 128 : UMMA_K * 2;
+      constexpr uint32_t B_KADV = B_MN ? UMMA_K * 128 : UMMA_K * 2;
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t acc_phase[2] = {0, 0};
+      int it = 0;
+      bool ok = true;
+      for (int u = pair_id; u < num_units && ok; u += num_pairs, ++it) {
+        const int ks = u / num_tiles;
+        const int kb0 = ks * kb_per;
+        const int kb1 = min(kb_total, kb0 + kb_per);
+        if (kb0 >= kb1) continue;
+        const int ab = it & 1;
+        if (!mbar_wait(&tempty_bar[ab], acc_phase[ab] ^ 1, abort_flag)) {
+          *abort_flag = ST_TIMEOUT_TMEM_EMPTY;
+          atomicCAS(g.status, 0, ST_TIMEOUT_TMEM_EMPTY);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + ab * BN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
+            *abort_flag = ST_TIMEOUT_FULL;
+            atomicCAS(g.status, 0, ST_TIMEOUT_FULL);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t adesc = make_sdesc_sw128(sa + k * A_KADV, A_LBO, 1024);
+            const uint64_t bdesc = make_sdesc_sw128(sb + k * B_KADV, B_LBO, 1024);
+            umma_bf16_pair(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          const uint32_t eb = smem_u32(&empty_bar[stage]);
+          umma_commit_pair(mapa_shared(eb, 0));   // frees this stage in both CTAs
+          umma_commit_pair(mapa_shared(eb, 1));
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        const uint32_t tb = smem_u32(&tfull_bar[ab]);
+        umma_commit_pair(mapa_shared(tb, 0));     // accumulator complete -> both epilogues
+        umma_commit_pair(mapa_shared(tb, 1));
+        acc_phase[ab] ^= 1;
+      }
+    }
+  } else {
+    // ----------------------------------------------------------- epilogue (both CTAs)
+    const int e = warp - 2;
+    const int quad = warp & 3;
+    const int part = e >> 2;
+    constexpr int COLS_PER_WARP = BN / 4;
+    uint8_t* my_stage = stage_out + e * 2048;
+    uint32_t acc_phase[2] = {0, 0};
+    int it = 0;
+    for (int u = pair_id; u < num_units; u += num_pairs, ++it) {
+      const int ks = u / num_tiles;
+      const int tile = u % num_tiles;
+      const int kb0 = ks * kb_per;
+      const int kb1 = min(kb_total, kb0 + kb_per);
+      if (kb0 >= kb1) continue;
+      const int ab = it & 1;
+      const int m0w = (tile / n_tiles) * (2 * BM) + rank * BM + quad * 32;
+      const int m = m0w + lane;
+      const int nbase = (tile % n_tiles) * BN + part * COLS_PER_WARP;
+      if (!mbar_wait(&tfull_bar[ab], acc_phase[ab], abort_flag)) {
+        *abort_flag = ST_TIMEOUT_TMEM_FULL;
+        atomicCAS(g.status, 0, ST_TIMEOUT_TMEM_FULL);
+        break;
+      }
+      acc_phase[ab] ^= 1;
+      tc_fence_after();
+      const uint32_t taddr =
+          tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + ab * BN + part * COLS_PER_WARP;
+      // a warp whose 32 rows lie entirely past M has nothing to store (its accumulator rows came
+      // from zero-filled loads); it still hands the buffer back
+      if (m0w < g.M)
+        epilogue_drain<COLS_PER_WARP>(g, tmOut, tmAux, taddr, m, m0w, nbase, m < g.M, my_stage, lane);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty_bar[ab]), 0));
+    }
+    if (lane == 0) tma_store_wait<0>();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();     // nobody signals the partner's barriers or reads TMEM after this point
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
+template <bool A_MN, bool B_MN>
+static int launch_pair(const void* A, long long lda, const void* B, long long ldb, const GemmArgs& g,
+                       int max_ctas, cudaStream_t stream) {
+  constexpr int HALF_N = PAIR_BN / 2;
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (!A_MN) rc = make_tmap_2d(&tmA, A, g.M, g.K, lda, BM, BK, 2, true);
+  else       rc = make_tmap_2d(&tmA, A, g.K, g.M, lda, BK, 64, 2, true);
+  if (rc) return rc;
+  if (!B_MN) rc = make_tmap_2d(&tmB, B, g.N, g.K, ldb, HALF_N, BK, 2, true);
+  else       rc = make_tmap_2d(&tmB, B, g.K, g.N, ldb, BK, 64, 2, true);
+  if (rc) return rc;
+  CUtensorMap tmOut, tmAux;
+  const AbGemmEpilogue& ep = g.ep;
+  if (ep.out_fp32) rc = make_tmap_2d_sw(&tmOut, ep.out, g.M, g.N, ep.ldo, 32, 16, 4, 64);
+  else             rc = make_tmap_2d_sw(&tmOut, ep.out, g.M, g.N, ep.ldo, 32, 16, 2, 32);
+  if (rc) return rc;
+  if (ep.act == 1) {
+    rc = make_tmap_2d_sw(&tmAux, ep.aux, g.M, g.N, ep.ldaux, 32, 16, 2, 32);
+    if (rc) return rc;
+  } else {
+    tmAux = tmOut;
+  }
+  constexpr int SMEM =
+      1024 + PAIR_STAGES * (BM * BK * 2 + HALF_N * BK * 2) + NUM_EPI_WARPS * 2048 + 256;
+  auto kern = gemm_bf16_tcgen05_pair_kernel<A_MN, B_MN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_set = true;
+  }
+  const int m_tiles = (g.M + 2 * BM - 1) / (2 * BM), n_tiles = (g.N + PAIR_BN - 1) / PAIR_BN;
+  const int units = m_tiles * n_tiles * g.k_splits;
+  int pairs = max_ctas / 2;
+  if (pairs > units) pairs = units;
+  if (pairs < 1) pairs = 1;
+  kern<<<2 * pairs, NUM_THREADS, SMEM, stream>>>(tmA, tmB, tmOut, tmAux, g);
+  return static_cast<int>(cudaGetLastError());
 }
 
 template <int BN, int STAGES, bool A_MN, bool B_MN>
@@ -423,6 +701,18 @@ extern "C" int ab_gemm_bf16(const void* A, int a_mn, long long lda, const void* 
     if (!a_mn && b_mn) return launch<128, 6, false, true>(A, lda, B, ldb, g, max_ctas, stream);
     if (a_mn && !b_mn) return launch<128, 6, true, false>(A, lda, B, ldb, g, max_ctas, stream);
     return launch<128, 6, true, true>(A, lda, B, ldb, g, max_ctas, stream);
+  }
+  // CTA pairs for the large shapes; the single-CTA kernel keeps the device-sized problems
+  // (m_limit / k_limit) and anything a caller pins with AB_GEMM_NO_PAIR=1 in the environment
+  static const bool no_pair = [] {
+    const char* v = getenv("AB_GEMM_NO_PAIR");
+    return v && v[0] == '1';
+  }();
+  if (!no_pair && !ep->m_limit && !ep->k_limit && M >= 512 && N >= 256 && max_ctas >= 2) {
+    if (!a_mn && !b_mn) return launch_pair<false, false>(A, lda, B, ldb, g, max_ctas, stream);
+    if (!a_mn && b_mn) return launch_pair<false, true>(A, lda, B, ldb, g, max_ctas, stream);
+    if (a_mn && !b_mn) return launch_pair<true, false>(A, lda, B, ldb, g, max_ctas, stream);
+    return launch_pair<true, true>(A, lda, B, ldb, g, max_ctas, stream);
   }
   if (!a_mn && !b_mn) return launch<256, 4, false, false>(A, lda, B, ldb, g, max_ctas, stream);
   if (!a_mn && b_mn) return launch<256, 4, false, true>(A, lda, B, ldb, g, max_ctas, stream);

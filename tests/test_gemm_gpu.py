@@ -13,7 +13,9 @@ def _ref(a, b, a_mn, b_mn):
 
 @pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 320), (384, 768, 1024), (200, 264, 136),
-                                   (1000, 128, 512), (64, 64, 64)])
+                                   (1000, 128, 512), (64, 64, 64),
+                                   # large enough for the CTA-pair kernel, with ragged edges
+                                   (1000, 264, 136), (640, 768, 320), (2304, 1024, 192)])
 def test_gemm_layouts(a_mn, b_mn, M, N, K):
     from allie_b200.ops import _lib
     from allie_b200.ops.gemm import gemm
@@ -93,3 +95,21 @@ def test_gemm_big_and_timing():
     ref = (a @ w).float()
     assert torch.allclose(out.float(), ref, rtol=3e-2, atol=3e-2)
     _lib.check_status()
+
+
+def test_gemm_pair_split_k_accumulate():
+    """Weight-gradient shape on the CTA-pair kernel: MN-major operands, split-K, TMA reduce-add."""
+    from allie_b200.ops import _lib
+    from allie_b200.ops.gemm import gemm
+
+    torch.manual_seed(3)
+    dev = "cuda"
+    T, I, O = 4096, 1024, 768
+    x = torch.randn(T, I, device=dev).bfloat16()
+    dy = torch.randn(T, O, device=dev).bfloat16()
+    dw = torch.full((I, O), 2.0, device=dev)
+    gemm(x, dy, a_mn=True, b_mn=True, out=dw, accumulate=True, k_splits=4)
+    ref = 2.0 + x.float().t() @ dy.float()
+    torch.cuda.synchronize()
+    _lib.check_status()
+    assert torch.allclose(dw, ref, rtol=1e-3, atol=0.2)
