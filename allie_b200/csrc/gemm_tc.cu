@@ -167,6 +167,70 @@ __device__ __forceinline__ void epilogue_drain(const GemmArgs& g, const CUtensor
   }
 }
 
+// Drain used by the CTA-pair kernel: the same per-round math, but several 16-column rounds are
+// staged side by side in one 4 KB tile per warp and leave in one TMA store with 128-byte rows
+// (64 bf16 or 32 fp32 columns; 64-byte rows when a second bf16 output shares the tile).  Wide
+// rows matter: the store path costs per row segment, not per byte.
+template <int COLS>
+__device__ __forceinline__ void epilogue_drain_wide(const GemmArgs& g, const CUtensorMap& tmOut,
+                                                    const CUtensorMap& tmAux, uint32_t taddr, int m,
+                                                    int m0w, int nbase, bool row_ok, uint8_t* stg,
+                                                    int lane) {
+  const bool two = g.ep.act == 1, f32 = g.ep.out_fp32 != 0;
+  const int gcols = (f32 || two) ? 32 : 64;             // columns per TMA store (warp-uniform)
+#pragma unroll 1
+  for (int g0 = 0; g0 < COLS; g0 += gcols) {
+    const int gn0 = nbase + g0;
+    if (gn0 >= g.N) break;                              // warp-uniform
+    if (lane == 0) tma_store_wait_read<0>();            // staging tile free again
+    __syncwarp();
+#pragma unroll 1
+    for (int rd = 0; rd < gcols / 16; ++rd) {
+      const int n0 = gn0 + rd * 16;
+      if (n0 >= g.N) break;
+      uint32_t r[16];
+      tmem_ld16(taddr + g0 + rd * 16, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int grp = 0; grp < 2; ++grp) {
+        const int n = n0 + grp * 8;
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[grp * 8 + j]);
+        uint4 pre = make_uint4(0, 0, 0, 0);
+        epilogue_math8(g, v, pre, m, n, row_ok && n < g.N);
+        if (f32) {
+          // 32 fp32 columns = 128-byte rows, 128B swizzle: 16-byte chunk index ^= row & 7
+          uint8_t* rowp = stg + lane * 128;
+          const int c = rd * 4 + grp * 2, sw = lane & 7;
+          *reinterpret_cast<float4*>(rowp + ((c ^ sw) << 4)) = make_float4(v[0], v[1], v[2], v[3]);
+          *reinterpret_cast<float4*>(rowp + (((c + 1) ^ sw) << 4)) = make_float4(v[4], v[5], v[6], v[7]);
+        } else {
+          uint4 o;
+          o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
+          o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
+          const int c = rd * 2 + grp;
+          if (two) {   // 32 bf16 columns = 64-byte rows, 64B swizzle; pre-activation tile 2 KB further
+            const uint32_t off = lane * 64 + ((c ^ ((lane >> 1) & 3)) << 4);
+            *reinterpret_cast<uint4*>(stg + off) = o;
+            *reinterpret_cast<uint4*>(stg + 2048 + off) = pre;
+          } else {     // 64 bf16 columns = 128-byte rows, 128B swizzle
+            *reinterpret_cast<uint4*>(stg + lane * 128 + ((c ^ (lane & 7)) << 4)) = o;
+          }
+        }
+      }
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      if (g.ep.accumulate) tma_reduce_add_2d(&tmOut, stg, gn0, m0w);
+      else                 tma_store_2d(&tmOut, stg, gn0, m0w);
+      if (two) tma_store_2d(&tmAux, stg + 2048, gn0, m0w);
+      tma_store_commit();
+    }
+  }
+}
+
 template <int BN, int STAGES, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
@@ -373,7 +437,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
 // CTA-pair variant: a cluster of two CTAs computes a 256 x 256 output tile with
 // tcgen05.mma.cta_group::2 (instruction shape 256 x 256 x 16).  CTA r of the pair stages rows
 // [r*128, r*128+128) of the A tile and columns [r*128, r*128+128) of the B tile in its own shared
-// memory (32 KB per stage instead of 48 KB, so the ring is PAIR_STAGES deep and each B byte is
+// memory (32 KB per stage instead of 48 KB, so the ring is five stages deep and each B byte is
 // fetched by one SM instead of two) and owns accumulator rows [r*128, r*128+128) in its own TMEM.
 // Only the leader (rank 0) issues MMAs.  Barrier protocol:
 //   full[s]    leader only, 1 arrival (leader producer's expect_tx) + the bytes of both CTAs' loads
@@ -381,7 +445,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
 //   tfull[b]   one per CTA, 1 arrival: committed by the leader to both
 //   tempty[b]  leader only, 2 x NUM_EPI_WARPS arrivals: the epilogue warps of both CTAs
 // Loads are plain unicast TMA loads whose completion is counted on the leader's barrier.
-constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_STAGES = 5;
+constexpr int PAIR_WARP_STAGING = 4096;   // one wide staging tile per epilogue warp
 constexpr int PAIR_BN = 256;      // instruction N; each CTA stages PAIR_BN / 2 columns of B
 
 template <bool A_MN, bool B_MN>
@@ -402,7 +467,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA,
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* stage_out = smem + STAGES * STAGE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(stage_out + NUM_EPI_WARPS * 2048);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(stage_out + NUM_EPI_WARPS * PAIR_WARP_STAGING);
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + STAGES;
   uint64_t* tfull_bar = bars + 2 * STAGES;
@@ -553,7 +618,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA,
     const int quad = warp & 3;
     const int part = e >> 2;
     constexpr int COLS_PER_WARP = BN / 4;
-    uint8_t* my_stage = stage_out + e * 2048;
+    uint8_t* my_stage = stage_out + e * PAIR_WARP_STAGING;
     uint32_t acc_phase[2] = {0, 0};
     int it = 0;
     for (int u = pair_id; u < num_units; u += num_pairs, ++it) {
@@ -578,7 +643,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA,
       // a warp whose 32 rows lie entirely past M has nothing to store (its accumulator rows came
       // from zero-filled loads); it still hands the buffer back
       if (m0w < g.M)
-        epilogue_drain<COLS_PER_WARP>(g, tmOut, tmAux, taddr, m, m0w, nbase, m < g.M, my_stage, lane);
+        epilogue_drain_wide<COLS_PER_WARP>(g, tmOut, tmAux, taddr, m, m0w, nbase, m < g.M, my_stage, lane);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty_bar[ab]), 0));
@@ -609,17 +674,19 @@ static int launch_pair(const void* A, long long lda, const void* B, long long ld
   if (rc) return rc;
   CUtensorMap tmOut, tmAux;
   const AbGemmEpilogue& ep = g.ep;
-  if (ep.out_fp32) rc = make_tmap_2d_sw(&tmOut, ep.out, g.M, g.N, ep.ldo, 32, 16, 4, 64);
-  else             rc = make_tmap_2d_sw(&tmOut, ep.out, g.M, g.N, ep.ldo, 32, 16, 2, 32);
+  // store boxes of 32 rows with 128-byte rows (64-byte rows when two bf16 outputs share the tile)
+  if (ep.out_fp32)       rc = make_tmap_2d_sw(&tmOut, ep.out, g.M, g.N, ep.ldo, 32, 32, 4, 128);
+  else if (ep.act == 1)  rc = make_tmap_2d_sw(&tmOut, ep.out, g.M, g.N, ep.ldo, 32, 32, 2, 64);
+  else                   rc = make_tmap_2d_sw(&tmOut, ep.out, g.M, g.N, ep.ldo, 32, 64, 2, 128);
   if (rc) return rc;
   if (ep.act == 1) {
-    rc = make_tmap_2d_sw(&tmAux, ep.aux, g.M, g.N, ep.ldaux, 32, 16, 2, 32);
+    rc = make_tmap_2d_sw(&tmAux, ep.aux, g.M, g.N, ep.ldaux, 32, 32, 2, 64);
     if (rc) return rc;
   } else {
     tmAux = tmOut;
   }
-  constexpr int SMEM =
-      1024 + PAIR_STAGES * (BM * BK * 2 + HALF_N * BK * 2) + NUM_EPI_WARPS * 2048 + 256;
+  constexpr int SMEM = 1024 + PAIR_STAGES * (BM * BK * 2 + HALF_N * BK * 2) +
+                       NUM_EPI_WARPS * PAIR_WARP_STAGING + 256;
   auto kern = gemm_bf16_tcgen05_pair_kernel<A_MN, B_MN>;
   static bool attr_set = false;
   if (!attr_set) {

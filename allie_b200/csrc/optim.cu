@@ -139,36 +139,57 @@ int ab_cast_bf16(const float* src, void* dst, long long n, cudaStream_t stream) 
 
 // ---------------------------------------------------------------------------------------------
 // colsum: out[n] += sum_m x[m][n] for a bf16 matrix (bias gradients).  A block covers
-// ROWS rows and 2048 columns; each thread owns 8 adjacent columns.
+// 128 rows and 1024 columns: 128 column threads (8 adjacent columns each) times two row
+// phases, eight independent 16-byte loads in flight per thread.
 namespace ab {
+constexpr int CS_ROWS = 128;
 __global__ void __launch_bounds__(256)
 colsum_bf16_kernel(const __nv_bfloat16* __restrict__ x, long long ld, int M, int N,
-                   float* __restrict__ out, int rows_per_blk, const int* __restrict__ m_limit) {
-  const int c = (blockIdx.x * 256 + threadIdx.x) * 8;
-  if (c >= N) return;
+                   float* __restrict__ out, const int* __restrict__ m_limit) {
+  __shared__ float part[128][9];
+  const int tx = threadIdx.x & 127, ty = threadIdx.x >> 7;
+  const int c = (blockIdx.x * 128 + tx) * 8;
   if (m_limit) M = min(M, __ldg(m_limit));
-  const int r0 = blockIdx.y * rows_per_blk;
-  const int r1 = min(M, r0 + rows_per_blk);
-  if (r0 >= r1) return;
+  const int r0 = blockIdx.y * CS_ROWS;
+  const int r1 = min(M, r0 + CS_ROWS);
   float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-  for (int r = r0; r < r1; ++r) {
-    const uint4 v = *reinterpret_cast<const uint4*>(x + (long long)r * ld + c);
-    s[0] += bf16_lo(v.x); s[1] += bf16_hi(v.x); s[2] += bf16_lo(v.y); s[3] += bf16_hi(v.y);
-    s[4] += bf16_lo(v.z); s[5] += bf16_hi(v.z); s[6] += bf16_lo(v.w); s[7] += bf16_hi(v.w);
+  if (c < N) {
+    const __nv_bfloat16* base = x + c;
+    for (int r = r0 + ty; r < r1; r += 16) {
+      uint4 v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int rr = r + 2 * j;
+        v[j] = rr < r1 ? __ldcs(reinterpret_cast<const uint4*>(base + (long long)rr * ld))
+                       : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        s[0] += bf16_lo(v[j].x); s[1] += bf16_hi(v[j].x); s[2] += bf16_lo(v[j].y); s[3] += bf16_hi(v[j].y);
+        s[4] += bf16_lo(v[j].z); s[5] += bf16_hi(v[j].z); s[6] += bf16_lo(v[j].w); s[7] += bf16_hi(v[j].w);
+      }
+    }
   }
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(out + c), "f"(s[0]),
-               "f"(s[1]), "f"(s[2]), "f"(s[3]) : "memory");
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(out + c + 4), "f"(s[4]),
-               "f"(s[5]), "f"(s[6]), "f"(s[7]) : "memory");
+  if (ty == 1) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) part[tx][j] = s[j];
+  }
+  __syncthreads();
+  if (ty == 0 && c < N && r0 < r1) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s[j] += part[tx][j];
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(out + c), "f"(s[0]),
+                 "f"(s[1]), "f"(s[2]), "f"(s[3]) : "memory");
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(out + c + 4), "f"(s[4]),
+                 "f"(s[5]), "f"(s[6]), "f"(s[7]) : "memory");
+  }
 }
 }  // namespace ab
 
 extern "C" int ab_colsum_bf16(const void* x, long long ld, int M, int N, float* out,
                               const int* m_limit, cudaStream_t stream) {
   if ((N & 7) || (ld & 7)) return -1;
-  const int rows_per_blk = 128;
-  dim3 grid((N / 8 + 255) / 256, (M + rows_per_blk - 1) / rows_per_blk);
-  ab::colsum_bf16_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, ld, M, N, out,
-                                                   rows_per_blk, m_limit);
+  dim3 grid((N / 8 + 127) / 128, (M + ab::CS_ROWS - 1) / ab::CS_ROWS);
+  ab::colsum_bf16_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, ld, M, N, out, m_limit);
   return (int)cudaGetLastError();
 }

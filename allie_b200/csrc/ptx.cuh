@@ -75,15 +75,38 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint64_t* bar, uint32_t parity
       : "memory");
   return ok;
 }
+// Same test, but the thread may stay suspended for up to `hint_ns` nanoseconds waiting for the
+// phase to complete before the instruction returns (it wakes as soon as the phase completes), so a
+// polling loop around it issues far fewer instructions.
+__device__ __forceinline__ uint32_t mbar_try_wait_suspend(uint64_t* bar, uint32_t parity,
+                                                          uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred P;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok;
+}
+#ifndef AB_MBAR_SUSPEND_NS
+#define AB_MBAR_SUSPEND_NS 2000u
+#endif
 // Bounded wait.  Returns false when the budget ran out (or another thread of
-// the CTA has already raised `*abort_flag`).
+// the CTA has already raised `*abort_flag`).  `sleep_ns` > 0 puts the thread to sleep between
+// polls: for waits with slack (an epilogue waiting for the next accumulator, a producer waiting
+// for a free stage) this keeps the polling warps out of the issue slots and the power budget.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
-                                          volatile int* abort_flag) {
+                                          volatile int* abort_flag, uint32_t sleep_ns = 0) {
   if (mbar_try_wait(bar, parity)) return true;
   long long t0 = clock64();
   uint32_t spins = 0;
-  while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 0x3ff) == 0) {
+  while (!mbar_try_wait_suspend(bar, parity, AB_MBAR_SUSPEND_NS)) {
+    if (sleep_ns) __nanosleep(sleep_ns);
+    if ((++spins & 0x3f) == 0) {
       if (*abort_flag) return false;
       if (clock64() - t0 > AB_SPIN_CYCLES) return false;
     }

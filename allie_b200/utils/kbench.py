@@ -1,7 +1,7 @@
 """Kernel micro-benchmarks: one kernel, one shape, CUDA-event timing after warm-up, achieved
 TFLOP/s or GB/s against the measured peaks of the machine (``MEASURED_PEAKS.json`` when present).
 
-    python -m allie_b200.utils.kbench gemm --m 32768 --n 4096 --k 1024 [--epilogue gelu|resid|none] [--wgrad]
+    python -m allie_b200.utils.kbench gemm --m 32768 --n 4096 --k 1024 [--epilogue bias|gelu|dgelu|resid|none] [--wgrad]
     python -m allie_b200.utils.kbench attn --batch 64 --seq 512 --heads 16 --hd 64 [--dropout 0.1] [--bwd]
     python -m allie_b200.utils.kbench layernorm --rows 32768 --d 1024 [--bwd]
     python -m allie_b200.utils.kbench adamw --n 300000000
@@ -47,7 +47,7 @@ def main(argv=None) -> dict:
     ap.add_argument("kernel", choices=["gemm", "attn", "layernorm", "adamw"])
     ap.add_argument("--m", type=int, default=32768); ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=1024)
-    ap.add_argument("--epilogue", default="none", choices=["none", "bias", "gelu", "resid"])
+    ap.add_argument("--epilogue", default="none", choices=["none", "bias", "gelu", "dgelu", "resid"])
     ap.add_argument("--wgrad", action="store_true")
     ap.add_argument("--batch", type=int, default=64); ap.add_argument("--seq", type=int, default=512)
     ap.add_argument("--heads", type=int, default=16); ap.add_argument("--hd", type=int, default=64)
@@ -72,6 +72,9 @@ def main(argv=None) -> dict:
             elif a.epilogue == "gelu":
                 o = torch.empty(M, N, device=dev, dtype=torch.bfloat16); pre = torch.empty_like(o)
                 fn = lambda: gemm(x, w, b_mn=True, bias=bias, act=1, aux=pre, out=o)
+            elif a.epilogue == "dgelu":   # dgrad through GELU: out = (x @ w) * gelu'(saved pre-activation)
+                o = torch.empty(M, N, device=dev, dtype=torch.bfloat16); pre = torch.randn(M, N, device=dev).bfloat16()
+                fn = lambda: gemm(x, w, b_mn=True, act=2, aux=pre, out=o)
             else:
                 o = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
                 fn = lambda: gemm(x, w, b_mn=True, bias=bias if a.epilogue == "bias" else None, out=o)
