@@ -1,5 +1,6 @@
 """Decode strategies on the CPU oracle model with a tiny random network."""
 import math
+import zlib
 
 import pytest
 import torch
@@ -49,7 +50,7 @@ class FakeRunner(ModelRunner):
         self.calls += len(games)
         logits, vals, times = [], [], []
         for g in games:
-            gen = torch.Generator().manual_seed(hash(" ".join(g.moves)) % (2 ** 31))
+            gen = torch.Generator().manual_seed(zlib.crc32(" ".join(g.moves).encode()))
             logits.append(torch.randn(self.vocab, generator=gen))
             vals.append(torch.tanh(torch.randn((), generator=gen)))
             times.append(torch.randn((), generator=gen) * 0.3)
