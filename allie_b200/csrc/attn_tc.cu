@@ -167,6 +167,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnArgs a) {
     const float dscale = dropout_scale(a.thr16);
     const uint64_t row_elem0 = (static_cast<uint64_t>(b * a.H + h) * a.T + q_idx) * a.T + hf * 64;
     bool ok = true;
+    // Dropout keep bits of this thread's 64 keys of one key tile (two words of 32).  They do not
+    // depend on the scores, so the generator runs for tile j + 1 while the tensor core computes
+    // P V of tile j (the math warps would only be waiting then); the words are also what the
+    // backward pass reads back, so it never re-runs the generator.
+    uint32_t keep_w0 = 0xffffffffu, keep_w1 = 0xffffffffu;
+    auto make_keep = [&](int j) {
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const uint64_t e0 = row_elem0 + static_cast<uint64_t>(j) * AT_BN + c * 32;
+        uint32_t word = 0;
+#pragma unroll
+        for (int g = 0; g < 4; ++g)
+          word |= dropout_keep8(a.seed, a.stream_id, (e0 >> 3) + g, a.thr16) << (8 * g);
+        if (c == 0) keep_w0 = word; else keep_w1 = word;
+        if (a.drop_mask && q_idx < a.T) a.drop_mask[e0 >> 5] = word;
+      }
+    };
+    if (a.thr16 && nkv > 0) make_keep(0);
     for (int j = 0; j < nkv && ok; ++j) {
       if (!mbar_wait(s_full, j & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
@@ -209,18 +227,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnArgs a) {
           rs += p[i];
         }
         if (a.thr16) {
-          uint32_t word = 0;
+          const uint32_t word = c ? keep_w1 : keep_w0;
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            const uint64_t e0 = row_elem0 + j * AT_BN + c * 32 + g * 8;
-            const uint32_t keep = dropout_keep8(a.seed, a.stream_id, e0 >> 3, a.thr16);
-            word |= keep << (8 * g);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) p[g * 8 + i] = ((keep >> i) & 1u) ? p[g * 8 + i] * dscale : 0.f;
-          }
-          // keep bits of these 32 keys, for the backward pass (so it never re-runs the generator)
-          if (a.drop_mask && q_idx < a.T)
-            a.drop_mask[(row_elem0 + j * AT_BN + c * 32) >> 5] = word;
+          for (int i = 0; i < 32; ++i) p[i] = ((word >> i) & 1u) ? p[i] * dscale : 0.f;
         }
         uint8_t* panel = sP + hf * 16384;
 #pragma unroll
@@ -238,6 +247,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnArgs a) {
       if (lane == 0) { mbar_arrive(s_empty); mbar_arrive(p_full); }   // S reusable, P ready
       l_part = l_part * alpha + rs;
       m_run = m_new;
+      if (a.thr16 && j + 1 < nkv) make_keep(j + 1);
       // fold in this tile's PV (this thread's HD/2 output columns)
       if (!mbar_wait(pv_full, j & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();

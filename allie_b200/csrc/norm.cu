@@ -97,11 +97,26 @@ __device__ __forceinline__ float4 ln_dy_eff(const LnBwdArgs& a, uint2 p, bool ha
 
 // Row kernel: every global load of a row (x, dy, incoming residual gradient) is issued up front,
 // so a row costs one memory round trip; dy stays packed in registers and gamma*dy is recomputed.
-template <int NV_MAX>
+//
+// PARAMS: the warp also accumulates dgamma / dbeta of its rows in a private shared-memory row
+// (2 x d floats per warp, plain read-add-write, no atomics); the block folds its eight rows and
+// issues one vector atomic per four columns at the end.  This saves the second pass over x and dy
+// that a separate column kernel needs.
+template <int NV_MAX, bool PARAMS>
 __global__ void __launch_bounds__(LN_WARPS * 32, NV_MAX <= 8 ? 2 : 1)
 ln_bwd_kernel(const LnBwdArgs a) {
+  extern __shared__ __align__(16) float ln_acc[];     // [LN_WARPS][2][d] when PARAMS
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int d = a.d, nv = d >> 7;
+  float4* acc_g = reinterpret_cast<float4*>(ln_acc + (warp * 2 + 0) * d);
+  float4* acc_b = reinterpret_cast<float4*>(ln_acc + (warp * 2 + 1) * d);
+  if (PARAMS) {
+    for (int c4 = lane; c4 < (d >> 2); c4 += 32) {
+      acc_g[c4] = make_float4(0.f, 0.f, 0.f, 0.f);
+      acc_b[c4] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    __syncwarp();
+  }
   const float dscale = dropout_scale(a.drop_thr16);
   const bool has_dy = a.dy != nullptr, has_r = a.dres_in != nullptr;
   for (int row = blockIdx.x * LN_WARPS + warp; row < a.M; row += gridDim.x * LN_WARPS) {
@@ -148,6 +163,14 @@ ln_bwd_kernel(const LnBwdArgs a) {
         const int c4 = lane + 32 * i;
         const float4 dyv = ln_dy_eff(a, dyp[i], has_dy, c4, sc0, sc1);
         const float4 g = __ldg(reinterpret_cast<const float4*>(a.gamma) + c4);
+        if (PARAMS) {
+          float4 t = acc_g[c4];
+          t.x += dyv.x * xh[i].x; t.y += dyv.y * xh[i].y; t.z += dyv.z * xh[i].z; t.w += dyv.w * xh[i].w;
+          acc_g[c4] = t;
+          float4 u = acc_b[c4];
+          u.x += dyv.x; u.y += dyv.y; u.z += dyv.z; u.w += dyv.w;
+          acc_b[c4] = u;
+        }
         float4 o;
         o.x = (dyv.x * g.x - m1 - xh[i].x * m2) * rstd + rv[i].x;
         o.y = (dyv.y * g.y - m1 - xh[i].y * m2) * rstd + rv[i].y;
@@ -172,43 +195,24 @@ ln_bwd_kernel(const LnBwdArgs a) {
         }
       }
   }
-}
-
-// dgamma[c] += sum_m dy[m,c] * xhat[m,c], dbeta[c] += sum_m dy[m,c].  Column-parallel: a block
-// covers 1024 columns (warp w -> columns 128w.., lane -> one float4) and a chunk of rows, so every
-// row read is one contiguous 4 KB segment; partial sums stay in registers and finish with one
-// vector atomic per thread.
-__global__ void __launch_bounds__(256)
-ln_bwd_params_kernel(const LnBwdArgs a, int rows_per_blk) {
-  const int c = (blockIdx.y * 256 + threadIdx.x) * 4;
-  if (c >= a.d) return;
-  const int r0 = blockIdx.x * rows_per_blk;
-  const int r1 = min(a.M, r0 + rows_per_blk);
-  float4 dg = make_float4(0.f, 0.f, 0.f, 0.f), db = dg;
-  float4 w0 = dg, w1 = dg;
-  if (a.s0) w0 = __ldg(reinterpret_cast<const float4*>(a.w0 + c));
-  if (a.s1) w1 = __ldg(reinterpret_cast<const float4*>(a.w1 + c));
-#pragma unroll 4
-  for (int r = r0; r < r1; ++r) {
-    const float4 xv = *reinterpret_cast<const float4*>(a.x + (long long)r * a.d + c);
-    float4 dyv = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (a.dy) {
-      const uint2 p = *reinterpret_cast<const uint2*>(a.dy + (long long)r * a.d + c);
-      dyv = make_float4(bf16_lo(p.x), bf16_hi(p.x), bf16_lo(p.y), bf16_hi(p.y));
+  if (PARAMS) {
+    __syncthreads();
+    for (int c4 = threadIdx.x; c4 < (d >> 2); c4 += LN_WARPS * 32) {
+      float4 sg = make_float4(0.f, 0.f, 0.f, 0.f), sb = sg;
+#pragma unroll
+      for (int w = 0; w < LN_WARPS; ++w) {
+        const float4 tg = reinterpret_cast<const float4*>(ln_acc + (w * 2 + 0) * d)[c4];
+        const float4 tb = reinterpret_cast<const float4*>(ln_acc + (w * 2 + 1) * d)[c4];
+        sg.x += tg.x; sg.y += tg.y; sg.z += tg.z; sg.w += tg.w;
+        sb.x += tb.x; sb.y += tb.y; sb.z += tb.z; sb.w += tb.w;
+      }
+      asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(a.dgamma + c4 * 4),
+                   "f"(sg.x), "f"(sg.y), "f"(sg.z), "f"(sg.w) : "memory");
+      if (a.dbeta)
+        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(a.dbeta + c4 * 4),
+                     "f"(sb.x), "f"(sb.y), "f"(sb.z), "f"(sb.w) : "memory");
     }
-    if (a.s0) { const float s = a.s0[r]; dyv.x += s * w0.x; dyv.y += s * w0.y; dyv.z += s * w0.z; dyv.w += s * w0.w; }
-    if (a.s1) { const float s = a.s1[r]; dyv.x += s * w1.x; dyv.y += s * w1.y; dyv.z += s * w1.z; dyv.w += s * w1.w; }
-    const float mean = a.rms ? 0.f : a.mean[r];
-    const float rstd = a.rstd[r];
-    dg.x += dyv.x * (xv.x - mean) * rstd; dg.y += dyv.y * (xv.y - mean) * rstd;
-    dg.z += dyv.z * (xv.z - mean) * rstd; dg.w += dyv.w * (xv.w - mean) * rstd;
-    db.x += dyv.x; db.y += dyv.y; db.z += dyv.z; db.w += dyv.w;
   }
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(a.dgamma + c), "f"(dg.x),
-               "f"(dg.y), "f"(dg.z), "f"(dg.w) : "memory");
-  if (a.dbeta)
-    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(a.dbeta + c), "f"(db.x),
-                 "f"(db.y), "f"(db.z), "f"(db.w) : "memory");
 }
 
 }  // namespace ab
@@ -245,15 +249,28 @@ int ab_layernorm_bwd(const void* dy, const float* x, const float* mean, const fl
   a.dbeta = dbeta; a.s0 = s0; a.w0 = w0; a.s1 = s1; a.w1 = w1; a.M = M; a.d = d; a.rms = rms;
   a.drop_seed = drop_seed; a.drop_stream = drop_stream; a.drop_thr16 = drop_thr16;
   int grid = (M + LN_WARPS - 1) / LN_WARPS;
-  if (grid > 148 * 16) grid = 148 * 16;
-  if (d <= 1024) ln_bwd_kernel<8><<<grid, LN_WARPS * 32, 0, stream>>>(a);
-  else           ln_bwd_kernel<16><<<grid, LN_WARPS * 32, 0, stream>>>(a);
-  if (dgamma) {
-    int rows_per_blk = (M + 148 * 4 - 1) / (148 * 4);
-    if (rows_per_blk < 8) rows_per_blk = 8;
-    dim3 g2((M + rows_per_blk - 1) / rows_per_blk, (d + 1023) / 1024);
-    ln_bwd_params_kernel<<<g2, 256, 0, stream>>>(a, rows_per_blk);
+  if (!dgamma) {
+    if (grid > 148 * 16) grid = 148 * 16;
+    if (d <= 1024) ln_bwd_kernel<8, false><<<grid, LN_WARPS * 32, 0, stream>>>(a);
+    else           ln_bwd_kernel<16, false><<<grid, LN_WARPS * 32, 0, stream>>>(a);
+    return (int)cudaGetLastError();
   }
+  // with parameter gradients: exactly the resident blocks, each warp keeps its column sums
+  const int smem = LN_WARPS * 2 * d * (int)sizeof(float);
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(ln_bwd_kernel<8, true>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, LN_WARPS * 2 * 1024 * 4);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(ln_bwd_kernel<16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               LN_WARPS * 2 * 2048 * 4);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  const int resident = d <= 1024 ? 148 * 2 : 148;
+  if (grid > resident) grid = resident;
+  if (d <= 1024) ln_bwd_kernel<8, true><<<grid, LN_WARPS * 32, smem, stream>>>(a);
+  else           ln_bwd_kernel<16, true><<<grid, LN_WARPS * 32, smem, stream>>>(a);
   return (int)cudaGetLastError();
 }
 }

@@ -183,6 +183,13 @@ class Trainer:
             self.grad_sync = GradSync(model, self.engine, mode=self.grad_sync_mode)
         self.load_ckpt("last")
 
+    @property
+    def expert_parallel(self) -> bool:
+        """True when this rank holds only its slice of the expert banks: a forward pass is then a
+        collective, so evaluation and checkpointing run on every rank (rank 0 logs and writes)."""
+        e = self.engine
+        return bool(self.ddp and self.ddp_world_size > 1 and e is not None and e.arena.total > e.arena.sync_end)
+
     # --------------------------------------------------------------- training
     def get_lr(self) -> float:
         it = self.iter_num
@@ -250,14 +257,15 @@ class Trainer:
                            self.gradient_accumulation_steps * self.ddp_world_size)
         while True:
             lr = self.get_lr()
-            if self.eval_interval > 0 and self.iter_num % self.eval_interval == 0 and self.master_process:
+            if self.eval_interval > 0 and self.iter_num % self.eval_interval == 0 and (
+                    self.master_process or self.expert_parallel):
                 self._drain(pending, losses, all_=True)
                 val_log = self.validate()
                 self.metrics.log({"iter": self.iter_num, "lr": lr,
                                   "train/loss": sum(losses) / len(losses) if losses else None} | val_log)
             if self.save_interval > 0 and self.iter_num % self.save_interval == 0:
                 self._gather_optimizer_state()        # collective when the optimizer is sharded
-                if self.master_process:
+                if self.master_process or self.expert_parallel:
                     self.save_ckpt("last")
             loss = self.train_step()
             if loss.is_cuda:
@@ -293,7 +301,7 @@ class Trainer:
     # ------------------------------------------------------------- evaluation
     @torch.no_grad()
     def evaluate(self, dataset) -> dict[str, float]:
-        assert self.master_process
+        assert self.master_process or self.expert_parallel
         t0 = time.time()
         losses = defaultdict(list)
         keys = ["lm_loss", "value_loss", "time_loss", "loss"]
@@ -326,12 +334,14 @@ class Trainer:
         if out["loss"] < self.best_val_loss:
             logger.info(f"new best val loss {out['loss']:.4f}")
             self.best_val_loss = out["loss"]
+            if self.expert_parallel:
+                self._gather_optimizer_state()
             self.save_ckpt("best")
         return {f"val/{k}": v for k, v in out.items() if k.endswith("loss")}
 
     def test(self) -> None:
         self.load_ckpt("best")
-        if self.master_process:
+        if self.master_process or self.expert_parallel:
             out = self.evaluate(self.test_dataset)
             if "loss" in out:
                 logger.info(f"test: loss {out['loss']:.4f}, time {out['time']:.2f}s")
@@ -349,7 +359,10 @@ class Trainer:
         the replicated flat layout the checkpoint writer reads.  Every rank must call this."""
         if self.grad_sync is not None and self.grad_sync.fused and self.grad_sync.nvl.epoch > 0:
             a = self.engine.arena
-            a.exp_avg, a.exp_avg_sq = self.grad_sync.nvl.gather_state()
+            a.ensure_state()          # rank-local (expert) moments already live behind sync_end
+            m, v = self.grad_sync.nvl.gather_state()
+            a.exp_avg[:a.sync_end].copy_(m[:a.sync_end])
+            a.exp_avg_sq[:a.sync_end].copy_(v[:a.sync_end])
 
     def load_ckpt(self, ckpt_type: str) -> None:
         from .checkpoint import load_checkpoint
@@ -371,4 +384,5 @@ class Trainer:
         path = join(self.output_dir, f"{ckpt_type}.pt")
         save_checkpoint(path, self.model, self.engine, self.optimizer, self.iter_num, self.best_val_loss,
                         lr=self.lr, betas=self.betas, weight_decay=self.weight_decay)
-        logger.info(f"saved checkpoint to {path}")
+        if self.master_process:
+            logger.info(f"saved checkpoint to {path}")

@@ -108,7 +108,7 @@ def main(argv=None) -> dict:
             dy = torch.randn(M, d, device=dev).bfloat16(); dx = torch.randn(M, d, device=dev); dyb = torch.empty_like(dy)
             dg = torch.zeros(d, device=dev); db = torch.zeros(d, device=dev)
             fn = lambda: K.layernorm_bwd(dy, x, mean, rstd, g, dx, dx, dyb, dg, db, drop_p=0.1, drop_seed=1, drop_stream=1)
-            nbytes = M * d * (2 + 4 + 4 + 4 + 2) + M * d * (2 + 4)      # row kernel + parameter kernel
+            nbytes = M * d * (2 + 4 + 4 + 4 + 2)      # dy, x, residual gradient in; dx, masked bf16 copy out
         else:
             fn = lambda: K.layernorm_fwd(x, g, b, y, mean, rstd, 1e-5)
             nbytes = M * d * 6

@@ -57,11 +57,30 @@ def main():
             wins.append(torch.from_numpy(w))
         losses.append(float(tr.train_step(wins)))
         tr.iter_num += 1
+    reload_ok = None
+    if moe and device.startswith("cuda"):
+        # checkpoint round trip: the file holds whole expert banks whatever the rank count, and
+        # loading it gives every rank back exactly its own slice of weights and Adam moments
+        import torch.distributed as dist
+
+        tr._gather_optimizer_state()
+        tr.save_ckpt("last")
+        if dist.is_initialized():
+            dist.barrier()
+        arena = tr.engine.arena
+        before = {n: p.detach().clone() for n, p in model.named_parameters()}
+        m_before, v_before = arena.exp_avg.clone(), arena.exp_avg_sq.clone()
+        arena.master.zero_(); arena.exp_avg.zero_(); arena.exp_avg_sq.zero_()
+        tr.load_ckpt("last")
+        reload_ok = (all(torch.equal(before[n], p.detach()) for n, p in model.named_parameters())
+                     and torch.equal(m_before[arena.sync_end:], arena.exp_avg[arena.sync_end:])
+                     and torch.equal(v_before[arena.sync_end:], arena.exp_avg_sq[arena.sync_end:])
+                     and torch.equal(m_before[:arena.sync_end], arena.exp_avg[:arena.sync_end]))
     flat = torch.cat([p.detach().float().reshape(-1).cpu() for _, p in sorted(model.named_parameters())])
     fused = bool(tr.grad_sync is not None and tr.grad_sync.fused)
     named = {n: p.detach().float().cpu() for n, p in model.named_parameters()}
     torch.save({"params": flat, "named": named, "rank": rank, "world": world, "losses": losses, "fused": fused,
-                "multimem": bool(fused and tr.grad_sync.nvl.multimem)},
+                "reload_ok": reload_ok, "multimem": bool(fused and tr.grad_sync.nvl.multimem)},
                os.path.join(out_dir, f"params_{mode}_{rank}.pt"))
     if device.startswith("cuda"):
         from allie_b200.ops import _lib

@@ -77,3 +77,14 @@ def test_expert_parallel_two_ranks_match_single_rank(tmp_path):
                 want = want[r * El:(r + 1) * El]
             d = (p - want).abs()
             assert d.max().item() < 3 * 2e-3 and d.mean().item() < 2e-4, (name, r, d.max().item(), d.mean().item())
+        assert got["reload_ok"] is True
+    # the two-rank checkpoint stores whole expert banks, laid out like the single-rank file
+    ck1 = torch.load(one / "run_collective" / "last.pt", weights_only=False)
+    ck2 = torch.load(two / "run_fused" / "last.pt", weights_only=False)
+    assert ck1["model"].keys() == ck2["model"].keys()
+    for k, v in ck1["model"].items():
+        assert ck2["model"][k].shape == v.shape, k
+        d = (ck2["model"][k].float() - v.float()).abs()
+        assert d.max().item() < 3 * 2e-3, (k, d.max().item())
+    for i, st in ck1["optimizer"]["state"].items():
+        assert ck2["optimizer"]["state"][i]["exp_avg"].shape == st["exp_avg"].shape, i
