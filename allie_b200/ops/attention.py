@@ -40,3 +40,12 @@ def attention_bwd(qkv, out, lse, dout, dqkv, delta, B: int, T: int, H: int, hd: 
     if rc != 0:
         raise RuntimeError(f"ab_attn_bwd failed with code {rc} (B={B} T={T} H={H} hd={hd})")
     _lib.count_launches(3)  # delta + (two backward kernels | fused backward + dQ conversion)
+
+
+def set_backward_schedule(mode: int) -> None:
+    """Schedule of the single-kernel head_dim-64 backward: 0 = chosen from the problem shape
+    (persistent walk when there are at least four (batch, head) slices per SM), 1 = one key tile
+    per CTA, 2 = persistent walk over (batch, head) slices."""
+    rc = _lib.cuda().ab_attn_bwd_schedule(c_int(mode))
+    if rc != 0:
+        raise ValueError(f"bad attention backward schedule {mode}")

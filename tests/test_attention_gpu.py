@@ -22,7 +22,7 @@ def _ref(qkv, B, T, H, hd, mask=None, scale_keep=1.0):
 
 
 @pytest.mark.parametrize("B,T,H,hd", [(2, 128, 2, 64), (2, 512, 3, 64), (1, 200, 2, 64), (2, 256, 2, 128),
-                                      (1, 40, 1, 128)])
+                                      (1, 40, 1, 128), (20, 384, 16, 64)])
 def test_attention_fwd_bwd_no_dropout(B, T, H, hd):
     from allie_b200.ops import _lib
     from allie_b200.ops.attention import attention_bwd, attention_fwd
@@ -44,9 +44,14 @@ def test_attention_fwd_bwd_no_dropout(B, T, H, hd):
     delta = torch.zeros(B, H, T, device=dev)
     o_ref.backward(dout.float())
     g = leaf.grad
-    # two-kernel backward, and for head_dim 64 also the single-kernel one with its fp32 dQ accumulator
-    variants = [None] + ([torch.zeros(B * T, d, device=dev)] if hd == 64 else [])
-    for dq_acc in variants:
+    # two-kernel backward, and for head_dim 64 also the single-kernel one with its fp32 dQ
+    # accumulator under both of its schedules (1 = one key tile per CTA, 2 = persistent walk)
+    from allie_b200.ops.attention import set_backward_schedule
+
+    variants = [(None, 0)] + ([(torch.zeros(B * T, d, device=dev), 1), (torch.zeros(B * T, d, device=dev), 2)]
+                              if hd == 64 else [])
+    for dq_acc, schedule in variants:
+        set_backward_schedule(schedule)
         dqkv = torch.zeros(B * T, 3 * d, device=dev, dtype=torch.bfloat16)
         attention_bwd(qkv, out, lse, dout, dqkv, delta, B, T, H, hd, 0.0, 0, 0, None, dq_acc)
         torch.cuda.synchronize()
@@ -59,6 +64,7 @@ def test_attention_fwd_bwd_no_dropout(B, T, H, hd):
             assert rel < 2e-2, (name, rel.item(), dq_acc is not None)
         if dq_acc is not None:
             assert float(dq_acc.abs().max()) == 0.0     # handed back cleared
+    set_backward_schedule(0)
 
 
 def test_attention_dropout_mask_consistency():
@@ -106,7 +112,10 @@ def test_attention_dropout_mask_consistency():
     delta = torch.zeros(B, H, T, device=dev)
     o_ref.backward(dout.float())
     # regenerate the mask / read the stored bits; two-kernel / single-kernel backward
-    for use_bits, fused in ((False, False), (True, False), (False, True), (True, True)):
+    from allie_b200.ops.attention import set_backward_schedule
+
+    for use_bits, fused in ((False, 0), (True, 0), (False, 1), (True, 1), (False, 2), (True, 2)):
+        set_backward_schedule(fused)           # 0: two-kernel backward; 1, 2: the fused kernel's schedules
         dqkv = torch.zeros(B * T, 3 * d, device=dev, dtype=torch.bfloat16)
         dq_acc = torch.zeros(B * T, d, device=dev) if fused else None
         attention_bwd(qkv, out, lse, dout, dqkv, delta, B, T, H, hd, p, seed, stream,
@@ -115,3 +124,4 @@ def test_attention_dropout_mask_consistency():
         _lib.check_status()
         rel = (dqkv.float() - leaf.grad).norm() / leaf.grad.norm()
         assert rel < 3e-2, (rel.item(), use_bits, fused)
+    set_backward_schedule(0)
