@@ -343,6 +343,15 @@ attn_bwd_fused64_kernel(const __grid_constant__ CUtensorMap tmQKV,
 // P/dS math of the first pair of key tile w + 1, while the tensor core already works on that pair.
 // So the per-key-tile prologue (TMEM allocation, barrier set-up, first loads) and tail, which cost
 // as much as two pairs in the one-tile-per-CTA kernel, are paid once per CTA.
+#ifdef AB_ATTN_PROFILE
+// development aid: CTA 0 stamps the clock at five points of its first 64 pairs (math warp 0) and at
+// the two issue points of the MMA thread
+#define AB_PSTAMP(base, g, k) do { if (g_attn_dbg && blockIdx.x == 0 && (g) < 64) \
+    g_attn_dbg[(base) + (g) * 8 + (k)] = clock64(); } while (0)
+#else
+#define AB_PSTAMP(base, g, k) do { } while (0)
+#endif
+
 struct FbWalk {
   int bh, own, it, nt, bh_end, step;
   int w, g;      // key tiles and pairs done so far by this CTA
@@ -361,7 +370,8 @@ struct FbWalk {
 __global__ void __launch_bounds__(FB_THREADS, 1)
 attn_bwd_fused64_persistent_kernel(const __grid_constant__ CUtensorMap tmQKV,
                                    const __grid_constant__ CUtensorMap tmDO,
-                                   const __grid_constant__ CUtensorMap tmDQ, const AttnBwdArgs a) {
+                                   const __grid_constant__ CUtensorMap tmDQ,
+                                   const __grid_constant__ CUtensorMap tmDKV, const AttnBwdArgs a) {
   constexpr int HD = 64;
   constexpr uint32_t IDESC_S = make_idesc_bf16(128, 128, 0, 0);
   constexpr uint32_t IDESC_T = make_idesc_bf16(128, HD, 1, 1);
@@ -414,6 +424,7 @@ attn_bwd_fused64_persistent_kernel(const __grid_constant__ CUtensorMap tmQKV,
     tma_prefetch_desc(&tmQKV);
     tma_prefetch_desc(&tmDO);
     tma_prefetch_desc(&tmDQ);
+    tma_prefetch_desc(&tmDKV);
   }
   if (warp == FB_MMA_WARP) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
   tc_fence_before();
@@ -458,6 +469,7 @@ attn_bwd_fused64_persistent_kernel(const __grid_constant__ CUtensorMap tmQKV,
         if (p.first() && !mbar_wait(&kv_full[p.w & 1], (p.w >> 1) & 1, abort_flag)) return false;
         if (!mbar_wait(&full[st], (p.g >> 1) & 1, abort_flag)) return false;
         if (p.g > 0 && !mbar_wait(sdp_empty, (p.g - 1) & 1, abort_flag)) return false;
+        AB_PSTAMP(512, p.g, 0);
         tc_fence_after();
         const uint32_t k0 = smem_u32(sK + (p.w & 1) * FB_TILE), v0 = smem_u32(sV + (p.w & 1) * FB_TILE);
         const uint32_t q = smem_u32(sQ + st * FB_TILE), dO = smem_u32(sDO + st * FB_TILE);
@@ -478,6 +490,7 @@ attn_bwd_fused64_persistent_kernel(const __grid_constant__ CUtensorMap tmQKV,
         if (p.g >= 2 && !mbar_wait(&dq_empty[p.g & 1], ((p.g - 2) >> 1) & 1, abort_flag)) return false;
         // dV / dK of the previous key tile must have been read out before they are overwritten
         if (p.first() && p.w > 0 && !mbar_wait(acc_empty, (p.w - 1) & 1, abort_flag)) return false;
+        AB_PSTAMP(512, p.g, 1);
         tc_fence_after();
         const uint32_t k0 = smem_u32(sK + (p.w & 1) * FB_TILE);
         const uint32_t q = smem_u32(sQ + st * FB_TILE), dO = smem_u32(sDO + st * FB_TILE);
@@ -562,6 +575,33 @@ attn_bwd_fused64_persistent_kernel(const __grid_constant__ CUtensorMap tmQKV,
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty);
+      if ((a.T & 127) == 0) {
+        // 32 rows x 32 bf16 columns per warp: staged with 64-byte swizzle, one TMA store.  (Plain
+        // stores of 64-byte row pieces 6 KB apart kept the load/store unit busy for thousands of
+        // cycles per key tile and delayed every other warp's shared-memory traffic with them.)
+        if (lane == 0) tma_store_wait_read<0>();
+        __syncwarp();
+        uint8_t* rowp = my_dq + lane * 64;
+        const int sw = (lane >> 1) & 3;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint4 wv;
+          wv.x = pack_bf16x2(__uint_as_float(v[q4 * 8 + 0]), __uint_as_float(v[q4 * 8 + 1]));
+          wv.y = pack_bf16x2(__uint_as_float(v[q4 * 8 + 2]), __uint_as_float(v[q4 * 8 + 3]));
+          wv.z = pack_bf16x2(__uint_as_float(v[q4 * 8 + 4]), __uint_as_float(v[q4 * 8 + 5]));
+          wv.w = pack_bf16x2(__uint_as_float(v[q4 * 8 + 6]), __uint_as_float(v[q4 * 8 + 7]));
+          *reinterpret_cast<uint4*>(rowp + ((q4 ^ sw) << 4)) = wv;
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(&tmDKV, my_dq, (cb < 2 ? 2 * d_model : d_model) + h * HD + (cb & 1) * 32,
+                       b * a.T + own * 128 + quad * 32);
+          tma_store_commit();
+        }
+        return true;
+      }
+      // ragged last tile: rows past T belong to the next sequence, so store row by row
       const int t_idx = own * 128 + r;
       if (t_idx < a.T) {
         __nv_bfloat16* dst = a.dqkv + (static_cast<long long>(b) * a.T + t_idx) * (3 * d_model) + h * HD +
@@ -580,30 +620,58 @@ attn_bwd_fused64_persistent_kernel(const __grid_constant__ CUtensorMap tmQKV,
     };
 
     int prev_row0 = 0, prev_h = 0, prev_b = 0, prev_own = 0;     // pair g - 1 / its key tile
-    FbWalk p = start;
-    for (; p.valid() && ok; p.next()) {
-      const int b = p.bh / a.H, h = p.bh % a.H;
-      const int qi = p.own + p.it;
-      const int q_idx = qi * 128 + r;
+    // per-row inputs of a pair: log-sum-exp, delta and the 32 dropout keep bits of this thread's
+    // columns.  They are fetched one pair ahead so their latency never sits in the pair's chain.
+    // Addresses advance by fixed strides from one query tile to the next, so they are rebuilt from
+    // the indices only at the first pair of a key tile.
+    long long row_off = 0;          // (batch*head) * T + query index of this thread's row
+    long long keep_off = 0;         // word index of its 32 keep bits
+    auto fetch = [&](const FbWalk& w, float& lse_l2, float& dlt, uint32_t& keep32) {
+      const int q_idx = (w.own + w.it) * 128 + r;
       const bool q_ok = q_idx < a.T;
-      const long long bh = p.bh;
-      const float lse_l2 = q_ok ? a.lse[bh * a.T + q_idx] * LOG2E : 0.f;
-      const float dlt = q_ok ? a.delta[bh * a.T + q_idx] : 0.f;
-      const bool diag = p.it == 0;
-      const uint64_t row_elem0 = (static_cast<uint64_t>(bh) * a.T + q_idx) * a.T + p.own * 128 + cb * 32;
-      uint32_t keep32 = 0xffffffffu;
+      if (w.it == 0) {
+        row_off = static_cast<long long>(w.bh) * a.T + q_idx;
+        keep_off = (row_off * a.T + w.own * 128 + cb * 32) >> 5;
+      } else {
+        row_off += 128;
+        keep_off += 4ll * a.T;      // 128 rows of T / 32 words
+      }
+      lse_l2 = q_ok ? a.lse[row_off] * LOG2E : 0.f;
+      dlt = q_ok ? a.delta[row_off] : 0.f;
+      keep32 = 0xffffffffu;
       if (a.thr16) {
         if (a.drop_mask) {
-          keep32 = q_ok ? a.drop_mask[row_elem0 >> 5] : 0u;
+          keep32 = q_ok ? a.drop_mask[keep_off] : 0u;
         } else {
+          const uint64_t row_elem0 = static_cast<uint64_t>(row_off) * a.T + w.own * 128 + cb * 32;
           keep32 = 0;
 #pragma unroll
           for (int g4 = 0; g4 < 4; ++g4)
             keep32 |= dropout_keep8(a.seed, a.stream_id, (row_elem0 >> 3) + g4, a.thr16) << (8 * g4);
         }
       }
+    };
+    FbWalk p = start;
+    int b = 0, h = 0;
+    float lse_l2 = 0.f, dlt = 0.f;
+    uint32_t keep32 = 0xffffffffu;
+    if (p.valid()) fetch(p, lse_l2, dlt, keep32);
+    for (; p.valid() && ok; p.next()) {
+      if (threadIdx.x == 0) AB_PSTAMP(0, p.g, 0);
+      if (p.it == 0 && p.own == 0) { b = p.bh / a.H; h = p.bh - b * a.H; }
+      const int qi = p.own + p.it;
+      const int q_idx = qi * 128 + r;
+      const bool q_ok = q_idx < a.T;
+      const bool diag = p.it == 0;
+      float n_lse = 0.f, n_dlt = 0.f;
+      uint32_t n_keep = 0xffffffffu;
+      {
+        FbWalk q = p;
+        q.next();
+        if (q.valid()) fetch(q, n_lse, n_dlt, n_keep);
+      }
       if (!mbar_wait(sdp_full, p.g & 1, abort_flag)) { ok = false; break; }
-      if (p.g > 0 && !mbar_wait(pds_empty, (p.g - 1) & 1, abort_flag)) { ok = false; break; }
+      if (threadIdx.x == 0) AB_PSTAMP(0, p.g, 1);
       tc_fence_after();
 #pragma unroll
       for (int hf = 0; hf < 2; ++hf) {
@@ -621,6 +689,12 @@ attn_bwd_fused64_persistent_kernel(const __grid_constant__ CUtensorMap tmQKV,
           if (diag) fb_math16<true, false>(sv, dv, pp, ds, r, col0, q_ok, sl2, lse_l2, dlt, a.scale, dscale, k16);
           else      fb_math16<false, false>(sv, dv, pp, ds, r, col0, q_ok, sl2, lse_l2, dlt, a.scale, dscale, k16);
         }
+        if (hf == 0) {
+          // the shared P / dS tiles feed the previous pair's dV / dK / dQ products until
+          // pds_empty completes; the first half of this pair's math has run under them
+          if (p.g > 0 && !mbar_wait(pds_empty, (p.g - 1) & 1, abort_flag)) { ok = false; break; }
+          if (threadIdx.x == 0) AB_PSTAMP(0, p.g, 2);
+        }
         const uint32_t poff = (col0 >> 6) * 16384;
 #pragma unroll
         for (int g2 = 0; g2 < 2; ++g2) {
@@ -634,16 +708,20 @@ attn_bwd_fused64_persistent_kernel(const __grid_constant__ CUtensorMap tmQKV,
           *reinterpret_cast<uint4*>(sDS + off) = wv;
         }
       }
+      if (!ok) break;
       tc_fence_before();
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) { mbar_arrive(sdp_empty); mbar_arrive(pds_full); }
+      if (threadIdx.x == 0) AB_PSTAMP(0, p.g, 3);
       // work left over from the previous pair, done while the tensor core runs this one
       if (p.g > 0) {
         ok = drain_dq(p.g - 1, prev_row0, prev_h);
         if (ok && p.first()) ok = finish_tile(p.w - 1, prev_b, prev_h, prev_own);
       }
+      if (threadIdx.x == 0) AB_PSTAMP(0, p.g, 4);
       prev_row0 = b * a.T + qi * 128; prev_h = h; prev_b = b; prev_own = p.own;
+      lse_l2 = n_lse; dlt = n_dlt; keep32 = n_keep;
     }
     if (ok && p.g > 0) {
       ok = drain_dq(p.g - 1, prev_row0, prev_h);
@@ -723,8 +801,12 @@ int launch_attn_bwd_fused64(const CUtensorMap& tq, const CUtensorMap& td, const 
       if (e != cudaSuccess) return (int)e;
       attr = true;
     }
+    CUtensorMap tdkv;     // the packed dQKV activation, boxes of 32 rows x 32 columns for dK / dV
+    rc = make_tmap_2d_sw(&tdkv, a.dqkv, rows, 3 * d, 3 * d, 32, 32, 2, 64);
+    if (rc) return rc;
     const int bh = a.B * a.H;
-    attn_bwd_fused64_persistent_kernel<<<bh < 148 ? bh : 148, FB_THREADS, SMEM, stream>>>(tq, td, tdq, a);
+    attn_bwd_fused64_persistent_kernel<<<bh < 148 ? bh : 148, FB_THREADS, SMEM, stream>>>(tq, td, tdq,
+                                                                                          tdkv, a);
   }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
