@@ -22,7 +22,8 @@ constexpr int FWD_THREADS = (FWD_MATH_WARPS + 2) * 32;
 
 template <int HD>
 __global__ void __launch_bounds__(FWD_THREADS, HD <= 64 ? 2 : 1)
-attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnArgs a) {
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmO,
+                const AttnArgs a) {
   constexpr int PANELS = HD / 64;               // 64-column panels per Q/K/V tile
   constexpr int TILE_BYTES = 128 * HD * 2;      // one Q / K / V tile
   constexpr int P_BYTES = 128 * 128 * 2;
@@ -278,7 +279,33 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnArgs a) {
       if (ok && hf == 1) l_part = fs[r];
     }
     if (!ok) { *abort_flag = ST_TIMEOUT_TMEM_FULL; atomicCAS(a.status, 0, ST_TIMEOUT_TMEM_FULL); }
-    if (ok && q_idx < a.T) {
+    if (ok && (a.T & 127) == 0) {
+      // Whole tile in range: the warp stages its 32 rows x HD/2 columns in the (now idle) P tile
+      // and stores them with one TMA store.  Direct stores of 64-byte row pieces one row pitch
+      // apart keep the load/store unit busy far longer than the bytes justify.
+      const float inv = 1.f / l_part;
+      constexpr int ROW_BYTES = OC * 2;                 // 64 (64B swizzle) or 128 (128B swizzle)
+      uint8_t* stg = sP + warp * (32 * ROW_BYTES);
+      uint8_t* rowp = stg + lane * ROW_BYTES;
+      const int sw = ROW_BYTES == 64 ? ((lane >> 1) & 3) : (lane & 7);
+#pragma unroll
+      for (int g = 0; g < OC / 8; ++g) {
+        uint4 w;
+        w.x = pack_bf16x2(o[g * 8 + 0] * inv, o[g * 8 + 1] * inv);
+        w.y = pack_bf16x2(o[g * 8 + 2] * inv, o[g * 8 + 3] * inv);
+        w.z = pack_bf16x2(o[g * 8 + 4] * inv, o[g * 8 + 5] * inv);
+        w.w = pack_bf16x2(o[g * 8 + 6] * inv, o[g * 8 + 7] * inv);
+        *reinterpret_cast<uint4*>(rowp + ((g ^ sw) << 4)) = w;
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_2d(&tmO, stg, h * HD + hf * OC, b * a.T + qt * AT_BM + (warp & 3) * 32);
+        tma_store_commit();
+      }
+      if (a.lse && hf == 0) a.lse[(static_cast<long long>(b) * a.H + h) * a.T + q_idx] = m_run * a.scale + logf(l_part);
+      if (lane == 0) tma_store_wait_read<0>();          // the staging tile outlives the read
+    } else if (ok && q_idx < a.T) {
       const float inv = 1.f / l_part;
       __nv_bfloat16* orow = a.out + (static_cast<long long>(b) * a.T + q_idx) * d_model + h * HD + hf * OC;
 #pragma unroll
@@ -313,25 +340,32 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnArgs a) {
 namespace ab {
 
 
+// One thread per 16-byte chunk of O / dO (hd / 8 adjacent lanes share one (row, head)), so a
+// warp reads 512 contiguous bytes of each tensor; the lanes of a (row, head) fold their partial
+// dot products with shuffles.
 __global__ void __launch_bounds__(256)
 attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
                   float* __restrict__ delta, int B, int T, int H, int hd) {
-  const long long idx = blockIdx.x * 256ll + threadIdx.x;   // (row, head)
-  if (idx >= static_cast<long long>(B) * T * H) return;
-  const int hh = static_cast<int>(idx % H);
-  const long long row = idx / H;
-  const uint4* po = reinterpret_cast<const uint4*>(o + (row * H + hh) * hd);
-  const uint4* pd = reinterpret_cast<const uint4*>(dout + (row * H + hh) * hd);
+  const int cpr = hd >> 3;                                    // chunks per (row, head): 8 or 16
+  const long long total = static_cast<long long>(B) * T * H * cpr;
+  const long long gid = blockIdx.x * 256ll + threadIdx.x;
   float s = 0.f;
-  for (int c = 0; c < hd / 8; ++c) {
-    const uint4 x = po[c], y = pd[c];
-    s += bf16_lo(x.x) * bf16_lo(y.x) + bf16_hi(x.x) * bf16_hi(y.x);
+  if (gid < total) {
+    const uint4 x = __ldcs(reinterpret_cast<const uint4*>(o) + gid);
+    const uint4 y = __ldcs(reinterpret_cast<const uint4*>(dout) + gid);
+    s = bf16_lo(x.x) * bf16_lo(y.x) + bf16_hi(x.x) * bf16_hi(y.x);
     s += bf16_lo(x.y) * bf16_lo(y.y) + bf16_hi(x.y) * bf16_hi(y.y);
     s += bf16_lo(x.z) * bf16_lo(y.z) + bf16_hi(x.z) * bf16_hi(y.z);
     s += bf16_lo(x.w) * bf16_lo(y.w) + bf16_hi(x.w) * bf16_hi(y.w);
   }
-  const int bb = static_cast<int>(row / T), t = static_cast<int>(row % T);
-  delta[(static_cast<long long>(bb) * H + hh) * T + t] = s;
+  for (int off = 1; off < cpr; off <<= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+  if (gid < total && (gid & (cpr - 1)) == 0) {
+    const long long rh = gid / cpr;                           // row * H + head
+    const int hh = static_cast<int>(rh % H);
+    const long long row = rh / H;
+    const int bb = static_cast<int>(row / T), t = static_cast<int>(row % T);
+    delta[(static_cast<long long>(bb) * H + hh) * T + t] = s;
+  }
 }
 
 constexpr int BWD_MATH_WARPS = 16;
@@ -630,6 +664,11 @@ int launch_attn_bwd_fused64(const CUtensorMap& tq, const CUtensorMap& td, const 
 
 template <int HD>
 static int launch_attn_fwd(const CUtensorMap& tm, const AttnArgs& a, cudaStream_t stream) {
+  // output map: boxes of 32 rows x HD/2 columns (one math warp's share of a query tile)
+  CUtensorMap tmo;
+  const int rc_o = make_tmap_2d_sw(&tmo, a.out, (uint64_t)a.B * a.T, (uint64_t)a.H * HD, (uint64_t)a.H * HD,
+                                   32, HD / 2, 2, HD);   // HD/2 bf16 columns = HD bytes per row
+  if (rc_o) return rc_o;
   constexpr int SMEM = 5 * 128 * HD * 2 + 128 * 128 * 2 + 1024;
   auto kern = attn_fwd_kernel<HD>;
   static bool attr = false;
@@ -643,7 +682,7 @@ static int launch_attn_fwd(const CUtensorMap& tm, const AttnArgs& a, cudaStream_
     attr = true;
   }
   dim3 grid((a.T + 127) / 128, a.H, a.B);
-  kern<<<grid, FWD_THREADS, SMEM, stream>>>(tm, a);
+  kern<<<grid, FWD_THREADS, SMEM, stream>>>(tm, tmo, a);
   return (int)cudaGetLastError();
 }
 
@@ -701,7 +740,7 @@ int ab_attn_bwd(const void* qkv, const void* out, const float* lse, const void* 
   if (rc) return rc;
   rc = make_tmap_2d(&td, dout, (uint64_t)B * T, (uint64_t)H * hd, (uint64_t)H * hd, 128, 64, 2, true);
   if (rc) return rc;
-  const long long n = (long long)B * T * H;
+  const long long n = (long long)B * T * H * (hd / 8);
   attn_delta_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(
       (const __nv_bfloat16*)out, (const __nv_bfloat16*)dout, delta, B, T, H, hd);
   AttnBwdArgs a;
