@@ -13,7 +13,13 @@
 
 namespace ab {
 
-// grid (n_trees, H), block 128.  Lane owns hd/32 consecutive dims of the head.
+// grid (n_trees, H), block 128.  A key's row for one head is HD/8 chunks of 16 bytes; the block is
+// 128 / (HD/8) key groups times HD/8 chunk lanes, so the lanes of a group read one contiguous row
+// and the groups walk the keys in parallel with every load independent of the others (the kernel
+// is a stream over the tree's K/V rows and has to run at memory speed).  Two passes: scores into
+// shared memory and the block maximum, then probabilities times V.
+constexpr int DEC_MAX_KEYS = 1024;     // prompt slots + ancestor list per tree
+
 template <int HD>
 __global__ void __launch_bounds__(128)
 decode_attn_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ kc,
@@ -21,66 +27,87 @@ decode_attn_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restr
                    const int* __restrict__ slot, const int* __restrict__ prefix_len,
                    const int* __restrict__ anc, int anc_stride, const int* __restrict__ n_anc,
                    __nv_bfloat16* __restrict__ out, int H, int S, float scale) {
-  constexpr int E = HD / 32;             // dims per lane
+  constexpr int CH = HD / 8;             // 16-byte chunks per row = lanes per key group
+  constexpr int KG = 128 / CH;           // key groups per block
   const int t = blockIdx.x, h = blockIdx.y;
   if (!active[t]) return;
+  __shared__ float s_score[DEC_MAX_KEYS];
+  __shared__ float s_red[4];
+  __shared__ float s_acc[KG][HD];
   const int d = H * HD;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int c = tid % CH, kg = tid / CH;
   const __nv_bfloat16* row = qkv + static_cast<long long>(t) * 3 * d;
   const long long cache_base = static_cast<long long>(t) * S * d + h * HD;
   // append this token's key / value (self is the last entry of the ancestor list)
-  if (warp == 0) {
-    const long long dst = cache_base + static_cast<long long>(slot[t]) * d + lane * E;
+  if (tid < CH) {
+    const long long dst = cache_base + static_cast<long long>(slot[t]) * d + tid * 8;
+    *reinterpret_cast<uint4*>(kc + dst) = *reinterpret_cast<const uint4*>(row + d + h * HD + tid * 8);
+    *reinterpret_cast<uint4*>(vc + dst) = *reinterpret_cast<const uint4*>(row + 2 * d + h * HD + tid * 8);
+  }
+  float q[8];
+  {
+    const uint4 qv = *reinterpret_cast<const uint4*>(row + h * HD + c * 8);
+    q[0] = bf16_lo(qv.x) * scale; q[1] = bf16_hi(qv.x) * scale; q[2] = bf16_lo(qv.y) * scale;
+    q[3] = bf16_hi(qv.y) * scale; q[4] = bf16_lo(qv.z) * scale; q[5] = bf16_hi(qv.z) * scale;
+    q[6] = bf16_lo(qv.w) * scale; q[7] = bf16_hi(qv.w) * scale;
+  }
+  __syncthreads();                        // the appended row is visible to the whole block
+  const int P = prefix_len[t];
+  const int n = min(P + n_anc[t], DEC_MAX_KEYS);
+  const int* anc_t = anc + static_cast<long long>(t) * anc_stride;
+  // ---- pass 1: scores
+  float mx = -INFINITY;
+#pragma unroll 4
+  for (int i0 = 0; i0 < n; i0 += KG) {     // uniform trip count: the shuffles below need every lane
+    const int i = i0 + kg;
+    const bool live = i < n;
+    uint4 kv = make_uint4(0, 0, 0, 0);
+    if (live) {
+      const int sl = i < P ? i : anc_t[i - P];
+      kv = *reinterpret_cast<const uint4*>(kc + cache_base + static_cast<long long>(sl) * d + c * 8);
+    }
+    float dot = q[0] * bf16_lo(kv.x) + q[1] * bf16_hi(kv.x) + q[2] * bf16_lo(kv.y) + q[3] * bf16_hi(kv.y) +
+                q[4] * bf16_lo(kv.z) + q[5] * bf16_hi(kv.z) + q[6] * bf16_lo(kv.w) + q[7] * bf16_hi(kv.w);
 #pragma unroll
-    for (int e = 0; e < E; ++e) {
-      kc[dst + e] = row[d + h * HD + lane * E + e];
-      vc[dst + e] = row[2 * d + h * HD + lane * E + e];
+    for (int o = CH / 2; o; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    if (live) {
+      if (c == 0) s_score[i] = dot;
+      mx = fmaxf(mx, dot);
     }
   }
-  float q[E];
 #pragma unroll
-  for (int e = 0; e < E; ++e) q[e] = __bfloat162float(row[h * HD + lane * E + e]) * scale;
+  for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if (lane == 0) s_red[warp] = mx;
   __syncthreads();
-  const int P = prefix_len[t], A = n_anc[t];
-  float m = -INFINITY, l = 0.f, acc[E];
-#pragma unroll
-  for (int e = 0; e < E; ++e) acc[e] = 0.f;
-  for (int i = warp; i < P + A; i += 4) {
-    const int s = i < P ? i : anc[t * anc_stride + (i - P)];
-    const long long off = cache_base + static_cast<long long>(s) * d + lane * E;
-    float kv[E], dot = 0.f;
-#pragma unroll
-    for (int e = 0; e < E; ++e) { kv[e] = __bfloat162float(kc[off + e]); dot += q[e] * kv[e]; }
-#pragma unroll
-    for (int o = 16; o; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-    const float m_new = fmaxf(m, dot);
-    const float a = __expf(m - m_new), p = __expf(dot - m_new);
-    l = l * a + p;
-#pragma unroll
-    for (int e = 0; e < E; ++e) acc[e] = acc[e] * a + p * __bfloat162float(vc[off + e]);
-    m = m_new;
+  const float M = fmaxf(fmaxf(s_red[0], s_red[1]), fmaxf(s_red[2], s_red[3]));
+  // ---- pass 2: probabilities x V (this thread: 8 dims of the keys of its group)
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  float l = 0.f;
+#pragma unroll 4
+  for (int i = kg; i < n; i += KG) {
+    const int sl = i < P ? i : anc_t[i - P];
+    const uint4 vv = *reinterpret_cast<const uint4*>(vc + cache_base + static_cast<long long>(sl) * d + c * 8);
+    const float p = __expf(s_score[i] - M);
+    l += p;
+    acc[0] += p * bf16_lo(vv.x); acc[1] += p * bf16_hi(vv.x); acc[2] += p * bf16_lo(vv.y); acc[3] += p * bf16_hi(vv.y);
+    acc[4] += p * bf16_lo(vv.z); acc[5] += p * bf16_hi(vv.z); acc[6] += p * bf16_lo(vv.w); acc[7] += p * bf16_hi(vv.w);
   }
-  __shared__ float sm[4], sl[4], sacc[4][HD];
-  if (lane == 0) { sm[warp] = m; sl[warp] = l; }
 #pragma unroll
-  for (int e = 0; e < E; ++e) sacc[warp][lane * E + e] = acc[e];
+  for (int e = 0; e < 8; ++e) s_acc[kg][c * 8 + e] = acc[e];
+  // every lane of a key group carries the same l; count each group once
+  if (c != 0) l = 0.f;
+#pragma unroll
+  for (int o = 16; o; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+  __syncthreads();                        // also orders the s_red reads above before the writes below
+  if (lane == 0) s_red[warp] = l;
   __syncthreads();
-  if (warp == 0) {
-    float M = fmaxf(fmaxf(sm[0], sm[1]), fmaxf(sm[2], sm[3]));
-    float L = 0.f, o[E];
+  if (tid < HD) {
+    const float L = s_red[0] + s_red[1] + s_red[2] + s_red[3];
+    float o = 0.f;
 #pragma unroll
-    for (int e = 0; e < E; ++e) o[e] = 0.f;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) {
-      const float f = sm[w] == -INFINITY ? 0.f : __expf(sm[w] - M);
-      L += sl[w] * f;
-#pragma unroll
-      for (int e = 0; e < E; ++e) o[e] += sacc[w][lane * E + e] * f;
-    }
-    const float inv = 1.f / L;
-#pragma unroll
-    for (int e = 0; e < E; ++e)
-      out[static_cast<long long>(t) * d + h * HD + lane * E + e] = __float2bfloat16(o[e] * inv);
+    for (int g = 0; g < KG; ++g) o += s_acc[g][tid];
+    out[static_cast<long long>(t) * d + h * HD + tid] = __float2bfloat16(o / L);
   }
 }
 

@@ -77,12 +77,12 @@ struct GemmArgs {
 // accumulators and leaves as the final values; `pre` receives the bf16 pre-activation when
 // act == 1.  Reads (bias, aux for act == 2, residual) are predicated by the caller's `ok`.
 __device__ __forceinline__ void epilogue_math8(const GemmArgs& g, float* v, uint4& pre, int m, int n,
-                                               bool ok) {
+                                               bool ok, bool add_bias) {
   const AbGemmEpilogue& ep = g.ep;
 #pragma unroll
   for (int j = 0; j < 8; ++j) v[j] *= ep.alpha;
   if (!ok) return;
-  if (ep.bias) {
+  if (ep.bias && add_bias) {      // with split-K only the first split carries the bias
     const float4 b0 = __ldg(reinterpret_cast<const float4*>(ep.bias + n));
     const float4 b1 = __ldg(reinterpret_cast<const float4*>(ep.bias + n + 4));
     v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
@@ -122,7 +122,7 @@ template <int COLS>
 __device__ __forceinline__ void epilogue_drain(const GemmArgs& g, const CUtensorMap& tmOut,
                                                const CUtensorMap& tmAux, uint32_t taddr, int m,
                                                int m0w, int nbase, bool row_ok, uint8_t* my_stage,
-                                               int lane) {
+                                               int lane, bool add_bias) {
 #pragma unroll 1
   for (int rd = 0; rd < COLS / 16; ++rd) {      // rounds of 16 columns
     const int n0 = nbase + rd * 16;
@@ -139,7 +139,7 @@ __device__ __forceinline__ void epilogue_drain(const GemmArgs& g, const CUtensor
 #pragma unroll
       for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[grp * 8 + j]);
       uint4 pre = make_uint4(0, 0, 0, 0);
-      epilogue_math8(g, v, pre, m, n, row_ok && n < g.N);
+      epilogue_math8(g, v, pre, m, n, row_ok && n < g.N, add_bias);
       if (g.ep.out_fp32) {
         // 16 fp32 columns = 64-byte rows, 64B swizzle: 16-byte chunk index ^= (row >> 1) & 3
         uint8_t* rowp = my_stage + lane * 64;
@@ -175,7 +175,7 @@ template <int COLS>
 __device__ __forceinline__ void epilogue_drain_wide(const GemmArgs& g, const CUtensorMap& tmOut,
                                                     const CUtensorMap& tmAux, uint32_t taddr, int m,
                                                     int m0w, int nbase, bool row_ok, uint8_t* stg,
-                                                    int lane) {
+                                                    int lane, bool add_bias) {
   const bool two = g.ep.act == 1, f32 = g.ep.out_fp32 != 0;
   const int gcols = (f32 || two) ? 32 : 64;             // columns per TMA store (warp-uniform)
 #pragma unroll 1
@@ -198,7 +198,7 @@ __device__ __forceinline__ void epilogue_drain_wide(const GemmArgs& g, const CUt
 #pragma unroll
         for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[grp * 8 + j]);
         uint4 pre = make_uint4(0, 0, 0, 0);
-        epilogue_math8(g, v, pre, m, n, row_ok && n < g.N);
+        epilogue_math8(g, v, pre, m, n, row_ok && n < g.N, add_bias);
         if (f32) {
           // 32 fp32 columns = 128-byte rows, 128B swizzle: 16-byte chunk index ^= row & 7
           uint8_t* rowp = stg + lane * 128;
@@ -417,7 +417,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + ab * BN + part * COLS_PER_WARP;
       const int m0w = (tile / n_tiles) * BM + quad * 32;   // first row of this warp's block
       const bool row_ok = m < Meff;
-      epilogue_drain<COLS_PER_WARP>(g, tmOut, tmAux, taddr, m, m0w, nbase, row_ok, my_stage, lane);
+      epilogue_drain<COLS_PER_WARP>(g, tmOut, tmAux, taddr, m, m0w, nbase, row_ok, my_stage, lane, ks == 0);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[ab]);
@@ -643,7 +643,8 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA,
       // a warp whose 32 rows lie entirely past M has nothing to store (its accumulator rows came
       // from zero-filled loads); it still hands the buffer back
       if (m0w < g.M)
-        epilogue_drain_wide<COLS_PER_WARP>(g, tmOut, tmAux, taddr, m, m0w, nbase, m < g.M, my_stage, lane);
+        epilogue_drain_wide<COLS_PER_WARP>(g, tmOut, tmAux, taddr, m, m0w, nbase, m < g.M, my_stage, lane,
+                                           ks == 0);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty_bar[ab]), 0));

@@ -73,6 +73,8 @@ struct LnBwdArgs {
   __nv_bfloat16* dbranch;    // [M,d] out or null: bf16(dropout_mask * dx)
   float* dgamma;             // [d] accumulated
   float* dbeta;              // [d] accumulated or null
+  float* dbias;              // [d] accumulated or null: column sums of the masked copy (the bias
+                             // gradient of the projection whose output that copy is the gradient of)
   // optional rank-2 term: dy_eff[m,c] = dy[m,c] + s0[m]*w0[c] + s1[m]*w1[c]
   const float* s0; const float* w0; const float* s1; const float* w1;
   int M, d, rms;
@@ -99,21 +101,25 @@ __device__ __forceinline__ float4 ln_dy_eff(const LnBwdArgs& a, uint2 p, bool ha
 // so a row costs one memory round trip; dy stays packed in registers and gamma*dy is recomputed.
 //
 // PARAMS: the warp also accumulates dgamma / dbeta of its rows in a private shared-memory row
-// (2 x d floats per warp, plain read-add-write, no atomics); the block folds its eight rows and
+// (3 x d floats per warp: dgamma, dbeta and the column sums of the masked copy; plain
+// read-add-write, no atomics); the block folds its eight rows and
 // issues one vector atomic per four columns at the end.  This saves the second pass over x and dy
 // that a separate column kernel needs.
 template <int NV_MAX, bool PARAMS>
 __global__ void __launch_bounds__(LN_WARPS * 32, NV_MAX <= 8 ? 2 : 1)
 ln_bwd_kernel(const LnBwdArgs a) {
-  extern __shared__ __align__(16) float ln_acc[];     // [LN_WARPS][2][d] when PARAMS
+  extern __shared__ __align__(16) float ln_acc[];     // [LN_WARPS][3][d] when PARAMS
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int d = a.d, nv = d >> 7;
-  float4* acc_g = reinterpret_cast<float4*>(ln_acc + (warp * 2 + 0) * d);
-  float4* acc_b = reinterpret_cast<float4*>(ln_acc + (warp * 2 + 1) * d);
+  float4* acc_g = reinterpret_cast<float4*>(ln_acc + (warp * 3 + 0) * d);
+  float4* acc_b = reinterpret_cast<float4*>(ln_acc + (warp * 3 + 1) * d);
+  float4* acc_c = reinterpret_cast<float4*>(ln_acc + (warp * 3 + 2) * d);
+  const bool want_bias = PARAMS && a.dbias != nullptr && a.dbranch != nullptr;
   if (PARAMS) {
     for (int c4 = lane; c4 < (d >> 2); c4 += 32) {
       acc_g[c4] = make_float4(0.f, 0.f, 0.f, 0.f);
       acc_b[c4] = make_float4(0.f, 0.f, 0.f, 0.f);
+      acc_c[c4] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
     __syncwarp();
   }
@@ -192,20 +198,30 @@ ln_bwd_kernel(const LnBwdArgs a) {
           p.x = pack_bf16x2(m.x, m.y);
           p.y = pack_bf16x2(m.z, m.w);
           dbr[c4] = p;
+          if (want_bias) {
+            float4 t = acc_c[c4];
+            t.x += m.x; t.y += m.y; t.z += m.z; t.w += m.w;
+            acc_c[c4] = t;
+          }
         }
       }
   }
   if (PARAMS) {
     __syncthreads();
     for (int c4 = threadIdx.x; c4 < (d >> 2); c4 += LN_WARPS * 32) {
-      float4 sg = make_float4(0.f, 0.f, 0.f, 0.f), sb = sg;
+      float4 sg = make_float4(0.f, 0.f, 0.f, 0.f), sb = sg, sc = sg;
 #pragma unroll
       for (int w = 0; w < LN_WARPS; ++w) {
-        const float4 tg = reinterpret_cast<const float4*>(ln_acc + (w * 2 + 0) * d)[c4];
-        const float4 tb = reinterpret_cast<const float4*>(ln_acc + (w * 2 + 1) * d)[c4];
+        const float4 tg = reinterpret_cast<const float4*>(ln_acc + (w * 3 + 0) * d)[c4];
+        const float4 tb = reinterpret_cast<const float4*>(ln_acc + (w * 3 + 1) * d)[c4];
+        const float4 tc = reinterpret_cast<const float4*>(ln_acc + (w * 3 + 2) * d)[c4];
         sg.x += tg.x; sg.y += tg.y; sg.z += tg.z; sg.w += tg.w;
         sb.x += tb.x; sb.y += tb.y; sb.z += tb.z; sb.w += tb.w;
+        sc.x += tc.x; sc.y += tc.y; sc.z += tc.z; sc.w += tc.w;
       }
+      if (want_bias)
+        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(a.dbias + c4 * 4),
+                     "f"(sc.x), "f"(sc.y), "f"(sc.z), "f"(sc.w) : "memory");
       asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(a.dgamma + c4 * 4),
                    "f"(sg.x), "f"(sg.y), "f"(sg.z), "f"(sg.w) : "memory");
       if (a.dbeta)
@@ -237,7 +253,7 @@ int ab_layernorm_fwd(const float* x, const float* gamma, const float* beta, void
 
 int ab_layernorm_bwd(const void* dy, const float* x, const float* mean, const float* rstd,
                      const float* gamma, const float* dres_in, float* dx, void* dbranch,
-                     float* dgamma, float* dbeta, const float* s0, const float* w0,
+                     float* dgamma, float* dbeta, float* dbias, const float* s0, const float* w0,
                      const float* s1, const float* w1, int M, int d, int rms,
                      unsigned long long drop_seed, unsigned int drop_stream,
                      unsigned int drop_thr16, cudaStream_t stream) {
@@ -246,7 +262,7 @@ int ab_layernorm_bwd(const void* dy, const float* x, const float* mean, const fl
   LnBwdArgs a;
   a.dy = (const __nv_bfloat16*)dy; a.x = x; a.mean = mean; a.rstd = rstd; a.gamma = gamma;
   a.dres_in = dres_in; a.dx = dx; a.dbranch = (__nv_bfloat16*)dbranch; a.dgamma = dgamma;
-  a.dbeta = dbeta; a.s0 = s0; a.w0 = w0; a.s1 = s1; a.w1 = w1; a.M = M; a.d = d; a.rms = rms;
+  a.dbeta = dbeta; a.dbias = dbias; a.s0 = s0; a.w0 = w0; a.s1 = s1; a.w1 = w1; a.M = M; a.d = d; a.rms = rms;
   a.drop_seed = drop_seed; a.drop_stream = drop_stream; a.drop_thr16 = drop_thr16;
   int grid = (M + LN_WARPS - 1) / LN_WARPS;
   if (!dgamma) {
@@ -256,14 +272,14 @@ int ab_layernorm_bwd(const void* dy, const float* x, const float* mean, const fl
     return (int)cudaGetLastError();
   }
   // with parameter gradients: exactly the resident blocks, each warp keeps its column sums
-  const int smem = LN_WARPS * 2 * d * (int)sizeof(float);
+  const int smem = LN_WARPS * 3 * d * (int)sizeof(float);
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(ln_bwd_kernel<8, true>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, LN_WARPS * 2 * 1024 * 4);
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, LN_WARPS * 3 * 1024 * 4);
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(ln_bwd_kernel<16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               LN_WARPS * 2 * 2048 * 4);
+                               LN_WARPS * 3 * 2048 * 4);
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }

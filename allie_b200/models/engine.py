@@ -373,9 +373,15 @@ class B200Engine:
             K.heads_bwd_w(buf["h"], buf["dv"], buf["dt"], self.wv[2].view(-1), self.bv[2],
                           self.wt[2].view(-1), self.bt[2])
             s0, w0, s1, w1 = buf["dv"], self.wv[0].view(-1), buf["dt"], self.wt[0].view(-1)
+        # every LayerNorm backward also emits the masked bf16 gradient of the branch below it and,
+        # when that branch ends in a dense projection, the column sums that are its bias gradient
+        def proj_bias_grad(layer):
+            return None if layer["moe"] else layer["pr_b"][2]
+
         K.layernorm_bwd(dsmall, buf["x"][nl], buf["meanf"], buf["rstdf"], self.lnf_w[0], None, dx, dyb,
                         self.lnf_w[2], self.lnf_b[2], s0=s0, w0=w0, s1=s1, w1=w1, rms=self.rms,
-                        drop_seed=seed, drop_stream=2 + 3 * (nl - 1), drop_p=p_res)
+                        drop_seed=seed, drop_stream=2 + 3 * (nl - 1), drop_p=p_res,
+                        dbias=proj_bias_grad(self.layers[nl - 1]))
         for l in range(nl - 1, -1, -1):
             L = self.layers[l]
             # ---- MLP
@@ -383,17 +389,15 @@ class B200Engine:
                 self._moe(l, B * T, True).backward(dyb, buf["ln2"][l], dsmall, self._aux_coef())
             else:
                 gemm(buf["act"][l], dyb, a_mn=True, b_mn=True, out=L["pr_w"][2], accumulate=True)
-                K.colsum_bf16(dyb, L["pr_b"][2])
                 gemm(dyb, L["pr_w"][1], b_mn=False, out=dpre, act=2, aux=buf["pre"][l])
                 gemm(buf["ln2"][l], dpre, a_mn=True, b_mn=True, out=L["fc_w"][2], accumulate=True)
                 K.colsum_bf16(dpre, L["fc_b"][2])
                 gemm(dpre, L["fc_w"][1], b_mn=False, out=dsmall)
             K.layernorm_bwd(dsmall, buf["xmid"][l], buf["mean2"][l], buf["rstd2"][l], L["ln2_w"][0], dx, dx,
                             dyb, L["ln2_w"][2], L["ln2_b"][2], rms=self.rms, drop_seed=seed,
-                            drop_stream=1 + 3 * l, drop_p=p_res)
+                            drop_stream=1 + 3 * l, drop_p=p_res, dbias=L["o_b"][2])
             # ---- attention
             gemm(buf["attn"][l], dyb, a_mn=True, b_mn=True, out=L["o_w"][2], accumulate=True)
-            K.colsum_bf16(dyb, L["o_b"][2])
             gemm(dyb, L["o_w"][1], b_mn=False, out=dsmall)
             self._attention_bwd(buf["qkv"][l], buf["attn"][l], buf["lse"][l], dsmall, dqkv, B, T, p_att,
                                 seed, 3 + 3 * l, buf["dmask"][l] if "dmask" in buf else None)
@@ -402,7 +406,8 @@ class B200Engine:
             gemm(dqkv, L["qkv_w"][1], b_mn=False, out=dsmall)
             K.layernorm_bwd(dsmall, buf["x"][l], buf["mean1"][l], buf["rstd1"][l], L["ln1_w"][0], dx, dx,
                             dyb if l > 0 else None, L["ln1_w"][2], L["ln1_b"][2], rms=self.rms,
-                            drop_seed=seed, drop_stream=max(0, 2 + 3 * (l - 1)), drop_p=p_res if l > 0 else 0.0)
+                            drop_seed=seed, drop_stream=max(0, 2 + 3 * (l - 1)), drop_p=p_res if l > 0 else 0.0,
+                            dbias=proj_bias_grad(self.layers[l - 1]) if l > 0 else None)
         K.embed_bwd(buf["ids"], buf["pos"], dx, self.wte[2], self.wpe[2], self.ctrl_w[2], V, seed, 0, p_emb)
 
     # ------------------------------------------------------------- public API

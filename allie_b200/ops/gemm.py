@@ -79,6 +79,15 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     out_fp32 = out.dtype == torch.float32
     if accumulate:
         assert out_fp32
+    if (k_splits is None and resid is not None and resid.data_ptr() == out.data_ptr() and drop_p == 0.0
+            and act == 0 and M <= 512 and m_limit is None and k_limit is None):
+        # Skinny in-place residual update (decode steps): x += a @ b + bias.  A few output tiles
+        # with a long K loop leave most SMs idle, so the contraction is split over more CTAs and
+        # the partial products are reduce-added into x; the first split adds the bias.
+        tiles = -(-M // 128) * -(-N // 128)
+        ks = max(1, min(K // 256, 128 // max(tiles, 1)))
+        if ks > 1:
+            accumulate, resid, k_splits = True, None, ks
     if k_splits is None:
         k_splits = pick_k_splits(M, N, K) if (accumulate and out_fp32) else 1
     ep = _lib.GemmEpilogue()

@@ -29,11 +29,13 @@ def layernorm_fwd(x, gamma, beta, y, mean, rstd, eps: float, rms: bool = False) 
 
 def layernorm_bwd(dy, x, mean, rstd, gamma, dres_in, dx, dbranch, dgamma, dbeta, *, s0=None, w0=None,
                   s1=None, w1=None, rms: bool = False, drop_seed: int = 0, drop_stream: int = 0,
-                  drop_p: float = 0.0) -> None:
+                  drop_p: float = 0.0, dbias=None) -> None:
+    """``dbias`` (optional, fp32 [d], accumulated): column sums of ``dbranch``, i.e. the bias gradient
+    of the projection whose output gradient ``dbranch`` is; needs ``dgamma``."""
     M, d = x.shape
     _ck(_lib.cuda().ab_layernorm_bwd(
         ptr(dy), ptr(x), ptr(mean), ptr(rstd), ptr(gamma), ptr(dres_in), ptr(dx), ptr(dbranch),
-        ptr(dgamma), ptr(dbeta), ptr(s0), ptr(w0), ptr(s1), ptr(w1), c_int(M), c_int(d),
+        ptr(dgamma), ptr(dbeta), ptr(dbias), ptr(s0), ptr(w0), ptr(s1), ptr(w1), c_int(M), c_int(d),
         c_int(int(rms)), c_ulonglong(drop_seed), c_uint(drop_stream),
         c_uint(_lib.dropout_thr16(drop_p)), stream_ptr()), "ab_layernorm_bwd")
 

@@ -12,6 +12,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+from time import perf_counter
 from ctypes import POINTER, c_float, c_int, c_void_p
 from dataclasses import dataclass, field
 
@@ -169,6 +170,9 @@ class BatchedMCTS:
                         slot=np.zeros(n, i32), n_anc=np.zeros(n, i32), n_legal=np.zeros(n, i32),
                         anc=np.zeros((n, anc_max), i32), legal=np.zeros((n, legal_max), i32))
         self.total_rollouts = 0
+        # host wall-clock seconds spent in the three phases of the search loop (select on the CPU,
+        # leaf evaluation on the GPU including its copies, backup on the CPU)
+        self.phase_seconds = {"select": 0.0, "evaluate": 0.0, "backup": 0.0}
 
     def __del__(self):
         try:
@@ -210,16 +214,24 @@ class BatchedMCTS:
                 cp[t] = c_puct_per_tree(b)
             self.lib.mcts_set_budget(self.h, t, int(b))
         r = self.req
+        ph = self.phase_seconds
+        clock = perf_counter
         while True:
+            t0 = clock()
             nreq = self.lib.mcts_select(self.h, _fp(cp), _ip(r["need_eval"]), _ip(r["tok"]), _ip(r["pos"]),
                                         _ip(r["slot"]), _ip(r["anc"]), self.anc_max, _ip(r["n_anc"]),
                                         _ip(r["legal"]), self.legal_max, _ip(r["n_legal"]))
+            t1 = clock()
+            ph["select"] += t1 - t0
             if nreq == 0:
                 break
             pri, val = self.ev.step(r)
             pri = np.ascontiguousarray(pri, dtype=np.float32)
             val = np.ascontiguousarray(val, dtype=np.float32)
+            t2 = clock()
+            ph["evaluate"] += t2 - t1
             self.lib.mcts_backup(self.h, _fp(pri), pri.shape[1], _fp(val), int(self.dummy))
+            ph["backup"] += clock() - t2
         results = []
         mv = np.zeros(self.legal_max, np.int32); vis = np.zeros(self.legal_max, np.int32)
         pr = np.zeros(self.legal_max, np.float32); va = np.zeros(self.legal_max, np.float32)

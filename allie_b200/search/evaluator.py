@@ -27,6 +27,7 @@ class KVLeafEvaluator:
         self.eng = engine
         cfg = engine.cfg
         self.n, self.S = n_trees, max_prefix + max_nodes
+        assert max_prefix + anc_max <= 1024, "the decode attention kernel scores at most 1024 keys per tree"
         self.max_prefix, self.anc_max, self.legal_max = max_prefix, anc_max, legal_max
         dev, d, F, V, L = engine.device, cfg.n_embd, cfg.ffn_dim, cfg.vocab_size, cfg.n_layer
         bf, f32, i32 = torch.bfloat16, torch.float32, torch.int32
@@ -105,7 +106,7 @@ class KVLeafEvaluator:
         lib = _lib.cuda()
         K.embed_fwd(self.view(rd, "tok"), self.view(rd, "pos"), eng.wte[0], eng.wpe[0], eng.ctrl_w[0],
                     self.x[0], V, 0, 0, 0.0)
-        x, xm = self.x
+        x = self.x[0]
         scale = 1.0 / cfg.head_dim ** 0.5
         for l, Ly in enumerate(eng.layers):
             K.layernorm_fwd(x, Ly["ln1_w"][0], Ly["ln1_b"][0], self.ln, self.stat[0], self.stat[1], eps, eng.rms)
@@ -117,10 +118,11 @@ class KVLeafEvaluator:
                                     c_int(self.S), c_float(scale), stream_ptr())
             assert rc == 0
             _lib.count_launches(1)
-            gemm(self.att, Ly["o_w"][1], b_mn=True, out=xm, bias=Ly["o_b"][0], resid=x)
-            K.layernorm_fwd(xm, Ly["ln2_w"][0], Ly["ln2_b"][0], self.ln, self.stat[0], self.stat[1], eps, eng.rms)
+            # residual updates in place: with a few hundred rows they run as split-K reduce-adds
+            gemm(self.att, Ly["o_w"][1], b_mn=True, out=x, bias=Ly["o_b"][0], resid=x)
+            K.layernorm_fwd(x, Ly["ln2_w"][0], Ly["ln2_b"][0], self.ln, self.stat[0], self.stat[1], eps, eng.rms)
             gemm(self.ln, Ly["fc_w"][1], b_mn=True, out=self.act, bias=Ly["fc_b"][0], act=1, aux=self.pre)
-            gemm(self.act, Ly["pr_w"][1], b_mn=True, out=x, bias=Ly["pr_b"][0], resid=xm)
+            gemm(self.act, Ly["pr_w"][1], b_mn=True, out=x, bias=Ly["pr_b"][0], resid=x)
         K.layernorm_fwd(x, eng.lnf_w[0], eng.lnf_b[0], self.h, self.stat[0], self.stat[1], eps, eng.rms)
         gemm(self.h, eng.wte[1], b_mn=False, out=self.logits)
         has_heads = eng.reg is not None

@@ -78,6 +78,7 @@ def main():
         bm.search(games[: args.trees], n_sims=8)           # warm-up (graph capture, first launches)
         torch.cuda.synchronize()
         ev.positions = 0
+        bm.phase_seconds = {k: 0.0 for k in bm.phase_seconds}
         l0 = _lib.LAUNCHES
         t0 = time.perf_counter()
         res = bm.search(games)
@@ -86,7 +87,8 @@ def main():
         _lib.check_status()
         out.update(value=ev.positions / dt, seconds=dt, positions=ev.positions, steps=ev.kv.steps,
                    moves_per_s=len(games) / dt, latency_per_move_batch_s=dt, gpu_launches=_lib.LAUNCHES - l0,
-                   sims_done=int(sum(r.n_sims for r in res)))
+                   sims_done=int(sum(r.n_sims for r in res)),
+                   phase_seconds={k: round(v, 4) for k, v in bm.phase_seconds.items()})
     else:
         from allie_b200.search import MCTS
 

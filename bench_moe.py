@@ -3,7 +3,7 @@
 Config: 24 layers, d_model 2048, 16 heads of 128, every third block routes top-2 over 64 experts
 of FFN 4096 (dense FFN 4096 elsewhere; about 9.3 B parameters), context 512, vocab 2048, softmax
 router with load-balance loss, expert parallelism over all ranks, global batch 512 sequences
-(micro-batch 8 per GPU), dropout 0.1, bf16 tensor-core math.  Synthetic tokens, random init.
+(micro-batch 32 per GPU: 512 routed token slots per expert and micro-step), dropout 0.1, bf16 tensor-core math.  Synthetic tokens, random init.
 
     torchrun --nproc-per-node 8 bench_moe.py --gpus 8              # this framework
     torchrun --nproc-per-node 8 bench_moe.py --gpus 8 --impl torch # plain-PyTorch EP baseline
@@ -22,10 +22,11 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 from bench import ClockSampler, barrier_sync, dist_info, max_over_ranks, synthetic_stream  # noqa: E402
 
-SEQ_LEN, GLOBAL_BATCH, MICRO_BATCH = 512, 512, 8
+SEQ_LEN, GLOBAL_BATCH, MICRO_BATCH = 512, 512, 32
 
 
 def main():
+    global MICRO_BATCH
     import numpy as np
     import torch
 
@@ -37,7 +38,9 @@ def main():
     ap.add_argument("--layers", type=int, default=24)
     ap.add_argument("--experts", type=int, default=64)
     ap.add_argument("--global-batch", type=int, default=GLOBAL_BATCH)
+    ap.add_argument("--micro-batch", type=int, default=MICRO_BATCH)
     args = ap.parse_args()
+    MICRO_BATCH = args.micro_batch
     rank, world, local = dist_info()
     assert world == args.gpus
     os.environ.setdefault("ALLIE_NO_WANDB", "1")
@@ -64,7 +67,7 @@ def main():
         model = initialize_model(tok, "gpt2-medium", use_control_token=True, use_regression_head=True, **shape)
         trainer.setup_dataloaders(tok, stream, [], [])
         trainer.setup_model(model)
-        trainer.iter_num = 100
+        trainer.iter_num = 2000          # past the warm-up: both arms step at lr 3e-4
         dev = trainer.engine.device
         wins = [trainer.sampler.next().clone().to(dev) for _ in range(max(ga, 4))]
         step = lambda i: trainer.train_step([wins[(i * ga + m) % len(wins)] for m in range(ga)])
@@ -108,8 +111,9 @@ def main():
             return loss.detach()
         counter = lambda: 0
         check = lambda: None
+    trace = []                       # device-side loss of every step, read back after the timed region
     for i in range(args.warmup):
-        step(i)
+        trace.append(step(i).clone())
     torch.cuda.synchronize()
     check()
     sampler = ClockSampler(local)
@@ -120,6 +124,7 @@ def main():
     e0.record()
     for i in range(args.steps):
         loss = step(args.warmup + i)
+        trace.append(loss.clone())
     e1.record()
     barrier_sync(world)
     clocks = sampler.stop()
@@ -133,7 +138,8 @@ def main():
            "config": {"model": f"{args.layers}L d2048 16H hd128, MoE every 3rd layer: {args.experts} experts x FFN 4096, top-2",
                       "global_batch": ga * MICRO_BATCH * world, "seq_len": SEQ_LEN, "micro_batch": MICRO_BATCH,
                       "grad_accum": ga, "parallelism": f"dp{world}+ep{world}", "params_per_rank": n_params},
-           "clocks": clocks, "gpu_launches": counter() - l0, "final_loss": float(loss if loss.dim() == 0 else loss[0])}
+           "clocks": clocks, "gpu_launches": counter() - l0, "final_loss": float(loss if loss.dim() == 0 else loss[0]),
+           "loss_per_step": [round(float(t if t.dim() == 0 else t[0]), 3) for t in trace]}
     if rank == 0:
         print(json.dumps(res), flush=True)
 

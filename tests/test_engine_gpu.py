@@ -20,7 +20,7 @@ def _windows(tok, B, T, seed=0):
     return words
 
 
-@pytest.mark.parametrize("n_embd,n_head", [(256, 4), (512, 4)])     # head sizes 64 and 128
+@pytest.mark.parametrize("n_embd,n_head", [(256, 4), (512, 4), (1280, 20), (2048, 16)])   # head sizes 64, 128; the large-ablation and MoE widths
 def test_dense_engine_matches_oracle(n_embd, n_head):
     from allie_b200.data import UCITokenizer
     from allie_b200.models import initialize_model

@@ -113,3 +113,22 @@ def test_gemm_pair_split_k_accumulate():
     torch.cuda.synchronize()
     _lib.check_status()
     assert torch.allclose(dw, ref, rtol=1e-3, atol=0.2)
+
+
+def test_gemm_skinny_residual_update_in_place():
+    """Decode-sized x += a @ w + bias: few output tiles, long K (taken by the split-K route)."""
+    from allie_b200.ops import _lib
+    from allie_b200.ops.gemm import gemm
+
+    torch.manual_seed(4)
+    dev = "cuda"
+    for M, N, K in ((256, 1024, 4096), (192, 1024, 1024), (40, 768, 2048)):
+        a = torch.randn(M, K, device=dev).bfloat16()
+        w = (torch.randn(K, N, device=dev) * 0.03).bfloat16()
+        bias = torch.randn(N, device=dev)
+        x = torch.randn(M, N, device=dev)
+        want = x + a.float() @ w.float() + bias
+        gemm(a, w, b_mn=True, bias=bias, resid=x, out=x)
+        torch.cuda.synchronize()
+        _lib.check_status()
+        assert torch.allclose(x, want, rtol=1e-3, atol=3e-2), (M, N, K, (x - want).abs().max().item())

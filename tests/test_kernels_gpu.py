@@ -89,9 +89,12 @@ def test_layernorm_backward_dropout_copy_is_masked_and_scaled():
     dbranch = torch.empty(M, d, device=DEV, dtype=torch.bfloat16)
     dgamma = torch.zeros(d, device=DEV)
     dbeta = torch.zeros(d, device=DEV)
+    dbias = torch.full((d,), 0.5, device=DEV)
     K.layernorm_bwd(dy, x, mean, rstd, g, dres, dx, dbranch, dgamma, dbeta, drop_seed=11, drop_stream=5,
-                    drop_p=0.25)
+                    drop_p=0.25, dbias=dbias)
     _done()
+    # fused bias gradient of the projection below: column sums of the masked copy, accumulated
+    assert torch.allclose(dbias, 0.5 + dbranch.float().sum(0), rtol=1e-2, atol=0.5)
     kept = dbranch != 0
     frac = kept.float().mean().item()
     assert abs(frac - 0.75) < 0.01, frac
