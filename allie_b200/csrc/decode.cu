@@ -8,18 +8,18 @@
 //   policy_epilogue : per tree, softmax over the logits of the leaf's legal moves only, plus value,
 //                     think time and the resign logit, packed into one row for a single
 //                     device-to-host copy
-// Cache layout per layer: K and V as [tree][slot][H*hd] bf16.
+// Cache layout per layer: K and V as [tree][head][slot][hd] bf16, so the rows one (tree, head)
+// attention block streams are contiguous in memory.
 #include "ptx.cuh"
 
 namespace ab {
 
 // grid (n_trees, H), block 128.  A key's row for one head is HD/8 chunks of 16 bytes; the block is
 // 128 / (HD/8) key groups times HD/8 chunk lanes, so the lanes of a group read one contiguous row
-// and the groups walk the keys in parallel with every load independent of the others (the kernel
-// is a stream over the tree's K/V rows and has to run at memory speed).  Two passes: scores into
-// shared memory and the block maximum, then probabilities times V.
-constexpr int DEC_MAX_KEYS = 1024;     // prompt slots + ancestor list per tree
-
+// and the groups walk the keys in parallel.  One pass with a running maximum per group: the K and V
+// chunks of a key are fetched together and every load is independent of the arithmetic, so the
+// kernel streams the tree's K/V rows at memory speed; the groups' partial results are merged at
+// the end.
 template <int HD>
 __global__ void __launch_bounds__(128)
 decode_attn_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ kc,
@@ -29,19 +29,19 @@ decode_attn_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restr
                    __nv_bfloat16* __restrict__ out, int H, int S, float scale) {
   constexpr int CH = HD / 8;             // 16-byte chunks per row = lanes per key group
   constexpr int KG = 128 / CH;           // key groups per block
+  constexpr int UNROLL = 4;
   const int t = blockIdx.x, h = blockIdx.y;
   if (!active[t]) return;
-  __shared__ float s_score[DEC_MAX_KEYS];
-  __shared__ float s_red[4];
+  __shared__ float s_m[KG], s_l[KG];
   __shared__ float s_acc[KG][HD];
   const int d = H * HD;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tid = threadIdx.x;
   const int c = tid % CH, kg = tid / CH;
   const __nv_bfloat16* row = qkv + static_cast<long long>(t) * 3 * d;
-  const long long cache_base = static_cast<long long>(t) * S * d + h * HD;
+  const long long cache_base = (static_cast<long long>(t) * H + h) * S * HD;
   // append this token's key / value (self is the last entry of the ancestor list)
   if (tid < CH) {
-    const long long dst = cache_base + static_cast<long long>(slot[t]) * d + tid * 8;
+    const long long dst = cache_base + static_cast<long long>(slot[t]) * HD + tid * 8;
     *reinterpret_cast<uint4*>(kc + dst) = *reinterpret_cast<const uint4*>(row + d + h * HD + tid * 8);
     *reinterpret_cast<uint4*>(vc + dst) = *reinterpret_cast<const uint4*>(row + 2 * d + h * HD + tid * 8);
   }
@@ -52,61 +52,72 @@ decode_attn_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restr
     q[3] = bf16_hi(qv.y) * scale; q[4] = bf16_lo(qv.z) * scale; q[5] = bf16_hi(qv.z) * scale;
     q[6] = bf16_lo(qv.w) * scale; q[7] = bf16_hi(qv.w) * scale;
   }
-  __syncthreads();                        // the appended row is visible to the whole block
+  // No barrier: the token's own key (the last entry of the ancestor list) is read from the
+  // packed QKV row it was just copied from, never back from the cache.
   const int P = prefix_len[t];
-  const int n = min(P + n_anc[t], DEC_MAX_KEYS);
+  const int n = P + n_anc[t];
   const int* anc_t = anc + static_cast<long long>(t) * anc_stride;
-  // ---- pass 1: scores
-  float mx = -INFINITY;
-#pragma unroll 4
-  for (int i0 = 0; i0 < n; i0 += KG) {     // uniform trip count: the shuffles below need every lane
-    const int i = i0 + kg;
-    const bool live = i < n;
-    uint4 kv = make_uint4(0, 0, 0, 0);
-    if (live) {
-      const int sl = i < P ? i : anc_t[i - P];
-      kv = *reinterpret_cast<const uint4*>(kc + cache_base + static_cast<long long>(sl) * d + c * 8);
-    }
-    float dot = q[0] * bf16_lo(kv.x) + q[1] * bf16_hi(kv.x) + q[2] * bf16_lo(kv.y) + q[3] * bf16_hi(kv.y) +
-                q[4] * bf16_lo(kv.z) + q[5] * bf16_hi(kv.z) + q[6] * bf16_lo(kv.w) + q[7] * bf16_hi(kv.w);
-#pragma unroll
-    for (int o = CH / 2; o; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-    if (live) {
-      if (c == 0) s_score[i] = dot;
-      mx = fmaxf(mx, dot);
-    }
-  }
-#pragma unroll
-  for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-  if (lane == 0) s_red[warp] = mx;
-  __syncthreads();
-  const float M = fmaxf(fmaxf(s_red[0], s_red[1]), fmaxf(s_red[2], s_red[3]));
-  // ---- pass 2: probabilities x V (this thread: 8 dims of the keys of its group)
+  const __nv_bfloat16* kbase = kc + cache_base + c * 8;
+  const __nv_bfloat16* vbase = vc + cache_base + c * 8;
+  const __nv_bfloat16* kself = row + d + h * HD + c * 8;
+  const __nv_bfloat16* vself = row + 2 * d + h * HD + c * 8;
+  float m = -INFINITY, l = 0.f;
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-  float l = 0.f;
-#pragma unroll 4
-  for (int i = kg; i < n; i += KG) {
-    const int sl = i < P ? i : anc_t[i - P];
-    const uint4 vv = *reinterpret_cast<const uint4*>(vc + cache_base + static_cast<long long>(sl) * d + c * 8);
-    const float p = __expf(s_score[i] - M);
-    l += p;
-    acc[0] += p * bf16_lo(vv.x); acc[1] += p * bf16_hi(vv.x); acc[2] += p * bf16_lo(vv.y); acc[3] += p * bf16_hi(vv.y);
-    acc[4] += p * bf16_lo(vv.z); acc[5] += p * bf16_hi(vv.z); acc[6] += p * bf16_lo(vv.w); acc[7] += p * bf16_hi(vv.w);
+  // uniform trip count over the block: the group shuffles below need every lane of the warp
+  for (int i0 = 0; i0 < n; i0 += KG * UNROLL) {
+    uint4 kv[UNROLL], vv[UNROLL];
+    bool live[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int i = i0 + u * KG + kg;
+      live[u] = i < n;
+      kv[u] = make_uint4(0, 0, 0, 0);
+      vv[u] = kv[u];
+      if (live[u]) {
+        if (i == n - 1) {
+          kv[u] = *reinterpret_cast<const uint4*>(kself);
+          vv[u] = *reinterpret_cast<const uint4*>(vself);
+        } else {
+          const long long off = static_cast<long long>(i < P ? i : anc_t[i - P]) * HD;
+          kv[u] = *reinterpret_cast<const uint4*>(kbase + off);
+          vv[u] = *reinterpret_cast<const uint4*>(vbase + off);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      float dot = q[0] * bf16_lo(kv[u].x) + q[1] * bf16_hi(kv[u].x) + q[2] * bf16_lo(kv[u].y) +
+                  q[3] * bf16_hi(kv[u].y) + q[4] * bf16_lo(kv[u].z) + q[5] * bf16_hi(kv[u].z) +
+                  q[6] * bf16_lo(kv[u].w) + q[7] * bf16_hi(kv[u].w);
+#pragma unroll
+      for (int o = CH / 2; o; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+      if (live[u]) {                      // uniform within the key group
+        const float m_new = fmaxf(m, dot);
+        const float a = __expf(m - m_new), p = __expf(dot - m_new);
+        l = l * a + p;
+        acc[0] = acc[0] * a + p * bf16_lo(vv[u].x); acc[1] = acc[1] * a + p * bf16_hi(vv[u].x);
+        acc[2] = acc[2] * a + p * bf16_lo(vv[u].y); acc[3] = acc[3] * a + p * bf16_hi(vv[u].y);
+        acc[4] = acc[4] * a + p * bf16_lo(vv[u].z); acc[5] = acc[5] * a + p * bf16_hi(vv[u].z);
+        acc[6] = acc[6] * a + p * bf16_lo(vv[u].w); acc[7] = acc[7] * a + p * bf16_hi(vv[u].w);
+        m = m_new;
+      }
+    }
   }
+  if (c == 0) { s_m[kg] = m; s_l[kg] = l; }
 #pragma unroll
   for (int e = 0; e < 8; ++e) s_acc[kg][c * 8 + e] = acc[e];
-  // every lane of a key group carries the same l; count each group once
-  if (c != 0) l = 0.f;
-#pragma unroll
-  for (int o = 16; o; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
-  __syncthreads();                        // also orders the s_red reads above before the writes below
-  if (lane == 0) s_red[warp] = l;
   __syncthreads();
   if (tid < HD) {
-    const float L = s_red[0] + s_red[1] + s_red[2] + s_red[3];
-    float o = 0.f;
+    float M = -INFINITY;
 #pragma unroll
-    for (int g = 0; g < KG; ++g) o += s_acc[g][tid];
+    for (int g = 0; g < KG; ++g) M = fmaxf(M, s_m[g]);
+    float L = 0.f, o = 0.f;
+#pragma unroll
+    for (int g = 0; g < KG; ++g) {
+      const float f = s_m[g] == -INFINITY ? 0.f : __expf(s_m[g] - M);
+      L += s_l[g] * f;
+      o += s_acc[g][tid] * f;
+    }
     out[static_cast<long long>(t) * d + h * HD + tid] = __float2bfloat16(o / L);
   }
 }
@@ -114,16 +125,17 @@ decode_attn_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restr
 // rows of qkv [n_trees * Lp, 3d] -> cache slots [tree][pos] for pos < len[tree]
 __global__ void __launch_bounds__(256)
 kv_store_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ kc,
-                __nv_bfloat16* __restrict__ vc, const int* __restrict__ len, int Lp, int S, int d) {
+                __nv_bfloat16* __restrict__ vc, const int* __restrict__ len, int Lp, int S, int d,
+                int hd) {
   const int t = blockIdx.y, p = blockIdx.x;
   if (p >= len[t]) return;
   const uint4* src = reinterpret_cast<const uint4*>(qkv + (static_cast<long long>(t) * Lp + p) * 3 * d);
-  uint4* dk = reinterpret_cast<uint4*>(kc + (static_cast<long long>(t) * S + p) * d);
-  uint4* dv = reinterpret_cast<uint4*>(vc + (static_cast<long long>(t) * S + p) * d);
-  const int n8 = d / 8;
+  const int n8 = d / 8, hd8 = hd / 8, H = d / hd;
   for (int i = threadIdx.x; i < n8; i += 256) {
-    dk[i] = src[n8 + i];
-    dv[i] = src[2 * n8 + i];
+    const int h = i / hd8, c = i - h * hd8;
+    const long long dst = (((static_cast<long long>(t) * H + h) * S + p) * hd) / 8 + c;
+    reinterpret_cast<uint4*>(kc)[dst] = src[n8 + i];
+    reinterpret_cast<uint4*>(vc)[dst] = src[2 * n8 + i];
   }
 }
 
@@ -180,11 +192,11 @@ int ab_decode_attn(const void* qkv, void* kc, void* vc, const int* active, const
 }
 
 int ab_kv_store(const void* qkv, void* kc, void* vc, const int* len, int n_trees, int Lp, int S, int d,
-                cudaStream_t stream) {
-  if (d % 8) return -1;
+                int hd, cudaStream_t stream) {
+  if (d % 8 || hd % 8 || d % hd) return -1;
   dim3 grid(Lp, n_trees);
   ab::kv_store_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)qkv, (__nv_bfloat16*)kc,
-                                                (__nv_bfloat16*)vc, len, Lp, S, d);
+                                                (__nv_bfloat16*)vc, len, Lp, S, d, hd);
   return (int)cudaGetLastError();
 }
 

@@ -27,7 +27,6 @@ class KVLeafEvaluator:
         self.eng = engine
         cfg = engine.cfg
         self.n, self.S = n_trees, max_prefix + max_nodes
-        assert max_prefix + anc_max <= 1024, "the decode attention kernel scores at most 1024 keys per tree"
         self.max_prefix, self.anc_max, self.legal_max = max_prefix, anc_max, legal_max
         dev, d, F, V, L = engine.device, cfg.n_embd, cfg.ffn_dim, cfg.vocab_size, cfg.n_layer
         bf, f32, i32 = torch.bfloat16, torch.float32, torch.int32
@@ -84,7 +83,7 @@ class KVLeafEvaluator:
 
         def hook(l, qkv):
             rc = _lib.cuda().ab_kv_store(ptr(qkv), ptr(self.kc[l]), ptr(self.vc[l]), ptr(len_dev), c_int(n),
-                                         c_int(Lp), c_int(self.S), c_int(d), stream_ptr())
+                                         c_int(Lp), c_int(self.S), c_int(d), c_int(eng.cfg.head_dim), stream_ptr())
             assert rc == 0
             _lib.count_launches(1)
 
