@@ -5,6 +5,7 @@ TFLOP/s or GB/s against the measured peaks of the machine (``MEASURED_PEAKS.json
     python -m allie_b200.utils.kbench attn --batch 64 --seq 512 --heads 16 --hd 64 [--dropout 0.1] [--bwd]
     python -m allie_b200.utils.kbench layernorm --rows 32768 --d 1024 [--bwd]
     python -m allie_b200.utils.kbench adamw --n 300000000
+    python -m allie_b200.utils.kbench colsum --rows 32768 --d 4096
 
 Also the workload to put under ``ncu`` (``--iters`` small).  Inputs are sized beyond the 126 MB L2.
 """
@@ -44,7 +45,7 @@ def main(argv=None) -> dict:
     from ..ops.gemm import gemm
 
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "attn", "layernorm", "adamw"])
+    ap.add_argument("kernel", choices=["gemm", "attn", "layernorm", "adamw", "colsum"])
     ap.add_argument("--m", type=int, default=32768); ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=1024)
     ap.add_argument("--epilogue", default="none", choices=["none", "bias", "gelu", "dgelu", "resid"])
@@ -113,6 +114,13 @@ def main(argv=None) -> dict:
             fn = lambda: K.layernorm_fwd(x, g, b, y, mean, rstd, 1e-5)
             nbytes = M * d * 6
         s = _time(fn, a.iters, a.warmup)
+        out.update(shape=[M, d], seconds=s, gbs=nbytes / s / 1e9, frac_of_measured_hbm=nbytes / s / 1e9 / peaks["hbm_gbs"])
+    elif a.kernel == "colsum":
+        M, d = a.rows, a.d
+        x = torch.randn(M, d, device=dev).bfloat16(); o = torch.zeros(d, device=dev)
+        fn = lambda: K.colsum_bf16(x, o)
+        s = _time(fn, a.iters, a.warmup)
+        nbytes = M * d * 2
         out.update(shape=[M, d], seconds=s, gbs=nbytes / s / 1e9, frac_of_measured_hbm=nbytes / s / 1e9 / peaks["hbm_gbs"])
     else:
         n = a.n if a.n > 1 << 20 else 300_000_000
