@@ -35,7 +35,9 @@ BASELINE_TOKENS_PER_S = 2.17e5   # derived from the reference README: 8x RTX A60
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons with nvidia-smi.  ``start()`` launches the sampler
+    (during warm-up, so it is already producing rows), ``mark()`` is called at the start of the
+    timed region and ``stop()`` summarises the rows sampled after the mark."""
 
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -45,15 +47,19 @@ class ClockSampler:
         self.rows: list[list[str]] = []
         self.proc = None
         self.idx = gpu_index
+        self.first = 0
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50",
                  "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._pump, daemon=True).start()
         except Exception:
             self.proc = None
+
+    def mark(self):
+        self.first = len(self.rows)
 
     def _pump(self):
         for line in self.proc.stdout:
@@ -69,7 +75,7 @@ class ClockSampler:
             pass
         sm, mx, reasons = [], None, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
+        for r in self.rows[self.first:]:
             if len(r) < 9:
                 continue
             try:
@@ -178,14 +184,15 @@ def run_ours(args) -> dict:
         loss = trainer.train_step(ws)
         sink.copy_(loss, non_blocking=True)
 
+    sampler = ClockSampler(local)
+    sampler.start()
     for i in range(args.warmup):
         step_device(i)
     torch.cuda.synchronize()
     _lib.check_status()
 
-    sampler = ClockSampler(local)
-    sampler.start()
     barrier_sync(world)
+    sampler.mark()
     launches0 = _lib.LAUNCHES
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -297,9 +304,11 @@ def run_reference(args) -> dict:
 
     def hook(optimizer, a, kw):
         state["n"] += 1
-        if state["n"] == W:
+        if state["n"] == 1:
             sampler.start()
+        if state["n"] == W:
             barrier_sync(world)
+            sampler.mark()
             state["wall0"] = time.perf_counter()
             e0.record()
         elif state["n"] == W + K:

@@ -112,13 +112,14 @@ def main():
         counter = lambda: 0
         check = lambda: None
     trace = []                       # device-side loss of every step, read back after the timed region
+    sampler = ClockSampler(local)
+    sampler.start()
     for i in range(args.warmup):
         trace.append(step(i).clone())
     torch.cuda.synchronize()
     check()
-    sampler = ClockSampler(local)
-    sampler.start()
     barrier_sync(world)
+    sampler.mark()
     l0 = counter()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
