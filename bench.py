@@ -239,7 +239,8 @@ def run_ours(args) -> dict:
                    "grad_accum": ga, "parallelism": f"dp{world}",
                    "l2_policy": "inputs larger than L2: each micro-step streams >1 GB of activations "
                                 "and 1.2 GB of fp32 weights+grads, distinct windows per micro-step",
-                   "grad_sync": "fused-nvlink" if (trainer.grad_sync and trainer.grad_sync.fused)
+                   "grad_sync": ("fused-nvlink-multimem" if trainer.grad_sync.nvl.multimem else "fused-nvlink-p2p")
+                                if (trainer.grad_sync and trainer.grad_sync.fused)
                                 else ("all_reduce" if world > 1 else "none")},
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
