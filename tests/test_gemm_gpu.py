@@ -132,3 +132,23 @@ def test_gemm_skinny_residual_update_in_place():
         torch.cuda.synchronize()
         _lib.check_status()
         assert torch.allclose(x, want, rtol=1e-3, atol=3e-2), (M, N, K, (x - want).abs().max().item())
+
+
+@pytest.mark.parametrize("M,N,K", [(1000, 328, 192), (2048, 1024, 256), (640, 72, 128)])
+def test_gemm_gelu_backward_epilogue_ragged(M, N, K):
+    """out = (dy @ w^T) * gelu'(pre) on shapes with ragged row / column tiles (the CTA-pair kernel
+    fetches the pre-activation tiles by TMA one tile ahead)."""
+    from allie_b200.ops import _lib
+    from allie_b200.ops.gemm import gemm
+
+    torch.manual_seed(5)
+    dev = "cuda"
+    dy = torch.randn(M, K, device=dev).bfloat16()
+    wt = (torch.randn(N, K, device=dev) * 0.05).bfloat16()
+    pre = torch.randn(M, N, device=dev).bfloat16()
+    out = gemm(dy, wt, act=2, aux=pre)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    x = pre.float().requires_grad_(True)
+    torch.nn.functional.gelu(x, approximate="tanh").backward(dy.float() @ wt.float().t())
+    assert torch.allclose(out.float(), x.grad, rtol=3e-2, atol=3e-2), (out.float() - x.grad).abs().max().item()
