@@ -32,23 +32,28 @@ constexpr int FB_THREADS = (FB_MATH_WARPS + 2) * 32;
 constexpr int FB_TILE = 128 * 64 * 2;       // one 128 x 64 bf16 tile
 constexpr int FB_P = 128 * 128 * 2;
 
+// P and dS for 16 adjacent keys of one query row.
+//   p_i  = exp2(s_i * sl2 - lse_l2)                       (0 on masked keys)
+//   P_i  = keep_i ? p_i * dscale : 0                      (what multiplies dO in dV)
+//   dS_i = p_i * ((keep_i ? dP_i * dscale : 0) - delta) * scale
+// A row outside the sequence passes lse_l2 = +inf, which makes every p_i zero without a select;
+// the dropout decision is applied as a multiplication by m_i = keep_i ? dscale : 0.
 template <bool DIAG, bool DROP>
 __device__ __forceinline__ void fb_math16(const uint32_t* sv, const uint32_t* dv, float* p, float* ds,
-                                          int r, int col0, bool q_ok, float sl2, float lse_l2,
-                                          float dlt, float scale, float dscale, uint32_t keep16) {
+                                          int r, int col0, float sl2, float lse_l2,
+                                          float dlt_s, float scale, float dscale, uint32_t keep16) {
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
-    const bool live = q_ok && (!DIAG || (col0 + i) <= r);
-    const float pi = live ? ex2_fast(__uint_as_float(sv[i]) * sl2 - lse_l2) : 0.f;
-    float dpe = __uint_as_float(dv[i]);
+    float pi = ex2_fast(__uint_as_float(sv[i]) * sl2 - lse_l2);
+    if (DIAG) pi = (col0 + i) <= r ? pi : 0.f;
     if (DROP) {
-      const bool kp = (keep16 >> i) & 1u;
-      dpe = kp ? dpe * dscale : 0.f;
-      p[i] = kp ? pi * dscale : 0.f;
+      const float mi = ((keep16 >> i) & 1u) ? dscale : 0.f;
+      p[i] = pi * mi;
+      ds[i] = pi * (__uint_as_float(dv[i]) * (mi * scale) - dlt_s);
     } else {
       p[i] = pi;
+      ds[i] = pi * (__uint_as_float(dv[i]) * scale - dlt_s);
     }
-    ds[i] = pi * (dpe - dlt) * scale;
   }
 }
 
@@ -240,7 +245,7 @@ attn_bwd_fused64_kernel(const __grid_constant__ CUtensorMap tmQKV,
       const int qi = own + it;
       const int q_idx = qi * 128 + r;
       const bool q_ok = q_idx < a.T;
-      const float lse_l2 = q_ok ? a.lse[bh * a.T + q_idx] * LOG2E : 0.f;
+      const float lse_l2 = q_ok ? a.lse[bh * a.T + q_idx] * LOG2E : INFINITY;
       const float dlt = q_ok ? a.delta[bh * a.T + q_idx] : 0.f;
       const bool diag = it == 0;
       const uint64_t row_elem0 = (static_cast<uint64_t>(bh) * a.T + q_idx) * a.T + own * 128 + cb * 32;
@@ -269,11 +274,11 @@ attn_bwd_fused64_kernel(const __grid_constant__ CUtensorMap tmQKV,
         float p[16], ds[16];
         const uint32_t k16 = keep32 >> (hf * 16);
         if (a.thr16) {
-          if (diag) fb_math16<true, true>(sv, dv, p, ds, r, col0, q_ok, sl2, lse_l2, dlt, a.scale, dscale, k16);
-          else      fb_math16<false, true>(sv, dv, p, ds, r, col0, q_ok, sl2, lse_l2, dlt, a.scale, dscale, k16);
+          if (diag) fb_math16<true, true>(sv, dv, p, ds, r, col0, sl2, lse_l2, dlt * a.scale, a.scale, dscale, k16);
+          else      fb_math16<false, true>(sv, dv, p, ds, r, col0, sl2, lse_l2, dlt * a.scale, a.scale, dscale, k16);
         } else {
-          if (diag) fb_math16<true, false>(sv, dv, p, ds, r, col0, q_ok, sl2, lse_l2, dlt, a.scale, dscale, k16);
-          else      fb_math16<false, false>(sv, dv, p, ds, r, col0, q_ok, sl2, lse_l2, dlt, a.scale, dscale, k16);
+          if (diag) fb_math16<true, false>(sv, dv, p, ds, r, col0, sl2, lse_l2, dlt * a.scale, a.scale, dscale, k16);
+          else      fb_math16<false, false>(sv, dv, p, ds, r, col0, sl2, lse_l2, dlt * a.scale, a.scale, dscale, k16);
         }
         const uint32_t poff = (col0 >> 6) * 16384;
 #pragma unroll
@@ -636,7 +641,7 @@ attn_bwd_fused64_persistent_kernel(const __grid_constant__ CUtensorMap tmQKV,
         row_off += 128;
         keep_off += 4ll * a.T;      // 128 rows of T / 32 words
       }
-      lse_l2 = q_ok ? a.lse[row_off] * LOG2E : 0.f;
+      lse_l2 = q_ok ? a.lse[row_off] * LOG2E : INFINITY;
       dlt = q_ok ? a.delta[row_off] : 0.f;
       keep32 = 0xffffffffu;
       if (a.thr16) {
@@ -683,11 +688,11 @@ attn_bwd_fused64_persistent_kernel(const __grid_constant__ CUtensorMap tmQKV,
         float pp[16], ds[16];
         const uint32_t k16 = keep32 >> (hf * 16);
         if (a.thr16) {
-          if (diag) fb_math16<true, true>(sv, dv, pp, ds, r, col0, q_ok, sl2, lse_l2, dlt, a.scale, dscale, k16);
-          else      fb_math16<false, true>(sv, dv, pp, ds, r, col0, q_ok, sl2, lse_l2, dlt, a.scale, dscale, k16);
+          if (diag) fb_math16<true, true>(sv, dv, pp, ds, r, col0, sl2, lse_l2, dlt * a.scale, a.scale, dscale, k16);
+          else      fb_math16<false, true>(sv, dv, pp, ds, r, col0, sl2, lse_l2, dlt * a.scale, a.scale, dscale, k16);
         } else {
-          if (diag) fb_math16<true, false>(sv, dv, pp, ds, r, col0, q_ok, sl2, lse_l2, dlt, a.scale, dscale, k16);
-          else      fb_math16<false, false>(sv, dv, pp, ds, r, col0, q_ok, sl2, lse_l2, dlt, a.scale, dscale, k16);
+          if (diag) fb_math16<true, false>(sv, dv, pp, ds, r, col0, sl2, lse_l2, dlt * a.scale, a.scale, dscale, k16);
+          else      fb_math16<false, false>(sv, dv, pp, ds, r, col0, sl2, lse_l2, dlt * a.scale, a.scale, dscale, k16);
         }
         if (hf == 0) {
           // the shared P / dS tiles feed the previous pair's dV / dK / dQ products until
