@@ -631,7 +631,9 @@ attn_bwd_fused64_persistent_kernel(const __grid_constant__ CUtensorMap tmQKV,
     // the indices only at the first pair of a key tile.
     long long row_off = 0;          // (batch*head) * T + query index of this thread's row
     long long keep_off = 0;         // word index of its 32 keep bits
-    auto fetch = [&](const FbWalk& w, float& lse_l2, float& dlt, uint32_t& keep32) {
+    // (fetch only issues the loads: no arithmetic on the loaded values here, so nothing waits for
+    // them before the next pair needs them)
+    auto fetch = [&](const FbWalk& w, float& lse_raw, float& dlt, uint32_t& keep32) {
       const int q_idx = (w.own + w.it) * 128 + r;
       const bool q_ok = q_idx < a.T;
       if (w.it == 0) {
@@ -641,12 +643,14 @@ attn_bwd_fused64_persistent_kernel(const __grid_constant__ CUtensorMap tmQKV,
         row_off += 128;
         keep_off += 4ll * a.T;      // 128 rows of T / 32 words
       }
-      lse_l2 = q_ok ? a.lse[row_off] * LOG2E : INFINITY;
-      dlt = q_ok ? a.delta[row_off] : 0.f;
+      lse_raw = INFINITY;
+      dlt = 0.f;
+      if (q_ok) { lse_raw = a.lse[row_off]; dlt = a.delta[row_off]; }
       keep32 = 0xffffffffu;
       if (a.thr16) {
         if (a.drop_mask) {
-          keep32 = q_ok ? a.drop_mask[keep_off] : 0u;
+          keep32 = 0u;
+          if (q_ok) keep32 = a.drop_mask[keep_off];
         } else {
           const uint64_t row_elem0 = static_cast<uint64_t>(row_off) * a.T + w.own * 128 + cb * 32;
           keep32 = 0;
@@ -658,9 +662,9 @@ attn_bwd_fused64_persistent_kernel(const __grid_constant__ CUtensorMap tmQKV,
     };
     FbWalk p = start;
     int b = 0, h = 0;
-    float lse_l2 = 0.f, dlt = 0.f;
+    float lse_raw = 0.f, dlt = 0.f;
     uint32_t keep32 = 0xffffffffu;
-    if (p.valid()) fetch(p, lse_l2, dlt, keep32);
+    if (p.valid()) fetch(p, lse_raw, dlt, keep32);
     for (; p.valid() && ok; p.next()) {
       if (threadIdx.x == 0) AB_PSTAMP(0, p.g, 0);
       if (p.it == 0 && p.own == 0) { b = p.bh / a.H; h = p.bh - b * a.H; }
@@ -675,9 +679,11 @@ attn_bwd_fused64_persistent_kernel(const __grid_constant__ CUtensorMap tmQKV,
         q.next();
         if (q.valid()) fetch(q, n_lse, n_dlt, n_keep);
       }
+      if (threadIdx.x == 0) AB_PSTAMP(0, p.g, 5);
       if (!mbar_wait(sdp_full, p.g & 1, abort_flag)) { ok = false; break; }
       if (threadIdx.x == 0) AB_PSTAMP(0, p.g, 1);
       tc_fence_after();
+      const float lse_l2 = lse_raw * LOG2E;          // +inf for rows outside the sequence
 #pragma unroll
       for (int hf = 0; hf < 2; ++hf) {
         const int col0 = cb * 32 + hf * 16;
@@ -726,7 +732,7 @@ attn_bwd_fused64_persistent_kernel(const __grid_constant__ CUtensorMap tmQKV,
       }
       if (threadIdx.x == 0) AB_PSTAMP(0, p.g, 4);
       prev_row0 = b * a.T + qi * 128; prev_h = h; prev_b = b; prev_own = p.own;
-      lse_l2 = n_lse; dlt = n_dlt; keep32 = n_keep;
+      lse_raw = n_lse; dlt = n_dlt; keep32 = n_keep;
     }
     if (ok && p.g > 0) {
       ok = drain_dq(p.g - 1, prev_row0, prev_h);
