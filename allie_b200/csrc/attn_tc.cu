@@ -52,8 +52,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
   uint64_t* p_full = bars + 11;
   uint64_t* pv_full = bars + 12;
   uint64_t* pv_empty = bars + 13;
-  uint64_t* xchg = bars + 14;               // row statistics exchange between the two column halves
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  // row statistics exchange between the two column halves: one barrier per TMEM lane quarter,
+  // shared by the two warps that own the same 32 query rows (the quarters do not wait for each other)
+  uint64_t* xchg = bars + 14 + (threadIdx.x >> 5 & 3);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* s_stat = reinterpret_cast<int*>(tmem_slot + 2);       // [128 rows] running row maximum (ordered-int coded)
 
@@ -72,7 +74,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
     }
     mbar_init(s_full, 1); mbar_init(s_empty, FWD_MATH_WARPS);
     mbar_init(p_full, FWD_MATH_WARPS); mbar_init(pv_full, 1); mbar_init(pv_empty, FWD_MATH_WARPS);
-    mbar_init(xchg, FWD_MATH_WARPS);
+    for (int i = 0; i < 4; ++i) mbar_init(bars + 14 + i, 2);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmQKV);
