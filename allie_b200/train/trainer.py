@@ -33,6 +33,7 @@ import torch.distributed as dist
 from ..config import Config, save_config as _save_config
 from ..data import Batch, UCITokenizer, json_to_game
 from ..utils.logging import setup_logging
+from ..utils.trace import PhaseTracer
 from ..utils.metrics import MetricsSink
 
 logger = logging.getLogger(__name__)
@@ -129,6 +130,7 @@ class Trainer:
         self.iter_num = 0
         self.best_val_loss = float("inf")
         self.engine = None
+        self.tracer = PhaseTracer(device=self.device)
         self.optimizer = None
         self.grad_sync = None
 
@@ -212,24 +214,28 @@ class Trainer:
         synchronising."""
         lr = self.get_lr()
         ga = self.gradient_accumulation_steps
+        tr = self.tracer
         if self.engine is not None:
             eng = self.engine
             loss = None
             for ms in range(ga):
-                w = windows[ms] if windows is not None else self.sampler.next()
-                if not w.is_cuda:
-                    w = w.to(eng.device, non_blocking=True)
-                loss = eng.micro_step(w)
+                with tr.phase("data"):
+                    w = windows[ms] if windows is not None else self.sampler.next()
+                    if not w.is_cuda:
+                        w = w.to(eng.device, non_blocking=True)
+                with tr.phase("forward_backward"):
+                    loss = eng.micro_step(w)
             world = self.ddp_world_size
-            if self.grad_sync is not None and self.grad_sync.fused:
-                # reduce-scatter + clip + AdamW + all-gather in the NVLink kernels
-                self.grad_sync.fused_step(lr, self.betas, 1e-8, self.weight_decay, self.grad_clip)
-            else:
-                if self.grad_sync is not None:
-                    self.grad_sync.all_reduce_sum()
-                eng.optimizer_step(lr, self.betas, 1e-8, self.weight_decay, self.grad_clip,
-                                   grad_scale=1.0 / world)
-            eng.zero_grad()
+            with tr.phase("grad_sync_optimizer"):
+                if self.grad_sync is not None and self.grad_sync.fused:
+                    # reduce-scatter + clip + AdamW + all-gather in the NVLink kernels
+                    self.grad_sync.fused_step(lr, self.betas, 1e-8, self.weight_decay, self.grad_clip)
+                else:
+                    if self.grad_sync is not None:
+                        self.grad_sync.all_reduce_sum()
+                    eng.optimizer_step(lr, self.betas, 1e-8, self.weight_decay, self.grad_clip,
+                                       grad_scale=1.0 / world)
+                eng.zero_grad()
             return loss[0]
         # CPU oracle path
         for g in self.optimizer.param_groups:
@@ -237,16 +243,19 @@ class Trainer:
         self.model.train()
         loss = None
         for ms in range(ga):
-            w = windows[ms] if windows is not None else self.sampler.next()
-            batch = self.tokenizer.unpack(w.to(torch.int64) & 0xFFFFFFFF)
-            loss = self.model(**batch)["loss"]
-            loss.backward()
-        if self.grad_sync is not None:
-            self.grad_sync.all_reduce_mean_torch()
-        if self.grad_clip > 0.0:
-            torch.nn.utils.clip_grad_norm_(self.model.parameters(), self.grad_clip)
-        self.optimizer.step()
-        self.optimizer.zero_grad(set_to_none=True)
+            with tr.phase("data"):
+                w = windows[ms] if windows is not None else self.sampler.next()
+                batch = self.tokenizer.unpack(w.to(torch.int64) & 0xFFFFFFFF)
+            with tr.phase("forward_backward"):
+                loss = self.model(**batch)["loss"]
+                loss.backward()
+        with tr.phase("grad_sync_optimizer"):
+            if self.grad_sync is not None:
+                self.grad_sync.all_reduce_mean_torch()
+            if self.grad_clip > 0.0:
+                torch.nn.utils.clip_grad_norm_(self.model.parameters(), self.grad_clip)
+            self.optimizer.step()
+            self.optimizer.zero_grad(set_to_none=True)
         return loss.detach()
 
     def train(self) -> None:
@@ -285,6 +294,9 @@ class Trainer:
                 steps = max(1, self.log_interval) if self.iter_num > 0 else 1
                 logger.info(f"train - iter {self.iter_num}: loss {loss_mean:.4f}, time {dt:.2f}s")
                 logger.debug(f"throughput {tokens_per_step * steps / max(dt, 1e-9):.0f} tokens/s")
+                if self.tracer.enabled:
+                    phases = self.tracer.summary()
+                    logger.info("phases - " + ", ".join(f"{k} {v['ms']:.1f} ms / {v['count']}" for k, v in phases.items()))
             self.iter_num += 1
             if self.iter_num > self.max_iters:
                 break

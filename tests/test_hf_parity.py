@@ -1,0 +1,51 @@
+"""The oracle decoder against Hugging Face's GPT-2: same state-dict keys and tensor layout (Conv1D
+``[in, out]`` weights, tied lm_head), and the same logits from the same weights.  This is what makes
+checkpoints interchangeable with the reference, whose model is ``GPT2LMHeadModel`` inside the two
+wrappers (``src/modeling/model.py:19-20,69-70,165-179``)."""
+import pytest
+import torch
+
+transformers = pytest.importorskip("transformers")
+
+
+def _models():
+    from allie_b200.data import UCITokenizer
+    from allie_b200.models import initialize_model
+
+    torch.manual_seed(0)
+    tok = UCITokenizer(max_length=64, vocab_size_multiple_of=128)
+    ours = initialize_model(tok, "gpt2", use_control_token=True, use_regression_head=True, n_layer=2,
+                            n_embd=64, n_head=2, n_positions=64, resid_pdrop=0.0, embd_pdrop=0.0,
+                            attn_pdrop=0.0)
+    cfg = transformers.GPT2Config(vocab_size=len(tok), n_positions=64, n_embd=64, n_layer=2, n_head=2,
+                                  resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0,
+                                  activation_function="gelu_new")
+    hf = transformers.GPT2LMHeadModel(cfg)
+    return tok, ours.eval(), hf.eval()
+
+
+def test_state_dict_keys_and_shapes_match_hf_gpt2():
+    tok, ours, hf = _models()
+    inner = {k[len("model.model."):]: v for k, v in ours.state_dict().items() if k.startswith("model.model.")}
+    want = {k: v for k, v in hf.state_dict().items() if not k.endswith(".attn.bias") and not k.endswith(".attn.masked_bias")}
+    assert set(inner) == set(want), (sorted(set(inner) ^ set(want)))
+    for k, v in want.items():
+        assert tuple(inner[k].shape) == tuple(v.shape), k
+    # what the wrappers add on top of the HF module
+    extra = sorted(k for k in ours.state_dict() if not k.startswith("model.model."))
+    assert extra == ["model.control_embeds.weight", "time_head.0.bias", "time_head.0.weight",
+                     "value_head.0.bias", "value_head.0.weight"]
+
+
+def test_logits_match_hf_gpt2_on_the_same_weights():
+    tok, ours, hf = _models()
+    sd = {k: v for k, v in hf.state_dict().items() if not k.endswith(".attn.bias") and not k.endswith(".attn.masked_bias")}
+    inner = ours.model.model
+    missing, unexpected = inner.load_state_dict(sd, strict=False)
+    assert not unexpected and not missing, (missing, unexpected)
+    ids = torch.randint(0, 1968, (3, 40))
+    with torch.no_grad():
+        want = hf(input_ids=ids).logits
+        got = inner(input_ids=ids)
+    got = got["logits"] if isinstance(got, dict) else (got.logits if hasattr(got, "logits") else got)
+    assert torch.allclose(got, want, atol=2e-4, rtol=1e-4), (got - want).abs().max().item()
