@@ -8,7 +8,9 @@ games whose prompts are 1-300 tokens long.  Every leaf evaluation is one KV-cach
     python bench_mcts.py                       # batched C++ search + KV-cached sm_100a evaluator
     python bench_mcts.py --impl sequential     # the reference algorithm: one tree at a time, every
                                                # leaf re-encodes its whole game at batch 1
-Prints one JSON line.
+    torchrun --nproc-per-node 8 bench_mcts.py --gpus 8   # one independent 256-tree search per GPU
+Prints one JSON line (rank 0; with several GPUs the value is the sum of positions over the ranks
+divided by the slowest rank's time, and the p50 per-move latency is the median over ranks).
 """
 from __future__ import annotations
 
@@ -54,13 +56,22 @@ def main():
     ap.add_argument("--impl", default="batched", choices=["batched", "sequential"])
     ap.add_argument("--small", action="store_true", help="tiny model (smoke test)")
     ap.add_argument("--seq-positions", type=int, default=4, help="root positions for --impl sequential")
+    ap.add_argument("--gpus", type=int, default=1)
     args = ap.parse_args()
+    rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
+    assert world == args.gpus, "launch with torchrun --nproc-per-node <gpus>"
+    if torch.cuda.is_available():
+        torch.cuda.set_device(local)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl" if torch.cuda.is_available() else "gloo")
     torch.manual_seed(0)
     tok = UCITokenizer(max_length=512, vocab_size_multiple_of=128)
     shape = dict(n_layer=2, n_embd=256, n_head=4) if args.small else dict(n_layer=24, n_embd=1024, n_head=16)
     model = initialize_model(tok, "gpt2-medium", use_control_token=True, use_regression_head=True,
                              n_positions=1024, **shape)
-    rng = np.random.default_rng(0)
+    rng = np.random.default_rng(rank)          # different root positions on every rank
     out = {"metric": "MCTS leaf-eval positions/sec", "unit": "positions/s", "impl": args.impl,
            "dtype": "bf16", "data": "synthetic random legal games, prompts of 1-300 tokens",
            "config": {"model": "tiny" if args.small else "gpt2-medium-like 24L d1024 16H", "trees": args.trees,
@@ -113,7 +124,23 @@ def main():
                    p50_move_latency_s=dt / len(games),
                    note="sequential PUCT, batch-1 full re-encode per leaf, fp32 PyTorch model "
                         "(the reference's decode path, src/evaluation/decode.py:336-467)")
-    print(json.dumps(out), flush=True)
+    out["n_gpus"] = world
+    if world > 1:
+        import torch.distributed as dist
+
+        dev = "cuda" if torch.cuda.is_available() else "cpu"
+        stats = torch.tensor([float(out["positions"]), float(out["seconds"])], dtype=torch.float64, device=dev)
+        allv = [torch.zeros_like(stats) for _ in range(world)]
+        dist.all_gather(allv, stats)
+        positions = sum(float(v[0]) for v in allv)
+        slowest = max(float(v[1]) for v in allv)
+        out.update(value=positions / slowest, positions=int(positions), seconds=slowest,
+                   per_rank_seconds=[round(float(v[1]), 4) for v in allv],
+                   latency_per_move_batch_s=sorted(float(v[1]) for v in allv)[world // 2])
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(out), flush=True)
 
 
 if __name__ == "__main__":

@@ -15,7 +15,8 @@ def _ref(a, b, a_mn, b_mn):
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 320), (384, 768, 1024), (200, 264, 136),
                                    (1000, 128, 512), (64, 64, 64),
                                    # large enough for the CTA-pair kernel, with ragged edges
-                                   (1000, 264, 136), (640, 768, 320), (2304, 1024, 192)])
+                                   (1000, 264, 136), (640, 768, 320), (2304, 1024, 192),
+                                   (512, 256, 64), (768, 512, 40)])      # one K block; ragged K
 def test_gemm_layouts(a_mn, b_mn, M, N, K):
     from allie_b200.ops import _lib
     from allie_b200.ops.gemm import gemm
