@@ -222,6 +222,16 @@ def run_ours(args) -> dict:
     wall_ms = (time.perf_counter() - t0) * 1e3
     e2e_ms = max_over_ranks(max(g0.elapsed_time(g1), wall_ms), world)
 
+    # phase breakdown (outside both timed regions): device time of data / forward+backward /
+    # gradient synchronisation + optimizer per step, from the trainer's CUDA-event phase timers
+    trainer.tracer.enabled = True
+    trainer.tracer.summary()
+    for i in range(2):
+        step_device(i)
+    phases = {k: round(v["ms"] / 2, 3) for k, v in trainer.tracer.summary().items()}
+    phases = {k: max_over_ranks(v, world) for k, v in phases.items()}
+    trainer.tracer.enabled = False
+
     tokens_per_step = GLOBAL_BATCH * SEQ_LEN
     value = tokens_per_step * args.steps / (ms / 1e3)
     e2e_value = tokens_per_step * args.steps / (e2e_ms / 1e3)
@@ -246,6 +256,7 @@ def run_ours(args) -> dict:
         "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
                 "h2d_bytes_per_step": ga * MICRO_BATCH * SEQ_LEN * 4, "d2h_bytes_per_step": 4},
         "gpu_launches": launches,
+        "phase_ms_per_step": phases,
         "final_loss": final_loss,
         "model_tflops_per_gpu": value * flops_per_token / world / 1e12,
     }
