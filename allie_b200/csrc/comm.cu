@@ -45,25 +45,38 @@ nvl_reduce_scatter_kernel(const RsArgs a) {
   float ss = 0.f;
   float* mine = static_cast<float*>(a.grads.ptr[a.rank]) + a.shard_off;
   const long long n4 = a.shard_n >> 2;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4;
-       i += (long long)gridDim.x * blockDim.x) {
-    float4 s;
-    if (a.mc_grads) {
-      s = multimem_ld_reduce_f4(a.mc_grads + a.shard_off + i * 4);
-    } else {
-      s = make_float4(0.f, 0.f, 0.f, 0.f);
+  // four independent 16-byte reductions in flight per thread: one NVLink round trip is several
+  // microseconds, so a single outstanding load per thread leaves the links half idle
+  constexpr int RS_UNROLL = 4;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; i0 < n4; i0 += stride * RS_UNROLL) {
+    float4 s[RS_UNROLL];
 #pragma unroll
-      for (int p = 0; p < MAX_RANKS; ++p)
-        if (p < a.world) {
-          // start with the next rank so the peers' links are loaded evenly
-          const int src = (a.rank + 1 + p) % a.world;
-          const float4 v = ld_relaxed_sys_f4(static_cast<const float*>(a.grads.ptr[src]) +
-                                             a.shard_off + i * 4);
-          s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
-        }
+    for (int u = 0; u < RS_UNROLL; ++u) {
+      const long long i = i0 + u * stride;
+      s[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (i >= n4) continue;
+      if (a.mc_grads) {
+        s[u] = multimem_ld_reduce_f4(a.mc_grads + a.shard_off + i * 4);
+      } else {
+#pragma unroll
+        for (int p = 0; p < MAX_RANKS; ++p)
+          if (p < a.world) {
+            // start with the next rank so the peers' links are loaded evenly
+            const int src = (a.rank + 1 + p) % a.world;
+            const float4 v = ld_relaxed_sys_f4(static_cast<const float*>(a.grads.ptr[src]) +
+                                               a.shard_off + i * 4);
+            s[u].x += v.x; s[u].y += v.y; s[u].z += v.z; s[u].w += v.w;
+          }
+      }
     }
-    reinterpret_cast<float4*>(mine)[i] = s;
-    ss += s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w;
+#pragma unroll
+    for (int u = 0; u < RS_UNROLL; ++u) {
+      const long long i = i0 + u * stride;
+      if (i >= n4) continue;
+      reinterpret_cast<float4*>(mine)[i] = s[u];
+      ss += s[u].x * s[u].x + s[u].y * s[u].y + s[u].z * s[u].z + s[u].w * s[u].w;
+    }
   }
 #pragma unroll
   for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
