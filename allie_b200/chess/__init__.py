@@ -38,6 +38,9 @@ def _h():
         lib.chess_perft.restype = c_ulonglong
         lib.chess_set_fen.argtypes = [c_void_p, c_char_p]
         lib.chess_vocab_uci.argtypes = [c_int, ctypes.c_char_p]
+        for fn in ("chess_castling_mask", "chess_ep_square", "chess_fullmove"):
+            getattr(lib, fn).argtypes = [c_void_p]
+        lib.chess_is_repetition.argtypes = [c_void_p, c_int]
         _configured = True
     return lib
 
@@ -105,6 +108,136 @@ class Board:
 
     def perft(self, depth: int) -> int:
         return int(_h().chess_perft(self._h, depth))
+
+    # ---- position text and move classification (used by annotation, PGN prompts and the UCI client)
+    @property
+    def fullmove_number(self) -> int:
+        return int(_h().chess_fullmove(self._h))
+
+    @property
+    def halfmove_clock(self) -> int:
+        return int(_h().chess_halfmove_clock(self._h))
+
+    @property
+    def ep_square(self) -> int | None:
+        sq = int(_h().chess_ep_square(self._h))
+        return None if sq < 0 else sq
+
+    def ply(self) -> int:
+        return int(_h().chess_ply(self._h))
+
+    def is_capture(self, uci: str) -> bool:
+        return self.piece_at(_sq(uci[2:4])) != 0 or self.is_en_passant(uci)
+
+    def is_en_passant(self, uci: str) -> bool:
+        """A pawn that changes file onto an empty square."""
+        return (abs(self.piece_at(_sq(uci[:2]))) == 1 and uci[0] != uci[2]
+                and self.piece_at(_sq(uci[2:4])) == 0)
+
+    def is_castling(self, uci: str) -> bool:
+        """A king that moves two files."""
+        return abs(self.piece_at(_sq(uci[:2]))) == 6 and abs(ord(uci[0]) - ord(uci[2])) == 2
+
+    def is_repetition(self, count: int = 3) -> bool:
+        return bool(_h().chess_is_repetition(self._h, count))
+
+    def can_claim_threefold_repetition(self) -> bool:
+        """The position has occurred three times, or some legal move reaches such a position
+        (the two cases in which a player may claim the draw)."""
+        if self.is_repetition(3):
+            return True
+        for mv in self.legal_moves_uci():
+            nxt = self.copy()
+            nxt.push_uci(mv)
+            if nxt.is_repetition(3):
+                return True
+        return False
+
+    def fen(self) -> str:
+        """Forsyth-Edwards notation; the en-passant field is set only when a capture onto it is legal."""
+        rows = []
+        for r in range(7, -1, -1):
+            row, gap = "", 0
+            for f in range(8):
+                p = self.piece_at(r * 8 + f)
+                if p == 0:
+                    gap += 1
+                    continue
+                if gap:
+                    row, gap = row + str(gap), 0
+                ch = " pnbrqk"[abs(p)]
+                row += ch.upper() if p > 0 else ch
+            rows.append(row + (str(gap) if gap else ""))
+        m = int(_h().chess_castling_mask(self._h))
+        rights = "".join(c for i, c in enumerate("KQkq") if m >> i & 1) or "-"
+        ep = "-"
+        if self.ep_square is not None:
+            name = "abcdefgh"[self.ep_square % 8] + str(self.ep_square // 8 + 1)
+            if any(mv[2:4] == name and self.is_en_passant(mv) for mv in self.legal_moves_uci()):
+                ep = name
+        return (f"{'/'.join(rows)} {'w' if self.turn else 'b'} {rights} {ep} "
+                f"{self.halfmove_clock} {self.fullmove_number}")
+
+    def san(self, uci: str) -> str:
+        """Standard algebraic notation of a legal move, with minimal disambiguation and the
+        check / mate suffix."""
+        legal = self.legal_moves_uci()
+        if uci not in legal:
+            raise ValueError(f"illegal uci: {uci!r}")
+        src = _sq(uci[:2])
+        piece = abs(self.piece_at(src))
+        if self.is_castling(uci):
+            text = "O-O" if uci[2] == "g" else "O-O-O"
+        else:
+            capture = self.is_capture(uci)
+            if piece == 1:
+                text = (uci[0] + "x" if capture else "") + uci[2:4]
+                if len(uci) == 5:
+                    text += "=" + uci[4].upper()
+            else:
+                others = [mv for mv in legal if mv != uci and mv[2:4] == uci[2:4]
+                          and abs(self.piece_at(_sq(mv[:2]))) == piece]
+                dis = ""
+                if others:
+                    if all(mv[0] != uci[0] for mv in others):
+                        dis = uci[0]
+                    elif all(mv[1] != uci[1] for mv in others):
+                        dis = uci[1]
+                    else:
+                        dis = uci[:2]
+                text = " PNBRQK"[piece] + dis + ("x" if capture else "") + uci[2:4]
+        nxt = self.copy()
+        nxt.push_uci(uci)
+        if nxt.is_check():
+            text += "#" if not nxt.legal_move_ids() else "+"
+        return text
+
+    def parse_san(self, san: str) -> str:
+        """The legal move (UCI text) that a SAN token denotes; ValueError if none or several do."""
+        want = san.rstrip("+#!?").replace("0-0-0", "O-O-O").replace("0-0", "O-O")
+        hits = [mv for mv in self.legal_moves_uci() if self.san(mv).rstrip("+#") == want]
+        if len(hits) != 1:
+            raise ValueError(f"cannot resolve SAN {san!r} (candidates {hits})")
+        return hits[0]
+
+    def push_san(self, san: str) -> str:
+        uci = self.parse_san(san)
+        self.push_uci(uci)
+        return uci
+
+    def movetext(self) -> str:
+        """PGN movetext of the game so far: ``1. e4 e5 2. Nf3 ...`` (replayed from the start)."""
+        b, parts = Board(), []
+        for i, mv in enumerate(self.move_stack):
+            if i % 2 == 0:
+                parts.append(f"{i // 2 + 1}.")
+            parts.append(b.san(mv))
+            b.push_uci(mv)
+        return " ".join(parts)
+
+
+def _sq(name: str) -> int:
+    return (int(name[1]) - 1) * 8 + (ord(name[0]) - 97)
 
 
 def vocab_uci(token_id: int) -> str:

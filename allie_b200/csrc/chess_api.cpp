@@ -122,3 +122,17 @@ extern "C" int chess_set_fen(void* h, const char* fen) {
   }
   return 1;
 }
+
+// Position details a FEN string and the move-type flags need.
+extern "C" {
+// bit 0 = K, 1 = Q, 2 = k, 3 = q
+int chess_castling_mask(void* h) {
+  const Board* b = static_cast<Board*>(h);
+  return ((b->castling & chess::bit(7)) ? 1 : 0) | ((b->castling & chess::bit(0)) ? 2 : 0) |
+         ((b->castling & chess::bit(63)) ? 4 : 0) | ((b->castling & chess::bit(56)) ? 8 : 0);
+}
+int chess_ep_square(void* h) { return static_cast<Board*>(h)->ep_square; }
+int chess_fullmove(void* h) { return static_cast<Board*>(h)->fullmove; }
+// 1 if the current position has occurred at least `count` times since the last irreversible move
+int chess_is_repetition(void* h, int count) { return static_cast<Board*>(h)->is_repetition(count) ? 1 : 0; }
+}
