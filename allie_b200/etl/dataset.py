@@ -1,18 +1,25 @@
 """JSONL -> training stream and friends (reference ``src/data/sample-lichess.py``,
-``create-np-dataset.py``, ``concat-np-memmaps.py``, ``compute-elo-stats.py``, ``random-games.py``).
+``create-np-dataset.py``, ``concat-np-memmaps.py``, ``compute-elo-stats.py``, ``random-games.py``,
+``compute-position-values.py``, ``download-puzzles-dataset.py``).
 
     python -m allie_b200.etl.dataset sample  in.jsonl out_prefix      # ELO-balanced, val/test split
     python -m allie_b200.etl.dataset tokenize train.jsonl train.bin   # flat uint32 memmap
     python -m allie_b200.etl.dataset concat a.bin b.bin out.bin
     python -m allie_b200.etl.dataset elo-stats in.jsonl
     python -m allie_b200.etl.dataset random-games out.jsonl --n 1000
+    python -m allie_b200.etl.dataset position-values games.jsonl      # Stockfish value per ply, in place
+    python -m allie_b200.etl.dataset puzzles lichess_db_puzzle.csv out_dir [--download]
 """
 from __future__ import annotations
 
 import argparse
 import collections
+import csv
 import json
+import os
 import random
+import urllib.request
+from urllib.parse import urlparse
 
 import numpy as np
 
@@ -100,6 +107,64 @@ def random_games(dst: str, n: int = 1000, max_plies: int = 120, seed: int = 0) -
                                 "moves-seconds": [rng.randint(0, 20) for _ in g.moves]}) + "\n")
 
 
+def position_values(src: str, dst: str | None = None, nodes: int = 10_000_000, evaluator=None) -> int:
+    """Adds ``moves-eval`` (centipawns after each move, from the mover's side) and ``position-values``
+    (the same squashed to [-1, 1] by ``2 / (1 + exp(-0.00368208 cp)) - 1``) to every row.
+    ``evaluator(moves, nodes) -> white-relative centipawns`` defaults to the cached Stockfish call;
+    the file is rewritten in place unless ``dst`` is given."""
+    from ..evaluation import utils as eval_utils
+
+    evaluator = evaluator or eval_utils.stockfish_eval
+    rows = []
+    with open(src) as f:
+        for line in f:
+            if not line.strip():
+                continue
+            row = json.loads(line)
+            moves, evals = row["moves-uci"].split(), []
+            for i in range(len(moves)):
+                white_cp = evaluator(moves[: i + 1], nodes)
+                evals.append(white_cp if i % 2 == 0 else -white_cp)     # ply i was white's iff i is even
+            row["moves-eval"] = evals
+            row["position-values"] = [eval_utils.cp_to_value(e) for e in evals]
+            rows.append(row)
+    tmp = (dst or src) + ".tmp"
+    with open(tmp, "w") as f:
+        for row in rows:
+            f.write(json.dumps(row) + "\n")
+    os.replace(tmp, dst or src)
+    return len(rows)
+
+
+def puzzles(csv_path: str, out_dir: str, per_theme: int = 100, seed: int = 0, download: bool = False,
+            fetch=None) -> dict[str, list[str]]:
+    """Samples ``per_theme`` puzzles for each of the themes mateIn1 .. mateIn5 from the Lichess puzzle
+    CSV, writes ``mateIn<k>.csv`` and returns the source game ids per theme.  With ``download`` the
+    annotated PGN of every source game is fetched into ``out_dir/pgn`` (needs network access;
+    ``fetch(url) -> bytes`` can replace the HTTP call)."""
+    rng = random.Random(seed)
+    with open(csv_path, newline="") as f:
+        reader = csv.DictReader(f)
+        fields, rows = reader.fieldnames, list(reader)
+    os.makedirs(os.path.join(out_dir, "pgn"), exist_ok=True)
+    fetch = fetch or (lambda url: urllib.request.urlopen(url, timeout=60).read())
+    ids: dict[str, list[str]] = {}
+    for k in range(1, 6):
+        theme = f"mateIn{k}"
+        pool = [r for r in rows if theme in r["Themes"].split()]
+        subset = rng.sample(pool, min(per_theme, len(pool)))
+        with open(os.path.join(out_dir, f"{theme}.csv"), "w", newline="") as f:
+            w = csv.DictWriter(f, fieldnames=fields)
+            w.writeheader()
+            w.writerows(subset)
+        ids[theme] = [urlparse(r["GameUrl"]).path.split("/")[1] for r in subset]
+        if download:
+            for gid in ids[theme]:
+                with open(os.path.join(out_dir, "pgn", f"{gid}.pgn"), "wb") as f:
+                    f.write(fetch(f"https://lichess.org/game/export/{gid}?literate=1"))
+    return ids
+
+
 def main(argv=None) -> None:
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -108,7 +173,16 @@ def main(argv=None) -> None:
     s = sub.add_parser("concat"); s.add_argument("parts", nargs="+"); s.add_argument("dst")
     s = sub.add_parser("elo-stats"); s.add_argument("src")
     s = sub.add_parser("random-games"); s.add_argument("dst"); s.add_argument("--n", type=int, default=1000)
+    s = sub.add_parser("position-values"); s.add_argument("src"); s.add_argument("--nodes", type=int, default=10_000_000)
+    s = sub.add_parser("puzzles"); s.add_argument("csv"); s.add_argument("out_dir"); s.add_argument("--n", type=int, default=100)
+    s.add_argument("--download", action="store_true")
     a = ap.parse_args(argv)
+    if a.cmd == "position-values":
+        print(position_values(a.src, nodes=a.nodes), "games")
+        return
+    if a.cmd == "puzzles":
+        print(json.dumps({k: len(v) for k, v in puzzles(a.csv, a.out_dir, a.n, download=a.download).items()}))
+        return
     if a.cmd == "sample":
         sample(a.src, a.prefix, a.target)
     elif a.cmd == "tokenize":

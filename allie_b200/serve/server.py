@@ -21,7 +21,7 @@ from typing import Any
 import torch
 
 from ..data import Game, UCITokenizer
-from ..search import DECODE_STRATEGIES, DecodeResult, DecodeStrategy
+from ..search import DECODE_STRATEGIES, DecodeResult, DecodeStrategy, decode_batch
 
 logger = logging.getLogger(__name__)
 
@@ -95,8 +95,15 @@ def algorithm_test(algorithm: DecodeStrategy, every: int = 2, max_plies: int | N
     return dt
 
 
-def build_algorithm(alias: str, model, tokenizer: UCITokenizer, device: str | None = None) -> DecodeStrategy:
+def build_algorithm(alias: str, model, tokenizer: UCITokenizer, device: str | None = None,
+                    batched: bool = False, max_batch: int = 64) -> DecodeStrategy:
+    """The system's strategy.  With ``batched`` its many-games-per-call form is built when one is
+    registered (``<algorithm>-batched``), with one search tree per connection of a full batch."""
     system = SYSTEMS[alias]
+    if batched and f"{system.algorithm}-batched" in DECODE_STRATEGIES:
+        extra = {} if system.algorithm == "policy" else {"n_trees": max_batch}
+        return DECODE_STRATEGIES[f"{system.algorithm}-batched"](model, tokenizer, device=device,
+                                                               **system.algorithm_config, **extra)
     if system.algorithm not in DECODE_STRATEGIES:
         raise RuntimeError(f"system {alias!r} needs the external engine {system.algorithm!r}, "
                            "which is not available in this installation")
@@ -109,9 +116,9 @@ def _answer(conn: socket.socket, res: DecodeResult) -> None:
 
 def serve(alias: str, model, tokenizer: UCITokenizer, device: str | None = None, host: str = "localhost",
           port: int | None = None, self_test: bool = True, max_requests: int | None = None,
-          max_batch: int = 64) -> None:
+          max_batch: int = 64, batched: bool = True, client_timeout: float = 10.0) -> None:
     system = SYSTEMS[alias]
-    algorithm = build_algorithm(alias, model, tokenizer, device)
+    algorithm = build_algorithm(alias, model, tokenizer, device, batched=batched, max_batch=max_batch)
     if self_test:
         algorithm_test(algorithm, max_plies=12)
     srv = socket.socket(socket.AF_INET, socket.SOCK_STREAM)
@@ -126,15 +133,27 @@ def serve(alias: str, model, tokenizer: UCITokenizer, device: str | None = None,
             # everything already waiting in the backlog joins this batch
             while len(conns) < max_batch and select.select([srv], [], [], 0)[0]:
                 conns.append(srv.accept()[0])
+            ready: list[tuple[socket.socket, Game]] = []
             for conn in conns:
                 try:
+                    conn.settimeout(client_timeout)
                     game = assign_elo(Game(**recv_dict(conn)), system)
-                    _answer(conn, algorithm.decode_full(game))
+                    game.legal_moves                      # replays the moves: an illegal game fails here
+                    ready.append((conn, game))
                 except (ConnectionError, OSError, ValueError, TypeError, KeyError) as e:
                     logger.warning(f"request failed: {type(e).__name__}: {e}")
-                finally:
                     conn.close()
-                    served += 1
+            try:
+                results = decode_batch(algorithm, [g for _, g in ready]) if ready else []
+                for (conn, _), res in zip(ready, results):
+                    try:
+                        _answer(conn, res)
+                    except (ConnectionError, OSError) as e:
+                        logger.warning(f"reply failed: {type(e).__name__}: {e}")
+            finally:
+                for conn, _ in ready:
+                    conn.close()
+                served += len(conns)
     except KeyboardInterrupt:
         logger.info("interrupted")
     finally:
@@ -143,7 +162,8 @@ def serve(alias: str, model, tokenizer: UCITokenizer, device: str | None = None,
 
 
 def main(argv: list[str] | None = None) -> None:
-    """``python -m allie_b200.serve.server <alias> [config.yaml]`` - loads ``{output_dir}/best.pt``."""
+    """``python -m allie_b200.serve.server <alias> [config.yaml] [--sequential]`` - loads
+    ``{output_dir}/best.pt``; ``--sequential`` answers one request at a time like the reference."""
     import sys
     from os.path import join
 
@@ -151,7 +171,10 @@ def main(argv: list[str] | None = None) -> None:
     from ..models import initialize_model
     from ..utils.logging import setup_logging
 
-    argv = sys.argv[1:] if argv is None else argv
+    argv = list(sys.argv[1:] if argv is None else argv)
+    batched = "--sequential" not in argv
+    if not batched:
+        argv.remove("--sequential")
     alias = argv[0]
     cfg = load_config(argv[1] if len(argv) > 1 else "pretrain_config/medium.yaml")
     setup_logging()
@@ -160,7 +183,7 @@ def main(argv: list[str] | None = None) -> None:
     ckpt = torch.load(join(cfg.trainer_config.output_dir, "best.pt"), map_location="cpu", weights_only=False)
     model.load_state_dict(ckpt["model"])
     model.eval()
-    serve(alias, model, tokenizer)
+    serve(alias, model, tokenizer, batched=batched)
 
 
 if __name__ == "__main__":

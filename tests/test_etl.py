@@ -43,3 +43,28 @@ def test_parse_game_and_stream(tmp_path):
     assert n == np.memmap(tmp_path / "a.bin", dtype=np.uint32, mode="r").size
     assert concat([str(tmp_path / "a.bin"), str(tmp_path / "a.bin")], str(tmp_path / "c.bin")) == 2 * n
     assert elo_stats(str(tmp_path / "g.jsonl"))["n"] == 40
+
+
+def test_position_values_and_puzzles(tmp_path):
+    from allie_b200.etl.dataset import position_values, puzzles
+
+    src = tmp_path / "g.jsonl"
+    src.write_text(json.dumps({"moves-uci": "e2e4 e7e5 g1f3"}) + "\n")
+    n = position_values(str(src), evaluator=lambda moves, nodes: 100 * len(moves))   # white-relative cp
+    row = json.loads(src.read_text())
+    assert n == 1 and row["moves-eval"] == [100, -200, 300]
+    assert abs(row["position-values"][0] - (2 / (1 + np.exp(-0.368208)) - 1)) < 1e-9
+    assert row["position-values"][1] < 0 < row["position-values"][2] < 1
+
+    csv_path = tmp_path / "p.csv"
+    lines = ["PuzzleId,FEN,Moves,Rating,Themes,GameUrl"]
+    for i in range(30):
+        lines.append(f"p{i},8/8/8/8/8/8/8/K6k w - - 0 1,a1a2,1500,short mateIn{i % 5 + 1},https://lichess.org/game{i}/black#10")
+    csv_path.write_text("\n".join(lines) + "\n")
+    fetched = []
+    ids = puzzles(str(csv_path), str(tmp_path / "out"), per_theme=4, download=True,
+                  fetch=lambda url: fetched.append(url) or b"[Event \"x\"]\n")
+    assert sorted(ids) == [f"mateIn{k}" for k in range(1, 6)] and all(len(v) == 4 for v in ids.values())
+    assert len(fetched) == 20 and fetched[0].startswith("https://lichess.org/game/export/game")
+    assert len((tmp_path / "out" / "mateIn3.csv").read_text().splitlines()) == 5
+    assert len(list((tmp_path / "out" / "pgn").iterdir())) == 20

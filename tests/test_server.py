@@ -53,3 +53,48 @@ def test_round_trip_and_broken_client():
         assert isinstance(ans["think_time"], float)
     th.join(timeout=10)
     assert not th.is_alive()
+
+
+def test_waiting_connections_share_one_batched_search():
+    """Several clients connect before the server looks at any of them; an MCTS system answers them
+    from one batched search, and the stress-test client reports success against a policy system."""
+    from allie_b200.serve import stress_test
+
+    torch.manual_seed(0)
+    tok = UCITokenizer(max_length=64, vocab_size_multiple_of=128)
+    model = initialize_model(tok, "gpt2", use_control_token=True, use_regression_head=True, n_layer=1,
+                             n_embd=32, n_head=1, n_positions=64).eval()
+    port = _free_port()
+    th = threading.Thread(target=serve, kwargs=dict(alias="humanlike-mcts-rb", model=model, tokenizer=tok,
+                                                    device="cpu", port=port, self_test=False, max_requests=4,
+                                                    max_batch=4), daemon=True)
+    th.start()
+    games = [Game("180+0", 1500, 1600, None, False, mv, [1] * len(mv))
+             for mv in (["e2e4"], ["d2d4", "d7d5"], [], ["e2e4", "e7e5", "g1f3"])]
+    conns = []
+    for g in games:
+        for _ in range(50):
+            try:
+                c = socket.create_connection(("localhost", port), timeout=30)
+                break
+            except OSError:
+                time.sleep(0.1)
+        send_dict(c, g.to_dict())
+        conns.append(c)
+    for c, g in zip(conns, games):
+        ans = recv_dict(c)
+        c.close()
+        assert ans["move"] in g.legal_moves
+    th.join(timeout=30)
+    assert not th.is_alive()
+
+    port = _free_port()
+    th = threading.Thread(target=serve, kwargs=dict(alias="humanlike", model=model, tokenizer=tok, device="cpu",
+                                                    port=port, self_test=False, max_requests=7), daemon=True)
+    th.start()
+    time.sleep(0.5)
+    assert stress_test.query(("localhost", port)) is not None
+    res = stress_test.run(port, runs=6, clients=2)
+    assert res["success"] and res["answered"] == 6 and res["latency_p50_s"] > 0
+    th.join(timeout=30)
+    assert not th.is_alive()
