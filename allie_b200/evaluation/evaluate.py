@@ -38,29 +38,51 @@ def read_jsonl(path: str, n_rows: int | None = None) -> list[dict]:
     return rows
 
 
-def evaluate_quick(strategy: DecodeStrategy, rows: list[dict]) -> dict:
-    n = match = legal_top = resign_pred = resign_true = 0
-    legal_mass, time_err, value_err = [], [], []
+def iter_scores(strategy: DecodeStrategy, rows: list[dict], batch_size: int = 256):
+    """Yields ``(row, ply, game, ScoreResult)`` for every prefix of every game.  Strategies with a
+    ``score_batch`` method get ``batch_size`` positions per call (one network pass or one batched
+    tree search); the others are called position by position like the reference."""
+    pending: list[tuple[dict, int, object]] = []
+
+    def flush():
+        if not pending:
+            return
+        games = [g for _, _, g in pending]
+        if hasattr(strategy, "score_batch"):
+            scores = strategy.score_batch(games)
+        else:
+            scores = [strategy.score_full(g, g.legal_moves) for g in games]
+        for (row, i, g), s in zip(pending, scores):
+            yield row, i, g, s
+        pending.clear()
+
     for row in rows:
+        for i in range(len(row["moves-uci"].split())):
+            pending.append((row, i, json_to_partial_game(row, i)))
+            if len(pending) >= batch_size:
+                yield from flush()
+    yield from flush()
+
+
+def evaluate_quick(strategy: DecodeStrategy, rows: list[dict], batch_size: int = 256) -> dict:
+    n = match = legal_top = resign_pred = 0
+    legal_mass, time_err, value_err = [], [], []
+    for row, i, g, s in iter_scores(strategy, rows, batch_size):
         moves = row["moves-uci"].split()
         outcome = {"1-0": 1.0, "0-1": -1.0}.get(row.get("result"), 0.0)
-        for i in range(len(moves)):
-            g = json_to_partial_game(row, i)
-            legal = g.legal_moves
-            s = strategy.score_full(g, legal)
-            probs = s.legal_move_probabilities
-            choice = int(probs.multinomial(1)[0]) if strategy.sample is True else int(probs.argmax())
-            n += 1
-            match += int(legal[choice] == moves[i])
-            if s.top_move_legal is not None:
-                legal_top += int(s.top_move_legal)
-                legal_mass.append(s.sampled_move_legal)
-            resign_pred += int(bool(s.resigned))
-            if s.think_time is not None and g.next_move_seconds is not None:
-                time_err.append(abs(s.think_time - g.next_move_seconds))
-            if s.white_advantage is not None:
-                value_err.append((s.white_advantage - outcome) ** 2)
-        resign_true += int(row.get("termination") == "Normal")
+        legal = g.legal_moves
+        probs = s.legal_move_probabilities
+        choice = int(probs.multinomial(1)[0]) if strategy.sample is True else int(probs.argmax())
+        n += 1
+        match += int(legal[choice] == moves[i])
+        if s.top_move_legal is not None:
+            legal_top += int(s.top_move_legal)
+            legal_mass.append(s.sampled_move_legal)
+        resign_pred += int(bool(s.resigned))
+        if s.think_time is not None and g.next_move_seconds is not None:
+            time_err.append(abs(s.think_time - g.next_move_seconds))
+        if s.white_advantage is not None:
+            value_err.append((s.white_advantage - outcome) ** 2)
     return {"positions": n, "move_match": match / max(n, 1), "top_move_legal": legal_top / max(n, 1),
             "legal_mass": float(np.mean(legal_mass)) if legal_mass else None,
             "resign_rate": resign_pred / max(n, 1),
@@ -68,31 +90,25 @@ def evaluate_quick(strategy: DecodeStrategy, rows: list[dict]) -> dict:
             "value_mse": float(np.mean(value_err)) if value_err else None}
 
 
-def evaluate_value(strategy: DecodeStrategy, rows: list[dict]) -> dict:
+def evaluate_value(strategy: DecodeStrategy, rows: list[dict], batch_size: int = 256) -> dict:
     from .utils import cp_to_value, stockfish_eval
 
     err = []
-    for row in rows:
-        moves = row["moves-uci"].split()
-        for i in range(len(moves)):
-            g = json_to_partial_game(row, i)
-            s = strategy.score_full(g, g.legal_moves)
-            err.append((s.white_advantage - cp_to_value(stockfish_eval(moves[:i]))) ** 2)
+    for row, i, g, s in iter_scores(strategy, rows, batch_size):
+        err.append((s.white_advantage - cp_to_value(stockfish_eval(row["moves-uci"].split()[:i]))) ** 2)
     return {"positions": len(err), "value_vs_stockfish_mse": float(np.mean(err)) if err else None}
 
 
-def evaluate(strategy: DecodeStrategy, rows: list[dict]) -> dict:
+def evaluate(strategy: DecodeStrategy, rows: list[dict], batch_size: int = 256) -> dict:
+    from ..search.batched_strategies import pick_move
     from .utils import move_quality
 
     cpl, acc = [], []
-    for row in rows:
-        moves = row["moves-uci"].split()
-        for i in range(len(moves)):
-            g = json_to_partial_game(row, i)
-            mv = strategy.decode(g)
-            c, a = move_quality(moves[:i], mv)
-            cpl.append(c)
-            acc.append(a)
+    for row, i, g, s in iter_scores(strategy, rows, batch_size):
+        mv = pick_move(strategy, g, g.legal_moves, s.legal_move_probabilities)
+        c, a = move_quality(row["moves-uci"].split()[:i], mv)
+        cpl.append(c)
+        acc.append(a)
     return {"positions": len(cpl), "centipawn_loss": float(np.mean(cpl)) if cpl else None,
             "accuracy": float(np.mean(acc)) if acc else None}
 
@@ -113,6 +129,8 @@ def main(argv: list[str] | None = None) -> dict:
     ap.add_argument("--maia_elo", type=int, default=None)
     ap.add_argument("--checkpoint", default=None, help="defaults to {output_dir}/best.pt; 'none' = random init")
     ap.add_argument("--device", default=None)
+    ap.add_argument("--batch_size", type=int, default=256,
+                    help="positions per call for the strategies that score many games at once")
     args = ap.parse_args(argv)
     random.seed(42); np.random.seed(42); torch.manual_seed(42)
     cfg = load_config(args.config)
@@ -126,11 +144,11 @@ def main(argv: list[str] | None = None) -> dict:
                                               precision="float32", **json.loads(args.decode_args))
     rows = read_jsonl(args.dataset, 5 if args.debug else args.n_rows)
     if args.quick:
-        metrics = evaluate_quick(strategy, rows)
+        metrics = evaluate_quick(strategy, rows, args.batch_size)
     elif args.value:
-        metrics = evaluate_value(strategy, rows)
+        metrics = evaluate_value(strategy, rows, args.batch_size)
     else:
-        metrics = evaluate(strategy, rows)
+        metrics = evaluate(strategy, rows, args.batch_size)
     result = {"alias": args.alias or args.decode, "config": args.config, "dataset": args.dataset,
               "decode": args.decode, "decode_args": json.loads(args.decode_args), "sample": args.sample,
               **metrics, **strategy.run_stats()}

@@ -21,6 +21,7 @@ import math
 import torch
 import torch.nn.functional as F
 
+from ..moves import NUM_CHESS_MOVES
 from ..data import TIME_MEAN, TIME_STDEV, Game, apply_time_normalization, undo_time_normalization
 from .strategies import DECODE_STRATEGIES, DecodeResult, DecodeStrategy, Policy, ScoreResult
 
@@ -51,8 +52,10 @@ class BatchedPolicy(Policy):
             pov = 1 if g.board.turn else -1
             resigned = bool(float(logits[self.tokenizer.resigned_token_id]) > float(move_logits.max())
                             and pov * raw < -0.9)
-            out.append(ScoreResult(F.softmax(move_logits / self.temperature, dim=0), think, resigned,
-                                   white_advantage=raw))
+            all_probs = F.softmax(logits[:NUM_CHESS_MOVES] / self.temperature, dim=0)
+            top_legal = self.tokenizer.tokens[int(all_probs.argmax())] in legal
+            out.append(ScoreResult(F.softmax(move_logits / self.temperature, dim=0), think, resigned, all_probs,
+                                   top_legal, float(all_probs[ids].sum()), raw))
         return out
 
     def decode_batch(self, games: list[Game]) -> list[DecodeResult]:
