@@ -144,7 +144,10 @@ def serve(alias: str, model, tokenizer: UCITokenizer, device: str | None = None,
                     logger.warning(f"request failed: {type(e).__name__}: {e}")
                     conn.close()
             try:
-                results = decode_batch(algorithm, [g for _, g in ready]) if ready else []
+                if hasattr(algorithm, "decode_batch"):
+                    results = iter(decode_batch(algorithm, [g for _, g in ready]) if ready else [])
+                else:                                     # one at a time: each answer leaves as soon as it exists
+                    results = (algorithm.decode_full(g) for _, g in ready)
                 for (conn, _), res in zip(ready, results):
                     try:
                         _answer(conn, res)
