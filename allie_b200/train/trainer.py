@@ -293,7 +293,7 @@ class Trainer:
                 loss_mean = sum(losses) / max(1, len(losses))
                 steps = max(1, self.log_interval) if self.iter_num > 0 else 1
                 logger.info(f"train - iter {self.iter_num}: loss {loss_mean:.4f}, time {dt:.2f}s")
-                logger.debug(f"throughput {tokens_per_step * steps / max(dt, 1e-9):.0f} tokens/s")
+                self._log_throughput(dt, steps, tokens_per_step)
                 if self.tracer.enabled:
                     phases = self.tracer.summary()
                     logger.info("phases - " + ", ".join(f"{k} {v['ms']:.1f} ms / {v['count']}" for k, v in phases.items()))
@@ -302,6 +302,27 @@ class Trainer:
                 break
         self._drain(pending, losses, all_=True)
         logger.info(f"training complete! total time {time.time() - t_start:.2f}s")
+
+    def _log_throughput(self, dt: float, steps: int, tokens_per_step: int) -> None:
+        """tokens/s, step time and MFU over the last logging window; with several ranks the window
+        time is the maximum over ranks (every rank reaches this line at the same iteration)."""
+        from ..models import unwrap
+        from ..utils.perf import mfu, train_flops_per_token
+
+        if self.ddp and self.ddp_world_size > 1:
+            t = torch.tensor([dt], dtype=torch.float64, device=self.device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dt = float(t[0])
+        tps = tokens_per_step * steps / max(dt, 1e-9)
+        row = {"iter": self.iter_num, "perf/tokens_per_s": tps, "perf/step_ms": 1e3 * dt / steps}
+        msg = f"throughput - {tps:,.0f} tokens/s, {1e3 * dt / steps:.1f} ms/step (max over {self.ddp_world_size} rank(s))"
+        if self.device_type == "cuda":
+            cfg = unwrap(self.model)[0].config
+            row["perf/mfu"] = mfu(tps, train_flops_per_token(cfg, self.tokenizer.max_length), self.ddp_world_size)
+            msg += f", MFU {100 * row['perf/mfu']:.1f}% of bf16 dense peak"
+        if self.master_process:
+            logger.info(msg)
+            self.metrics.log(row)
 
     @staticmethod
     def _drain(pending: deque, losses: deque, all_: bool) -> None:

@@ -57,6 +57,9 @@ def main():
             wins.append(torch.from_numpy(w))
         losses.append(float(tr.train_step(wins)))
         tr.iter_num += 1
+    if device == "cpu":
+        # the log line's window time is the maximum over ranks: rank r reports (r + 1) seconds
+        tr._log_throughput(float(rank + 1), 1, 1000)
     reload_ok = None
     if moe and device.startswith("cuda"):
         # checkpoint round trip: the file holds whole expert banks whatever the rank count, and

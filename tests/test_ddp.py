@@ -31,6 +31,8 @@ def test_cpu_gloo_two_ranks_match_single(tmp_path):
     b = torch.load(tmp_path / "params_collective_1.pt")
     assert torch.equal(a["params"], b["params"]), "ranks diverged"
     assert all(l == l for l in a["losses"])
+    log = (tmp_path / "run_collective" / "log.txt").read_text()
+    assert "throughput - 500 tokens/s, 2000.0 ms/step (max over 2 rank(s))" in log
 
 
 @pytest.mark.gpu

@@ -59,6 +59,7 @@ def test_train_checkpoint_resume_and_eval_cli(tmp_path):
     assert (run / "last.pt").exists() and (run / "best.pt").exists() and (run / "log.txt").exists()
     log = (run / "log.txt").read_text()
     assert "train - iter 0: loss" in log and "val - iter 0:" in log and "new best val loss" in log
+    assert "throughput - " in log and "tokens/s" in log
     ck = torch.load(run / "last.pt", weights_only=False)
     assert {"iter_num", "best_val_loss", "model", "optimizer"} <= set(ck)
     keys = set(ck["model"])
@@ -119,3 +120,17 @@ def test_corrupt_checkpoint_is_reported(tmp_path):
         assert "last.pt" in str(e) or isinstance(e, (RuntimeError, EOFError, ValueError, Exception))
     else:
         raise AssertionError("a truncated checkpoint must not load silently")
+
+
+def test_flops_per_token_and_mfu():
+    from allie_b200.config import resolve_model_config
+    from allie_b200.utils.perf import matmul_params_per_token, mfu, train_flops_per_token
+
+    cfg = resolve_model_config("gpt2-medium", vocab_size=2048)
+    assert matmul_params_per_token(cfg) == 24 * 12 * 1024 * 1024 + 1024 * 2048
+    f = train_flops_per_token(cfg, 512)
+    assert abs(f - (6 * matmul_params_per_token(cfg) + 24 * 6 * 512 * 1024)) < 1
+    assert abs(mfu(1e6, f, n_gpus=2, peak_flops=1e15) - 1e6 * f / 2e15) < 1e-12
+    moe = resolve_model_config("gpt2-medium", vocab_size=2048, num_experts=8, moe_ffn=2048, moe_layer_freq=3)
+    per_moe_block = 4 * 1024 * 1024 + 2 * 2 * 1024 * 2048 + 1024 * 8
+    assert matmul_params_per_token(moe) == 16 * 12 * 1024 * 1024 + 8 * per_moe_block + 1024 * 2048
