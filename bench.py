@@ -1,6 +1,6 @@
 """Headline benchmark: training throughput (tokens/s) of the GPT-2-medium-shaped Allie model.
 
-Config (fixed): 24 layers, d_model 1024, 16 heads, MLP 4096, context 512, vocab 2048, policy +
+Config (default, the headline): 24 layers, d_model 1024, 16 heads, MLP 4096, context 512, vocab 2048, policy +
 value + think-time losses, dropout 0.1 as the reference trains, bf16 tensor-core math with fp32
 residual stream / master weights, global batch 512 sequences per optimizer step (micro-batch 64 per
 GPU, gradient accumulation 8 / n_gpus: strong scaling), AdamW with global-norm clipping.
@@ -8,6 +8,7 @@ Synthetic uniform-random move tokens with two leading ELO tokens per window, ran
 
     python bench.py --gpus N --steps K --warmup W            # this framework
     python bench.py --impl reference --gpus N ...             # the unmodified reference trainer
+    python bench.py --model large ...                         # large-ablation shape: 32 layers, d_model 1280, 20 heads
 
 For N > 1 launch under ``python -m torch.distributed.run --nproc-per-node N``.  Rank 0 prints one
 JSON line.  ``value`` is timed on the device with CUDA events around exactly K optimizer steps,
@@ -30,6 +31,8 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 MODEL = dict(n_layer=24, n_embd=1024, n_head=16, n_positions=1024)
+# --model large: the large-ablation shape (about twice the medium parameter count)
+MODELS = {"medium": MODEL, "large": dict(n_layer=32, n_embd=1280, n_head=20, n_positions=1024)}
 SEQ_LEN, VOCAB_MULT, GLOBAL_BATCH, MICRO_BATCH = 512, 128, 512, 64
 BASELINE_TOKENS_PER_S = 2.17e5   # derived from the reference README: 8x RTX A6000, ~2 weeks
 
@@ -163,7 +166,7 @@ def run_ours(args) -> dict:
     tok = UCITokenizer(max_length=SEQ_LEN, vocab_size_multiple_of=VOCAB_MULT)
     torch.manual_seed(1234)
     model = initialize_model(tok, "gpt2-medium", use_control_token=True, use_regression_head=True,
-                             use_pretrained=False, **MODEL)
+                             use_pretrained=False, **MODELS[args.model])
     stream = synthetic_stream(64 * 1024 * SEQ_LEN // 8, len(tok), SEQ_LEN, seed=7 + rank)
     trainer.setup_dataloaders(tok, stream, [], [])
     trainer.setup_model(model)
@@ -236,15 +239,17 @@ def run_ours(args) -> dict:
     value = tokens_per_step * args.steps / (ms / 1e3)
     e2e_value = tokens_per_step * args.steps / (e2e_ms / 1e3)
     n_params = sum(p.numel() for p in model.parameters())
-    flops_per_token = 6 * (n_params - 2048 * 1024 - 1024 * 1024) + 6 * 2048 * 1024 + 12 * 24 * 1024 * SEQ_LEN
+    shape = MODELS[args.model]
+    L, d, V = shape["n_layer"], shape["n_embd"], len(tok)
+    flops_per_token = 6 * (n_params - V * d - shape["n_positions"] * d) + 6 * V * d + 12 * L * d * SEQ_LEN
     result = {
-        "metric": "train tokens/sec (medium config)", "value": value, "unit": "tokens/s",
+        "metric": f"train tokens/sec ({args.model} config)", "value": value, "unit": "tokens/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": value / BASELINE_TOKENS_PER_S, "dtype": "bf16", "data": "synthetic",
         "impl": "allie_b200",
-        "config": {"model": "gpt2-medium-like 24L d1024 16H mlp4096 ctx512 vocab2048 + control token "
-                            "+ value/time heads, dropout 0.1",
+        "config": {"model": f"gpt2-{args.model}-like {L}L d{d} {shape['n_head']}H mlp{4 * d} ctx512 vocab2048 "
+                            "+ control token + value/time heads, dropout 0.1",
                    "global_batch": GLOBAL_BATCH, "seq_len": SEQ_LEN, "micro_batch": MICRO_BATCH,
                    "grad_accum": ga, "parallelism": f"dp{world}",
                    "l2_policy": "inputs larger than L2: each micro-step streams >1 GB of activations "
@@ -302,8 +307,9 @@ def run_reference(args) -> dict:
                       log_interval=10**9, save_interval=0)
     tok = UCITokenizer(max_length=SEQ_LEN, vocab_size_multiple_of=VOCAB_MULT)
     torch.manual_seed(1234)
+    shape = {k: v for k, v in MODELS[args.model].items() if args.model != "medium"}   # HF config overrides
     model = initialize_model(tok, os.path.join(ROOT, "baseline", "gpt2-medium"), use_control_token=True,
-                             use_regression_head=True, use_pretrained=False)
+                             use_regression_head=True, use_pretrained=False, **shape)
     stream = synthetic_stream(64 * 1024 * SEQ_LEN // 8, len(tok), SEQ_LEN, seed=7 + rank)
     trainer.setup_dataloaders(tok, stream, [], [])
     trainer.setup_model(model)
@@ -338,11 +344,12 @@ def run_reference(args) -> dict:
     tokens_per_step = GLOBAL_BATCH * SEQ_LEN
     value = tokens_per_step * K / (ms / 1e3)
     result = {
-        "metric": "train tokens/sec (medium config)", "value": value, "unit": "tokens/s",
+        "metric": f"train tokens/sec ({args.model} config)", "value": value, "unit": "tokens/s",
         "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms / K, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": value / BASELINE_TOKENS_PER_S, "dtype": "bf16",
         "data": "synthetic", "impl": "reference",
-        "config": {"model": "gpt2-medium 24L d1024 16H ctx512 vocab2048 + control token + value/time heads",
+        "config": {"model": ("gpt2-medium 24L d1024 16H" if args.model == "medium" else "gpt2-large-like 32L d1280 20H")
+                            + " ctx512 vocab2048 + control token + value/time heads",
                    "global_batch": GLOBAL_BATCH, "seq_len": SEQ_LEN, "micro_batch": MICRO_BATCH,
                    "grad_accum": ga, "parallelism": f"dp{world}",
                    "stack": "reference Trainer.train(): autocast bf16 + torch.compile + DDP + fused AdamW",
@@ -363,6 +370,8 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="medium", choices=sorted(MODELS),
+                    help="medium = the headline config; large = the large-ablation shape (32L, d1280, 20H)")
     args = ap.parse_args()
     rank, world, _ = dist_info()
     if args.gpus > 1 and world == 1:
