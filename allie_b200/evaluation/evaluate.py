@@ -140,8 +140,13 @@ def main(argv: list[str] | None = None) -> dict:
     if ckpt_path != "none":
         model.load_state_dict(torch.load(ckpt_path, map_location="cpu", weights_only=False)["model"])
     model.eval()
+    decode_args = json.loads(args.decode_args)
+    if args.decode == "maia":
+        decode_args.setdefault("maia_elo", args.maia_elo)
+        if args.alias is None:
+            args.alias = "maia-closest" if args.maia_elo is None else f"maia-{args.maia_elo}"
     strategy = DECODE_STRATEGIES[args.decode](model, tokenizer, sample=args.sample, device=args.device,
-                                              precision="float32", **json.loads(args.decode_args))
+                                              precision="float32", **decode_args)
     rows = read_jsonl(args.dataset, 5 if args.debug else args.n_rows)
     if args.quick:
         metrics = evaluate_quick(strategy, rows, args.batch_size)

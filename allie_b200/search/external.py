@@ -18,30 +18,42 @@ from .strategies import DECODE_STRATEGIES, DecodeStrategy, ScoreResult
 
 
 class Maia(DecodeStrategy):
-    """Closest-rated Maia network (1100..1900), one node per move."""
+    """Maia networks (1100..1900) through ``lc0``, one node per move.  ``maia_elo=None`` loads every
+    network found and plays the one rated closest to the side to move; with ``opening_strategy``
+    the first ten plies are answered by that strategy instead (the server gives Maia the policy
+    system as its opening book)."""
 
     def __init__(self, model=None, tokenizer=None, sample=False, device=None, precision="float32",
-                 maia_dir: str = "maia-weights", **kwargs):
-        self.model, self.tokenizer, self.sample = model, tokenizer, sample
+                 maia_elo: int | None = None, maia_weights_dir: str = "maia-weights",
+                 opening_strategy: DecodeStrategy | None = None, engine_path: str = "lc0", **kwargs):
+        self.model, self.tokenizer, self.sample = model, tokenizer, False
+        self.opening_strategy = opening_strategy
         self.engines: dict[int, UCIEngine] = {}
-        for elo in range(1100, 2000, 100):
-            w = os.path.join(maia_dir, f"maia-{elo}.pb.gz")
-            if os.path.exists(w):
-                self.engines[elo] = UCIEngine("lc0", args=[f"--weights={w}"])
+        for elo in (range(1100, 2000, 100) if maia_elo is None else [maia_elo]):
+            for name in (f"maia-{elo}.pb", f"maia-{elo}.pb.gz"):
+                w = os.path.join(maia_weights_dir, name)
+                if os.path.exists(w):
+                    self.engines[elo] = UCIEngine(engine_path, {"Threads": 4, "WeightsFile": w})
+                    break
         if not self.engines:
-            raise EngineUnavailable("Maia needs the lc0 binary and maia-<elo>.pb.gz weights")
+            raise EngineUnavailable(f"Maia needs the lc0 binary and maia-<elo>.pb weights in {maia_weights_dir!r}")
 
     def score_full(self, game: Game, legal_moves: list[str]) -> ScoreResult:
+        if self.opening_strategy is not None and len(game.moves) < 10:
+            return self.opening_strategy.score_full(game, legal_moves)
         elo = game.white_elo if game.board.turn else game.black_elo
-        best = min(self.engines, key=lambda e: abs(e - (elo or 1500)))
+        assert elo is not None, game
+        best = min(self.engines, key=lambda e: abs(e - elo))
         _, _, mv = self.engines[best].analyse(game.moves, nodes=1)
         probs = torch.zeros(len(legal_moves))
         probs[legal_moves.index(mv)] = 1.0
-        return ScoreResult(probs, None, False)
+        return ScoreResult(probs)
 
     def cleanup(self) -> None:
         for e in self.engines.values():
             e.quit()
+        if self.opening_strategy is not None:
+            self.opening_strategy.cleanup()
 
 
 class GPT35Turbo(DecodeStrategy):

@@ -60,6 +60,8 @@ SYSTEMS: dict[str, System] = {
     "humanlike-mcts-rb": System(20608, None, "mcts", {"n_sims": 50, "sample": "rating-based"}),
 }
 
+DEFAULT_SYSTEM = "humanlike"
+
 # Deep Blue - Kasparov 1997, game 2 (the reference's start-up self test replays it)
 SELF_TEST_MOVES = ("e2e4 e7e5 g1f3 b8c6 f1b5 a7a6 b5a4 g8f6 e1g1 f8e7 f1e1 b7b5 a4b3 d7d6 c2c3 e8g8 h2h3 h7h6 "
                    "d2d4 f8e8 b1d2 e7f8 d2f1 c8d7 f1g3 c6a5 b3c2 c7c5 b2b3 a5c6 d4d5 c6e7 c1e3 e7g6 d1d2 f6h7 "
@@ -100,6 +102,11 @@ def build_algorithm(alias: str, model, tokenizer: UCITokenizer, device: str | No
     """The system's strategy.  With ``batched`` its many-games-per-call form is built when one is
     registered (``<algorithm>-batched``), with one search tree per connection of a full batch."""
     system = SYSTEMS[alias]
+    if system.algorithm == "maia":
+        # Maia plays its first ten plies from the default (policy) system, like the reference server
+        book = build_algorithm(DEFAULT_SYSTEM, model, tokenizer, device)
+        return DECODE_STRATEGIES["maia"](model, tokenizer, device=device, opening_strategy=book,
+                                         **system.algorithm_config)
     if batched and f"{system.algorithm}-batched" in DECODE_STRATEGIES:
         extra = {} if system.algorithm == "policy" else {"n_trees": max_batch}
         return DECODE_STRATEGIES[f"{system.algorithm}-batched"](model, tokenizer, device=device,
