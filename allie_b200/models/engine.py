@@ -185,6 +185,20 @@ class B200Engine:
             self._moe_layers[(l, key)] = MoELayer(self._moe_ctx[key], self.layers[l], train)
         return self._moe_layers[(l, key)]
 
+    def moe_stats(self) -> dict | None:
+        """Routing statistics of the last training forward pass of this rank (None for a dense
+        model or before the first pass): the summed load-balance loss, whether any expert buffer
+        overflowed its capacity, and per MoE layer how many (token, choice) pairs this rank's
+        tokens sent to every expert.  Reads a few small device tensors; call it at logging time."""
+        layers = {l: m for (l, key), m in self._moe_layers.items() if key[1]}
+        if not layers:
+            return None
+        ctx = next(iter(layers.values())).ctx
+        counts = {l: m.counts.tolist() for l, m in sorted(layers.items())}
+        worst = max(max(c) / max(1.0, sum(c) / len(c)) for c in counts.values())
+        return {"aux_loss": float(ctx.aux_total), "overflow": bool(int(ctx.overflow[0])),
+                "expert_tokens": counts, "max_over_mean_load": worst}
+
     # ---------------------------------------------------------------- views
     def _n(self, p: nn.Parameter) -> str:
         return self._names[id(p)]

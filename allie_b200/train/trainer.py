@@ -18,6 +18,7 @@ synchronous data parallelism the reference intends); only rank 0 validates, logs
 """
 from __future__ import annotations
 
+import json
 import logging
 import math
 import os
@@ -320,6 +321,13 @@ class Trainer:
             cfg = unwrap(self.model)[0].config
             row["perf/mfu"] = mfu(tps, train_flops_per_token(cfg, self.tokenizer.max_length), self.ddp_world_size)
             msg += f", MFU {100 * row['perf/mfu']:.1f}% of bf16 dense peak"
+        stats = self.engine.moe_stats() if self.engine is not None else None
+        if stats is not None:
+            row |= {"moe/aux_loss": stats["aux_loss"], "moe/max_over_mean_load": stats["max_over_mean_load"],
+                    "moe/overflow": int(stats["overflow"])}
+            msg += (f"; moe aux {stats['aux_loss']:.4f}, busiest expert {stats['max_over_mean_load']:.2f}x the mean"
+                    + (", capacity overflow" if stats["overflow"] else ""))
+            logger.debug("moe expert tokens " + json.dumps(stats["expert_tokens"]))
         if self.master_process:
             logger.info(msg)
             self.metrics.log(row)

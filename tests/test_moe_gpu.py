@@ -43,6 +43,10 @@ def test_moe_engine_matches_oracle():
     ctx = next(iter(eng._moe_ctx.values()))
     assert int(ctx.overflow.item()) == 0
     assert abs(float(ctx.aux_total) - float(out["aux_loss"])) < 2e-2 * max(1.0, float(out["aux_loss"]))
+    stats = eng.moe_stats()
+    assert stats is not None and not stats["overflow"] and abs(stats["aux_loss"] - float(ctx.aux_total)) < 1e-6
+    assert list(stats["expert_tokens"]) == [2] and sum(stats["expert_tokens"][2]) == B * T * 2
+    assert stats["max_over_mean_load"] >= 1.0
     refp = dict(ref.named_parameters())
     worst = {}
     for n, p in m.named_parameters():
