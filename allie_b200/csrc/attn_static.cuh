@@ -1,10 +1,10 @@
 // Attention backward for callers that must not allocate device memory.
 //
 // This entry point has no counterpart in the reference project; it exists for embedders of this
-// library that run where cudaMalloc is off limits - inside a CUDA-graph capture region, inside a
-// host process that has handed its whole memory budget to another allocator, or in a real-time
-// serving loop where an allocation (and the implicit device synchronisation it can cause) is not
-// acceptable.  The regular entry point, ab_attn_bwd, asks its caller for a scratch buffer
+// library that run where cudaMalloc is off limits - inside a host process that has handed its
+// whole device memory budget to another allocator, in a plugin whose host only lends it streams
+// and buffers, or in a real-time serving loop where an allocation (and the implicit device
+// synchronisation it can cause) is not acceptable.  The regular entry point, ab_attn_bwd, asks its caller for a scratch buffer
 // (`delta`, one float per (batch, head, position)); this variant keeps that scratch in a
 // file-scope __device__ array inside the library instead, so the caller passes only inputs and
 // outputs.

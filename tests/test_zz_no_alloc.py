@@ -2,8 +2,8 @@
 symbol, against the regular entry point.
 
 Some embedders of the kernel library cannot call cudaMalloc where they run attention backward (a
-CUDA-graph capture region, a process whose memory is owned by another allocator, a latency-critical
-serving loop).  For them the library keeps the kernel's scratch in a static device array.  This
+process whose device memory is owned by another allocator, a plugin whose host lends it only
+streams and buffers, a latency-critical serving loop).  For them the library keeps the kernel's scratch in a static device array.  This
 test checks that the variant returns what the regular entry returns, twice in a row (the scratch
 is shared between calls and must not leak state from one into the next), and that oversize
 problems are rejected instead of overrunning the array.  It is collected last on purpose.
