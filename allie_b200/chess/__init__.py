@@ -96,12 +96,31 @@ class Board:
     def is_game_over(self) -> bool:
         return _h().chess_termination(self._h) != 0
 
-    def outcome(self) -> Outcome | None:
+    def outcome(self, claim_draw: bool = False) -> Outcome | None:
+        """How the game ended, or None while it continues.  With ``claim_draw`` a position in
+        which a player may claim the fifty-move or threefold-repetition draw counts as ended."""
         t = _h().chess_termination(self._h)
         if t == 0:
+            if claim_draw and self.can_claim_fifty_moves():
+                return Outcome("fifty_moves", None)
+            if claim_draw and self.can_claim_threefold_repetition():
+                return Outcome("threefold_repetition", None)
             return None
         w = _h().chess_winner(self._h)
         return Outcome(TERMINATIONS[t], None if w < 0 else bool(w))
+
+    def can_claim_fifty_moves(self) -> bool:
+        """Fifty moves without a capture or pawn move are complete, or a legal move completes them."""
+        if self.halfmove_clock >= 100:
+            return True
+        if self.halfmove_clock >= 99:
+            for mv in self.legal_moves_uci():
+                if abs(self.piece_at(_sq(mv[:2]))) != 1 and not self.is_capture(mv):
+                    return True
+        return False
+
+    def can_claim_draw(self) -> bool:
+        return self.can_claim_fifty_moves() or self.can_claim_threefold_repetition()
 
     def piece_at(self, sq: int) -> int:
         return _h().chess_piece_at(self._h, sq)

@@ -13,6 +13,7 @@ from __future__ import annotations
 import argparse
 import json
 import logging
+import os
 import random
 from os.path import join
 
@@ -20,7 +21,7 @@ import numpy as np
 import torch
 
 from ..config import load_config
-from ..data import UCITokenizer, json_to_partial_game
+from ..data import UCITokenizer, json_to_game, json_to_partial_game
 from ..models import initialize_model
 from ..search import DECODE_STRATEGIES, DecodeStrategy
 
@@ -39,10 +40,11 @@ def read_jsonl(path: str, n_rows: int | None = None) -> list[dict]:
 
 
 def iter_scores(strategy: DecodeStrategy, rows: list[dict], batch_size: int = 256):
-    """Yields ``(row, ply, game, ScoreResult)`` for every prefix of every game.  Strategies with a
-    ``score_batch`` method get ``batch_size`` positions per call (one network pass or one batched
-    tree search); the others are called position by position like the reference."""
-    pending: list[tuple[dict, int, object]] = []
+    """Yields ``(row index, ply, game, ScoreResult)`` for every prefix of every game, in order.
+    Strategies with a ``score_batch`` method get ``batch_size`` positions per call (one network
+    pass or one batched tree search); the others are called position by position like the
+    reference."""
+    pending: list[tuple[int, int, object]] = []
 
     def flush():
         if not pending:
@@ -52,70 +54,122 @@ def iter_scores(strategy: DecodeStrategy, rows: list[dict], batch_size: int = 25
             scores = strategy.score_batch(games)
         else:
             scores = [strategy.score_full(g, g.legal_moves) for g in games]
-        for (row, i, g), s in zip(pending, scores):
-            yield row, i, g, s
+        for (r, i, g), s in zip(pending, scores):
+            yield r, i, g, s
         pending.clear()
 
-    for row in rows:
+    for r, row in enumerate(rows):
         for i in range(len(row["moves-uci"].split())):
-            pending.append((row, i, json_to_partial_game(row, i)))
+            pending.append((r, i, json_to_partial_game(row, i)))
             if len(pending) >= batch_size:
                 yield from flush()
     yield from flush()
 
 
+def _choice(strategy: DecodeStrategy, probs: torch.Tensor) -> int:
+    return int(probs.multinomial(1)[0]) if strategy.sample else int(probs.argmax())
+
+
+def _mean(xs) -> float | None:
+    xs = list(xs)
+    return float(np.mean(xs)) if xs else None
+
+
 def evaluate_quick(strategy: DecodeStrategy, rows: list[dict], batch_size: int = 256) -> dict:
-    n = match = legal_top = resign_pred = 0
-    legal_mass, time_err, value_err = [], [], []
-    for row, i, g, s in iter_scores(strategy, rows, batch_size):
-        moves = row["moves-uci"].split()
-        outcome = {"1-0": 1.0, "0-1": -1.0}.get(row.get("result"), 0.0)
+    """Move match, legality, resignation, think time and value for every position; no engine.
+    ``games`` holds one record per input row with the reference's per-ply lists
+    (``src/evaluation/evaluate.py:63-126``); the other keys are means over all positions."""
+    games = [dict(row) | {"model-move": [], "human-move": [], "top-move-legal": [], "sampled-move-legal": [],
+                          "human-resigned": [], "model-resigned": [], "model-think-time": [],
+                          "model-white-advantage": []} for row in rows]
+    time_err, value_err = [], []
+    for r, i, g, s in iter_scores(strategy, rows, batch_size):
+        rec, row = games[r], rows[r]
         legal = g.legal_moves
-        probs = s.legal_move_probabilities
-        choice = int(probs.multinomial(1)[0]) if strategy.sample is True else int(probs.argmax())
-        n += 1
-        match += int(legal[choice] == moves[i])
+        rec["model-move"].append(legal[_choice(strategy, s.legal_move_probabilities)])
+        rec["human-move"].append(row["moves-uci"].split()[i])
         if s.top_move_legal is not None:
-            legal_top += int(s.top_move_legal)
-            legal_mass.append(s.sampled_move_legal)
-        resign_pred += int(bool(s.resigned))
-        if s.think_time is not None and g.next_move_seconds is not None:
-            time_err.append(abs(s.think_time - g.next_move_seconds))
+            rec["top-move-legal"].append(bool(s.top_move_legal))
+        if s.sampled_move_legal is not None:
+            rec["sampled-move-legal"].append(s.sampled_move_legal)
+        if s.resigned is not None:
+            rec["human-resigned"].append(False)
+            rec["model-resigned"].append(bool(s.resigned))
+        if s.think_time is not None:
+            rec["model-think-time"].append(s.think_time)
+            if g.next_move_seconds is not None:
+                time_err.append(abs(s.think_time - g.next_move_seconds))
         if s.white_advantage is not None:
+            rec["model-white-advantage"].append(s.white_advantage)
+            outcome = {"1-0": 1.0, "0-1": -1.0}.get(row.get("result"), 0.0)
             value_err.append((s.white_advantage - outcome) ** 2)
-    return {"positions": n, "move_match": match / max(n, 1), "top_move_legal": legal_top / max(n, 1),
-            "legal_mass": float(np.mean(legal_mass)) if legal_mass else None,
-            "resign_rate": resign_pred / max(n, 1),
-            "think_time_mae": float(np.mean(time_err)) if time_err else None,
-            "value_mse": float(np.mean(value_err)) if value_err else None}
+    for rec, row in zip(games, rows):
+        game = json_to_game(row)
+        if game.normal_termination and game.board.outcome(claim_draw=True) is None:
+            # a normally terminated game without a result on the board: the human resigned here
+            rec["human-resigned"].append(True)
+            rec["model-resigned"].append(bool(strategy.decode_full(game).resigned))
+    flat = lambda key: [x for rec in games for x in rec[key]]
+    n = len(flat("model-move"))
+    match = sum(int(a == b) for a, b in zip(flat("model-move"), flat("human-move")))
+    hr, mr = flat("human-resigned"), flat("model-resigned")
+    return {"games": games, "positions": n, "move_match": match / max(n, 1),
+            "top_move_legal": sum(flat("top-move-legal")) / max(n, 1), "legal_mass": _mean(flat("sampled-move-legal")),
+            "resign_rate": sum(mr) / max(len(mr), 1),
+            "resign_agreement": _mean(int(a == b) for a, b in zip(hr, mr)),
+            "think_time_mae": _mean(time_err), "value_mse": _mean(value_err)}
 
 
 def evaluate_value(strategy: DecodeStrategy, rows: list[dict], batch_size: int = 256) -> dict:
+    """Value head against Stockfish (``src/evaluation/evaluate.py:33-60``): per game the model's
+    white advantage and the engine's white-relative centipawns for every position."""
     from .utils import cp_to_value, stockfish_eval
 
+    games = [dict(row) | {"model-move": [], "stockfish-eval": [], "model-white-advantage": []} for row in rows]
     err = []
-    for row, i, g, s in iter_scores(strategy, rows, batch_size):
-        err.append((s.white_advantage - cp_to_value(stockfish_eval(row["moves-uci"].split()[:i]))) ** 2)
-    return {"positions": len(err), "value_vs_stockfish_mse": float(np.mean(err)) if err else None}
+    for r, i, g, s in iter_scores(strategy, rows, batch_size):
+        if s.white_advantage is None:
+            continue
+        cp = stockfish_eval(rows[r]["moves-uci"].split()[:i])
+        games[r]["model-white-advantage"].append(s.white_advantage)
+        games[r]["stockfish-eval"].append(cp)
+        err.append((s.white_advantage - cp_to_value(cp)) ** 2)
+    return {"games": games, "positions": len(err), "value_vs_stockfish_mse": _mean(err)}
 
 
 def evaluate(strategy: DecodeStrategy, rows: list[dict], batch_size: int = 256) -> dict:
-    from ..search.batched_strategies import pick_move
-    from .utils import move_quality
+    """Stockfish centipawn loss and Lichess accuracy of the model's move in every position
+    (``src/evaluation/evaluate.py:129-187``)."""
+    from . import utils as eval_utils
 
-    cpl, acc = [], []
-    for row, i, g, s in iter_scores(strategy, rows, batch_size):
-        mv = pick_move(strategy, g, g.legal_moves, s.legal_move_probabilities)
-        c, a = move_quality(row["moves-uci"].split()[:i], mv)
-        cpl.append(c)
-        acc.append(a)
-    return {"positions": len(cpl), "centipawn_loss": float(np.mean(cpl)) if cpl else None,
-            "accuracy": float(np.mean(acc)) if acc else None}
+    games = [dict(row) | {"model-centipawn-loss": [], "model-lichess-accuracy": [], "model-move": [],
+                          "human-move": [], "top-move": [], "top-move-legal": [], "sampled-move-legal": []}
+             for row in rows]
+    for r, i, g, s in iter_scores(strategy, rows, batch_size):
+        rec, moves = games[r], rows[r]["moves-uci"].split()
+        legal, probs = g.legal_moves, s.legal_move_probabilities
+        model_move = legal[_choice(strategy, probs)]
+        loss, acc = eval_utils.move_quality(moves[:i], model_move)
+        rec["model-centipawn-loss"].append(loss)
+        rec["model-lichess-accuracy"].append(acc)
+        rec["model-move"].append(model_move)
+        rec["top-move"].append(legal[int(probs.argmax())])
+        rec["human-move"].append(moves[i])
+        if s.top_move_legal is not None:
+            rec["top-move-legal"].append(bool(s.top_move_legal))
+        if s.sampled_move_legal is not None:
+            rec["sampled-move-legal"].append(s.sampled_move_legal)
+    if eval_utils._engine is not None:
+        eval_utils._engine.quit()
+        eval_utils._engine = None
+    cpl = [x for rec in games for x in rec["model-centipawn-loss"]]
+    acc = [x for rec in games for x in rec["model-lichess-accuracy"]]
+    return {"games": games, "positions": len(cpl), "centipawn_loss": _mean(cpl), "accuracy": _mean(acc)}
 
 
 def main(argv: list[str] | None = None) -> dict:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--config", required=True)
+    ap.add_argument("--config", default=None)
     ap.add_argument("--quick", action="store_true")
     ap.add_argument("--value", action="store_true")
     ap.add_argument("--dataset", required=True)
@@ -132,19 +186,24 @@ def main(argv: list[str] | None = None) -> dict:
     ap.add_argument("--batch_size", type=int, default=256,
                     help="positions per call for the strategies that score many games at once")
     args = ap.parse_args(argv)
+    assert not (args.quick and args.value), "--quick and --value exclude each other"
     random.seed(42); np.random.seed(42); torch.manual_seed(42)
-    cfg = load_config(args.config)
-    tokenizer = UCITokenizer(**cfg.data_config.tokenizer_config)
-    model = initialize_model(tokenizer, **{**cfg.model_config, "use_pretrained": False})
-    ckpt_path = args.checkpoint or join(cfg.trainer_config.output_dir, "best.pt")
-    if ckpt_path != "none":
-        model.load_state_dict(torch.load(ckpt_path, map_location="cpu", weights_only=False)["model"])
-    model.eval()
     decode_args = json.loads(args.decode_args)
+    model = tokenizer = None
     if args.decode == "maia":
         decode_args.setdefault("maia_elo", args.maia_elo)
         if args.alias is None:
             args.alias = "maia-closest" if args.maia_elo is None else f"maia-{args.maia_elo}"
+    if args.config is not None:
+        cfg = load_config(args.config)
+        tokenizer = UCITokenizer(**cfg.data_config.tokenizer_config)
+        model = initialize_model(tokenizer, **{**cfg.model_config, "use_pretrained": False})
+        ckpt_path = args.checkpoint or join(cfg.trainer_config.output_dir, "best.pt")
+        if ckpt_path != "none":
+            model.load_state_dict(torch.load(ckpt_path, map_location="cpu", weights_only=False)["model"])
+        model.eval()
+    elif args.decode not in ("maia", "gpt-3.5-turbo"):
+        ap.error("--config is required for strategies that run the model")
     strategy = DECODE_STRATEGIES[args.decode](model, tokenizer, sample=args.sample, device=args.device,
                                               precision="float32", **decode_args)
     rows = read_jsonl(args.dataset, 5 if args.debug else args.n_rows)
@@ -154,13 +213,15 @@ def main(argv: list[str] | None = None) -> dict:
         metrics = evaluate_value(strategy, rows, args.batch_size)
     else:
         metrics = evaluate(strategy, rows, args.batch_size)
-    result = {"alias": args.alias or args.decode, "config": args.config, "dataset": args.dataset,
-              "decode": args.decode, "decode_args": json.loads(args.decode_args), "sample": args.sample,
+    result = {"decode": args.decode, "alias": args.alias or args.decode, "n_rows": args.n_rows, "sample": args.sample,
+              "config": args.config, "dataset": args.dataset, **json.loads(args.decode_args),
               **metrics, **strategy.run_stats()}
     strategy.cleanup()
     if args.debug:
+        result.pop("games", None)
         print(json.dumps(result, indent=1))
     else:
+        os.makedirs(os.path.dirname(os.path.abspath(args.output_file)), exist_ok=True)
         with open(args.output_file, "a") as f:
             f.write(json.dumps(result) + "\n")
     return result

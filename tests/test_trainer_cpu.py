@@ -85,7 +85,15 @@ def test_train_checkpoint_resume_and_eval_cli(tmp_path):
     res = eval_main(["--config", str(tmp_path / "cfg.yaml"), "--dataset", str(tmp_path / "val.jsonl"), "--quick",
                      "--decode", "policy", "--output_file", str(tmp_path / "out.jsonl"), "--device", "cpu"])
     assert res["positions"] > 0 and 0 <= res["move_match"] <= 1 and res["top_move_legal"] is not None
-    assert json.loads((tmp_path / "out.jsonl").read_text().strip())["decode"] == "policy"
+    written = json.loads((tmp_path / "out.jsonl").read_text().strip())
+    assert written["decode"] == "policy" and len(written["games"]) == 2
+    rec = written["games"][0]
+    n0 = len(val[0]["moves-uci"].split())
+    assert rec["human-move"] == val[0]["moves-uci"].split() and len(rec["model-move"]) == n0
+    assert len(rec["top-move-legal"]) == n0 and len(rec["model-think-time"]) == n0
+    # these random games end "Normal" with no result on the board: the human resigned after the last ply
+    assert rec["human-resigned"] == [False] * n0 + [True] and len(rec["model-resigned"]) == n0 + 1
+    assert "games" not in res or res["games"] is not None
     # the many-positions-per-call strategy reports the same metrics, whatever the batch size
     for bs in ("3", "256"):
         rb = eval_main(["--config", str(tmp_path / "cfg.yaml"), "--dataset", str(tmp_path / "val.jsonl"), "--quick",

@@ -85,3 +85,35 @@ def test_maia_picks_network_by_rating_and_uses_opening_book(fake_engine, tmp_pat
     assert list(one.engines) == [1500] and one.decode(g) == "e4d5"
     m.cleanup(); one.cleanup()
     assert book.closed
+
+
+def test_full_and_value_evaluation_with_fake_stockfish(fake_engine, monkeypatch):
+    from allie_b200.evaluation.evaluate import evaluate, evaluate_value
+    from allie_b200.search import ScoreResult
+
+    class Greedy:
+        """Strategy stub: all mass on the first legal move; white advantage 0.25 everywhere."""
+        sample = False
+
+        def score_full(self, game, legal):
+            p = torch.zeros(len(legal))
+            p[0] = 1.0
+            return ScoreResult(p, white_advantage=0.25, top_move_legal=True, sampled_move_legal=0.5)
+
+    eval_utils._eval_cached.cache_clear()
+    monkeypatch.setattr(eval_utils, "_engine", UCIEngine(fake_engine))
+    rows = [{"moves-uci": "e2e4 d7d5 e4d5", "moves-seconds": [1, 1, 1], "time-control": "180+0", "white-elo": 1500,
+             "black-elo": 1500, "result": "1-0", "termination": "Normal"}]
+    out = evaluate(Greedy(), rows, batch_size=2)
+    rec = out["games"][0]
+    assert out["positions"] == 3 and rec["human-move"] == ["e2e4", "d7d5", "e4d5"]
+    assert rec["model-move"] == rec["top-move"] and len(rec["model-centipawn-loss"]) == 3
+    # the fake engine counts material only, so a quiet move loses nothing by its measure
+    assert rec["model-centipawn-loss"][2] == 0.0 and rec["model-lichess-accuracy"][2] == 100.0
+    assert eval_utils._engine is None                        # the engine process is shut down at the end
+    monkeypatch.setattr(eval_utils, "_engine", UCIEngine(fake_engine))
+    eval_utils._eval_cached.cache_clear()
+    val = evaluate_value(Greedy(), rows)
+    assert val["games"][0]["stockfish-eval"] == [0, 0, 0] and val["games"][0]["model-white-advantage"] == [0.25] * 3
+    assert abs(val["value_vs_stockfish_mse"] - 0.0625) < 1e-9
+    eval_utils._engine.quit()
