@@ -22,6 +22,8 @@ import json
 import logging
 import math
 import os
+import queue
+import threading
 import time
 from collections import defaultdict, deque
 from os.path import join
@@ -52,26 +54,71 @@ def count_params(model: torch.nn.Module) -> int:
 
 class WindowSampler:
     """Random fixed-length windows out of the flat token stream (``trainer.py:159-167``), gathered
-    straight into a pinned ``int32`` staging buffer (the words are < 2^31 only in their low 31 bits,
-    so they are carried bit-exact as int32)."""
+    straight into pinned ``int32`` staging buffers (the words are < 2^31 only in their low 31 bits,
+    so they are carried bit-exact as int32).
 
-    def __init__(self, data: np.ndarray, batch_size: int, seq_len: int, pin: bool, depth: int = 4):
+    A background thread keeps the next windows gathered while the training thread launches
+    kernels, so page faults of a memory-mapped stream never stall a step.  Buffers form a pool: one
+    handed out by ``next()`` goes back to the pool only after ``keep`` later ones were handed out,
+    which is far longer than its asynchronous host-to-device copy stays in flight (the launch
+    queue lets the host run at most a couple of micro-steps ahead of the device)."""
+
+    def __init__(self, data: np.ndarray, batch_size: int, seq_len: int, pin: bool, depth: int = 8,
+                 prefetch: bool = True):
         self.data, self.B, self.T = data, batch_size, seq_len
         self.n = len(data) - seq_len
         assert self.n > 0, "training stream shorter than one window"
+        assert depth >= 4
         self.bufs = [torch.empty((batch_size, seq_len), dtype=torch.int32, pin_memory=pin)
                      for _ in range(depth)]
-        self.i = 0
+        self.keep = depth - 2
         self.rng = np.random.default_rng(int.from_bytes(os.urandom(8), "little"))
         self.offs = np.arange(seq_len, dtype=np.int64)[None, :]
+        self._handed: deque = deque()
+        self._free: queue.Queue = queue.Queue()
+        for b in self.bufs:
+            self._free.put(b)
+        self._ready: queue.Queue = queue.Queue(maxsize=1)
+        self._stop = False
+        self._error: BaseException | None = None
+        self._thread = None
+        if prefetch:
+            self._thread = threading.Thread(target=self._produce, name="window-prefetch", daemon=True)
+            self._thread.start()
 
-    def next(self) -> torch.Tensor:
-        buf = self.bufs[self.i % len(self.bufs)]
-        self.i += 1
+    def _fill(self, buf: torch.Tensor) -> None:
         starts = self.rng.integers(0, self.n, size=(self.B, 1))
         win = self.data[(starts + self.offs).reshape(-1)]
         buf.numpy().view(np.uint32)[...] = np.asarray(win, dtype=np.uint32).reshape(self.B, self.T)
+
+    def _produce(self) -> None:
+        try:
+            while not self._stop:
+                buf = self._free.get()
+                if buf is None:
+                    return
+                self._fill(buf)
+                self._ready.put(buf)
+        except BaseException as e:      # surfaces in next(), on the training thread
+            self._error = e
+            self._ready.put(None)
+
+    def next(self) -> torch.Tensor:
+        if self._thread is None:
+            buf = self._free.get()
+            self._fill(buf)
+        else:
+            buf = self._ready.get()
+            if buf is None:
+                raise RuntimeError("window prefetch thread failed") from self._error
+        self._handed.append(buf)
+        if len(self._handed) > self.keep:
+            self._free.put(self._handed.popleft())
         return buf
+
+    def close(self) -> None:
+        self._stop = True
+        self._free.put(None)
 
 
 class Trainer:
@@ -392,6 +439,8 @@ class Trainer:
         if self.ddp and dist.is_initialized():
             dist.destroy_process_group()
         self.metrics.finish()
+        if getattr(self, "sampler", None) is not None:
+            self.sampler.close()
         logger.info("all done! exiting gracefully...")
 
     # ------------------------------------------------------------ checkpoints

@@ -142,3 +142,33 @@ def test_flops_per_token_and_mfu():
     moe = resolve_model_config("gpt2-medium", vocab_size=2048, num_experts=8, moe_ffn=2048, moe_layer_freq=3)
     per_moe_block = 4 * 1024 * 1024 + 2 * 2 * 1024 * 2048 + 1024 * 8
     assert matmul_params_per_token(moe) == 16 * 12 * 1024 * 1024 + 8 * per_moe_block + 1024 * 2048
+
+
+def test_window_sampler_prefetch_and_buffer_reuse():
+    from allie_b200.train.trainer import WindowSampler
+
+    data = np.arange(10_000, dtype=np.uint32) | np.uint32(1 << 31)       # top bit set: must survive as int32 bits
+    for prefetch in (True, False):
+        ws = WindowSampler(data, batch_size=3, seq_len=16, pin=False, depth=6, prefetch=prefetch)
+        live = []
+        for _ in range(40):
+            w = ws.next()
+            u = w.numpy().view(np.uint32)
+            assert u.shape == (3, 16) and np.all(u >> 31 == 1)
+            low = (u & 0x7FFFFFFF).astype(np.int64)
+            assert np.all(np.diff(low, axis=1) == 1) and low.max() < 10_000  # every row is a contiguous window
+            live.append((w, u.copy()))
+            live = live[-ws.keep:]
+            # the last `keep` windows handed out are distinct buffers and have not been overwritten
+            assert len({id(t) for t, _ in live}) == len(live)
+            assert all(np.array_equal(t.numpy().view(np.uint32), snap) for t, snap in live)
+        ws.close()
+    bad = WindowSampler(data, batch_size=3, seq_len=16, pin=False)
+    bad.next()
+    bad.data = None                                                      # the producer thread now fails
+    try:
+        for _ in range(12):
+            bad.next()
+        raise AssertionError("expected the prefetch failure to surface")
+    except RuntimeError as e:
+        assert "prefetch" in str(e)
