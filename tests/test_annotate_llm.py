@@ -122,3 +122,31 @@ def test_gpt35_strategy_with_fake_completion():
     mv = s.decode_full(g3).move                                    # illegal answer -> some legal move
     assert mv in g3.legal_moves and s.requests == 2
     assert s.run_stats() == {"completion_requests": 2}
+
+
+def test_san_writer_and_both_parsers_agree_on_random_games():
+    """Every legal move of positions along random games: SAN text -> move must give the move back,
+    through the board's own parser and through the PGN reader's resolver."""
+    import random
+
+    from allie_b200.etl.pgn import san_to_uci
+
+    rng = random.Random(7)
+    checked = 0
+    for _ in range(6):
+        b = Board()
+        for ply in range(60):
+            legal = b.legal_moves_uci()
+            if not legal or b.is_game_over():
+                break
+            sans = {}
+            for mv in legal:
+                s = b.san(mv)
+                assert s not in sans, (b.fen(), s, mv, sans[s])           # SAN is unambiguous
+                sans[s] = mv
+                if ply % 5 == 0:
+                    assert b.parse_san(s) == mv and san_to_uci(b, s) == mv, (b.fen(), s, mv)
+                    checked += 1
+            b.push_uci(rng.choice(legal))
+        assert Board(b.fen()).legal_moves_uci() == b.legal_moves_uci()
+    assert checked > 500

@@ -98,3 +98,37 @@ def test_waiting_connections_share_one_batched_search():
     assert res["success"] and res["answered"] == 6 and res["latency_p50_s"] > 0
     th.join(timeout=30)
     assert not th.is_alive()
+
+
+def test_bot_session_plays_both_colours_against_a_server():
+    from allie_b200.serve.client import BotSession, request_move
+
+    torch.manual_seed(0)
+    tok = UCITokenizer(max_length=64, vocab_size_multiple_of=128)
+    model = initialize_model(tok, "gpt2", use_control_token=True, use_regression_head=True, n_layer=1,
+                             n_embd=32, n_head=1, n_positions=64).eval()
+    port = _free_port()
+    th = threading.Thread(target=serve, kwargs=dict(alias="grandmaster", model=model, tokenizer=tok, device="cpu",
+                                                    port=port, self_test=False, max_requests=4), daemon=True)
+    th.start()
+    time.sleep(0.5)
+    white = BotSession(port, "180+0", 1500, 1500, bot_is_white=True)
+    black = BotSession(port, "180+0", 1500, 1500, bot_is_white=False)
+    for _ in range(2):
+        a = white.play()
+        assert not white.bot_to_move and white.moves[-1] == a["move"]
+        black.push(a["move"], 1.0)
+        b = black.play()
+        white.push(b["move"], 2.0)
+    assert white.moves == black.moves and len(white.moves) == 4 and white.moves_seconds[1] == 2
+    try:
+        black.push("a2a3")
+        black.push("a7a6")
+        white_turn = BotSession(port, "180+0", 1500, 1500, bot_is_white=False)
+        white_turn.play()
+        raise AssertionError("expected a turn error")
+    except RuntimeError:
+        pass
+    th.join(timeout=10)
+    assert not th.is_alive()
+    assert request_move.__doc__
