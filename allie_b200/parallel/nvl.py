@@ -47,6 +47,17 @@ def _ptr_array(ptrs) -> ctypes.Array:
     return arr
 
 
+def shard_bounds(n: int, world: int, rank: int) -> tuple[int, int]:
+    """(offset, length) of the slice of a flat arena of ``n`` elements that ``rank`` owns: equal
+    contiguous slices rounded up to 64 elements (so every shard starts on a 256-byte boundary and
+    the kernels' 16-byte vector accesses never straddle two owners); the last ranks may get a
+    shorter or empty slice."""
+    per = (n + world - 1) // world
+    per = (per + 63) // 64 * 64
+    off = min(n, per * rank)
+    return off, max(0, min(n, per * (rank + 1)) - off)
+
+
 class NvlGradOptimizer:
     def __init__(self, engine):
         a = engine.arena
@@ -72,11 +83,7 @@ class NvlGradOptimizer:
         self.mc_grad, self.mc_master, self.mc_shadow = mc if self.multimem else (0, 0, 0)
         # only the replicated region [0, sync_end) is reduced and sharded; rank-local (expert)
         # parameters behind it are updated in place by every rank for itself
-        n_sync = a.sync_end
-        per = (n_sync + self.world - 1) // self.world
-        per = (per + 63) // 64 * 64
-        self.shard_off = min(n_sync, per * self.rank)
-        self.shard_n = max(0, min(n_sync, per * (self.rank + 1)) - self.shard_off)
+        self.shard_off, self.shard_n = shard_bounds(a.sync_end, self.world, self.rank)
         self.total_norm = torch.zeros(1, dtype=torch.float32, device=dev)
         self.has_local = a.total > a.sync_end
         self.exp_avg = torch.zeros(max(self.shard_n, 4), dtype=torch.float32, device=dev)

@@ -90,3 +90,19 @@ def test_expert_parallel_two_ranks_match_single_rank(tmp_path):
         assert d.max().item() < 3 * 2e-3, (k, d.max().item())
     for i, st in ck1["optimizer"]["state"].items():
         assert ck2["optimizer"]["state"][i]["exp_avg"].shape == st["exp_avg"].shape, i
+
+
+def test_shard_bounds_tile_the_arena():
+    from allie_b200.parallel.nvl import shard_bounds
+
+    for n in (0, 1, 63, 64, 65, 1000, 4096, 354_871_296, 354_871_297):
+        for world in (1, 2, 3, 4, 8):
+            end = 0
+            for rank in range(world):
+                off, length = shard_bounds(n, world, rank)
+                assert off == end and off % 64 == 0 or length == 0, (n, world, rank, off, length)
+                assert length >= 0
+                end = off + length if length else end
+            assert end == n, (n, world, end)
+            sizes = [shard_bounds(n, world, r)[1] for r in range(world)]
+            assert max(sizes) <= -(-n // world) + 63                    # nobody owns much more than 1/world
