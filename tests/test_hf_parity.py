@@ -49,3 +49,33 @@ def test_logits_match_hf_gpt2_on_the_same_weights():
         got = inner(input_ids=ids)
     got = got["logits"] if isinstance(got, dict) else (got.logits if hasattr(got, "logits") else got)
     assert torch.allclose(got, want, atol=2e-4, rtol=1e-4), (got - want).abs().max().item()
+
+
+def test_use_pretrained_loads_a_local_gpt2_body(tmp_path):
+    """``use_pretrained`` with ``base_model`` = a local HF directory: every block weight and the
+    position table come from the checkpoint, the token embedding is re-drawn with the pretrained
+    embedding's mean and spread (its vocabulary is text, not chess moves)."""
+    from allie_b200.data import UCITokenizer
+    from allie_b200.models import initialize_model
+
+    torch.manual_seed(1)
+    cfg = transformers.GPT2Config(vocab_size=500, n_positions=64, n_embd=64, n_layer=2, n_head=2,
+                                  activation_function="gelu_new")
+    hf = transformers.GPT2LMHeadModel(cfg)
+    with torch.no_grad():
+        hf.transformer.wte.weight.mul_(5.0).add_(0.3)
+    hf.save_pretrained(tmp_path / "gpt2-local")
+    tok = UCITokenizer(max_length=64, vocab_size_multiple_of=128)
+    ours = initialize_model(tok, str(tmp_path / "gpt2-local"), use_control_token=True, use_regression_head=True,
+                            use_pretrained=True)
+    inner = ours.model.model
+    assert inner.config.n_layer == 2 and inner.config.vocab_size == len(tok)      # vocabulary is ours
+    hsd = hf.state_dict()
+    for k in ("transformer.wpe.weight", "transformer.h.1.mlp.c_fc.weight", "transformer.h.0.attn.c_attn.bias",
+              "transformer.ln_f.weight"):
+        assert torch.equal(inner.state_dict()[k], hsd[k]), k
+    wte = inner.transformer.wte.weight
+    assert wte.shape == (len(tok), 64)
+    assert abs(wte.mean().item() - hsd["transformer.wte.weight"].mean().item()) < 0.02
+    assert abs(wte.std().item() / hsd["transformer.wte.weight"].std().item() - 1) < 0.1
+    assert inner.lm_head.weight.data_ptr() == wte.data_ptr()                      # still tied
