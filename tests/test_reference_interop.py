@@ -1,0 +1,69 @@
+"""Interchange with the unmodified reference package (skipped when it is not installed under
+``baseline/_ref``): a checkpoint written by this framework's trainer loads strictly into the
+reference's model and optimizer, both tokenizers decode raw windows identically, and both models
+return the same logits and losses from the same weights (CPU)."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+
+pytestmark = pytest.mark.skipif(not os.path.isdir(os.path.join(ROOT, "baseline", "_ref", "modeling")),
+                                reason="reference package not installed under baseline/_ref")
+
+
+def test_checkpoint_tokenizer_and_forward_match_the_reference(tmp_path):
+    from allie_b200.config import Config
+    from allie_b200.data import UCITokenizer
+    from allie_b200.models import initialize_model
+    from allie_b200.train.trainer import Trainer
+
+    os.environ["ALLIE_NO_WANDB"] = "1"
+    shape = dict(n_layer=2, n_embd=64, n_head=2, n_positions=64, resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0)
+    tok_kw = dict(max_length=48, vocab_size_multiple_of=128)
+    tok = UCITokenizer(**tok_kw)
+    rng = np.random.default_rng(3)
+    stream = (rng.integers(0, 1968, size=4096).astype(np.uint32)
+              | (rng.integers(0, 40, size=4096).astype(np.uint32) << 16)
+              | (rng.integers(0, 3, size=4096).astype(np.uint32) << 14))
+    tr = Trainer(Config({"trainer_config": {}}), output_dir=str(tmp_path / "run"), device="cpu", batch_size=4,
+                 max_iters=2, decay_iters=2, warmup_iters=0, eval_interval=0, log_interval=-1, save_interval=0,
+                 lr=1e-3, min_lr=1e-4, weight_decay=0.01, use_wandb=False)
+    torch.manual_seed(0)
+    model = initialize_model(tok, "gpt2", use_control_token=True, use_regression_head=True, **shape)
+    tr.setup_dataloaders(tok, stream, [], [])
+    tr.setup_model(model)
+    tr.train()                                            # three AdamW steps: the optimizer has state
+    tr.save_ckpt("last")
+    ck = torch.load(tmp_path / "run" / "last.pt", weights_only=False)
+    windows = np.stack([stream[i:i + 48] for i in (0, 100, 200)])
+    windows[:, 0] = len(tok) + 1500                       # ELO pseudo-tokens in front, as in real windows
+    windows[:, 1] = len(tok) + 2250
+    windows[2, 40:] = tok.pad_token_id                    # one padded row
+    torch.save({"model": ck["model"], "optimizer": ck["optimizer"], "tokenizer": tok_kw, "shape": shape,
+                "windows": windows.astype(np.int64)}, tmp_path / "ours.pt")
+    res = subprocess.run([sys.executable, os.path.join(HERE, "reference_worker.py"), str(tmp_path)],
+                         capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
+    ref = torch.load(tmp_path / "ref_out.pt", weights_only=False)
+
+    assert ref["vocab"] == len(tok) and ref["ids"] == {"bos": tok.bos_token_id, "pad": tok.pad_token_id}
+    batch = tok.pad_and_collate(list(windows.astype(np.uint32)))
+    assert set(batch) == set(ref["batch"])
+    for k, v in batch.items():
+        assert torch.equal(v.to(ref["batch"][k].dtype), ref["batch"][k]), k
+    model.eval()
+    with torch.no_grad():
+        out = model(**batch)
+    for k, want in ref["out"].items():
+        assert torch.allclose(out[k].float(), want, atol=2e-4, rtol=1e-4), (k, (out[k].float() - want).abs().max())
+    # the optimizer entry: same two groups, same numbering, moments arrive where the reference expects them
+    groups = ck["optimizer"]["param_groups"]
+    assert [len(g["params"]) for g in groups] == [ref["n_decay"], ref["n_no_decay"]]
+    assert ref["opt_step"] == float(ck["optimizer"]["state"][0]["step"]) > 0
+    assert abs(ref["opt_exp_avg_norm"] - float(ck["optimizer"]["state"][0]["exp_avg"].norm())) < 1e-6
