@@ -244,15 +244,31 @@ class Board:
         self.push_uci(uci)
         return uci
 
-    def movetext(self) -> str:
-        """PGN movetext of the game so far: ``1. e4 e5 2. Nf3 ...`` (replayed from the start)."""
-        b, parts = Board(), []
+    def movetext(self, columns: int | None = None, result: str | None = None) -> str:
+        """PGN movetext of the game so far: ``1. e4 e5 2. Nf3 ...`` (replayed from the start),
+        optionally followed by a result marker.  With ``columns`` the text is wrapped the way
+        python-chess's PGN exporter does it: tokens are a move number or a move, each with a
+        trailing space, and a token that no longer fits into the line starts a new one."""
+        b, tokens = Board(), []
         for i, mv in enumerate(self.move_stack):
             if i % 2 == 0:
-                parts.append(f"{i // 2 + 1}.")
-            parts.append(b.san(mv))
+                tokens.append(f"{i // 2 + 1}. ")
+            tokens.append(b.san(mv) + " ")
             b.push_uci(mv)
-        return " ".join(parts)
+        if result is not None:
+            tokens.append(result)
+        if columns is None:
+            return "".join(tokens).rstrip()
+        lines, cur = [], ""
+        for tok in tokens:
+            if columns - len(cur) < len(tok):
+                if cur:
+                    lines.append(cur.rstrip())
+                cur = ""
+            cur += tok
+        if cur:
+            lines.append(cur.rstrip())
+        return "\n".join(lines)
 
 
 def _sq(name: str) -> int:

@@ -55,9 +55,12 @@ class ChessLLM:
         """The prompt for ``board``, or None when the game is over."""
         if board.outcome() is not None:
             return None
-        text = board.movetext()
+        # The reference prints the game with python-chess (movetext wrapped at 80 columns, result
+        # marker "*" at the end), cuts the marker off and, with white to move, appends the number
+        # of the coming move.
+        text = board.movetext(columns=80, result="*")[:-1].strip()
         if board.turn:
-            text = (text + " " if text else "") + f"{board.fullmove_number}."
+            text = text + f" {board.fullmove_number}." if text else "1."
         return HEADER + text
 
     @staticmethod

@@ -8,6 +8,8 @@ games whose prompts are 1-300 tokens long.  Every leaf evaluation is one KV-cach
     python bench_mcts.py                       # batched C++ search + KV-cached sm_100a evaluator
     python bench_mcts.py --impl sequential     # the reference algorithm: one tree at a time, every
                                                # leaf re-encodes its whole game at batch 1
+    python bench_mcts.py --impl reference      # the unmodified reference package (baseline/_ref): its own
+                                               # model and MCTS strategy, python-chess replaced by a stand-in
     torchrun --nproc-per-node 8 bench_mcts.py --gpus 8   # one independent 256-tree search per GPU
 Prints one JSON line (rank 0; with several GPUs the value is the sum of positions over the ranks
 divided by the slowest rank's time, and the p50 per-move latency is the median over ranks).
@@ -43,6 +45,49 @@ def random_games(n, tok, rng, max_tokens=300):
     return games
 
 
+def run_reference(args, tok, games) -> dict:
+    """The reference package as installed under ``baseline/_ref``: its ``initialize_model`` (Hugging
+    Face GPT-2 inside its two wrappers, random init), its tokenizer and its ``MCTS`` strategy at
+    ``precision="float32"`` as its evaluation CLI runs it.  A position = one forward pass of its model."""
+    import torch
+
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "modeling")):
+        return {"unavailable": "baseline/_ref is missing (pip install --target was not run)"}
+    sys.path.insert(0, os.path.join(ROOT, "baseline", "shims"))
+    sys.path.insert(0, ref_dir)
+    try:
+        from evaluation.decode import MCTS
+        from modeling.data import Game, UCITokenizer
+        from modeling.model import initialize_model
+    except Exception as e:
+        return {"unavailable": f"reference import failed: {type(e).__name__}: {e}"[:300]}
+    dev = "cuda" if torch.cuda.is_available() else "cpu"
+    rtok = UCITokenizer(max_length=512, vocab_size_multiple_of=128)
+    shape = dict(n_layer=2, n_embd=256, n_head=4) if args.small else {}
+    torch.manual_seed(0)
+    model = initialize_model(rtok, os.path.join(ROOT, "baseline", "gpt2-medium"), use_control_token=True,
+                             use_regression_head=True, use_pretrained=False, **shape).to(dev).eval()
+    calls = [0]
+    model.register_forward_hook(lambda *a: calls.__setitem__(0, calls[0] + 1))
+    rgames = [Game(**g.to_dict()) for g in games]
+    strat = MCTS(model, rtok, sample=False, device=dev, precision="float32", n_sims=args.sims)
+    with torch.inference_mode():
+        strat.score_full(rgames[0], rgames[0].legal_moves)
+        if dev == "cuda":
+            torch.cuda.synchronize()
+        calls[0] = 0
+        t0 = time.perf_counter()
+        for g in rgames:
+            strat.score_full(g, g.legal_moves)
+        if dev == "cuda":
+            torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+    return {"value": calls[0] / dt, "seconds": dt, "positions": calls[0], "p50_move_latency_s": dt / len(rgames),
+            "note": "unmodified reference evaluation.decode.MCTS on its own model, one tree at a time, "
+                    "batch-1 full re-encode per leaf"}
+
+
 def main():
     import numpy as np
     import torch
@@ -53,7 +98,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--trees", type=int, default=256)
     ap.add_argument("--sims", type=int, default=400)
-    ap.add_argument("--impl", default="batched", choices=["batched", "sequential"])
+    ap.add_argument("--impl", default="batched", choices=["batched", "sequential", "reference"])
     ap.add_argument("--small", action="store_true", help="tiny model (smoke test)")
     ap.add_argument("--seq-positions", type=int, default=4, help="root positions for --impl sequential")
     ap.add_argument("--gpus", type=int, default=1)
@@ -73,7 +118,7 @@ def main():
                              n_positions=1024, **shape)
     rng = np.random.default_rng(rank)          # different root positions on every rank
     out = {"metric": "MCTS leaf-eval positions/sec", "unit": "positions/s", "impl": args.impl,
-           "dtype": "bf16", "data": "synthetic random legal games, prompts of 1-300 tokens",
+           "dtype": "bf16" if args.impl == "batched" else "fp32", "data": "synthetic random legal games, prompts of 1-300 tokens",
            "config": {"model": "tiny" if args.small else "gpt2-medium-like 24L d1024 16H", "trees": args.trees,
                       "sims": args.sims}}
     if args.impl == "batched":
@@ -100,7 +145,7 @@ def main():
                    moves_per_s=len(games) / dt, latency_per_move_batch_s=dt, gpu_launches=_lib.LAUNCHES - l0,
                    sims_done=int(sum(r.n_sims for r in res)),
                    phase_seconds={k: round(v, 4) for k, v in bm.phase_seconds.items()})
-    else:
+    elif args.impl == "sequential":
         from allie_b200.search import MCTS
 
         dev = "cuda" if torch.cuda.is_available() else "cpu"
@@ -125,6 +170,8 @@ def main():
                    note="sequential PUCT, batch-1 full re-encode per leaf, fp32 PyTorch model "
                         "(the reference's decode path, src/evaluation/decode.py:336-467)")
     out["n_gpus"] = world
+    if args.impl == "reference":
+        out.update(run_reference(args, tok, random_games(args.seq_positions, tok, rng)))
     if world > 1:
         import torch.distributed as dist
 

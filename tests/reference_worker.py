@@ -4,7 +4,11 @@ framework into the reference's model with ``strict=True``, collates the given ra
 reference's tokenizer, runs its forward pass, builds its optimizer and loads this framework's
 optimizer state into it.  Results go to ``<dir>/ref_out.pt``.
 
-usage: reference_worker.py <dir>      (reads <dir>/ours.pt)
+With ``decode`` as second argument it instead runs the reference's decode strategies (policy, MCTS,
+adaptive MCTS) on the given games with the given weights and writes their move distributions, think
+times and resign flags to ``<dir>/ref_decode.pt``, plus the prompts its PGN prompter builds.
+
+usage: reference_worker.py <dir> [decode]      (reads <dir>/ours.pt)
 """
 import os
 import sys
@@ -47,5 +51,41 @@ def main():
                os.path.join(d, "ref_out.pt"))
 
 
+def decode():
+    import chess
+    from evaluation.carlini import ChessLLM
+    from evaluation.decode import DECODE_STRATEGIES
+    from modeling.data import Game, UCITokenizer
+    from modeling.model import initialize_model
+
+    d = sys.argv[1]
+    blob = torch.load(os.path.join(d, "ours.pt"), weights_only=False)
+    tok = UCITokenizer(**blob["tokenizer"])
+    model = initialize_model(tok, os.path.join(ROOT, "baseline", "gpt2-medium"), use_control_token=True,
+                             use_regression_head=True, use_pretrained=False, **blob["shape"])
+    model.load_state_dict(blob["model"], strict=True)
+    model.eval()
+    games = [Game(**g) for g in blob["games"]]
+    out = {}
+    with torch.inference_mode():
+        for name, kwargs in blob["strategies"]:
+            strat = DECODE_STRATEGIES[name](model, tok, sample=False, device="cpu", precision="float32", **kwargs)
+            rows = []
+            for g in games:
+                s = strat.score_full(g, g.legal_moves)
+                rows.append({"legal": g.legal_moves, "probs": s.legal_move_probabilities.float().clone(),
+                             "think_time": s.think_time, "resigned": s.resigned,
+                             "move": strat.decode_full(g).move})
+            out[f"{name}:{sorted(kwargs.items())}"] = {"rows": rows, "stats": strat.run_stats()}
+    llm = ChessLLM(None, {"num_lookahead_tokens": 10})
+    prompts = []
+    for g in games:
+        board = chess.Board()
+        for mv in g.moves:
+            board.push_uci(mv)
+        prompts.append(llm.get_query_pgn(board))
+    torch.save({"decode": out, "prompts": prompts}, os.path.join(d, "ref_decode.pt"))
+
+
 if __name__ == "__main__":
-    main()
+    decode() if len(sys.argv) > 2 and sys.argv[2] == "decode" else main()

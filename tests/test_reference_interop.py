@@ -67,3 +67,60 @@ def test_checkpoint_tokenizer_and_forward_match_the_reference(tmp_path):
     assert [len(g["params"]) for g in groups] == [ref["n_decay"], ref["n_no_decay"]]
     assert ref["opt_step"] == float(ck["optimizer"]["state"][0]["step"]) > 0
     assert abs(ref["opt_exp_avg_norm"] - float(ck["optimizer"]["state"][0]["exp_avg"].norm())) < 1e-6
+
+
+def test_decode_strategies_and_prompts_match_the_reference(tmp_path):
+    """The unmodified reference ``policy`` / ``mcts`` / ``adaptive-mcts`` strategies (python-chess
+    replaced by a stand-in over this repository's move generator) against this framework's
+    sequential and batched strategies, same weights, fp32 on the CPU: same move distributions,
+    think times, resign flags and chosen moves; and the same PGN prompts for the completion baseline."""
+    import random
+
+    from allie_b200.chess import Board
+    from allie_b200.data import Game, UCITokenizer
+    from allie_b200.evaluation.chess_llm import ChessLLM
+    from allie_b200.models import initialize_model
+    from allie_b200.search import DECODE_STRATEGIES
+
+    shape = dict(n_layer=2, n_embd=64, n_head=2, n_positions=128, resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0)
+    tok_kw = dict(max_length=128, vocab_size_multiple_of=128)
+    tok = UCITokenizer(**tok_kw)
+    torch.manual_seed(4)
+    model = initialize_model(tok, "gpt2", use_control_token=True, use_regression_head=True, **shape).eval()
+    with torch.no_grad():                  # livelier heads than a fresh init: values and times that matter
+        for n, p in model.named_parameters():
+            if "head" in n or "wte" in n:
+                p.mul_(8.0)
+    rng = random.Random(5)
+    lines = [[], "f2f3 e7e5 g2g4".split(), "e2e4 e7e5 g1f3 b8c6 f1b5 a7a6".split()]
+    b = Board()
+    for _ in range(47):
+        b.push_uci(rng.choice(b.legal_moves_uci()))
+    lines.append(list(b.move_stack))       # long enough for the prompt's movetext to wrap
+    games = [Game("180+0", 1500 + 300 * i, 2300, None, False, mv, [3] * len(mv)) for i, mv in enumerate(lines)]
+    strategies = [("policy", {}), ("mcts", {"n_sims": 24}), ("mcts", {"n_sims": 9, "kl_reg_solution": False}),
+                  ("adaptive-mcts", {"mean_n_sims": 12})]
+    torch.save({"model": model.state_dict(), "tokenizer": tok_kw, "shape": shape,
+                "games": [g.to_dict() for g in games], "strategies": strategies}, tmp_path / "ours.pt")
+    res = subprocess.run([sys.executable, os.path.join(HERE, "reference_worker.py"), str(tmp_path), "decode"],
+                         capture_output=True, text=True, timeout=900)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
+    ref = torch.load(tmp_path / "ref_decode.pt", weights_only=False)
+
+    for name, kwargs in strategies:
+        want = ref["decode"][f"{name}:{sorted(kwargs.items())}"]
+        for variant in (name, name + "-batched"):
+            extra = {"n_trees": 3, "anc_max": 64} if variant.endswith("mcts-batched") else {}
+            strat = DECODE_STRATEGIES[variant](model, tok, sample=False, device="cpu", **kwargs, **extra)
+            for g, row in zip(games, want["rows"]):
+                assert g.legal_moves == row["legal"]
+                s = strat.score_full(g, g.legal_moves)
+                assert torch.allclose(s.legal_move_probabilities, row["probs"], atol=2e-4), (variant, kwargs, g.moves)
+                assert abs(s.think_time - row["think_time"]) < 1e-3 and bool(s.resigned) == bool(row["resigned"])
+                assert strat.decode_full(g).move == row["move"], (variant, kwargs, g.moves)
+            if "total_rollouts" in want["stats"]:
+                assert strat.run_stats()["total_rollouts"] == want["stats"]["total_rollouts"]
+    llm = ChessLLM(None)
+    for g, prompt in zip(games, ref["prompts"]):
+        assert llm.get_query_pgn(g.board) == prompt
+    assert "\n" in ref["prompts"][3].split("\n\n")[1]     # the long game's movetext did wrap
