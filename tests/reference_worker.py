@@ -37,6 +37,15 @@ def main():
     batch = tok.pad_and_collate(list(blob["windows"].astype(np.uint32)))
     with torch.no_grad():
         out = model(**batch)
+    from modeling.data import Game
+
+    words, collated = [], []
+    for g in blob.get("games", []):
+        game = Game(**g)
+        for flags in blob["tokenize_flags"]:
+            words.append(tok.tokenize(game, **flags).astype(np.int64))
+    if blob.get("games"):
+        collated = tok.pad_and_collate([Game(**g) for g in blob["games"]])
     decay, no_decay = partition_model_parameters(model)
     opt = torch.optim.AdamW([{"params": decay, "weight_decay": 0.01}, {"params": no_decay, "weight_decay": 0.0}],
                             lr=1e-3, betas=(0.9, 0.95))
@@ -45,6 +54,7 @@ def main():
     torch.save({"batch": {k: v for k, v in batch.items()},
                 "out": {k: out[k].float() for k in ("logits", "loss", "lm_loss", "value_loss", "time_loss",
                                                     "value_logits", "time_logits")},
+                "words": words, "collated_games": collated,
                 "vocab": len(tok), "ids": {"bos": tok.bos_token_id, "pad": tok.pad_token_id},
                 "n_decay": len(decay), "n_no_decay": len(no_decay),
                 "opt_step": float(first["step"]), "opt_exp_avg_norm": float(first["exp_avg"].norm())},

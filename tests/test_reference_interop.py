@@ -45,8 +45,16 @@ def test_checkpoint_tokenizer_and_forward_match_the_reference(tmp_path):
     windows[:, 0] = len(tok) + 1500                       # ELO pseudo-tokens in front, as in real windows
     windows[:, 1] = len(tok) + 2250
     windows[2, 40:] = tok.pad_token_id                    # one padded row
+    from allie_b200.data import Game
+
+    games = [Game("180+0", 1520, 2410, "1-0", True, "e2e4 e7e5 g1f3 b8c6".split(), [0, 3, 70, 12]),
+             Game("600+5", 900, 1100, "1/2-1/2", False, "d2d4 d7d5 c2c4".split(), [1, 1, 2]),
+             Game("60+0", 2000, 1990, None, False, ["g1f3"] * 1 + ["g8f6"], [5, 6]),
+             Game("180+2", 1500, 1500, "0-1", True, ["e2e4", "c7c5"] + ["g1f3", "b8c6", "f3g1", "c6b8"] * 15, [2] * 62)]
+    flags = [{}, {"add_elo": False}, {"add_time_control": False}, {"add_termination": False, "add_value": False}]
     torch.save({"model": ck["model"], "optimizer": ck["optimizer"], "tokenizer": tok_kw, "shape": shape,
-                "windows": windows.astype(np.int64)}, tmp_path / "ours.pt")
+                "windows": windows.astype(np.int64), "games": [g.to_dict() for g in games],
+                "tokenize_flags": flags}, tmp_path / "ours.pt")
     res = subprocess.run([sys.executable, os.path.join(HERE, "reference_worker.py"), str(tmp_path)],
                          capture_output=True, text=True, timeout=600)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
@@ -57,6 +65,14 @@ def test_checkpoint_tokenizer_and_forward_match_the_reference(tmp_path):
     assert set(batch) == set(ref["batch"])
     for k, v in batch.items():
         assert torch.equal(v.to(ref["batch"][k].dtype), ref["batch"][k]), k
+    # Game objects: the packed words (every flag combination) and the collated, truncated, padded batch
+    ours_words = [tok.tokenize(g, **f).astype(np.int64) for g in games for f in flags]
+    assert len(ours_words) == len(ref["words"])
+    for a, b_ in zip(ours_words, ref["words"]):
+        assert np.array_equal(a, b_)
+    collated = tok.pad_and_collate(list(games))
+    for k, v in collated.items():
+        assert torch.equal(v.to(ref["collated_games"][k].dtype), ref["collated_games"][k]), k
     model.eval()
     with torch.no_grad():
         out = model(**batch)
