@@ -8,7 +8,12 @@ With ``decode`` as second argument it instead runs the reference's decode strate
 adaptive MCTS) on the given games with the given weights and writes their move distributions, think
 times and resign flags to ``<dir>/ref_decode.pt``, plus the prompts its PGN prompter builds.
 
-usage: reference_worker.py <dir> [decode]      (reads <dir>/ours.pt)
+With ``train`` it runs the reference's own ``Trainer.train()`` on the CPU (fp32, no compile) from the
+given initial weights over the given sequence of raw windows (its random window iterator is replaced
+from outside by a fixed one) and writes the final parameters and the per-step learning rates to
+``<dir>/ref_train.pt``.
+
+usage: reference_worker.py <dir> [decode|train]      (reads <dir>/ours.pt)
 """
 import os
 import sys
@@ -97,5 +102,34 @@ def decode():
     torch.save({"decode": out, "prompts": prompts}, os.path.join(d, "ref_decode.pt"))
 
 
+def train():
+    os.environ.setdefault("WANDB_MODE", "disabled")
+    os.environ.setdefault("WANDB_SILENT", "true")
+    from modeling.data import UCITokenizer
+    from modeling.model import initialize_model
+    from modeling.trainer import Trainer
+    from omegaconf import OmegaConf
+
+    d = sys.argv[1]
+    blob = torch.load(os.path.join(d, "ours.pt"), weights_only=False)
+    tok = UCITokenizer(**blob["tokenizer"])
+    cfg = OmegaConf.create({"trainer_config": {}, "data_config": {}, "model_config": {}})
+    trainer = Trainer(cfg, output_dir=os.path.join(d, "ref_run"), device="cpu", dtype="float32", torch_compile=False,
+                      eval_interval=0, log_interval=10 ** 9, save_interval=0, **blob["trainer"])
+    model = initialize_model(tok, os.path.join(ROOT, "baseline", "gpt2-medium"), use_control_token=True,
+                             use_regression_head=True, use_pretrained=False, **blob["shape"])
+    model.load_state_dict(blob["model"], strict=True)
+    stream = np.zeros(4 * tok.max_length, dtype=np.uint32)
+    trainer.setup_dataloaders(tok, stream, [], [])
+    trainer.setup_model(model)
+    batches = [tok.pad_and_collate(list(w.astype(np.uint32))) for w in blob["windows"]]
+    trainer.train_dataiter = iter(batches)
+    lrs = []
+    trainer.optimizer.register_step_post_hook(lambda opt, a, k: lrs.append(opt.param_groups[0]["lr"]))
+    trainer.train()
+    torch.save({"params": {k: v.detach().clone() for k, v in trainer.model.state_dict().items()}, "lrs": lrs},
+               os.path.join(d, "ref_train.pt"))
+
+
 if __name__ == "__main__":
-    decode() if len(sys.argv) > 2 and sys.argv[2] == "decode" else main()
+    {"decode": decode, "train": train}.get(sys.argv[2] if len(sys.argv) > 2 else "", main)()

@@ -140,3 +140,54 @@ def test_decode_strategies_and_prompts_match_the_reference(tmp_path):
     for g, prompt in zip(games, ref["prompts"]):
         assert llm.get_query_pgn(g.board) == prompt
     assert "\n" in ref["prompts"][3].split("\n\n")[1]     # the long game's movetext did wrap
+
+
+def test_training_steps_match_the_reference_trainer(tmp_path):
+    """Four optimizer steps (two micro-batches each, warm-up then cosine decay, clipping, two AdamW
+    groups) of the reference's own ``Trainer.train()`` and of this trainer's CPU path, from the same
+    weights over the same windows: same learning rates, same parameters afterwards."""
+    from allie_b200.config import Config
+    from allie_b200.data import UCITokenizer
+    from allie_b200.models import initialize_model
+    from allie_b200.train.trainer import Trainer
+
+    os.environ["ALLIE_NO_WANDB"] = "1"
+    shape = dict(n_layer=2, n_embd=64, n_head=2, n_positions=64, resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0)
+    tok_kw = dict(max_length=32, vocab_size_multiple_of=128)
+    hyper = dict(batch_size=3, gradient_accumulation_steps=2, lr=2e-3, min_lr=2e-4, weight_decay=0.05, beta1=0.9,
+                 beta2=0.95, grad_clip=0.5, warmup_iters=2, decay_iters=5, max_iters=3)
+    tok = UCITokenizer(**tok_kw)
+    rng = np.random.default_rng(9)
+    n_batches = 2 * 4 + 1                                  # the reference draws one batch ahead
+    windows = (rng.integers(0, 1968, size=(n_batches, 3, 32)).astype(np.uint32)
+               | (rng.integers(0, 40, size=(n_batches, 3, 32)).astype(np.uint32) << 16)
+               | (rng.integers(0, 3, size=(n_batches, 3, 1)).astype(np.uint32) << 14))
+    windows[:, :, 0] = len(tok) + 1400
+    windows[:, :, 1] = len(tok) + 1900
+    torch.manual_seed(2)
+    model = initialize_model(tok, "gpt2", use_control_token=True, use_regression_head=True, **shape)
+    torch.save({"model": model.state_dict(), "tokenizer": tok_kw, "shape": shape, "trainer": hyper,
+                "windows": windows.astype(np.int64)}, tmp_path / "ours.pt")
+    res = subprocess.run([sys.executable, os.path.join(HERE, "reference_worker.py"), str(tmp_path), "train"],
+                         capture_output=True, text=True, timeout=900)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
+    ref = torch.load(tmp_path / "ref_train.pt", weights_only=False)
+
+    tr = Trainer(Config({"trainer_config": {}}), output_dir=str(tmp_path / "run"), device="cpu", eval_interval=0,
+                 log_interval=-1, save_interval=0, use_wandb=False, **hyper)
+    tr.setup_dataloaders(tok, np.zeros(4 * 32, dtype=np.uint32), [], [])
+    tr.setup_model(model)
+    lrs = []
+    for step in range(4):
+        lrs.append(tr.get_lr())
+        wins = [torch.from_numpy(windows[2 * step + ms].view(np.int32).copy()) for ms in range(2)]
+        tr.train_step(wins)
+        tr.iter_num += 1
+    assert len(ref["lrs"]) == 4 and np.allclose(lrs, ref["lrs"], rtol=1e-12, atol=0)
+    assert lrs[0] == 0.0 and lrs[2] == 2e-3 and lrs[3] < lrs[2]
+    ours = model.state_dict()
+    assert set(ours) == set(ref["params"])
+    worst = max((ours[k].float() - v.float()).abs().max().item() for k, v in ref["params"].items())
+    assert worst < 2e-5, worst
+    moved = (ours["model.model.transformer.h.0.mlp.c_fc.weight"] - torch.load(tmp_path / "ours.pt", weights_only=False)["model"]["model.model.transformer.h.0.mlp.c_fc.weight"]).abs().max().item()
+    assert moved > 1e-4                                    # the steps did change the weights
