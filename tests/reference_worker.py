@@ -120,14 +120,16 @@ def train():
                              use_regression_head=True, use_pretrained=False, **blob["shape"])
     model.load_state_dict(blob["model"], strict=True)
     stream = np.zeros(4 * tok.max_length, dtype=np.uint32)
-    trainer.setup_dataloaders(tok, stream, [], [])
+    trainer.setup_dataloaders(tok, stream, blob.get("val", []), [])
     trainer.setup_model(model)
     batches = [tok.pad_and_collate(list(w.astype(np.uint32))) for w in blob["windows"]]
     trainer.train_dataiter = iter(batches)
     lrs = []
     trainer.optimizer.register_step_post_hook(lambda opt, a, k: lrs.append(opt.param_groups[0]["lr"]))
     trainer.train()
-    torch.save({"params": {k: v.detach().clone() for k, v in trainer.model.state_dict().items()}, "lrs": lrs},
+    val = trainer.validate() if blob.get("val") else {}
+    torch.save({"params": {k: v.detach().clone() for k, v in trainer.model.state_dict().items()}, "lrs": lrs,
+                "val": val},
                os.path.join(d, "ref_train.pt"))
 
 

@@ -166,8 +166,11 @@ def test_training_steps_match_the_reference_trainer(tmp_path):
     windows[:, :, 1] = len(tok) + 1900
     torch.manual_seed(2)
     model = initialize_model(tok, "gpt2", use_control_token=True, use_regression_head=True, **shape)
+    from test_trainer_cpu import _random_games, _row
+
+    val = [_row(g) for g in _random_games(7, seed=3)]      # 7 games, batch size 3: a ragged last batch
     torch.save({"model": model.state_dict(), "tokenizer": tok_kw, "shape": shape, "trainer": hyper,
-                "windows": windows.astype(np.int64)}, tmp_path / "ours.pt")
+                "windows": windows.astype(np.int64), "val": val}, tmp_path / "ours.pt")
     res = subprocess.run([sys.executable, os.path.join(HERE, "reference_worker.py"), str(tmp_path), "train"],
                          capture_output=True, text=True, timeout=900)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
@@ -175,7 +178,7 @@ def test_training_steps_match_the_reference_trainer(tmp_path):
 
     tr = Trainer(Config({"trainer_config": {}}), output_dir=str(tmp_path / "run"), device="cpu", eval_interval=0,
                  log_interval=-1, save_interval=0, use_wandb=False, **hyper)
-    tr.setup_dataloaders(tok, np.zeros(4 * 32, dtype=np.uint32), [], [])
+    tr.setup_dataloaders(tok, np.zeros(4 * 32, dtype=np.uint32), val, [])
     tr.setup_model(model)
     lrs = []
     for step in range(4):
@@ -189,5 +192,9 @@ def test_training_steps_match_the_reference_trainer(tmp_path):
     assert set(ours) == set(ref["params"])
     worst = max((ours[k].float() - v.float()).abs().max().item() for k, v in ref["params"].items())
     assert worst < 2e-5, worst
+    got_val = tr.validate()                                # mean over batches of the per-batch losses
+    assert set(got_val) == set(ref["val"]) == {"val/lm_loss", "val/value_loss", "val/time_loss", "val/loss"}
+    for k, v in ref["val"].items():
+        assert abs(got_val[k] - v) < 1e-4 * max(1.0, abs(v)), (k, got_val[k], v)
     moved = (ours["model.model.transformer.h.0.mlp.c_fc.weight"] - torch.load(tmp_path / "ours.pt", weights_only=False)["model"]["model.model.transformer.h.0.mlp.c_fc.weight"]).abs().max().item()
     assert moved > 1e-4                                    # the steps did change the weights
