@@ -7,7 +7,7 @@ from __future__ import annotations
 
 import copy
 from dataclasses import asdict, dataclass, field
-from typing import Any, Iterator, Mapping
+from typing import Any, Mapping
 
 import yaml
 

@@ -7,7 +7,7 @@ from __future__ import annotations
 import functools
 import math
 
-from .uci import EngineUnavailable, UCIEngine
+from .uci import UCIEngine
 
 _engine: UCIEngine | None = None
 

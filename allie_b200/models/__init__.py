@@ -34,7 +34,7 @@ def _load_pretrained_body(model: GPT2LM, base_model: str) -> bool:
     body = {"transformer." + k: v for k, v in sd.items()
             if k not in ("wte.weight", "lm_head.weight") and not k.endswith(".attn.bias")
             and not k.endswith(".attn.masked_bias")}
-    missing, unexpected = model.load_state_dict(body, strict=False)
+    _, unexpected = model.load_state_dict(body, strict=False)
     if unexpected:
         logger.warning("unexpected pretrained keys: %s", unexpected[:5])
     if wte is not None:

@@ -19,8 +19,6 @@ autocast; GEMM operands are bf16 with fp32 accumulation.
 from __future__ import annotations
 
 import math
-from dataclasses import dataclass
-from typing import Iterable
 
 import torch
 import torch.nn as nn

@@ -8,8 +8,6 @@ from __future__ import annotations
 
 from ctypes import c_float, c_int, c_uint, c_ulonglong
 
-import torch
-
 from . import _lib
 from ._lib import ptr, stream_ptr
 

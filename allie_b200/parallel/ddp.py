@@ -15,7 +15,6 @@ The reference gets the same effect from ``DistributedDataParallel`` bucketed all
 from __future__ import annotations
 
 import logging
-import os
 
 import torch
 import torch.distributed as dist

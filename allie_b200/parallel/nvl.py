@@ -143,7 +143,6 @@ class NvlGradOptimizer:
     def gather_state(self) -> tuple[torch.Tensor, torch.Tensor]:
         """All ranks' moment shards concatenated to full flat arenas (for checkpoints)."""
         a = self.engine.arena
-        per = (self.exp_avg.numel() + 0)
         sizes = [torch.zeros(1, dtype=torch.int64, device=self.exp_avg.device) for _ in range(self.world)]
         dist.all_gather(sizes, torch.tensor([self.shard_n], dtype=torch.int64, device=self.exp_avg.device))
         mx = int(max(int(s) for s in sizes))

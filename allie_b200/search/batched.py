@@ -10,11 +10,9 @@ the KL-regularised policy, think time, resign flag.
 """
 from __future__ import annotations
 
-import ctypes
-import math
 from time import perf_counter
 from ctypes import POINTER, c_float, c_int, c_void_p
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 
 import numpy as np
 import torch

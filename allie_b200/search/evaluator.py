@@ -10,7 +10,6 @@ The step is a fixed sequence of kernels over static buffers and is replayed as a
 """
 from __future__ import annotations
 
-import ctypes
 from ctypes import c_float, c_int, c_longlong
 
 import numpy as np

@@ -16,7 +16,6 @@ import select
 import socket
 import time
 from dataclasses import dataclass, field
-from typing import Any
 
 import torch
 

@@ -27,7 +27,7 @@ import threading
 import time
 from collections import defaultdict, deque
 from os.path import join
-from typing import Any, Iterable, Optional
+from typing import Iterable, Optional
 
 import numpy as np
 import torch

@@ -1,5 +1,4 @@
 """Move server round trip over a real localhost socket (CPU)."""
-import json
 import socket
 import threading
 import time

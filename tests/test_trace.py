@@ -2,7 +2,6 @@
 import time
 
 import numpy as np
-import torch
 
 from allie_b200.utils.trace import PhaseTracer
 

@@ -8,7 +8,6 @@ test checks that the variant returns what the regular entry returns, twice in a 
 is shared between calls and must not leak state from one into the next), and that oversize
 problems are rejected instead of overrunning the array.  It is collected last on purpose.
 """
-import ctypes
 from ctypes import c_float, c_int, c_uint, c_ulonglong, c_void_p
 
 import pytest
