@@ -241,6 +241,8 @@ class B200Engine:
         if key in self._bufs:
             return self._bufs[key]
         cfg, dev = self.cfg, self.device
+        if T > cfg.n_positions:
+            raise ValueError(f"sequence length {T} exceeds the model's {cfg.n_positions} learned positions")
         M, d, F, V = B * T, cfg.n_embd, cfg.ffn_dim, cfg.vocab_size
         bf, f32, i32 = torch.bfloat16, torch.float32, torch.int32
         e = lambda *s, dt=bf: torch.empty(*s, dtype=dt, device=dev)

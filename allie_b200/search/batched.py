@@ -127,6 +127,7 @@ class KVStepEvaluator:
         self.tok, self.n = tokenizer, n_trees
         self.anc_max, self.legal_max = anc_max, legal_max
         self.max_slots = self.kv.S
+        self.max_positions = int(engine.cfg.n_positions)
         self.positions = 0
 
     def prefill(self, games: list[Game | None]):
@@ -197,6 +198,11 @@ class BatchedMCTS:
             if nl < 0:
                 raise ValueError(f"illegal move in game {t}")
             root_legal.append(legal_buf[:nl].copy())
+            # a leaf at depth k sits at position prefix_len + k - 1 of the learned position table
+            limit = getattr(self.ev, "max_positions", None)
+            if limit is not None and prefix_len + self.depth_limit > limit:
+                raise ValueError(f"game {t}: {prefix_len} tokens plus a search depth of {self.depth_limit} exceed "
+                                 f"the model's {limit} positions; lower depth_limit or the tokenizer's max_length")
         logits, value, time = self.ev.prefill(padded)
         budgets = np.zeros(n, np.int32)
         cp = np.full(n, self.c_puct, np.float32)

@@ -79,3 +79,18 @@ def test_partial_batch_and_budget_callable(tok_model):
     assert len(res) == 1 and res[0].n_sims == 17 and int(res[0].visits.sum()) == 17
     res0 = bm.search(games, n_sims=0)
     assert torch.allclose(res0[0].policy, torch.from_numpy(res0[0].priors))
+
+
+def test_search_refuses_positions_beyond_the_table(tok_model):
+    """An evaluator that names the size of the model's position table: a game whose tokens plus the
+    search depth would index past it is refused on the host, before anything is evaluated."""
+    tok, _ = tok_model
+    ev = RunnerStepEvaluator(FakeRunner(len(tok)), tok, 1, 64, 224)
+    ev.max_positions = 40
+    bm = BatchedMCTS(tok, ev, n_trees=1, n_sims=4, anc_max=64, depth_limit=30)
+    game = Game("180+0", 1500, 1600, None, False, GAMES[1], [1] * len(GAMES[1]))     # 8 tokens + depth 30 fits
+    assert int(bm.search([game])[0].visits.sum()) == 4
+    bm2 = BatchedMCTS(tok, ev, n_trees=1, n_sims=4, anc_max=64, depth_limit=33)
+    with pytest.raises(ValueError, match="positions"):
+        bm2.search([game])
+    assert ev.runner.calls == 1 + 4 + 0        # the refused search evaluated nothing
