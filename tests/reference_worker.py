@@ -92,6 +92,14 @@ def decode():
                              "think_time": s.think_time, "resigned": s.resigned,
                              "move": strat.decode_full(g).move})
             out[f"{name}:{sorted(kwargs.items())}"] = {"rows": rows, "stats": strat.run_stats()}
+    quick = None
+    if blob.get("rows"):
+        import pandas as pd
+        from evaluation.evaluate import evaluate_quick
+
+        with torch.inference_mode():
+            strat = DECODE_STRATEGIES["policy"](model, tok, sample=False, device="cpu", precision="float32")
+            quick = evaluate_quick(strat, pd.DataFrame(blob["rows"]))["games"]
     llm = ChessLLM(None, {"num_lookahead_tokens": 10})
     prompts = []
     for g in games:
@@ -99,7 +107,7 @@ def decode():
         for mv in g.moves:
             board.push_uci(mv)
         prompts.append(llm.get_query_pgn(board))
-    torch.save({"decode": out, "prompts": prompts}, os.path.join(d, "ref_decode.pt"))
+    torch.save({"decode": out, "prompts": prompts, "quick": quick}, os.path.join(d, "ref_decode.pt"))
 
 
 def train():

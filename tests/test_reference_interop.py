@@ -116,8 +116,13 @@ def test_decode_strategies_and_prompts_match_the_reference(tmp_path):
     games = [Game("180+0", 1500 + 300 * i, 2300, None, False, mv, [3] * len(mv)) for i, mv in enumerate(lines)]
     strategies = [("policy", {}), ("mcts", {"n_sims": 24}), ("mcts", {"n_sims": 9, "kl_reg_solution": False}),
                   ("adaptive-mcts", {"mean_n_sims": 12})]
+    from test_trainer_cpu import _random_games, _row
+
+    rows = [_row(g) for g in _random_games(4, seed=8)]
+    rows[1]["termination"] = "Time forfeit"                # not a resignation
     torch.save({"model": model.state_dict(), "tokenizer": tok_kw, "shape": shape,
-                "games": [g.to_dict() for g in games], "strategies": strategies}, tmp_path / "ours.pt")
+                "games": [g.to_dict() for g in games], "strategies": strategies, "rows": rows},
+               tmp_path / "ours.pt")
     res = subprocess.run([sys.executable, os.path.join(HERE, "reference_worker.py"), str(tmp_path), "decode"],
                          capture_output=True, text=True, timeout=900)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
@@ -198,3 +203,17 @@ def test_training_steps_match_the_reference_trainer(tmp_path):
         assert abs(got_val[k] - v) < 1e-4 * max(1.0, abs(v)), (k, got_val[k], v)
     moved = (ours["model.model.transformer.h.0.mlp.c_fc.weight"] - torch.load(tmp_path / "ours.pt", weights_only=False)["model"]["model.model.transformer.h.0.mlp.c_fc.weight"]).abs().max().item()
     assert moved > 1e-4                                    # the steps did change the weights
+
+    # the evaluation CLI's quick mode: the same per-game records as the reference's evaluate_quick
+    from allie_b200.evaluation.evaluate import evaluate_quick
+
+    for variant in ("policy", "policy-batched"):
+        strat = DECODE_STRATEGIES[variant](model, tok, sample=False, device="cpu")
+        mine = evaluate_quick(strat, rows, batch_size=5)["games"]
+        assert len(mine) == len(ref["quick"]) == 4
+        for a, b_ in zip(mine, ref["quick"]):
+            for key in ("model-move", "human-move", "top-move-legal", "human-resigned", "model-resigned"):
+                assert list(a[key]) == list(b_[key]), (variant, key)
+            for key in ("sampled-move-legal", "model-think-time", "model-white-advantage"):
+                assert np.allclose(a[key], b_[key], atol=2e-4), (variant, key)
+    assert ref["quick"][0]["human-resigned"][-1] is True and ref["quick"][1]["human-resigned"][-1] is False
