@@ -26,27 +26,41 @@ import numpy as np
 from ..data import Game, UCITokenizer, json_to_game
 
 
-def keep_probability(elo: int, counts: dict[int, int], target: int) -> float:
-    """Per-100-ELO-bin keep probability that flattens the rating histogram to ``target`` games."""
-    return min(1.0, target / max(1, counts.get(elo // 100, 1)))
+def elo_bin(row: dict) -> int:
+    """Rating bin of a game: the mean of both players' ratings, rounded to the nearest hundred
+    (reference ``sample-lichess.py:58-59``)."""
+    return round((int(row["white-elo"]) + int(row["black-elo"])) / 200)
 
 
-def sample(src: str, prefix: str, target_per_bin: int = 100_000, seed: int = 0) -> None:
+def keep_probability(bin_: int, counts: dict[int, int], target: int) -> float:
+    """Keep probability of a rating bin that flattens the histogram to ``target`` games per bin.
+    The reference ships these numbers as a fixed table computed on its 2022 blitz dump; here they
+    are computed from the file being sampled (a counting pass first)."""
+    return min(1.0, target / max(1, counts.get(bin_, 1)))
+
+
+def sample(src: str, prefix: str, target_per_bin: int = 100_000, seed: int = 0) -> dict[str, int]:
+    """ELO-balanced subsample split into ``<prefix>-train/val/test.jsonl`` with probabilities
+    1 - 3e-4 / 1e-4 / 2e-4; returns the number of games written per split."""
     rng = random.Random(seed)
     counts: dict[int, int] = collections.Counter()
     with open(src) as f:
         for line in f:
-            counts[int(json.loads(line)["white-elo"]) // 100] += 1
+            counts[elo_bin(json.loads(line))] += 1
     outs = {k: open(f"{prefix}-{k}.jsonl", "w") for k in ("train", "val", "test")}
+    written = dict.fromkeys(outs, 0)
     with open(src) as f:
         for line in f:
             row = json.loads(line)
-            if rng.random() > keep_probability(int(row["white-elo"]), counts, target_per_bin):
+            if rng.random() >= keep_probability(elo_bin(row), counts, target_per_bin):
                 continue
             u = rng.random()
-            outs["val" if u < 1e-4 else "test" if u < 3e-4 else "train"].write(line)
+            split = "val" if u < 1e-4 else "test" if u < 3e-4 else "train"
+            outs[split].write(line if line.endswith("\n") else line + "\n")
+            written[split] += 1
     for o in outs.values():
         o.close()
+    return written
 
 
 def tokenize(src: str, dst: str, seed: int = 0, tokenizer: UCITokenizer | None = None) -> int:
@@ -184,7 +198,7 @@ def main(argv=None) -> None:
         print(json.dumps({k: len(v) for k, v in puzzles(a.csv, a.out_dir, a.n, download=a.download).items()}))
         return
     if a.cmd == "sample":
-        sample(a.src, a.prefix, a.target)
+        print(json.dumps(sample(a.src, a.prefix, a.target)))
     elif a.cmd == "tokenize":
         print(tokenize(a.src, a.dst), "tokens")
     elif a.cmd == "concat":

@@ -68,3 +68,21 @@ def test_position_values_and_puzzles(tmp_path):
     assert len(fetched) == 20 and fetched[0].startswith("https://lichess.org/game/export/game")
     assert len((tmp_path / "out" / "mateIn3.csv").read_text().splitlines()) == 5
     assert len(list((tmp_path / "out" / "pgn").iterdir())) == 20
+
+
+def test_elo_balanced_sampling(tmp_path):
+    from allie_b200.etl.dataset import elo_bin, keep_probability, sample
+
+    assert elo_bin({"white-elo": 1449, "black-elo": 1450}) == 14 and elo_bin({"white-elo": "1551", "black-elo": 1550}) == 16
+    assert keep_probability(15, {15: 400}, 100) == 0.25 and keep_probability(30, {15: 400}, 100) == 1.0
+    src = tmp_path / "all.jsonl"
+    with open(src, "w") as f:
+        for i in range(3000):                                   # 2 400 games around 1500, 600 around 2200
+            elo = 1500 if i % 5 else 2200
+            f.write(json.dumps({"white-elo": elo, "black-elo": elo + 10, "moves-uci": "e2e4"}) + "\n")
+    written = sample(str(src), str(tmp_path / "s"), target_per_bin=600, seed=1)
+    rows = [json.loads(l) for l in open(tmp_path / "s-train.jsonl")]
+    assert written["train"] == len(rows) and sum(written.values()) <= 3000
+    low = sum(r["white-elo"] == 1500 for r in rows)
+    high = sum(r["white-elo"] == 2200 for r in rows)
+    assert 500 < low < 700 and 570 < high <= 600            # both bins end near the target
