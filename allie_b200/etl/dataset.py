@@ -72,8 +72,9 @@ def tokenize(src: str, dst: str, seed: int = 0, tokenizer: UCITokenizer | None =
     with open(src) as f:
         for line in f:
             g = json_to_game(json.loads(line))
-            u = rng.random()
-            chunks.append(tok.tokenize(g, add_elo=not u < 0.05, add_time_control=not 0.05 <= u < 0.10))
+            add_elo = rng.random() > 0.05                  # two independent draws, as the reference makes them
+            add_time_control = rng.random() > 0.05
+            chunks.append(tok.tokenize(g, add_elo=add_elo, add_time_control=add_time_control))
     rng.shuffle(chunks)
     flat = np.concatenate(chunks).astype(np.uint32)
     mm = np.memmap(dst, dtype=np.uint32, mode="w+", shape=flat.shape)

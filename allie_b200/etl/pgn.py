@@ -1,8 +1,8 @@
 """PGN -> JSONL rows (reference ``src/data/process-lichess.py:1-147``).
 
 Streams a (optionally zstd-compressed) Lichess PGN dump, keeps Blitz games longer than 8 plies and
-writes one JSON object per game with the keys the tokenizer expects: ``time-control, white-elo,
-black-elo, result, termination, moves-uci, moves-seconds``.  Seconds per move come from the clock
+writes one JSON object per game with the reference's keys: ``game-id, moves-uci, moves-seconds, event,
+result, white-elo, black-elo, termination, time-control, opening``.  Seconds per move come from the clock
 comments: previous clock of the same side minus the new clock plus the increment.  SAN is resolved
 against the C++ move generator (python-chess is not a dependency)."""
 from __future__ import annotations
@@ -91,9 +91,10 @@ def parse_game(text: str) -> dict | None:
         moves.append(uci)
     if len(moves) <= 8 or len(seconds) != len(moves):
         return None
-    return {"time-control": tc, "white-elo": int(tags["WhiteElo"]), "black-elo": int(tags["BlackElo"]),
-            "result": tags.get("Result", "*"), "termination": tags.get("Termination", ""),
-            "moves-uci": " ".join(moves), "moves-seconds": seconds}
+    return {"game-id": tags.get("Site", ""), "moves-uci": " ".join(moves), "moves-seconds": seconds,
+            "event": tags.get("Event", ""), "result": tags.get("Result", "*"),
+            "white-elo": int(tags["WhiteElo"]), "black-elo": int(tags["BlackElo"]),
+            "termination": tags.get("Termination", ""), "time-control": tc, "opening": tags.get("Opening", "")}
 
 
 def iter_games(stream: io.TextIOBase):
