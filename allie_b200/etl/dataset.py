@@ -95,14 +95,22 @@ def concat(parts: list[str], dst: str) -> int:
     return total
 
 
-def elo_stats(src: str) -> dict:
-    elos = []
+def elo_stats(src: str, dst: str | None = None) -> dict:
+    """Rating statistics of a games file.  ``histogram`` is what the reference computes
+    (``compute-elo-stats.py``): the number of games per mean-rating bin of 100 points, bins 0..49;
+    with ``dst`` it is written there as JSON, the input of a sampling table."""
+    elos, hist = [], [0] * 50
     with open(src) as f:
         for line in f:
             r = json.loads(line)
             elos += [int(r["white-elo"]), int(r["black-elo"])]
+            hist[min(49, elo_bin(r))] += 1
+    if dst is not None:
+        with open(dst, "w") as f:
+            json.dump(hist, f, indent=2)
     a = np.array(elos)
-    return {"n": int(a.size), "mean": float(a.mean()), "std": float(a.std()), "min": int(a.min()), "max": int(a.max())}
+    return {"n": int(a.size), "mean": float(a.mean()), "std": float(a.std()), "min": int(a.min()), "max": int(a.max()),
+            "histogram": hist}
 
 
 def random_games(dst: str, n: int = 1000, max_plies: int = 120, seed: int = 0) -> None:
@@ -186,7 +194,7 @@ def main(argv=None) -> None:
     s = sub.add_parser("sample"); s.add_argument("src"); s.add_argument("prefix"); s.add_argument("--target", type=int, default=100_000)
     s = sub.add_parser("tokenize"); s.add_argument("src"); s.add_argument("dst")
     s = sub.add_parser("concat"); s.add_argument("parts", nargs="+"); s.add_argument("dst")
-    s = sub.add_parser("elo-stats"); s.add_argument("src")
+    s = sub.add_parser("elo-stats"); s.add_argument("src"); s.add_argument("dst", nargs="?")
     s = sub.add_parser("random-games"); s.add_argument("dst"); s.add_argument("--n", type=int, default=1000)
     s = sub.add_parser("position-values"); s.add_argument("src"); s.add_argument("--nodes", type=int, default=10_000_000)
     s = sub.add_parser("puzzles"); s.add_argument("csv"); s.add_argument("out_dir"); s.add_argument("--n", type=int, default=100)
@@ -205,7 +213,7 @@ def main(argv=None) -> None:
     elif a.cmd == "concat":
         print(concat(a.parts, a.dst), "tokens")
     elif a.cmd == "elo-stats":
-        print(json.dumps(elo_stats(a.src)))
+        print(json.dumps(elo_stats(a.src, a.dst)))
     else:
         random_games(a.dst, a.n)
 

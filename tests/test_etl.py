@@ -42,7 +42,8 @@ def test_parse_game_and_stream(tmp_path):
     n = tokenize(str(tmp_path / "g.jsonl"), str(tmp_path / "a.bin"), tokenizer=tok)
     assert n == np.memmap(tmp_path / "a.bin", dtype=np.uint32, mode="r").size
     assert concat([str(tmp_path / "a.bin"), str(tmp_path / "a.bin")], str(tmp_path / "c.bin")) == 2 * n
-    assert elo_stats(str(tmp_path / "g.jsonl"))["n"] == 40
+    st = elo_stats(str(tmp_path / "g.jsonl"), str(tmp_path / "hist.json"))
+    assert st["n"] == 40 and sum(st["histogram"]) == 20 and json.load(open(tmp_path / "hist.json")) == st["histogram"]
 
 
 def test_position_values_and_puzzles(tmp_path):
