@@ -52,11 +52,12 @@ class System:
 
 
 SYSTEMS: dict[str, System] = {
-    "maia": System(20602, None, "maia", {"sample": False}),
+    "maia": System(20602, None, "maia", {}),
     "humanlike": System(20600, None, "policy", {"sample": True}),
     "grandmaster": System(20601, 2500, "policy", {"sample": False}),
-    "humanlike-adaptive-rb": System(20607, None, "adaptive-mcts", {"mean_n_sims": 50, "sample": "rating-based"}),
-    "humanlike-mcts-rb": System(20608, None, "mcts", {"n_sims": 50, "sample": "rating-based"}),
+    "humanlike-adaptive-rb": System(20607, None, "adaptive-mcts",
+                                    {"mean_n_sims": 50, "c_puct": 1.25, "sample": "rating-based"}),
+    "humanlike-mcts-rb": System(20608, None, "mcts", {"n_sims": 50, "c_puct": 1.25, "sample": "rating-based"}),
 }
 
 DEFAULT_SYSTEM = "humanlike"

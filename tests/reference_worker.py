@@ -56,7 +56,10 @@ def main():
                             lr=1e-3, betas=(0.9, 0.95))
     opt.load_state_dict(blob["optimizer"])
     first = opt.state_dict()["state"][0]
-    torch.save({"batch": {k: v for k, v in batch.items()},
+    from server.utils import SYSTEMS
+
+    systems = {a: (s.port, s.elo, s.algorithm, dict(s.algorithm_config)) for a, s in SYSTEMS.items()}
+    torch.save({"batch": {k: v for k, v in batch.items()}, "systems": systems,
                 "out": {k: out[k].float() for k in ("logits", "loss", "lm_loss", "value_loss", "time_loss",
                                                     "value_logits", "time_logits")},
                 "words": words, "collated_games": collated,

@@ -60,6 +60,9 @@ def test_checkpoint_tokenizer_and_forward_match_the_reference(tmp_path):
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
     ref = torch.load(tmp_path / "ref_out.pt", weights_only=False)
 
+    from allie_b200.serve import SYSTEMS
+
+    assert {a: (s.port, s.elo, s.algorithm, dict(s.algorithm_config)) for a, s in SYSTEMS.items()} == ref["systems"]
     assert ref["vocab"] == len(tok) and ref["ids"] == {"bos": tok.bos_token_id, "pad": tok.pad_token_id}
     batch = tok.pad_and_collate(list(windows.astype(np.uint32)))
     assert set(batch) == set(ref["batch"])
