@@ -172,28 +172,36 @@ def serve(alias: str, model, tokenizer: UCITokenizer, device: str | None = None,
 
 
 def main(argv: list[str] | None = None) -> None:
-    """``python -m allie_b200.serve.server <alias> [config.yaml] [--sequential]`` - loads
-    ``{output_dir}/best.pt``; ``--sequential`` answers one request at a time like the reference."""
-    import sys
+    """``python -m allie_b200.serve.server <alias> [config.yaml] [options]`` - loads
+    ``{output_dir}/best.pt`` (or ``--checkpoint``) and serves the system on its registry port."""
+    import argparse
     from os.path import join
 
     from ..config import load_config
     from ..models import initialize_model
     from ..utils.logging import setup_logging
 
-    argv = list(sys.argv[1:] if argv is None else argv)
-    batched = "--sequential" not in argv
-    if not batched:
-        argv.remove("--sequential")
-    alias = argv[0]
-    cfg = load_config(argv[1] if len(argv) > 1 else "pretrain_config/medium.yaml")
+    ap = argparse.ArgumentParser(description="Allie move server")
+    ap.add_argument("alias", choices=sorted(SYSTEMS))
+    ap.add_argument("config", nargs="?", default="pretrain_config/medium.yaml")
+    ap.add_argument("--sequential", action="store_true", help="one request at a time, like the reference server")
+    ap.add_argument("--max-batch", type=int, default=64, help="connections answered per batch")
+    ap.add_argument("--port", type=int, default=None, help="defaults to the system's registry port")
+    ap.add_argument("--host", default="localhost")
+    ap.add_argument("--device", default=None)
+    ap.add_argument("--checkpoint", default=None, help="defaults to {output_dir}/best.pt; 'none' = random init")
+    ap.add_argument("--no-self-test", action="store_true")
+    a = ap.parse_args(argv)
+    cfg = load_config(a.config)
     setup_logging()
     tokenizer = UCITokenizer(**cfg.data_config.tokenizer_config)
     model = initialize_model(tokenizer, **{**cfg.model_config, "use_pretrained": False})
-    ckpt = torch.load(join(cfg.trainer_config.output_dir, "best.pt"), map_location="cpu", weights_only=False)
-    model.load_state_dict(ckpt["model"])
+    path = a.checkpoint or join(cfg.trainer_config.output_dir, "best.pt")
+    if path != "none":
+        model.load_state_dict(torch.load(path, map_location="cpu", weights_only=False)["model"])
     model.eval()
-    serve(alias, model, tokenizer, batched=batched)
+    serve(a.alias, model, tokenizer, device=a.device, host=a.host, port=a.port, self_test=not a.no_self_test,
+          max_batch=a.max_batch, batched=not a.sequential)
 
 
 if __name__ == "__main__":
