@@ -4,10 +4,13 @@ Streams a (optionally zstd-compressed) Lichess PGN dump, keeps Blitz games longe
 writes one JSON object per game with the reference's keys: ``game-id, moves-uci, moves-seconds, event,
 result, white-elo, black-elo, termination, time-control, opening``.  Seconds per move come from the clock
 comments: previous clock of the same side minus the new clock plus the increment.  SAN is resolved
-against the C++ move generator (python-chess is not a dependency)."""
+against the C++ move generator (python-chess is not a dependency); the whole movetext of a game is
+parsed by one C++ call (``csrc/pgn_api.cpp``), with a Python statement of the same rules kept as its
+oracle."""
 from __future__ import annotations
 
 import argparse
+import ctypes
 import io
 import json
 import re
@@ -50,7 +53,39 @@ def san_to_uci(board: Board, san: str) -> str:
     return cands[0]
 
 
-def parse_game(text: str) -> dict | None:
+_native_ready = False
+
+
+def _native():
+    global _native_ready
+    from ..ops import _lib
+
+    lib = _lib.host()
+    if not _native_ready:
+        ip = ctypes.POINTER(ctypes.c_int)
+        lib.pgn_parse_movetext.argtypes = [ctypes.c_char_p, ctypes.c_int, ctypes.c_int, ctypes.c_char_p,
+                                           ctypes.c_int, ip, ctypes.c_int, ip]
+        _native_ready = True
+    return lib
+
+
+def parse_movetext(movetext: str, base: int, inc: int, max_moves: int = 1024) -> tuple[list[str], list[int]] | None:
+    """(UCI moves, seconds per move) of one game's movetext through the C++ parser
+    (``csrc/pgn_api.cpp``); None when a move cannot be resolved."""
+    out = ctypes.create_string_buffer(6 * max_moves + 8)
+    secs = (ctypes.c_int * max_moves)()
+    n_secs = ctypes.c_int(0)
+    n = _native().pgn_parse_movetext(movetext.encode(), base, inc, out, len(out), secs, max_moves,
+                                     ctypes.byref(n_secs))
+    if n < 0:
+        return None
+    return out.value.decode().split(), list(secs[: n_secs.value])
+
+
+def parse_game(text: str, native: bool = True) -> dict | None:
+    """One PGN game -> JSONL row, or None when the game is filtered out (not Blitz, unknown ratings,
+    no increment field, eight plies or fewer, clock comments missing, an unreadable move).
+    ``native=False`` takes the pure-Python parser (the oracle of the C++ one)."""
     tags, body = {}, []
     for line in text.splitlines():
         m = _TAG.match(line.strip())
@@ -65,6 +100,12 @@ def parse_game(text: str) -> dict | None:
         return None
     base, inc = (int(x) for x in tc.split("+"))
     movetext = " ".join(body)
+    if native:
+        parsed = parse_movetext(movetext, base, inc)
+        if parsed is None:
+            return None
+        moves, seconds = parsed
+        return _row(tags, tc, moves, seconds)
     tokens = re.findall(r"\{[^}]*\}|\S+", movetext)
     board = Board()
     moves, seconds = [], []
@@ -89,6 +130,10 @@ def parse_game(text: str) -> dict | None:
         except ValueError:
             return None
         moves.append(uci)
+    return _row(tags, tc, moves, seconds)
+
+
+def _row(tags: dict, tc: str, moves: list[str], seconds: list[int]) -> dict | None:
     if len(moves) <= 8 or len(seconds) != len(moves):
         return None
     return {"game-id": tags.get("Site", ""), "moves-uci": " ".join(moves), "moves-seconds": seconds,

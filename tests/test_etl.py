@@ -87,3 +87,45 @@ def test_elo_balanced_sampling(tmp_path):
     low = sum(r["white-elo"] == 1500 for r in rows)
     high = sum(r["white-elo"] == 2200 for r in rows)
     assert 500 < low < 700 and 570 < high <= 600            # both bins end near the target
+
+
+def _pgn_of_random_game(rng, plies, glue_numbers=False):
+    """A Lichess-style PGN of a random legal game with clock comments on every move."""
+    b = Board()
+    clocks, parts, ucis = [180, 180], [], []
+    for ply in range(plies):
+        legal = b.legal_moves_uci()
+        if not legal or b.is_game_over():
+            break
+        mv = legal[int(rng.integers(0, len(legal)))]
+        san = b.san(mv)
+        side = ply % 2
+        clocks[side] = max(0, clocks[side] - int(rng.integers(0, 6)) + 2)
+        clk = "{ [%%clk 0:%02d:%02d] }" % (clocks[side] // 60, clocks[side] % 60)
+        if side == 0:
+            parts.append(f"{ply // 2 + 1}.{san}" if glue_numbers else f"{ply // 2 + 1}. {san}")
+        else:
+            parts.append(f"{ply // 2 + 1}... {san}")
+        parts.append(clk)
+        b.push_uci(mv)
+        ucis.append(mv)
+    head = ('[Event "Rated Blitz game"]\n[Site "https://lichess.org/abc"]\n[Result "*"]\n[WhiteElo "1500"]\n'
+            '[BlackElo "1600"]\n[TimeControl "180+2"]\n[Termination "Normal"]\n[Opening "?"]\n\n')
+    return head + " ".join(parts) + " *\n", ucis
+
+
+def test_native_pgn_parser_matches_python_parser():
+    from allie_b200.etl.pgn import parse_movetext
+
+    rng = np.random.default_rng(11)
+    for k in range(12):
+        text, ucis = _pgn_of_random_game(rng, int(rng.integers(10, 120)), glue_numbers=k % 3 == 0)
+        fast, slow = parse_game(text), parse_game(text, native=False)
+        assert fast == slow and fast is not None
+        assert fast["moves-uci"].split() == ucis and fast["game-id"] == "https://lichess.org/abc"
+        assert len(fast["moves-seconds"]) == len(ucis) and min(fast["moves-seconds"]) >= 0
+    assert parse_game(PGN) == parse_game(PGN, native=False)
+    assert parse_movetext("1. e4 e5 2. Ke3", 180, 0) is None                 # illegal move
+    assert parse_movetext("1. e4 e5 2. Nf3 Nc6 3. Bb5 a6 4. O-O 1-0", 180, 0) == (
+        ["e2e4", "e7e5", "g1f3", "b8c6", "f1b5", "a7a6", "e1g1"], [])
+    assert parse_movetext("1. Nf3 Nf6 2. Ng1 Ng8 3. Nc3 Nc6 4. Nf3 Nf6 5. Nd4 Nd5 6. Ndb5 Ndb4", 60, 0)[0][-2:] == ["d4b5", "d5b4"]
