@@ -41,6 +41,7 @@ def _h():
         for fn in ("chess_castling_mask", "chess_ep_square", "chess_fullmove"):
             getattr(lib, fn).argtypes = [c_void_p]
         lib.chess_is_repetition.argtypes = [c_void_p, c_int]
+        lib.chess_parse_san.argtypes = [c_void_p, c_char_p, c_char_p]
         _configured = True
     return lib
 
@@ -232,12 +233,13 @@ class Board:
         return text
 
     def parse_san(self, san: str) -> str:
-        """The legal move (UCI text) that a SAN token denotes; ValueError if none or several do."""
-        want = san.rstrip("+#!?").replace("0-0-0", "O-O-O").replace("0-0", "O-O")
-        hits = [mv for mv in self.legal_moves_uci() if self.san(mv).rstrip("+#") == want]
-        if len(hits) != 1:
-            raise ValueError(f"cannot resolve SAN {san!r} (candidates {hits})")
-        return hits[0]
+        """The legal move (UCI text) that a SAN token denotes; ValueError if none or several do.
+        Check marks and annotations are ignored and more disambiguation than necessary is accepted
+        (resolved by the C++ core)."""
+        buf = ctypes.create_string_buffer(8)
+        if not _h().chess_parse_san(self._h, san.encode(), buf):
+            raise ValueError(f"cannot resolve SAN {san!r} in {self.fen()}")
+        return buf.value.decode()
 
     def push_san(self, san: str) -> str:
         uci = self.parse_san(san)

@@ -79,6 +79,15 @@ bool resolve_san(const Board& b, const char* tok, size_t n, Move& out) {
 
 extern "C" {
 
+// Resolves one SAN move without playing it; writes its UCI text.  Returns 1 on success.
+int chess_parse_san(void* h, const char* san, char* uci_out) {
+  Move m;
+  if (!resolve_san(*static_cast<Board*>(h), san, std::strlen(san), m)) return 0;
+  std::string u = chess::move_uci(m);
+  std::memcpy(uci_out, u.c_str(), u.size() + 1);
+  return 1;
+}
+
 // Plays one SAN move on the board; writes its UCI text (at most 5 characters + NUL).  Returns 1 on
 // success, 0 when the token fits no legal move or more than one.
 int chess_push_san(void* h, const char* san, char* uci_out) {

@@ -40,6 +40,10 @@ def test_san_disambiguation_promotion_and_mate():
     assert b.san("d8h4") == "Qh4#"
     with pytest.raises(ValueError):
         b.parse_san("Qh5")
+    start = Board()
+    assert start.parse_san("Ngf3") == "g1f3" and start.parse_san("e4!?") == "e2e4"   # over-specified / annotated
+    with pytest.raises(ValueError):
+        start.parse_san("Nbf3")
 
 
 def test_en_passant_flag_and_fen_field():
