@@ -41,9 +41,11 @@ class UCIEngine:
             if line.startswith(token):
                 return lines
 
-    def analyse(self, moves: list[str], nodes: int) -> tuple[int | None, int | None, str]:
-        """(centipawns from the side to move's view or None, mate distance or None, best move)."""
-        self._send("position startpos" + (" moves " + " ".join(moves) if moves else ""))
+    def analyse(self, moves: list[str], nodes: int, fen: str | None = None) -> tuple[int | None, int | None, str]:
+        """(centipawns from the side to move's view or None, mate distance or None, best move) of
+        the position reached by ``moves`` from the start position, or from ``fen``."""
+        self._send(("position startpos" if fen is None else f"position fen {fen}")
+                   + (" moves " + " ".join(moves) if moves else ""))
         self._send(f"go nodes {nodes}")
         cp = mate = None
         for line in self._wait("bestmove"):

@@ -36,6 +36,18 @@ def stockfish_eval(moves: list[str], nodes: int = 1_000_000) -> int:
     return _eval_cached(" ".join(moves), nodes)
 
 
+@functools.lru_cache(maxsize=1 << 16)
+def stockfish_eval_fen(fen: str, nodes: int = 1_000_000) -> int:
+    """White-relative centipawns of the position ``fen`` (forced mates count as +-1000, everything
+    is clamped to +-1000): the reference's ``compute_white_centipawn_score``."""
+    cp, mate, _ = get_engine().analyse([], nodes, fen=fen)
+    if mate is not None:
+        cp = 1000 if mate > 0 else -1000
+    cp = 0 if cp is None else cp
+    cp = cp if fen.split()[1] == "w" else -cp
+    return max(-1000, min(1000, cp))
+
+
 def win_percent(cp: float) -> float:
     return 50 + 50 * (2 / (1 + math.exp(-0.00368208 * cp)) - 1)
 
@@ -43,8 +55,7 @@ def win_percent(cp: float) -> float:
 def accuracy_from_win_percents(before: float, after: float) -> float:
     if after >= before:
         return 100.0
-    raw = 103.1668100711649 * math.exp(-0.04354415386753951 * (before - after)) - 3.166924740191411
-    return max(0.0, min(100.0, raw + 1))
+    return max(0.0, 103.1668 * math.exp(-0.04354 * (before - after)) - 3.1669)
 
 
 def move_quality(moves: list[str], move: str) -> tuple[float, float]:

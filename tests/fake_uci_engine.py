@@ -26,8 +26,12 @@ def main():
         elif parts[0] == "isready":
             print("readyok", flush=True)
         elif parts[0] == "position":
-            board = Board()
-            for mv in parts[3:] if len(parts) > 2 and parts[2] == "moves" else []:
+            if parts[1] == "fen":
+                board = Board(" ".join(parts[2:8]))
+                rest = parts[8:]
+            else:
+                board, rest = Board(), parts[2:]
+            for mv in rest[1:] if rest[:1] == ["moves"] else []:
                 board.push_uci(mv)
         elif parts[0] == "go":
             sign = 1 if board.turn else -1

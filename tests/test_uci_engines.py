@@ -40,6 +40,10 @@ def test_client_and_move_quality(fake_engine, monkeypatch):
     assert loss == 0.0 and acc == 100.0
     loss, acc = eval_utils.move_quality("e2e4 d7d5 g1f3 d5e4".split(), "f3g1")  # white keeps the deficit
     assert loss == 0.0
+    assert eval_utils.stockfish_eval_fen("4k3/8/8/8/8/8/8/R3K3 b - - 0 1") == 500       # white-relative at black's turn
+    assert eval_utils.accuracy_from_win_percents(50.0, 60.0) == 100.0
+    assert abs(eval_utils.accuracy_from_win_percents(60.0, 50.0) - (103.1668 * 2.718281828459045 ** -0.4354 - 3.1669)) < 1e-9
+    assert eval_utils.accuracy_from_win_percents(100.0, 0.0) == 0.0
     eng.quit()
     with pytest.raises(EngineUnavailable):
         UCIEngine("/nonexistent/engine")
