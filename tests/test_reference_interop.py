@@ -148,6 +148,19 @@ def test_decode_strategies_and_prompts_match_the_reference(tmp_path):
     for g, prompt in zip(games, ref["prompts"]):
         assert llm.get_query_pgn(g.board) == prompt
     assert "\n" in ref["prompts"][3].split("\n\n")[1]     # the long game's movetext did wrap
+    # the evaluation CLI's quick mode: the same per-game records as the reference's evaluate_quick
+    from allie_b200.evaluation.evaluate import evaluate_quick
+
+    for variant in ("policy", "policy-batched"):
+        strat = DECODE_STRATEGIES[variant](model, tok, sample=False, device="cpu")
+        mine = evaluate_quick(strat, rows, batch_size=5)["games"]
+        assert len(mine) == len(ref["quick"]) == 4
+        for a, b_ in zip(mine, ref["quick"]):
+            for key in ("model-move", "human-move", "top-move-legal", "human-resigned", "model-resigned"):
+                assert list(a[key]) == list(b_[key]), (variant, key)
+            for key in ("sampled-move-legal", "model-think-time", "model-white-advantage"):
+                assert np.allclose(a[key], b_[key], atol=2e-4), (variant, key)
+    assert ref["quick"][0]["human-resigned"][-1] is True and ref["quick"][1]["human-resigned"][-1] is False
 
 
 def test_training_steps_match_the_reference_trainer(tmp_path):
@@ -206,17 +219,3 @@ def test_training_steps_match_the_reference_trainer(tmp_path):
         assert abs(got_val[k] - v) < 1e-4 * max(1.0, abs(v)), (k, got_val[k], v)
     moved = (ours["model.model.transformer.h.0.mlp.c_fc.weight"] - torch.load(tmp_path / "ours.pt", weights_only=False)["model"]["model.model.transformer.h.0.mlp.c_fc.weight"]).abs().max().item()
     assert moved > 1e-4                                    # the steps did change the weights
-
-    # the evaluation CLI's quick mode: the same per-game records as the reference's evaluate_quick
-    from allie_b200.evaluation.evaluate import evaluate_quick
-
-    for variant in ("policy", "policy-batched"):
-        strat = DECODE_STRATEGIES[variant](model, tok, sample=False, device="cpu")
-        mine = evaluate_quick(strat, rows, batch_size=5)["games"]
-        assert len(mine) == len(ref["quick"]) == 4
-        for a, b_ in zip(mine, ref["quick"]):
-            for key in ("model-move", "human-move", "top-move-legal", "human-resigned", "model-resigned"):
-                assert list(a[key]) == list(b_[key]), (variant, key)
-            for key in ("sampled-move-legal", "model-think-time", "model-white-advantage"):
-                assert np.allclose(a[key], b_[key], atol=2e-4), (variant, key)
-    assert ref["quick"][0]["human-resigned"][-1] is True and ref["quick"][1]["human-resigned"][-1] is False
