@@ -139,6 +139,7 @@ def train():
     trainer.optimizer.register_step_post_hook(lambda opt, a, k: lrs.append(opt.param_groups[0]["lr"]))
     trainer.train()
     val = trainer.validate() if blob.get("val") else {}
+    trainer.save_ckpt("last")                      # the reference's own checkpoint file, for the reverse direction
     torch.save({"params": {k: v.detach().clone() for k, v in trainer.model.state_dict().items()}, "lrs": lrs,
                 "val": val},
                os.path.join(d, "ref_train.pt"))

@@ -217,5 +217,19 @@ def test_training_steps_match_the_reference_trainer(tmp_path):
     assert set(got_val) == set(ref["val"]) == {"val/lm_loss", "val/value_loss", "val/time_loss", "val/loss"}
     for k, v in ref["val"].items():
         assert abs(got_val[k] - v) < 1e-4 * max(1.0, abs(v)), (k, got_val[k], v)
+    # the reverse direction: the checkpoint the reference trainer wrote resumes this trainer
+    torch.manual_seed(99)
+    fresh = initialize_model(tok, "gpt2", use_control_token=True, use_regression_head=True, **shape)
+    tr2 = Trainer(Config({"trainer_config": {}}), output_dir=str(tmp_path / "ref_run"), device="cpu", eval_interval=0,
+                  log_interval=-1, save_interval=0, use_wandb=False, **hyper)
+    tr2.setup_dataloaders(tok, np.zeros(4 * 32, dtype=np.uint32), [], [])
+    tr2.setup_model(fresh)                                 # picks up ref_run/last.pt
+    ref_ck = torch.load(tmp_path / "ref_run" / "last.pt", weights_only=False)
+    assert tr2.iter_num == ref_ck["iter_num"] == 4
+    for k, v in fresh.state_dict().items():
+        assert torch.equal(v, ref_ck["model"][k]), k
+    st = tr2.optimizer.state_dict()["state"]
+    assert len(st) == len(ref_ck["optimizer"]["state"]) > 0
+    assert torch.equal(st[0]["exp_avg"], ref_ck["optimizer"]["state"][0]["exp_avg"])
     moved = (ours["model.model.transformer.h.0.mlp.c_fc.weight"] - torch.load(tmp_path / "ours.pt", weights_only=False)["model"]["model.model.transformer.h.0.mlp.c_fc.weight"]).abs().max().item()
     assert moved > 1e-4                                    # the steps did change the weights
