@@ -114,7 +114,7 @@ def evaluate_quick(strategy: DecodeStrategy, rows: list[dict], batch_size: int =
     match = sum(int(a == b) for a, b in zip(flat("model-move"), flat("human-move")))
     hr, mr = flat("human-resigned"), flat("model-resigned")
     return {"games": games, "positions": n, "move_match": match / max(n, 1),
-            "top_move_legal": sum(flat("top-move-legal")) / max(n, 1), "legal_mass": _mean(flat("sampled-move-legal")),
+            "top_move_legal": _mean(int(x) for x in flat("top-move-legal")), "legal_mass": _mean(flat("sampled-move-legal")),
             "resign_rate": sum(mr) / max(len(mr), 1),
             "resign_agreement": _mean(int(a == b) for a, b in zip(hr, mr)),
             "think_time_mae": _mean(time_err), "value_mse": _mean(value_err)}
