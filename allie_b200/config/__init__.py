@@ -54,9 +54,26 @@ def _fix_scalars(node):
     return node
 
 
+def _merge(base: dict, over: dict) -> dict:
+    out = dict(base)
+    for k, v in over.items():
+        out[k] = _merge(out[k], v) if isinstance(v, dict) and isinstance(out.get(k), dict) else v
+    return out
+
+
 def load_config(path: str) -> Config:
+    """Reads a YAML config.  A top-level ``inherit: other.yaml`` key (path relative to the file)
+    loads that file first and lays this file's keys over it, section by section, so that an
+    ablation states only what it changes; files without the key load exactly as written."""
     with open(path) as f:
-        return Config(_fix_scalars(yaml.safe_load(f) or {}))
+        data = _fix_scalars(yaml.safe_load(f) or {})
+    parent = data.pop("inherit", None)
+    if parent is not None:
+        import os
+
+        base = load_config(os.path.join(os.path.dirname(os.path.abspath(path)), parent))
+        data = _merge(base.to_container(), data)
+    return Config(data)
 
 
 def save_config(cfg: Mapping, path: str) -> None:

@@ -172,3 +172,16 @@ def test_window_sampler_prefetch_and_buffer_reuse():
         raise AssertionError("expected the prefetch failure to surface")
     except RuntimeError as e:
         assert "prefetch" in str(e)
+
+
+def test_config_inheritance(tmp_path):
+    (tmp_path / "base.yaml").write_text("trainer_config:\n  lr: 6e-4\n  batch_size: 32\nmodel_config:\n  base_model: gpt2\n")
+    (tmp_path / "sub").mkdir()
+    (tmp_path / "sub" / "child.yaml").write_text("inherit: ../base.yaml\ntrainer_config:\n  batch_size: 8\ndata_config:\n  train_file: x.bin\n")
+    cfg = load_config(str(tmp_path / "sub" / "child.yaml"))
+    assert cfg.trainer_config == {"lr": 6e-4, "batch_size": 8} and cfg.model_config.base_model == "gpt2"
+    assert cfg.data_config.train_file == "x.bin" and "inherit" not in cfg
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    short = load_config(os.path.join(root, "pretrain_config", "ablations", "short.yaml"))
+    assert short.trainer_config.max_iters == 1000000 and short.trainer_config.weight_decay == 1e-2
+    assert short.model_config.base_model == "gpt2-medium" and short.data_config.tokenizer_config.max_length == 512
