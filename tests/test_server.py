@@ -131,3 +131,35 @@ def test_bot_session_plays_both_colours_against_a_server():
     th.join(timeout=10)
     assert not th.is_alive()
     assert request_move.__doc__
+
+
+def test_uci_front_end_tracks_game_and_clocks():
+    import io
+
+    from allie_b200.serve.uci import UCIFrontEnd
+
+    asked = []
+
+    def ask(game):
+        asked.append(game)
+        return {"move": game.legal_moves[0], "think_time": 2.4, "resigned": len(game.moves) >= 2}
+
+    out = io.StringIO()
+    fe = UCIFrontEnd(ask, out)
+    script = ["uci", "setoption name BlackElo value 2100", "isready", "ucinewgame", "position startpos",
+              "go wtime 180000 btime 180000 winc 2000 binc 2000"]
+    for line in script:
+        assert fe.handle(line)
+    first = asked[0].legal_moves[0]
+    fe.handle(f"position startpos moves {first} e7e5")
+    fe.handle("go wtime 179600 btime 175000 winc 2000 binc 2000")       # black used 180 - 175 + 2 = 7 s
+    text = out.getvalue().splitlines()
+    assert "uciok" in text and "readyok" in text and text[-1] == f"bestmove {asked[1].legal_moves[0]}"
+    assert "info string predicted think time 2.4s" in text and "info string the model would resign here" in text
+    g = asked[1]
+    assert (g.time_control, g.white_elo, g.black_elo) == ("180+2", 1500, 2100)
+    assert g.moves == [first, "e7e5"] and g.moves_seconds == [2, 7]      # own predicted time, opponent's from the clock
+    fe.handle("position startpos moves d2d4")                            # another game: clocks forgotten
+    fe.handle("go movetime 1000")
+    assert asked[2].moves == ["d2d4"] and asked[2].moves_seconds == [0]
+    assert fe.handle("stop") and not fe.handle("quit")
