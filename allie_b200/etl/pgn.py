@@ -156,9 +156,22 @@ def iter_games(stream: io.TextIOBase):
 
 
 def open_pgn(path: str):
+    """Text stream of a PGN file: plain, ``.zst`` (through the ``zstandard`` module, else the ``zstd``
+    command line tool) or ``-`` for standard input (``zstdcat dump.pgn.zst | python -m allie_b200.etl.pgn - out.jsonl``)."""
+    if path == "-":
+        return sys.stdin
     if path.endswith(".zst"):
-        import zstandard
+        try:
+            import zstandard
+        except ImportError:
+            import shutil
+            import subprocess
 
+            if shutil.which("zstd") is None:
+                raise RuntimeError("reading .zst needs the zstandard module or the zstd tool; "
+                                   "or pipe the decompressed text to '-'") from None
+            proc = subprocess.Popen(["zstd", "-dc", path], stdout=subprocess.PIPE)
+            return io.TextIOWrapper(proc.stdout, encoding="utf-8")
         return io.TextIOWrapper(zstandard.ZstdDecompressor().stream_reader(open(path, "rb")), encoding="utf-8")
     return open(path, encoding="utf-8")
 

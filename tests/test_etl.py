@@ -129,3 +129,14 @@ def test_native_pgn_parser_matches_python_parser():
     assert parse_movetext("1. e4 e5 2. Nf3 Nc6 3. Bb5 a6 4. O-O 1-0", 180, 0) == (
         ["e2e4", "e7e5", "g1f3", "b8c6", "f1b5", "a7a6", "e1g1"], [])
     assert parse_movetext("1. Nf3 Nf6 2. Ng1 Ng8 3. Nc3 Nc6 4. Nf3 Nf6 5. Nd4 Nd5 6. Ndb5 Ndb4", 60, 0)[0][-2:] == ["d4b5", "d5b4"]
+
+
+def test_pgn_cli_reads_files_and_splits_games(tmp_path):
+    from allie_b200.etl.pgn import main as pgn_main
+
+    rng = np.random.default_rng(3)
+    games = [_pgn_of_random_game(rng, 30) for _ in range(9)]
+    (tmp_path / "dump.pgn").write_text("\n".join(text for text, _ in games))
+    pgn_main([str(tmp_path / "dump.pgn"), str(tmp_path / "out.jsonl"), "--workers", "2"])
+    rows = [json.loads(l) for l in open(tmp_path / "out.jsonl")]
+    assert [r["moves-uci"].split() for r in rows] == [ucis for _, ucis in games]
