@@ -145,7 +145,8 @@ def serve(alias: str, model, tokenizer: UCITokenizer, device: str | None = None,
                 try:
                     conn.settimeout(client_timeout)
                     game = assign_elo(Game(**recv_dict(conn)), system)
-                    game.legal_moves                      # replays the moves: an illegal game fails here
+                    if not game.legal_moves:              # replays the moves: an illegal game fails here
+                        raise ValueError("the game is over: no legal move to answer with")
                     ready.append((conn, game))
                 except (ConnectionError, OSError, ValueError, TypeError, KeyError) as e:
                     logger.warning(f"request failed: {type(e).__name__}: {e}")

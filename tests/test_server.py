@@ -35,7 +35,7 @@ def test_round_trip_and_broken_client():
                              n_embd=32, n_head=1, n_positions=64).eval()
     port = _free_port()
     th = threading.Thread(target=serve, kwargs=dict(alias="grandmaster", model=model, tokenizer=tok, device="cpu",
-                                                    port=port, self_test=False, max_requests=3), daemon=True)
+                                                    port=port, self_test=False, max_requests=5), daemon=True)
     th.start()
     for _ in range(50):
         try:
@@ -43,6 +43,10 @@ def test_round_trip_and_broken_client():
             break
         except OSError:
             time.sleep(0.1)
+    for bad in (["e2e5"], ["f2f3", "e7e5", "g2g4", "d8h4"]):             # an illegal move; a finished game
+        with socket.create_connection(("localhost", port), timeout=10) as c:
+            send_dict(c, Game("180+0", 1500, 1600, None, False, bad, [1] * len(bad)).to_dict())
+            assert c.recv(100) == b""                                    # closed without an answer
     game = Game("180+0", 1500, 1600, None, False, ["e2e4", "e7e5"], [1, 2])
     for _ in range(2):
         with socket.create_connection(("localhost", port), timeout=10) as c:
