@@ -100,7 +100,12 @@ class UCIFrontEnd:
         secs = [self.seconds.get(i, 0) for i in range(len(self.moves))]
         game = Game(tc, int(self.options["WhiteElo"]), int(self.options["BlackElo"]), None, False,
                     list(self.moves), secs)
-        ans = self.ask(game)
+        try:
+            ans = self.ask(game)
+        except (OSError, ValueError, KeyError) as e:     # server away, or it refused the game
+            self.say(f"info string no move from the server: {type(e).__name__}: {e}")
+            self.say("bestmove 0000")
+            return
         think = ans.get("think_time")
         if think is not None:
             self.say(f"info string predicted think time {think:.1f}s")

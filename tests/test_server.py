@@ -166,4 +166,8 @@ def test_uci_front_end_tracks_game_and_clocks():
     fe.handle("position startpos moves d2d4")                            # another game: clocks forgotten
     fe.handle("go movetime 1000")
     assert asked[2].moves == ["d2d4"] and asked[2].moves_seconds == [0]
+    down = UCIFrontEnd(lambda game: (_ for _ in ()).throw(ConnectionError("refused")), out)
+    down.handle("position startpos")
+    down.handle("go")
+    assert out.getvalue().splitlines()[-1] == "bestmove 0000"
     assert fe.handle("stop") and not fe.handle("quit")
