@@ -42,6 +42,7 @@ def _h():
             getattr(lib, fn).argtypes = [c_void_p]
         lib.chess_is_repetition.argtypes = [c_void_p, c_int]
         lib.chess_parse_san.argtypes = [c_void_p, c_char_p, c_char_p]
+        lib.chess_san.argtypes = [c_void_p, c_char_p, c_char_p]
         _configured = True
     return lib
 
@@ -200,7 +201,15 @@ class Board:
 
     def san(self, uci: str) -> str:
         """Standard algebraic notation of a legal move, with minimal disambiguation and the
-        check / mate suffix."""
+        check / mate suffix (written by the C++ core)."""
+        buf = ctypes.create_string_buffer(12)
+        if not _h().chess_san(self._h, uci.encode(), buf):
+            raise ValueError(f"illegal uci: {uci!r}")
+        return buf.value.decode()
+
+    def san_reference(self, uci: str) -> str:
+        """The same notation computed in Python from the public board queries; the oracle of
+        :meth:`san` in the tests."""
         legal = self.legal_moves_uci()
         if uci not in legal:
             raise ValueError(f"illegal uci: {uci!r}")

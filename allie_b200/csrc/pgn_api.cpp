@@ -79,6 +79,53 @@ bool resolve_san(const Board& b, const char* tok, size_t n, Move& out) {
 
 extern "C" {
 
+// Writes the SAN text of a legal move given as UCI text (minimal disambiguation, "+" / "#" suffix),
+// at most 8 characters + NUL.  Returns 1 on success, 0 when the move is not legal here.
+int chess_san(void* h, const char* uci, char* san_out) {
+  const Board& b = *static_cast<Board*>(h);
+  Move m;
+  if (!chess::parse_uci(uci, m)) return 0;
+  std::vector<Move> legal;
+  b.legal_moves(legal);
+  bool found = false;
+  for (const Move& l : legal) found = found || l == m;
+  if (!found) return 0;
+  const int pt = b.piece_type_at(m.from);
+  std::string s;
+  if (pt == chess::KING && std::abs(chess::file_of(m.to) - chess::file_of(m.from)) == 2) {
+    s = chess::file_of(m.to) > chess::file_of(m.from) ? "O-O" : "O-O-O";
+  } else {
+    const bool capture = (b.occ & chess::bit(m.to)) || b.is_en_passant(m);
+    const char ff = char('a' + chess::file_of(m.from)), fr = char('1' + chess::rank_of(m.from));
+    if (pt == chess::PAWN) {
+      if (capture) { s += ff; s += 'x'; }
+    } else {
+      s += " PNBRQK"[pt];
+      bool others = false, file_clash = false, rank_clash = false;
+      for (const Move& l : legal) {
+        if (l.to != m.to || l.from == m.from || b.piece_type_at(l.from) != pt) continue;
+        others = true;
+        if (chess::file_of(l.from) == chess::file_of(m.from)) file_clash = true;
+        if (chess::rank_of(l.from) == chess::rank_of(m.from)) rank_clash = true;
+      }
+      if (others) {
+        if (!file_clash) s += ff;
+        else if (!rank_clash) s += fr;
+        else { s += ff; s += fr; }
+      }
+      if (capture) s += 'x';
+    }
+    s += char('a' + chess::file_of(m.to));
+    s += char('1' + chess::rank_of(m.to));
+    if (m.promo) { s += '='; s += " PNBRQK"[m.promo]; }
+  }
+  Board next = b.light_copy();
+  next.apply(m);
+  if (next.is_check()) s += next.has_legal_move() ? '+' : '#';
+  std::memcpy(san_out, s.c_str(), s.size() + 1);
+  return 1;
+}
+
 // Resolves one SAN move without playing it; writes its UCI text.  Returns 1 on success.
 int chess_parse_san(void* h, const char* san, char* uci_out) {
   Move m;

@@ -146,6 +146,7 @@ def test_san_writer_and_both_parsers_agree_on_random_games():
             sans = {}
             for mv in legal:
                 s = b.san(mv)
+                assert s == b.san_reference(mv), (b.fen(), mv, s)         # C++ writer against the Python statement
                 assert s not in sans, (b.fen(), s, mv, sans[s])           # SAN is unambiguous
                 sans[s] = mv
                 if ply % 5 == 0:
