@@ -21,7 +21,8 @@ def main(argv: list[str] | None = None) -> None:
     trainer.setup_dataloaders(tokenizer, train_dataset, val_dataset, test_dataset)
     trainer.setup_model(model)
     trainer.train()
-    trainer.test()
+    if not trainer.stopped_early:        # a requested stop leaves right after its checkpoint; the requeued job resumes
+        trainer.test()
     trainer.cleanup()
 
 

@@ -306,7 +306,50 @@ class Trainer:
             self.optimizer.zero_grad(set_to_none=True)
         return loss.detach()
 
+    def request_stop(self, *_) -> None:
+        """Asks the training loop to write ``last.pt`` and return at its next safe point (signal
+        handler for SIGUSR1 / SIGTERM: schedulers send these shortly before they requeue a job)."""
+        self._stop_requested = True
+
+    def _install_signal_handlers(self) -> dict:
+        """Routes SIGUSR1 / SIGTERM to :meth:`request_stop` for the duration of ``train()``; returns
+        the handlers that were in place so they can be put back."""
+        import signal
+        import threading
+
+        old: dict = {}
+        if threading.current_thread() is not threading.main_thread():
+            return old
+        for sig in (signal.SIGUSR1, signal.SIGTERM):
+            try:
+                old[sig] = signal.signal(sig, self.request_stop)
+            except (ValueError, OSError):
+                pass
+        return old
+
+    def _stop_agreed(self) -> bool:
+        """True once any rank has been asked to stop; with several ranks this is a collective, so it
+        is only called where every rank passes in the same iteration."""
+        flag = bool(getattr(self, "_stop_requested", False))
+        if self.ddp and self.ddp_world_size > 1:
+            t = torch.tensor([float(flag)], device=self.device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            flag = bool(t[0] > 0)
+        return flag
+
     def train(self) -> None:
+        import signal
+
+        self._stop_requested = False
+        self.stopped_early = False
+        old = self._install_signal_handlers()
+        try:
+            self._train_loop()
+        finally:
+            for sig, handler in old.items():
+                signal.signal(sig, handler)
+
+    def _train_loop(self) -> None:
         t_start = t0 = time.time()
         losses: deque = deque(maxlen=100)
         pending: deque = deque()          # (device loss tensor, event) not yet read back
@@ -348,6 +391,18 @@ class Trainer:
             self.iter_num += 1
             if self.iter_num > self.max_iters:
                 break
+            # a requested stop is honoured between steps: every iteration in a single process, at
+            # the logging iterations (which all ranks share) when there are several ranks
+            single = not (self.ddp and self.ddp_world_size > 1)
+            at_log = self.log_interval > 0 and (self.iter_num - 1) % self.log_interval == 0
+            if (single or at_log) and self._stop_agreed():
+                self._drain(pending, losses, all_=True)
+                logger.info(f"stop requested: saving the checkpoint of iter {self.iter_num} and leaving the loop")
+                self._gather_optimizer_state()
+                if self.master_process or self.expert_parallel:
+                    self.save_ckpt("last")
+                self.stopped_early = True
+                return
         self._drain(pending, losses, all_=True)
         logger.info(f"training complete! total time {time.time() - t_start:.2f}s")
 

@@ -185,3 +185,22 @@ def test_config_inheritance(tmp_path):
     short = load_config(os.path.join(root, "pretrain_config", "ablations", "short.yaml"))
     assert short.trainer_config.max_iters == 1000000 and short.trainer_config.weight_decay == 1e-2
     assert short.model_config.base_model == "gpt2-medium" and short.data_config.tokenizer_config.max_length == 512
+
+
+def test_stop_signal_saves_a_checkpoint_and_resume_continues(tmp_path):
+    import signal
+    import threading
+
+    tr, _, _ = _make(tmp_path, max_iters=10_000, decay_iters=10_000, eval_interval=0, save_interval=0, log_interval=50)
+    threading.Timer(1.0, lambda: os.kill(os.getpid(), signal.SIGUSR1)).start()
+    tr.train()                                            # returns because of the signal, long before max_iters
+    assert tr.stopped_early and 0 < tr.iter_num < 10_000
+    ck = torch.load(tmp_path / "run" / "last.pt", weights_only=False)
+    assert ck["iter_num"] == tr.iter_num
+    assert "stop requested" in (tmp_path / "run" / "log.txt").read_text()
+    tr2, _, _ = _make(tmp_path, max_iters=tr.iter_num + 2, decay_iters=10_000, eval_interval=0, save_interval=0,
+                      log_interval=50)
+    assert tr2.iter_num == ck["iter_num"]                 # the requeued job picks up where the signal arrived
+    tr2.train()
+    assert not tr2.stopped_early and tr2.iter_num == ck["iter_num"] + 3
+    assert signal.getsignal(signal.SIGUSR1) is signal.SIG_DFL     # train() put the previous handlers back
