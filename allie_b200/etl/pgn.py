@@ -15,7 +15,7 @@ import io
 import json
 import re
 import sys
-from multiprocessing import Pool
+from multiprocessing import get_context
 
 from ..chess import Board
 
@@ -182,7 +182,8 @@ def main(argv=None) -> None:
     ap.add_argument("out")
     ap.add_argument("--workers", type=int, default=8)
     a = ap.parse_args(argv)
-    with open_pgn(a.pgn) as f, open(a.out, "w") as out, Pool(a.workers) as pool:
+    # worker processes are spawned, not forked: the parent may already run threads (BLAS, prefetch)
+    with open_pgn(a.pgn) as f, open(a.out, "w") as out, get_context("spawn").Pool(a.workers) as pool:
         n = 0
         for row in pool.imap(parse_game, iter_games(f), chunksize=64):
             if row is not None:
