@@ -145,6 +145,7 @@ class B200Engine:
         self.step_count = 0      # optimizer steps taken
         self.fwd_count = 0       # forward passes (dropout streams)
         self._bufs: dict[tuple, dict] = {}
+        self.max_inference_shapes = 6
         self._names = {id(p): n for n, p in model.named_parameters()}
         self._bind()
         self.gnorm_sq = torch.zeros(1, dtype=torch.float32, device=self.device)
@@ -239,7 +240,15 @@ class B200Engine:
     def _buffers(self, B: int, T: int, train: bool) -> dict:
         key = (B, T, train)
         if key in self._bufs:
+            self._bufs[key] = self._bufs.pop(key)          # most recently used goes last
             return self._bufs[key]
+        # Inference shapes vary with every request batch (rows x longest game): keep only the most
+        # recently used few sets, or a long-running server grows without bound.  Training shapes
+        # are fixed by the configuration and stay.
+        if not train:
+            idle = [k for k in self._bufs if not k[2]]
+            for k in idle[:max(0, len(idle) - (self.max_inference_shapes - 1))]:
+                del self._bufs[k]
         cfg, dev = self.cfg, self.device
         if T > cfg.n_positions:
             raise ValueError(f"sequence length {T} exceeds the model's {cfg.n_positions} learned positions")

@@ -204,3 +204,31 @@ def test_stop_signal_saves_a_checkpoint_and_resume_continues(tmp_path):
     tr2.train()
     assert not tr2.stopped_early and tr2.iter_num == ck["iter_num"] + 3
     assert signal.getsignal(signal.SIGUSR1) is signal.SIG_DFL     # train() put the previous handlers back
+
+
+def test_engine_keeps_a_bounded_number_of_inference_buffer_sets():
+    """The buffer cache of the engine, exercised on the CPU through a bare instance: training
+    shapes stay, inference shapes are kept least-recently-used up to a small number."""
+    from allie_b200.config import ModelConfig
+    from allie_b200.models.engine import B200Engine
+
+    eng = B200Engine.__new__(B200Engine)
+    eng.cfg = ModelConfig(vocab_size=128, n_positions=64, n_embd=16, n_layer=1, n_head=1, attn_pdrop=0.0)
+    eng.device, eng._bufs, eng.max_inference_shapes = torch.device("cpu"), {}, 3
+    train = eng._buffers(2, 8, True)
+    a = eng._buffers(1, 8, False)
+    for t in (16, 24):
+        eng._buffers(1, t, False)
+    assert eng._buffers(1, 8, False) is a                       # a hit refreshes the entry ...
+    eng._buffers(1, 32, False)                                  # ... so the next miss evicts (1, 16), not (1, 8)
+    keys = set(eng._bufs)
+    assert keys == {(2, 8, True), (1, 8, False), (1, 24, False), (1, 32, False)}
+    assert eng._buffers(2, 8, True) is train
+    for t in range(33, 40):
+        eng._buffers(2, t, False)
+    assert sum(1 for k in eng._bufs if not k[2]) == 3 and (2, 8, True) in eng._bufs
+    try:
+        eng._buffers(1, 65, False)
+        raise AssertionError("expected the position-table guard")
+    except ValueError as e:
+        assert "positions" in str(e)
