@@ -72,7 +72,7 @@ def main():
 def decode():
     import chess
     from evaluation.carlini import ChessLLM
-    from evaluation.decode import DECODE_STRATEGIES
+    from evaluation.decode import DECODE_STRATEGIES, ActionValue
     from modeling.data import Game, UCITokenizer
     from modeling.model import initialize_model
 
@@ -85,9 +85,10 @@ def decode():
     model.eval()
     games = [Game(**g) for g in blob["games"]]
     out = {}
+    classes = {**DECODE_STRATEGIES, "action-value": ActionValue}      # the reference leaves this one unregistered
     with torch.inference_mode():
         for name, kwargs in blob["strategies"]:
-            strat = DECODE_STRATEGIES[name](model, tok, sample=False, device="cpu", precision="float32", **kwargs)
+            strat = classes[name](model, tok, sample=False, device="cpu", precision="float32", **kwargs)
             rows = []
             for g in games:
                 s = strat.score_full(g, g.legal_moves)

@@ -118,7 +118,7 @@ def test_decode_strategies_and_prompts_match_the_reference(tmp_path):
     lines.append(list(b.move_stack))       # long enough for the prompt's movetext to wrap
     games = [Game("180+0", 1500 + 300 * i, 2300, None, False, mv, [3] * len(mv)) for i, mv in enumerate(lines)]
     strategies = [("policy", {}), ("mcts", {"n_sims": 24}), ("mcts", {"n_sims": 9, "kl_reg_solution": False}),
-                  ("adaptive-mcts", {"mean_n_sims": 12})]
+                  ("adaptive-mcts", {"mean_n_sims": 12}), ("action-value", {"batch_size": 7})]
     from test_trainer_cpu import _random_games, _row
 
     rows = [_row(g) for g in _random_games(4, seed=8)]
@@ -134,6 +134,8 @@ def test_decode_strategies_and_prompts_match_the_reference(tmp_path):
     for name, kwargs in strategies:
         want = ref["decode"][f"{name}:{sorted(kwargs.items())}"]
         for variant in (name, name + "-batched"):
+            if variant not in DECODE_STRATEGIES:
+                continue
             extra = {"n_trees": 3, "anc_max": 64} if variant.endswith("mcts-batched") else {}
             strat = DECODE_STRATEGIES[variant](model, tok, sample=False, device="cpu", **kwargs, **extra)
             for g, row in zip(games, want["rows"]):
