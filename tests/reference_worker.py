@@ -96,6 +96,12 @@ def decode():
                              "think_time": s.think_time, "resigned": s.resigned,
                              "move": strat.decode_full(g).move})
             out[f"{name}:{sorted(kwargs.items())}"] = {"rows": rows, "stats": strat.run_stats()}
+    sampled = []
+    with torch.inference_mode():
+        strat = DECODE_STRATEGIES["policy"](model, tok, sample="rating-based", device="cpu", precision="float32")
+        for i, g in enumerate(games):
+            torch.manual_seed(100 + i)
+            sampled.append(strat.decode_full(g).move)
     quick = None
     if blob.get("rows"):
         import pandas as pd
@@ -111,7 +117,7 @@ def decode():
         for mv in g.moves:
             board.push_uci(mv)
         prompts.append(llm.get_query_pgn(board))
-    torch.save({"decode": out, "prompts": prompts, "quick": quick}, os.path.join(d, "ref_decode.pt"))
+    torch.save({"decode": out, "prompts": prompts, "quick": quick, "sampled": sampled}, os.path.join(d, "ref_decode.pt"))
 
 
 def train():

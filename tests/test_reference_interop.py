@@ -146,6 +146,14 @@ def test_decode_strategies_and_prompts_match_the_reference(tmp_path):
                 assert strat.decode_full(g).move == row["move"], (variant, kwargs, g.moves)
             if "total_rollouts" in want["stats"]:
                 assert strat.run_stats()["total_rollouts"] == want["stats"]["total_rollouts"]
+    # rating-based sampling: arg-max for a 2200+ side after more than 8 plies, else a draw from the
+    # distribution - the same draw as the reference's when the generator starts from the same seed
+    for variant in ("policy", "policy-batched"):
+        strat = DECODE_STRATEGIES[variant](model, tok, sample="rating-based", device="cpu")
+        for i, g in enumerate(games):
+            torch.manual_seed(100 + i)
+            move = strat.decode_batch([g])[0].move if variant.endswith("batched") else strat.decode_full(g).move
+            assert move == ref["sampled"][i], (variant, i)
     llm = ChessLLM(None)
     for g, prompt in zip(games, ref["prompts"]):
         assert llm.get_query_pgn(g.board) == prompt
