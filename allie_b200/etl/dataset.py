@@ -39,9 +39,12 @@ def keep_probability(bin_: int, counts: dict[int, int], target: int) -> float:
     return min(1.0, target / max(1, counts.get(bin_, 1)))
 
 
-def sample(src: str, prefix: str, target_per_bin: int = 100_000, seed: int = 0) -> dict[str, int]:
-    """ELO-balanced subsample split into ``<prefix>-train/val/test.jsonl`` with probabilities
-    1 - 3e-4 / 1e-4 / 2e-4; returns the number of games written per split."""
+def sample(src: str, prefix: str, target_per_bin: int = 100_000, seed: int = 0, val_fraction: float = 1e-4,
+           test_fraction: float = 2e-4) -> dict[str, int]:
+    """ELO-balanced subsample split into ``<prefix>-train/val/test.jsonl``; a kept game goes to the
+    validation split with probability ``val_fraction``, to the test split with ``test_fraction``
+    (the reference's 1e-4 and 2e-4 by default, sized for tens of millions of games), else to
+    training.  Returns the number of games written per split."""
     rng = random.Random(seed)
     counts: dict[int, int] = collections.Counter()
     with open(src) as f:
@@ -55,7 +58,7 @@ def sample(src: str, prefix: str, target_per_bin: int = 100_000, seed: int = 0) 
             if rng.random() >= keep_probability(elo_bin(row), counts, target_per_bin):
                 continue
             u = rng.random()
-            split = "val" if u < 1e-4 else "test" if u < 3e-4 else "train"
+            split = "val" if u < val_fraction else "test" if u < val_fraction + test_fraction else "train"
             outs[split].write(line if line.endswith("\n") else line + "\n")
             written[split] += 1
     for o in outs.values():
@@ -192,6 +195,7 @@ def main(argv=None) -> None:
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="cmd", required=True)
     s = sub.add_parser("sample"); s.add_argument("src"); s.add_argument("prefix"); s.add_argument("--target", type=int, default=100_000)
+    s.add_argument("--val", type=float, default=1e-4); s.add_argument("--test", type=float, default=2e-4)
     s = sub.add_parser("tokenize"); s.add_argument("src"); s.add_argument("dst")
     s = sub.add_parser("concat"); s.add_argument("parts", nargs="+"); s.add_argument("dst")
     s = sub.add_parser("elo-stats"); s.add_argument("src"); s.add_argument("dst", nargs="?")
@@ -207,7 +211,7 @@ def main(argv=None) -> None:
         print(json.dumps({k: len(v) for k, v in puzzles(a.csv, a.out_dir, a.n, download=a.download).items()}))
         return
     if a.cmd == "sample":
-        print(json.dumps(sample(a.src, a.prefix, a.target)))
+        print(json.dumps(sample(a.src, a.prefix, a.target, val_fraction=a.val, test_fraction=a.test)))
     elif a.cmd == "tokenize":
         print(tokenize(a.src, a.dst), "tokens")
     elif a.cmd == "concat":
