@@ -29,6 +29,9 @@ def send_dict(sock: socket.socket, data: dict) -> None:
     sock.sendall(json.dumps(data).encode())
 
 
+MAX_MESSAGE_BYTES = 1 << 20       # a 512-ply game is a few KiB; anything near this size is not a request
+
+
 def recv_dict(sock: socket.socket) -> dict:
     """Accumulates 8 KiB chunks until the bytes parse as JSON."""
     buf = b""
@@ -37,6 +40,8 @@ def recv_dict(sock: socket.socket) -> dict:
         if not chunk:
             raise ConnectionError("peer closed before a complete JSON document arrived")
         buf += chunk
+        if len(buf) > MAX_MESSAGE_BYTES:
+            raise ValueError("message larger than any request can be")
         try:
             return json.loads(buf.decode())
         except (json.JSONDecodeError, UnicodeDecodeError):
