@@ -192,8 +192,14 @@ def test_stop_signal_saves_a_checkpoint_and_resume_continues(tmp_path):
     import threading
 
     tr, _, _ = _make(tmp_path, max_iters=10_000, decay_iters=10_000, eval_interval=0, save_interval=0, log_interval=50)
-    threading.Timer(1.0, lambda: os.kill(os.getpid(), signal.SIGUSR1)).start()
-    tr.train()                                            # returns because of the signal, long before max_iters
+    running = {"train": True}                             # the signal is only sent while train() owns the handler
+    timer = threading.Timer(1.0, lambda: running["train"] and os.kill(os.getpid(), signal.SIGUSR1))
+    timer.start()
+    try:
+        tr.train()                                        # returns because of the signal, long before max_iters
+    finally:
+        running["train"] = False
+        timer.cancel()
     assert tr.stopped_early and 0 < tr.iter_num < 10_000
     ck = torch.load(tmp_path / "run" / "last.pt", weights_only=False)
     assert ck["iter_num"] == tr.iter_num
