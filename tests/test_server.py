@@ -171,3 +171,59 @@ def test_uci_front_end_tracks_game_and_clocks():
     down.handle("go")
     assert out.getvalue().splitlines()[-1] == "bestmove 0000"
     assert fe.handle("stop") and not fe.handle("quit")
+
+
+def test_front_door_spreads_requests_and_skips_a_dead_backend(tmp_path):
+    from allie_b200.config import save_config
+    from allie_b200.serve.client import request_move
+    from allie_b200.serve.pool import FrontDoor, start_backends, wait_until_listening
+
+    torch.manual_seed(0)
+    tok = UCITokenizer(max_length=64, vocab_size_multiple_of=128)
+    model = initialize_model(tok, "gpt2", use_control_token=True, use_regression_head=True, n_layer=1,
+                             n_embd=32, n_head=1, n_positions=64).eval()
+    ports = [_free_port(), _free_port()]
+    dead = _free_port()                                    # nothing listens here
+    backends = [threading.Thread(target=serve, kwargs=dict(alias="grandmaster", model=model, tokenizer=tok, device="cpu",
+                                                           port=p, self_test=False, max_requests=50), daemon=True)
+                for p in ports]
+    for b in backends:
+        b.start()
+    wait_until_listening(ports, timeout=30)
+    door = FrontDoor([dead] + ports)
+    front = _free_port()
+    th = threading.Thread(target=door.serve, kwargs=dict(port=front, max_requests=9), daemon=True)
+    th.start()
+    time.sleep(0.3)
+    game = Game("180+0", 1500, 1600, None, False, ["e2e4", "e7e5"], [1, 2])
+    answers = []
+    clients = [threading.Thread(target=lambda: answers.append(request_move(front, game))) for _ in range(8)]
+    for c in clients:
+        c.start()
+    for c in clients:
+        c.join(timeout=60)
+    assert len(answers) == 8 and all(a["move"] in game.legal_moves for a in answers)
+    assert door.served[dead] == 0 and all(door.served[p] > 0 for p in ports) and sum(door.served.values()) == 8
+    over = Game("180+0", 1500, 1600, None, False, ["f2f3", "e7e5", "g2g4", "d8h4"], [1] * 4)
+    try:
+        request_move(front, over)                           # refused by the backend, passed on as a closed connection
+        raise AssertionError("expected a refusal")
+    except ConnectionError:
+        pass
+    th.join(timeout=30)
+    assert not th.is_alive() and all(v == 0 for v in door.in_flight.values())
+
+    # one real backend process started from a config file, as the command line does it
+    cfg = {"trainer_config": {"output_dir": str(tmp_path / "run")},
+           "data_config": {"tokenizer_config": {"max_length": 64, "vocab_size_multiple_of": 128}},
+           "model_config": dict(base_model="gpt2", use_control_token=True, use_regression_head=True, n_layer=1,
+                                n_embd=32, n_head=1, n_positions=64)}
+    save_config(cfg, str(tmp_path / "cfg.yaml"))
+    bport = _free_port()
+    procs, bports = start_backends("humanlike", str(tmp_path / "cfg.yaml"), ["cpu"], bport, checkpoint="none")
+    try:
+        wait_until_listening(bports, timeout=120)
+        assert request_move(bport, game)["move"] in game.legal_moves
+    finally:
+        for p in procs:
+            p.terminate()
