@@ -198,6 +198,8 @@ def main(argv: list[str] | None = None) -> None:
     ap.add_argument("--checkpoint", default=None, help="defaults to {output_dir}/best.pt; 'none' = random init")
     ap.add_argument("--no-self-test", action="store_true")
     a = ap.parse_args(argv)
+    if a.device and a.device.startswith("cuda:") and torch.cuda.is_available():
+        torch.cuda.set_device(a.device)         # kernels, streams and the status word follow the current device
     cfg = load_config(a.config)
     setup_logging()
     tokenizer = UCITokenizer(**cfg.data_config.tokenizer_config)

@@ -9,6 +9,7 @@ batched``), or one of them.
 
     python bench_serve.py                                  # humanlike (policy), both modes
     python bench_serve.py --alias humanlike-mcts-rb --requests 128
+    python bench_serve.py --servers 8 --requests 2048 --clients 512   # one backend process per GPU behind a front door
 Prints one JSON line.
 """
 from __future__ import annotations
@@ -33,21 +34,36 @@ def _free_port() -> int:
     return p
 
 
-def run_load(alias, model, tok, device, games, clients, batched, max_batch):
+def run_load(alias, model, tok, device, games, clients, batched, max_batch, pool=None):
+    """``pool``: None for one in-process server, else ``(config_path, devices)`` for one backend
+    process per device behind a front door (``allie_b200/serve/pool.py``)."""
     from allie_b200.serve.server import recv_dict, send_dict, serve
 
     port = _free_port()
     n = len(games)
-    th = threading.Thread(target=serve, kwargs=dict(alias=alias, model=model, tokenizer=tok, device=device,
-                                                    port=port, self_test=False, max_requests=n + 1,
-                                                    max_batch=max_batch, batched=batched), daemon=True)
+    procs = []
+    if pool is None:
+        th = threading.Thread(target=serve, kwargs=dict(alias=alias, model=model, tokenizer=tok, device=device,
+                                                        port=port, self_test=False, max_requests=n + 1,
+                                                        max_batch=max_batch, batched=batched), daemon=True)
+    else:
+        from allie_b200.serve.pool import FrontDoor, start_backends, wait_until_listening
+
+        config_path, devices = pool
+        first = 24000 + (os.getpid() % 500) * 16 + (8 if batched else 0)
+        procs, ports = start_backends(alias, config_path, devices, first, checkpoint="none", max_batch=max_batch,
+                                      sequential=not batched)
+        wait_until_listening(ports)
+        th = threading.Thread(target=FrontDoor(ports).serve, kwargs=dict(port=port, max_requests=n + len(devices)),
+                              daemon=True)
     th.start()
     deadline = time.time() + 600
     while True:                                   # the strategy (engine, KV cache) is built before the socket opens
         try:
-            with socket.create_connection(("localhost", port), timeout=5) as c:   # warm-up request
-                send_dict(c, games[0].to_dict())
-                recv_dict(c)
+            for _ in range(1 if pool is None else len(pool[1])):                   # warm-up request(s)
+                with socket.create_connection(("localhost", port), timeout=600) as c:
+                    send_dict(c, games[0].to_dict())
+                    recv_dict(c)
             break
         except OSError:
             if time.time() > deadline or not th.is_alive():
@@ -81,6 +97,8 @@ def run_load(alias, model, tok, device, games, clients, batched, max_batch):
         t.join()
     wall = time.perf_counter() - t0
     th.join(timeout=30)
+    for p in procs:
+        p.terminate()
     ok = sorted(x for x in lat if x is not None)
     return {"answered": len(ok), "seconds": round(wall, 4), "requests_per_s": round(len(ok) / wall, 2),
             "latency_p50_ms": round(1e3 * ok[len(ok) // 2], 2) if ok else None,
@@ -103,6 +121,8 @@ def main(argv=None):
     ap.add_argument("--mode", default="both", choices=["both", "batched", "sequential"])
     ap.add_argument("--small", action="store_true", help="tiny model (smoke test)")
     ap.add_argument("--device", default=None)
+    ap.add_argument("--servers", type=int, default=1,
+                    help="more than one: a backend process per GPU (cuda:0..N-1) behind a front door")
     args = ap.parse_args(argv)
     device = args.device or ("cuda" if torch.cuda.is_available() else "cpu")
     torch.manual_seed(0)
@@ -117,11 +137,27 @@ def main(argv=None):
         model = initialize_model(tok, "gpt2-medium", use_control_token=True, use_regression_head=True)
         games = random_games(args.requests, tok, rng, max_tokens=200)
     model.eval()
+    pool = None
+    if args.servers > 1:
+        import tempfile
+
+        from allie_b200.config import save_config
+
+        shape = (dict(base_model="gpt2", n_layer=2, n_embd=256, n_head=4, n_positions=128) if args.small
+                 else dict(base_model="gpt2-medium"))
+        cfg = {"trainer_config": {"output_dir": tempfile.mkdtemp(prefix="allie_serve_")},
+               "data_config": {"tokenizer_config": {"max_length": tok.max_length, "vocab_size_multiple_of": 128}},
+               "model_config": dict(use_control_token=True, use_regression_head=True, **shape)}
+        path = os.path.join(cfg["trainer_config"]["output_dir"], "config.yaml")
+        save_config(cfg, path)
+        devices = [f"cuda:{i}" for i in range(args.servers)] if device.startswith("cuda") else ["cpu"] * args.servers
+        pool = (path, devices)
     out = {"metric": "move server requests/s", "alias": args.alias, "requests": args.requests,
-           "clients": args.clients, "max_batch": args.max_batch, "device": device,
+           "clients": args.clients, "max_batch": args.max_batch, "device": device, "servers": args.servers,
            "model": "tiny" if args.small else "gpt2-medium shape, random init"}
     for mode in (["sequential", "batched"] if args.mode == "both" else [args.mode]):
-        out[mode] = run_load(args.alias, model, tok, device, games, args.clients, mode == "batched", args.max_batch)
+        out[mode] = run_load(args.alias, model, tok, device, games, args.clients, mode == "batched", args.max_batch,
+                             pool)
     if "batched" in out and "sequential" in out and out["sequential"]["requests_per_s"]:
         out["speedup"] = round(out["batched"]["requests_per_s"] / out["sequential"]["requests_per_s"], 2)
     print(json.dumps(out))
