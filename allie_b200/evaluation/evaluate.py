@@ -6,7 +6,8 @@
 Scores every prefix of every game of a JSONL file with a decode strategy.  Modes: ``--quick``
 (move-match, legality, resignation, think time, value; no engine), ``--value`` (value head vs
 Stockfish), default (Stockfish centipawn loss and accuracy per model move).  One JSON line is
-appended to ``--output_file``.  Weights come from ``{output_dir}/best.pt``.
+appended to ``--output_file``.  Weights come from ``{output_dir}/best.pt``.  Under ``torchrun`` the
+games are split over the ranks (one GPU each) and rank 0 merges the records and writes the line.
 """
 from __future__ import annotations
 
@@ -82,7 +83,6 @@ def evaluate_quick(strategy: DecodeStrategy, rows: list[dict], batch_size: int =
     games = [dict(row) | {"model-move": [], "human-move": [], "top-move-legal": [], "sampled-move-legal": [],
                           "human-resigned": [], "model-resigned": [], "model-think-time": [],
                           "model-white-advantage": []} for row in rows]
-    time_err, value_err = [], []
     for r, i, g, s in iter_scores(strategy, rows, batch_size):
         rec, row = games[r], rows[r]
         legal = g.legal_moves
@@ -97,23 +97,31 @@ def evaluate_quick(strategy: DecodeStrategy, rows: list[dict], batch_size: int =
             rec["model-resigned"].append(bool(s.resigned))
         if s.think_time is not None:
             rec["model-think-time"].append(s.think_time)
-            if g.next_move_seconds is not None:
-                time_err.append(abs(s.think_time - g.next_move_seconds))
         if s.white_advantage is not None:
             rec["model-white-advantage"].append(s.white_advantage)
-            outcome = {"1-0": 1.0, "0-1": -1.0}.get(row.get("result"), 0.0)
-            value_err.append((s.white_advantage - outcome) ** 2)
     for rec, row in zip(games, rows):
         game = json_to_game(row)
         if game.normal_termination and game.board.outcome(claim_draw=True) is None:
             # a normally terminated game without a result on the board: the human resigned here
             rec["human-resigned"].append(True)
             rec["model-resigned"].append(bool(strategy.decode_full(game).resigned))
+    return {"games": games, **summarize_quick(games)}
+
+
+def summarize_quick(games: list[dict]) -> dict:
+    """Means over all positions of the per-game records of :func:`evaluate_quick` (also used to
+    merge the records of several ranks)."""
     flat = lambda key: [x for rec in games for x in rec[key]]
     n = len(flat("model-move"))
     match = sum(int(a == b) for a, b in zip(flat("model-move"), flat("human-move")))
     hr, mr = flat("human-resigned"), flat("model-resigned")
-    return {"games": games, "positions": n, "move_match": match / max(n, 1),
+    time_err, value_err = [], []
+    for rec in games:
+        secs = list(rec["moves-seconds"])
+        time_err += [abs(t - secs[i]) for i, t in enumerate(rec["model-think-time"]) if i < len(secs)]
+        outcome = {"1-0": 1.0, "0-1": -1.0}.get(rec.get("result"), 0.0)
+        value_err += [(v - outcome) ** 2 for v in rec["model-white-advantage"]]
+    return {"positions": n, "move_match": match / max(n, 1),
             "top_move_legal": _mean(int(x) for x in flat("top-move-legal")), "legal_mass": _mean(flat("sampled-move-legal")),
             "resign_rate": sum(mr) / max(len(mr), 1),
             "resign_agreement": _mean(int(a == b) for a, b in zip(hr, mr)),
@@ -123,18 +131,23 @@ def evaluate_quick(strategy: DecodeStrategy, rows: list[dict], batch_size: int =
 def evaluate_value(strategy: DecodeStrategy, rows: list[dict], batch_size: int = 256) -> dict:
     """Value head against Stockfish (``src/evaluation/evaluate.py:33-60``): per game the model's
     white advantage and the engine's white-relative centipawns for every position."""
-    from .utils import cp_to_value, stockfish_eval
+    from .utils import stockfish_eval
 
     games = [dict(row) | {"model-move": [], "stockfish-eval": [], "model-white-advantage": []} for row in rows]
-    err = []
     for r, i, g, s in iter_scores(strategy, rows, batch_size):
         if s.white_advantage is None:
             continue
-        cp = stockfish_eval(rows[r]["moves-uci"].split()[:i])
         games[r]["model-white-advantage"].append(s.white_advantage)
-        games[r]["stockfish-eval"].append(cp)
-        err.append((s.white_advantage - cp_to_value(cp)) ** 2)
-    return {"games": games, "positions": len(err), "value_vs_stockfish_mse": _mean(err)}
+        games[r]["stockfish-eval"].append(stockfish_eval(rows[r]["moves-uci"].split()[:i]))
+    return {"games": games, **summarize_value(games)}
+
+
+def summarize_value(games: list[dict]) -> dict:
+    from .utils import cp_to_value
+
+    err = [(v - cp_to_value(cp)) ** 2 for rec in games
+           for v, cp in zip(rec["model-white-advantage"], rec["stockfish-eval"])]
+    return {"positions": len(err), "value_vs_stockfish_mse": _mean(err)}
 
 
 def evaluate(strategy: DecodeStrategy, rows: list[dict], batch_size: int = 256) -> dict:
@@ -162,9 +175,13 @@ def evaluate(strategy: DecodeStrategy, rows: list[dict], batch_size: int = 256) 
     if eval_utils._engine is not None:
         eval_utils._engine.quit()
         eval_utils._engine = None
+    return {"games": games, **summarize_full(games)}
+
+
+def summarize_full(games: list[dict]) -> dict:
     cpl = [x for rec in games for x in rec["model-centipawn-loss"]]
     acc = [x for rec in games for x in rec["model-lichess-accuracy"]]
-    return {"games": games, "positions": len(cpl), "centipawn_loss": _mean(cpl), "accuracy": _mean(acc)}
+    return {"positions": len(cpl), "centipawn_loss": _mean(cpl), "accuracy": _mean(acc)}
 
 
 def main(argv: list[str] | None = None) -> dict:
@@ -187,6 +204,14 @@ def main(argv: list[str] | None = None) -> dict:
                     help="positions per call for the strategies that score many games at once")
     args = ap.parse_args(argv)
     assert not (args.quick and args.value), "--quick and --value exclude each other"
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("gloo")            # only Python objects (the per-game records) cross ranks
+        if args.device is None and torch.cuda.is_available():
+            args.device = f"cuda:{int(os.environ.get('LOCAL_RANK', 0))}"
+            torch.cuda.set_device(args.device)
     random.seed(42); np.random.seed(42); torch.manual_seed(42)
     decode_args = json.loads(args.decode_args)
     model = tokenizer = None
@@ -207,16 +232,29 @@ def main(argv: list[str] | None = None) -> dict:
     strategy = DECODE_STRATEGIES[args.decode](model, tokenizer, sample=args.sample, device=args.device,
                                               precision="float32", **decode_args)
     rows = read_jsonl(args.dataset, 5 if args.debug else args.n_rows)
-    if args.quick:
-        metrics = evaluate_quick(strategy, rows, args.batch_size)
-    elif args.value:
-        metrics = evaluate_value(strategy, rows, args.batch_size)
-    else:
-        metrics = evaluate(strategy, rows, args.batch_size)
+    mine = rows[rank::world]                       # under torchrun every rank scores every world-th game
+    eval_fn, summarize = ((evaluate_quick, summarize_quick) if args.quick else
+                          (evaluate_value, summarize_value) if args.value else (evaluate, summarize_full))
+    metrics = eval_fn(strategy, mine, args.batch_size)
+    stats = strategy.run_stats()
+    strategy.cleanup()
+    if world > 1:
+        import torch.distributed as dist
+
+        parts = [None] * world
+        dist.all_gather_object(parts, (metrics["games"], stats))
+        dist.destroy_process_group()
+        if rank != 0:
+            return {}
+        games = [None] * len(rows)
+        for r, (g, _) in enumerate(parts):
+            games[r::world] = g                    # back into the order of the input file
+        metrics = {"games": games, **summarize(games)}
+        stats = {k: sum(st.get(k, 0) for _, st in parts) for k in parts[0][1]
+                 if isinstance(parts[0][1][k], (int, float))}
     result = {"decode": args.decode, "alias": args.alias or args.decode, "n_rows": args.n_rows, "sample": args.sample,
               "config": args.config, "dataset": args.dataset, **json.loads(args.decode_args),
-              **metrics, **strategy.run_stats()}
-    strategy.cleanup()
+              **metrics, **stats}
     if args.debug:
         result.pop("games", None)
         print(json.dumps(result, indent=1))

@@ -106,3 +106,55 @@ def test_shard_bounds_tile_the_arena():
             assert end == n, (n, world, end)
             sizes = [shard_bounds(n, world, r)[1] for r in range(world)]
             assert max(sizes) <= -(-n // world) + 63                    # nobody owns much more than 1/world
+
+
+def test_evaluation_cli_under_two_ranks_matches_one_process(tmp_path):
+    """The evaluation CLI under torchrun splits the games over the ranks and rank 0 merges the
+    records: the written line equals the single-process one."""
+    import json
+
+    from allie_b200.config import save_config
+    from allie_b200.etl.dataset import random_games
+
+    cfg = {"trainer_config": {"output_dir": str(tmp_path / "run")},
+           "data_config": {"tokenizer_config": {"max_length": 64, "vocab_size_multiple_of": 128}},
+           "model_config": dict(base_model="gpt2", use_control_token=True, use_regression_head=True, n_layer=1,
+                                n_embd=32, n_head=1, n_positions=64)}
+    save_config(cfg, str(tmp_path / "cfg.yaml"))
+    random_games(str(tmp_path / "games.jsonl"), n=5, max_plies=14, seed=4)
+    # both runs need the same weights: a random-init model saved as the checkpoint they load
+    import torch as _torch
+
+    from allie_b200.data import UCITokenizer
+    from allie_b200.models import initialize_model
+
+    tok = UCITokenizer(max_length=64, vocab_size_multiple_of=128)
+    _torch.manual_seed(0)
+    model = initialize_model(tok, **cfg["model_config"])
+    _torch.save({"model": model.state_dict()}, tmp_path / "w.pt")
+    common = ["-m", "allie_b200.evaluation.evaluate", "--config", str(tmp_path / "cfg.yaml"), "--dataset",
+              str(tmp_path / "games.jsonl"), "--quick", "--decode", "policy-batched", "--device", "cpu",
+              "--checkpoint", str(tmp_path / "w.pt")]
+    env = dict(os.environ, PYTHONPATH=os.path.dirname(HERE))
+    env.pop("RANK", None)
+    one = subprocess.run([sys.executable, *common, "--output_file", str(tmp_path / "one.jsonl")], env=env,
+                         capture_output=True, text=True, timeout=600)
+    assert one.returncode == 0, one.stderr[-3000:]
+    two = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                          "--master-addr", "127.0.0.1", "--master-port", "29631", *common, "--output_file",
+                          str(tmp_path / "two.jsonl")], env=env, capture_output=True, text=True, timeout=600)
+    assert two.returncode == 0, two.stderr[-3000:]
+    a = json.loads((tmp_path / "one.jsonl").read_text())
+    lines = (tmp_path / "two.jsonl").read_text().splitlines()
+    assert len(lines) == 1                                   # only rank 0 writes
+    b = json.loads(lines[0])
+    assert len(a["games"]) == len(b["games"]) == 5
+    for ga, gb in zip(a["games"], b["games"]):               # same games in the same order
+        for k in ("moves-uci", "model-move", "human-move", "top-move-legal", "human-resigned", "model-resigned"):
+            assert ga[k] == gb[k], k
+        for k in ("model-think-time", "model-white-advantage", "sampled-move-legal"):
+            # the two runs batch the positions differently: the last bits of a float may differ
+            assert len(ga[k]) == len(gb[k]) and all(abs(x - y) < 1e-4 for x, y in zip(ga[k], gb[k])), k
+    for k in ("positions", "move_match", "top_move_legal", "resign_rate"):
+        assert a[k] == b[k], k
+    assert abs(a["value_mse"] - b["value_mse"]) < 1e-6
