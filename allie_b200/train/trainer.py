@@ -306,9 +306,17 @@ class Trainer:
             self.optimizer.zero_grad(set_to_none=True)
         return loss.detach()
 
-    def request_stop(self, *_) -> None:
+    def request_stop(self, signum=None, frame=None) -> None:
         """Asks the training loop to write ``last.pt`` and return at its next safe point (signal
-        handler for SIGUSR1 / SIGTERM: schedulers send these shortly before they requeue a job)."""
+        handler for SIGUSR1 / SIGTERM: schedulers send these shortly before they requeue a job).
+        A second signal of the same kind is not held back: it takes the default action, so a process
+        that cannot reach a safe point (a rank stuck in a collective) can still be ended."""
+        if getattr(self, "_stop_requested", False) and signum is not None:
+            import signal
+
+            signal.signal(signum, signal.SIG_DFL)
+            os.kill(os.getpid(), signum)
+            return
         self._stop_requested = True
 
     def _install_signal_handlers(self) -> dict:
