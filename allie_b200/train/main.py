@@ -13,6 +13,8 @@ from .trainer import Trainer
 
 def main(argv: list[str] | None = None) -> None:
     argv = sys.argv[1:] if argv is None else argv
+    if len(argv) != 1:
+        raise SystemExit("usage: python -m allie_b200.train.main <config.yaml>   (under torchrun for several GPUs)")
     config = load_config(argv[0])
     trainer = Trainer(config, **config.trainer_config)
     trainer.save_config(config)
