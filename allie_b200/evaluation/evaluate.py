@@ -23,7 +23,7 @@ import torch
 
 from ..config import load_config
 from ..data import UCITokenizer, json_to_game, json_to_partial_game
-from ..models import initialize_model
+from ..models import initialize_model, load_model_state
 from ..search import DECODE_STRATEGIES, DecodeStrategy
 
 logger = logging.getLogger(__name__)
@@ -225,7 +225,7 @@ def main(argv: list[str] | None = None) -> dict:
         model = initialize_model(tokenizer, **{**cfg.model_config, "use_pretrained": False})
         ckpt_path = args.checkpoint or join(cfg.trainer_config.output_dir, "best.pt")
         if ckpt_path != "none":
-            model.load_state_dict(torch.load(ckpt_path, map_location="cpu", weights_only=False)["model"])
+            load_model_state(model, torch.load(ckpt_path, map_location="cpu", weights_only=False)["model"])
         model.eval()
     elif args.decode not in ("maia", "gpt-3.5-turbo"):
         ap.error("--config is required for strategies that run the model")

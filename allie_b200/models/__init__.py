@@ -43,6 +43,22 @@ def _load_pretrained_body(model: GPT2LM, base_model: str) -> bool:
     return True
 
 
+def load_model_state(model, state_dict: dict) -> None:
+    """``model.load_state_dict`` for checkpoints of the reference or of this framework: strict about
+    parameters, tolerant of the causal-mask buffers (``attn.bias`` / ``attn.masked_bias``) that
+    older Hugging Face GPT-2 versions wrote into their state dicts, and of a ``module.`` /
+    ``_orig_mod.`` prefix left by a DDP or ``torch.compile`` wrapper."""
+    clean = {}
+    for k, v in state_dict.items():
+        for prefix in ("module.", "_orig_mod."):
+            while k.startswith(prefix):
+                k = k[len(prefix):]
+        if k.endswith(".attn.bias") or k.endswith(".attn.masked_bias"):
+            continue
+        clean[k] = v
+    model.load_state_dict(clean)
+
+
 def initialize_model(tokenizer, base_model: str, use_control_token: bool = False,
                      use_regression_head: bool = False, use_pretrained: bool = False,
                      lm_loss_coef: float = 1.0, value_loss_coef: float = 1.0,

@@ -184,7 +184,7 @@ def main(argv: list[str] | None = None) -> None:
     from os.path import join
 
     from ..config import load_config
-    from ..models import initialize_model
+    from ..models import initialize_model, load_model_state
     from ..utils.logging import setup_logging
 
     ap = argparse.ArgumentParser(description="Allie move server")
@@ -206,7 +206,7 @@ def main(argv: list[str] | None = None) -> None:
     model = initialize_model(tokenizer, **{**cfg.model_config, "use_pretrained": False})
     path = a.checkpoint or join(cfg.trainer_config.output_dir, "best.pt")
     if path != "none":
-        model.load_state_dict(torch.load(path, map_location="cpu", weights_only=False)["model"])
+        load_model_state(model, torch.load(path, map_location="cpu", weights_only=False)["model"])
     model.eval()
     serve(a.alias, model, tokenizer, device=a.device, host=a.host, port=a.port, self_test=not a.no_self_test,
           max_batch=a.max_batch, batched=not a.sequential)

@@ -153,7 +153,9 @@ def load_checkpoint(path: str, model, engine, optimizer, device) -> dict:
     if engine is not None and _local_names(engine):
         shapes = engine.arena.shapes
         model_sd = {k: (_my_slice(v, shapes[k]) if k in shapes else v) for k, v in model_sd.items()}
-    model.load_state_dict(model_sd)
+    from ..models import load_model_state
+
+    load_model_state(model, model_sd)
     if engine is not None:
         engine.arena.refresh_shadow()
         _optimizer_state_into_engine(engine, ckpt["optimizer"])

@@ -79,3 +79,20 @@ def test_use_pretrained_loads_a_local_gpt2_body(tmp_path):
     assert abs(wte.mean().item() - hsd["transformer.wte.weight"].mean().item()) < 0.02
     assert abs(wte.std().item() / hsd["transformer.wte.weight"].std().item() - 1) < 0.1
     assert inner.lm_head.weight.data_ptr() == wte.data_ptr()                      # still tied
+
+
+def test_checkpoints_with_wrapper_prefixes_and_mask_buffers_load():
+    from allie_b200.models import load_model_state
+
+    tok, ours, _ = _models()
+    sd = {("_orig_mod." + k): v.clone() for k, v in ours.state_dict().items()}
+    sd["_orig_mod.model.model.transformer.h.0.attn.bias"] = torch.ones(1, 1, 64, 64)
+    sd["_orig_mod.model.model.transformer.h.0.attn.masked_bias"] = torch.tensor(-1e4)
+    with torch.no_grad():
+        for p in ours.parameters():
+            p.zero_()
+    load_model_state(ours, sd)
+    assert float(ours.state_dict()["model.model.transformer.wte.weight"].abs().sum()) > 0
+    sd.pop("_orig_mod.value_head.0.weight")
+    with pytest.raises(RuntimeError):
+        load_model_state(ours, sd)                # a missing parameter is still an error
