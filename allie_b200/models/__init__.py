@@ -17,12 +17,19 @@ Model = GPT2LM | CausalLMWithControlToken | CausalLMWithRegressionHead
 
 def _load_pretrained_body(model: GPT2LM, base_model: str) -> bool:
     """Copies GPT-2 body weights (everything except the token embedding / LM head) from a local
-    HF checkpoint directory and re-draws ``wte`` from N(mean, std) of the pretrained embedding
+    HF checkpoint directory (or the local Hugging Face cache of ``base_model``) and re-draws ``wte`` from N(mean, std) of the pretrained embedding
     (reference ``model.py:175-188``).  Returns False when no local weights exist."""
-    cand = [os.path.join(base_model, n) for n in ("pytorch_model.bin", "model.safetensors")]
+    import glob
+
+    # a local checkpoint directory, or the Hugging Face cache of a model fetched earlier
+    # (<HF_HOME>/hub/models--<name>/snapshots/<revision>/)
+    hub = os.path.join(os.environ.get("HF_HOME", os.path.join(os.path.expanduser("~"), ".cache", "huggingface")), "hub")
+    dirs = [base_model] + sorted(glob.glob(os.path.join(hub, "models--" + base_model.replace("/", "--"), "snapshots", "*")))
+    cand = [os.path.join(d, n) for d in dirs for n in ("model.safetensors", "pytorch_model.bin")]
     path = next((p for p in cand if os.path.exists(p)), None)
     if path is None:
         return False
+    logger.info("loading pretrained GPT-2 body from %s", path)
     if path.endswith(".safetensors"):
         from safetensors.torch import load_file
 

@@ -2,6 +2,8 @@
 ``[in, out]`` weights, tied lm_head), and the same logits from the same weights.  This is what makes
 checkpoints interchangeable with the reference, whose model is ``GPT2LMHeadModel`` inside the two
 wrappers (``src/modeling/model.py:19-20,69-70,165-179``)."""
+import os
+
 import pytest
 import torch
 
@@ -79,6 +81,19 @@ def test_use_pretrained_loads_a_local_gpt2_body(tmp_path):
     assert abs(wte.mean().item() - hsd["transformer.wte.weight"].mean().item()) < 0.02
     assert abs(wte.std().item() / hsd["transformer.wte.weight"].std().item() - 1) < 0.1
     assert inner.lm_head.weight.data_ptr() == wte.data_ptr()                      # still tied
+    # the same weights found through the Hugging Face cache layout when base_model is a name
+    import shutil
+
+    snap = tmp_path / "hf" / "hub" / "models--gpt2" / "snapshots" / "abc123"
+    shutil.copytree(tmp_path / "gpt2-local", snap)
+    os.environ["HF_HOME"] = str(tmp_path / "hf")
+    try:
+        named = initialize_model(tok, "gpt2", use_control_token=True, use_regression_head=True, use_pretrained=True,
+                                 n_layer=2, n_embd=64, n_head=2, n_positions=64)
+    finally:
+        del os.environ["HF_HOME"]
+    assert torch.equal(named.model.model.state_dict()["transformer.h.1.mlp.c_fc.weight"],
+                       hsd["transformer.h.1.mlp.c_fc.weight"])
 
 
 def test_checkpoints_with_wrapper_prefixes_and_mask_buffers_load():
