@@ -166,6 +166,7 @@ class Trainer:
         if self.master_process:
             os.makedirs(output_dir, exist_ok=True)
             setup_logging(output_dir, file=True)
+            self.metrics.path = join(output_dir, "metrics.jsonl")
         self.seed = seed
         self.lr, self.min_lr, self.decay_lr = lr, min_lr, decay_lr
         self.weight_decay = weight_decay

@@ -1,7 +1,8 @@
-"""Metric sink: forwards to Weights & Biases when it is importable and allowed, always mirrors to
-``metrics.jsonl``-style lines in the log.  The reference logs ``iter, lr, train/loss, val/*_loss,
-test/loss`` to the wandb project ``chess-lm`` with ``resume="allow"`` and falls back to offline mode
-when the service is unreachable (``src/modeling/trainer.py:88-106,254-261``)."""
+"""Metric sink: forwards to Weights & Biases when it is importable and allowed, and always mirrors
+every row to the debug log and, when a path is given, to a ``metrics.jsonl`` file (one JSON object
+per line).  The reference logs ``iter, lr, train/loss, val/*_loss, test/loss`` to the wandb project
+``chess-lm`` with ``resume="allow"`` and falls back to offline mode when the service is unreachable
+(``src/modeling/trainer.py:88-106,254-261``)."""
 from __future__ import annotations
 
 import json
@@ -12,8 +13,9 @@ logger = logging.getLogger(__name__)
 
 
 class MetricsSink:
-    def __init__(self, enabled: bool, project: str, name=None, run_id=None, config=None):
+    def __init__(self, enabled: bool, project: str, name=None, run_id=None, config=None, path: str | None = None):
         self.run = None
+        self.path = path                      # every row is also appended here as one JSON line
         self.history: list[dict] = []
         if not enabled or os.environ.get("ALLIE_NO_WANDB") == "1":
             return
@@ -36,6 +38,13 @@ class MetricsSink:
     def log(self, row: dict) -> None:
         self.history.append(row)
         logger.debug("metrics " + json.dumps(row))
+        if self.path is not None:
+            try:
+                with open(self.path, "a") as f:
+                    f.write(json.dumps(row) + "\n")
+            except OSError as e:
+                logger.warning(f"cannot write {self.path}: {e}")
+                self.path = None
         if self.run is not None:
             try:
                 self.run.log(row)

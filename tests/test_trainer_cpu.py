@@ -60,6 +60,8 @@ def test_train_checkpoint_resume_and_eval_cli(tmp_path):
     log = (run / "log.txt").read_text()
     assert "train - iter 0: loss" in log and "val - iter 0:" in log and "new best val loss" in log
     assert "throughput - " in log and "tokens/s" in log
+    rows = [json.loads(line) for line in (run / "metrics.jsonl").read_text().splitlines()]
+    assert any("val/loss" in r and "lr" in r for r in rows) and any("perf/tokens_per_s" in r for r in rows)
     ck = torch.load(run / "last.pt", weights_only=False)
     assert {"iter_num", "best_val_loss", "model", "optimizer"} <= set(ck)
     keys = set(ck["model"])
