@@ -101,8 +101,10 @@ extern "C" int chess_set_fen(void* h, const char* fen) {
   }
   if (*p != ' ') return 0;
   ++p;
+  if (*p != 'w' && *p != 'b') return 0;
   b->turn = (*p == 'w') ? chess::WHITE : chess::BLACK;
-  p += 2;
+  ++p;
+  if (*p == ' ') ++p;          // a FEN cut short after the side to move keeps the defaults below
   for (; *p && *p != ' '; ++p) {
     if (*p == 'K') b->castling |= chess::bit(7);
     if (*p == 'Q') b->castling |= chess::bit(0);
@@ -111,7 +113,13 @@ extern "C" int chess_set_fen(void* h, const char* fen) {
   }
   if (*p == ' ') ++p;
   b->ep_square = -1;
-  if (*p && *p != '-') { b->ep_square = (p[1] - '1') * 8 + (p[0] - 'a'); p += 2; } else if (*p) ++p;
+  if (*p && *p != '-') {
+    if (p[0] < 'a' || p[0] > 'h' || p[1] < '1' || p[1] > '8') return 0;
+    b->ep_square = (p[1] - '1') * 8 + (p[0] - 'a');
+    p += 2;
+  } else if (*p) {
+    ++p;
+  }
   b->halfmove_clock = 0;
   b->fullmove = 1;
   if (*p == ' ') {
