@@ -153,8 +153,8 @@ def serve(alias: str, model, tokenizer: UCITokenizer, device: str | None = None,
                     if not game.legal_moves:              # replays the moves: an illegal game fails here
                         raise ValueError("the game is over: no legal move to answer with")
                     ready.append((conn, game))
-                except (ConnectionError, OSError, ValueError, TypeError, KeyError) as e:
-                    logger.warning(f"request failed: {type(e).__name__}: {e}")
+                except (ConnectionError, OSError, ValueError, TypeError, KeyError, AttributeError) as e:
+                    logger.warning(f"request failed: {type(e).__name__}: {e}")     # a malformed request never ends the server
                     conn.close()
             try:
                 if hasattr(algorithm, "decode_batch"):

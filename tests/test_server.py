@@ -35,7 +35,7 @@ def test_round_trip_and_broken_client():
                              n_embd=32, n_head=1, n_positions=64).eval()
     port = _free_port()
     th = threading.Thread(target=serve, kwargs=dict(alias="grandmaster", model=model, tokenizer=tok, device="cpu",
-                                                    port=port, self_test=False, max_requests=5), daemon=True)
+                                                    port=port, self_test=False, max_requests=8), daemon=True)
     th.start()
     for _ in range(50):
         try:
@@ -47,6 +47,11 @@ def test_round_trip_and_broken_client():
         with socket.create_connection(("localhost", port), timeout=10) as c:
             send_dict(c, Game("180+0", 1500, 1600, None, False, bad, [1] * len(bad)).to_dict())
             assert c.recv(100) == b""                                    # closed without an answer
+    for junk in ([1, 2, 3], {"moves": [7]}, {"time_control": "180+0", "white_elo": 1, "black_elo": 2, "outcome": None,
+                                             "normal_termination": False, "moves": [12, None], "moves_seconds": [0, 0]}):
+        with socket.create_connection(("localhost", port), timeout=10) as c:
+            send_dict(c, junk)
+            assert c.recv(100) == b""
     game = Game("180+0", 1500, 1600, None, False, ["e2e4", "e7e5"], [1, 2])
     for _ in range(2):
         with socket.create_connection(("localhost", port), timeout=10) as c:
