@@ -122,6 +122,25 @@ def build_algorithm(alias: str, model, tokenizer: UCITokenizer, device: str | No
     return DECODE_STRATEGIES[system.algorithm](model, tokenizer, device=device, **system.algorithm_config)
 
 
+def _validated(game: Game) -> Game:
+    """Type checks of a request before it reaches the model (a malformed field would otherwise
+    surface as an exception in the middle of a batch)."""
+    if not (isinstance(game.time_control, str) and isinstance(game.moves, list) and isinstance(game.moves_seconds, list)):
+        raise ValueError("time_control must be a string, moves and moves_seconds lists")
+    for name in ("white_elo", "black_elo"):
+        elo = getattr(game, name)
+        if elo is not None and (isinstance(elo, bool) or not isinstance(elo, int) or not 0 <= elo <= 10000):
+            raise ValueError(f"{name} must be an integer rating")
+    if game.white_elo is None and game.black_elo is None:
+        raise ValueError("at least the opponent's rating is needed")
+    if len(game.moves) != len(game.moves_seconds) or not all(isinstance(m, str) for m in game.moves):
+        raise ValueError("moves must be strings, one entry of moves_seconds per move")
+    if not all(isinstance(t, (int, float)) and not isinstance(t, bool) and t >= 0 for t in game.moves_seconds):
+        raise ValueError("moves_seconds must be non-negative numbers")
+    game.moves_seconds = [int(t) for t in game.moves_seconds]
+    return game
+
+
 def _answer(conn: socket.socket, res: DecodeResult) -> None:
     send_dict(conn, {"move": res.move, "think_time": res.think_time, "resigned": res.resigned})
 
@@ -149,7 +168,7 @@ def serve(alias: str, model, tokenizer: UCITokenizer, device: str | None = None,
             for conn in conns:
                 try:
                     conn.settimeout(client_timeout)
-                    game = assign_elo(Game(**recv_dict(conn)), system)
+                    game = assign_elo(_validated(Game(**recv_dict(conn))), system)
                     if not game.legal_moves:              # replays the moves: an illegal game fails here
                         raise ValueError("the game is over: no legal move to answer with")
                     ready.append((conn, game))

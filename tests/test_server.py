@@ -35,7 +35,7 @@ def test_round_trip_and_broken_client():
                              n_embd=32, n_head=1, n_positions=64).eval()
     port = _free_port()
     th = threading.Thread(target=serve, kwargs=dict(alias="grandmaster", model=model, tokenizer=tok, device="cpu",
-                                                    port=port, self_test=False, max_requests=8), daemon=True)
+                                                    port=port, self_test=False, max_requests=10), daemon=True)
     th.start()
     for _ in range(50):
         try:
@@ -48,7 +48,11 @@ def test_round_trip_and_broken_client():
             send_dict(c, Game("180+0", 1500, 1600, None, False, bad, [1] * len(bad)).to_dict())
             assert c.recv(100) == b""                                    # closed without an answer
     for junk in ([1, 2, 3], {"moves": [7]}, {"time_control": "180+0", "white_elo": 1, "black_elo": 2, "outcome": None,
-                                             "normal_termination": False, "moves": [12, None], "moves_seconds": [0, 0]}):
+                                             "normal_termination": False, "moves": [12, None], "moves_seconds": [0, 0]},
+                 {"time_control": "180+0", "white_elo": "abc", "black_elo": 2, "outcome": None,
+                  "normal_termination": False, "moves": ["e2e4"], "moves_seconds": [0]},
+                 {"time_control": "180+0", "white_elo": 1500, "black_elo": 1500, "outcome": None,
+                  "normal_termination": False, "moves": ["e2e4"], "moves_seconds": []}):
         with socket.create_connection(("localhost", port), timeout=10) as c:
             send_dict(c, junk)
             assert c.recv(100) == b""
