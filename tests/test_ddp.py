@@ -35,6 +35,16 @@ def test_cpu_gloo_two_ranks_match_single(tmp_path):
     assert "throughput - 500 tokens/s, 2000.0 ms/step (max over 2 rank(s))" in log
 
 
+def test_cpu_gloo_two_ranks_with_moe_layers_stay_in_step(tmp_path):
+    """The MoE model (all experts on every rank on the CPU path) under 2 gloo ranks: router, expert
+    and dense gradients are all averaged, so the ranks end on identical parameters."""
+    _launch(2, tmp_path, "collective", "cpu", 29612, extra_args=("moe",))
+    a = torch.load(tmp_path / "params_collective_0.pt")
+    b = torch.load(tmp_path / "params_collective_1.pt")
+    assert torch.equal(a["params"], b["params"]), "ranks diverged"
+    assert all(l == l for l in a["losses"])
+
+
 @pytest.mark.gpu
 def test_fused_nvlink_path_matches_all_reduce(tmp_path):
     if torch.cuda.device_count() < 2:
