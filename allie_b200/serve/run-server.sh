@@ -32,8 +32,15 @@ trap requeue SIGUSR1
 trap 'stop_children; exit 0' SIGINT SIGTERM EXIT
 
 aliases=$(python -c 'from allie_b200.serve import SYSTEMS; print(" ".join(SYSTEMS))')
+# ALLIE_GPUS_PER_SYSTEM > 1: every system gets that many backend servers (one per GPU) behind its port
+gpus_per_system=${ALLIE_GPUS_PER_SYSTEM:-1}
 for alias in $aliases; do
-    python -u -m allie_b200.serve.server "$alias" "$config" >"$logs/$alias.out" 2>"$logs/$alias.err" &
+    if [ "$gpus_per_system" -gt 1 ]; then
+        python -u -m allie_b200.serve.pool "$alias" "$config" --gpus "$gpus_per_system" \
+            >"$logs/$alias.out" 2>"$logs/$alias.err" &
+    else
+        python -u -m allie_b200.serve.server "$alias" "$config" >"$logs/$alias.out" 2>"$logs/$alias.err" &
+    fi
     pids+=($!)
 done
 
