@@ -10,5 +10,6 @@ setup(
     package_data={"allie_b200": ["lib/*.so", "csrc/*", "serve/*.sh", "etl/*.sh"]},
     install_requires=["torch>=2.6", "numpy", "pyyaml"],
     extras_require={"hf": ["transformers"], "metrics": ["wandb"], "etl": ["zstandard"]},
+    entry_points={"console_scripts": ["allie = allie_b200.__main__:main"]},
     python_requires=">=3.10",
 )

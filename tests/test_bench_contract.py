@@ -54,3 +54,22 @@ def test_model_table():
     large = bench.MODELS["large"]
     assert (large["n_layer"], large["n_embd"], large["n_head"]) == (32, 1280, 20) and large["n_embd"] % 128 == 0
     assert bench.GLOBAL_BATCH % bench.MICRO_BATCH == 0 and bench.GLOBAL_BATCH // bench.MICRO_BATCH == 8
+
+
+def test_command_dispatcher(capsys, tmp_path):
+    from allie_b200.__main__ import COMMANDS, main
+    import importlib
+
+    for module, func, _ in COMMANDS.values():
+        assert callable(getattr(importlib.import_module(module), func))      # every command resolves
+    try:
+        main(["--help"])
+    except SystemExit as e:
+        assert e.code == 0
+    assert "stress-test" in capsys.readouterr().out
+    try:
+        main(["no-such-command"])
+    except SystemExit as e:
+        assert e.code == 2
+    main(["dataset", "random-games", str(tmp_path / "g.jsonl"), "--n", "3"])
+    assert len((tmp_path / "g.jsonl").read_text().splitlines()) == 3
