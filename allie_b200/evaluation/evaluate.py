@@ -200,6 +200,8 @@ def main(argv: list[str] | None = None) -> dict:
     ap.add_argument("--maia_elo", type=int, default=None)
     ap.add_argument("--checkpoint", default=None, help="defaults to {output_dir}/best.pt; 'none' = random init")
     ap.add_argument("--device", default=None)
+    ap.add_argument("--sequential", action="store_true",
+                    help="score one position per call like the reference, even where a batched form exists")
     ap.add_argument("--batch_size", type=int, default=256,
                     help="positions per call for the strategies that score many games at once")
     args = ap.parse_args(argv)
@@ -229,8 +231,13 @@ def main(argv: list[str] | None = None) -> dict:
         model.eval()
     elif args.decode not in ("maia", "gpt-3.5-turbo"):
         ap.error("--config is required for strategies that run the model")
-    strategy = DECODE_STRATEGIES[args.decode](model, tokenizer, sample=args.sample, device=args.device,
-                                              precision="float32", **decode_args)
+    # the many-positions-per-call form of a strategy returns the same results (checked against the
+    # reference) and is what makes MCTS evaluation practical; --sequential keeps the one-at-a-time form
+    implementation = args.decode
+    if not args.sequential and f"{args.decode}-batched" in DECODE_STRATEGIES:
+        implementation = f"{args.decode}-batched"
+    strategy = DECODE_STRATEGIES[implementation](model, tokenizer, sample=args.sample, device=args.device,
+                                                 precision="float32", **decode_args)
     rows = read_jsonl(args.dataset, 5 if args.debug else args.n_rows)
     mine = rows[rank::world]                       # under torchrun every rank scores every world-th game
     eval_fn, summarize = ((evaluate_quick, summarize_quick) if args.quick else
@@ -252,7 +259,7 @@ def main(argv: list[str] | None = None) -> dict:
         metrics = {"games": games, **summarize(games)}
         stats = {k: sum(st.get(k, 0) for _, st in parts) for k in parts[0][1]
                  if isinstance(parts[0][1][k], (int, float))}
-    result = {"decode": args.decode, "alias": args.alias or args.decode, "n_rows": args.n_rows, "sample": args.sample,
+    result = {"decode": args.decode, "implementation": implementation, "alias": args.alias or args.decode, "n_rows": args.n_rows, "sample": args.sample,
               "config": args.config, "dataset": args.dataset, **json.loads(args.decode_args),
               **metrics, **stats}
     if args.debug:

@@ -85,7 +85,8 @@ def test_train_checkpoint_resume_and_eval_cli(tmp_path):
     save_config(cfg, str(tmp_path / "cfg.yaml"))
     (tmp_path / "val.jsonl").write_text("\n".join(json.dumps(r) for r in val[:2]))
     res = eval_main(["--config", str(tmp_path / "cfg.yaml"), "--dataset", str(tmp_path / "val.jsonl"), "--quick",
-                     "--decode", "policy", "--output_file", str(tmp_path / "out.jsonl"), "--device", "cpu"])
+                     "--decode", "policy", "--sequential", "--output_file", str(tmp_path / "out.jsonl"), "--device", "cpu"])
+    assert res["implementation"] == "policy"
     assert res["positions"] > 0 and 0 <= res["move_match"] <= 1 and res["top_move_legal"] is not None
     written = json.loads((tmp_path / "out.jsonl").read_text().strip())
     assert written["decode"] == "policy" and len(written["games"]) == 2
@@ -99,7 +100,8 @@ def test_train_checkpoint_resume_and_eval_cli(tmp_path):
     # the many-positions-per-call strategy reports the same metrics, whatever the batch size
     for bs in ("3", "256"):
         rb = eval_main(["--config", str(tmp_path / "cfg.yaml"), "--dataset", str(tmp_path / "val.jsonl"), "--quick",
-                        "--decode", "policy-batched", "--debug", "--device", "cpu", "--batch_size", bs])
+                        "--decode", "policy", "--debug", "--device", "cpu", "--batch_size", bs])
+        assert rb["implementation"] == "policy-batched" and rb["decode"] == "policy"    # picked automatically
         assert rb["positions"] == res["positions"] and rb["move_match"] == res["move_match"]
         assert abs(rb["value_mse"] - res["value_mse"]) < 1e-5 and abs(rb["legal_mass"] - res["legal_mass"]) < 1e-5
 
