@@ -23,7 +23,8 @@ extern "C" {
 // * Returns -10 when B * H * T exceeds AB_ATTN_STATIC_MAX_ROWS; nothing is launched then.
 // * The first call on each device resolves the device address of the scratch array
 //   (cudaGetSymbolAddress, with that device current) and caches it; make that first call
-//   before any stream capture begins.
+//   before any stream capture begins.  Host threads may make that first call concurrently: each
+//   resolves the same address and the cache entry is an atomic.
 // * Every call on a device shares the one scratch array and fully overwrites the part it uses, so
 //   nothing needs clearing between calls - but two calls whose kernels overlap on the GPU (different
 //   streams, no ordering between them) race on it.  Order such calls yourself.

@@ -763,13 +763,17 @@ int ab_attn_bwd(const void* qkv, const void* out, const float* lse, const void* 
 
 // ------------------------------------------------------------------------------------------------
 // Allocation-free variant (see attn_static.cuh for who needs it and why).
+#include <atomic>
+
 #include "attn_static.cuh"
 
 namespace ab {
 // Scratch for `delta`.  In host code this name is only a handle; the device address is looked up
 // per device below.
 static __device__ __align__(256) float g_attn_static_delta[AB_ATTN_STATIC_MAX_ROWS];
-static float* g_attn_static_ptr[64] = {nullptr};
+// Per-device cache of the array's device address.  Host threads may fill an entry concurrently;
+// they all store the same value, and the atomic keeps the store and the loads untorn.
+static std::atomic<float*> g_attn_static_ptr[64];
 }  // namespace ab
 
 extern "C" int ab_attn_bwd_static(const void* qkv, const void* out, const float* lse,
@@ -784,13 +788,15 @@ extern "C" int ab_attn_bwd_static(const void* qkv, const void* out, const float*
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return (int)e;
   if (dev < 0 || dev >= 64) return -11;
-  if (!g_attn_static_ptr[dev]) {
+  float* scratch = g_attn_static_ptr[dev].load(std::memory_order_acquire);
+  if (!scratch) {
     // once per device, with that device current: turn the symbol into a device pointer
     void* p = nullptr;
     e = cudaGetSymbolAddress(&p, g_attn_static_delta);
     if (e != cudaSuccess) return (int)e;
-    g_attn_static_ptr[dev] = static_cast<float*>(p);
+    scratch = static_cast<float*>(p);
+    g_attn_static_ptr[dev].store(scratch, std::memory_order_release);
   }
-  return ab_attn_bwd(qkv, out, lse, dout, dqkv, g_attn_static_ptr[dev], drop_mask, nullptr, B, T, H, hd,
+  return ab_attn_bwd(qkv, out, lse, dout, dqkv, scratch, drop_mask, nullptr, B, T, H, hd,
                      scale, seed, stream_id, thr16, status, stream);
 }

@@ -19,6 +19,7 @@ autocast; GEMM operands are bf16 with fp32 accumulation.
 from __future__ import annotations
 
 import math
+import re
 
 import torch
 import torch.nn as nn
@@ -57,34 +58,93 @@ def partition_parameter_names(model: nn.Module) -> tuple[list[str], list[str]]:
     return sorted(decay), sorted(no_decay)
 
 
+def layer_of(name: str) -> int | None:
+    """Index of the transformer block a parameter belongs to (None for embeddings, final norm, heads)."""
+    m = re.search(r"\.h\.(\d+)\.", name)
+    return int(m.group(1)) if m else None
+
+
+def bucket_of(name: str, n_layer: int, layers_per_bucket: int) -> int:
+    """Gradient bucket of a parameter, numbered in the order backward completes them: the final
+    norm and the regression heads go with the last blocks (bucket 0), every following bucket takes
+    the next ``layers_per_bucket`` blocks going down, and the embeddings (whose gradient is only
+    complete after the embedding backward, the very last kernel) go with block 0."""
+    nb = max(1, -(-n_layer // layers_per_bucket))
+    l = layer_of(name)
+    if l is None:
+        first = any(k in name for k in ("ln_f.", "value_head", "time_head"))
+        return 0 if first else nb - 1
+    return (n_layer - 1 - l) // layers_per_bucket
+
+
+def arena_layout(model: nn.Module, local_names: frozenset = frozenset(), n_layer: int = 1,
+                 layers_per_bucket: int | None = None) -> dict:
+    """Where every parameter sits in the flat arenas.  The replicated parameters are laid out as
+    gradient buckets of ``layers_per_bucket`` transformer blocks each, in the order backward
+    finishes them (None: one bucket); inside a bucket come first the weight-decayed GEMM weights
+    (which ranks other than a slice's owner need only as bf16), then the weight-decayed
+    parameters the kernels read as fp32, then the rest.  Rank-local (expert-parallel) parameters
+    follow behind ``sync_end``.  Pure index arithmetic, no device needed."""
+    decay, no_decay = partition_parameter_names(model)
+    params = dict(model.named_parameters())
+    lpb = layers_per_bucket if layers_per_bucket else max(1, n_layer)
+    nb = max(1, -(-n_layer // lpb))
+    # weight-decayed matrices that the kernels read as fp32 (the two regression heads); every
+    # other weight-decayed parameter is a GEMM operand and is only ever read from its bf16 copy
+    fp32_read = [n for n in decay if "value_head" in n or "time_head" in n]
+    groups: list[tuple[list[str], bool]] = []
+    for b in range(nb):
+        mine = lambda names: [n for n in names if n not in local_names and bucket_of(n, n_layer, lpb) == b]
+        groups.append(([n for n in mine(decay) if n not in fp32_read], True))
+        groups.append((mine(fp32_read), True))
+        groups.append((mine(no_decay), False))
+    n_repl = len(groups)
+    groups.append(([n for n in decay if n in local_names], True))
+    groups.append(([n for n in no_decay if n in local_names], False))
+    offsets: dict[str, int] = {}
+    off = 0
+    bounds = []
+    for g, _ in groups:
+        start = off
+        for n in g:
+            offsets[n] = off
+            off += (params[n].numel() + ALIGN - 1) // ALIGN * ALIGN
+        bounds.append((start, off))
+    # gradient buckets: (start, end of the part other ranks need only as bf16, end of the
+    # weight-decayed part, end)
+    buckets = [(bounds[3 * b][0], bounds[3 * b][1], bounds[3 * b + 1][1], bounds[3 * b + 2][1]) for b in range(nb)]
+    # (start, end, apply weight decay) of every optimizer range, empty ones dropped and adjacent equal ones merged
+    regions: list[tuple[int, int, bool]] = []
+    for i, (s0, e0) in enumerate(bounds[:n_repl]):
+        if e0 > s0:
+            if regions and regions[-1][2] == groups[i][1] and regions[-1][1] == s0:
+                regions[-1] = (regions[-1][0], e0, groups[i][1])
+            else:
+                regions.append((s0, e0, groups[i][1]))
+    local_regions = [(s0, e0, groups[n_repl + i][1]) for i, (s0, e0) in enumerate(bounds[n_repl:]) if e0 > s0]
+    return dict(names=[n for g, _ in groups for n in g], decay_names=frozenset(decay), offsets=offsets,
+                buckets=buckets, sync_end=bounds[n_repl - 1][1], regions=regions + local_regions,
+                local_regions=local_regions, total=off, layers_per_bucket=lpb,
+                shapes={n: tuple(params[n].shape) for n in offsets})
+
+
 class ParamArena:
     """Flat storage for parameters / gradients / Adam state / bf16 shadows."""
 
     def __init__(self, model: nn.Module, device: torch.device, symmetric: bool = False,
-                 local_names: frozenset = frozenset()):
+                 local_names: frozenset = frozenset(), n_layer: int = 1, layers_per_bucket: int | None = None):
         """``symmetric``: allocate the master / gradient / shadow arenas in symmetric memory so
         peer GPUs can address them (the fused NVLink gradient path needs that).
         ``local_names``: parameters that differ per rank (expert-parallel weights); they are laid
-        out after the replicated ones and never take part in gradient synchronisation."""
-        decay, no_decay = partition_parameter_names(model)
+        out after the replicated ones and never take part in gradient synchronisation.
+        ``layers_per_bucket``: see :func:`arena_layout`."""
+        lay = arena_layout(model, local_names, n_layer, layers_per_bucket)
         params = dict(model.named_parameters())
-        groups = [[n for n in decay if n not in local_names], [n for n in no_decay if n not in local_names],
-                  [n for n in decay if n in local_names], [n for n in no_decay if n in local_names]]
-        self.names = [n for g in groups for n in g]
-        self.offsets: dict[str, int] = {}
-        off = 0
-        bounds = []
-        for g in groups:
-            start = off
-            for n in g:
-                self.offsets[n] = off
-                off += (params[n].numel() + ALIGN - 1) // ALIGN * ALIGN
-            bounds.append((start, off))
-        self.decay_end = bounds[0][1]          # replicated, weight-decayed
-        self.sync_end = bounds[1][1]           # end of the replicated region
-        # (start, end, apply weight decay) of every optimizer range
-        self.regions = [(bounds[0][0], bounds[0][1], True), (bounds[1][0], bounds[1][1], False),
-                        (bounds[2][0], bounds[2][1], True), (bounds[3][0], bounds[3][1], False)]
+        self.names, self.decay_names, self.offsets = lay["names"], lay["decay_names"], lay["offsets"]
+        self.buckets, self.sync_end = lay["buckets"], lay["sync_end"]
+        self.regions, self.local_regions = lay["regions"], lay["local_regions"]
+        self.layers_per_bucket = lay["layers_per_bucket"]
+        off = lay["total"]
         self.total = off
         self.symmetric = symmetric
         if symmetric:
@@ -124,7 +184,10 @@ class ParamArena:
 
 class B200Engine:
     def __init__(self, model: nn.Module, device: str | torch.device = "cuda", seed: int = 1234,
-                 symmetric: bool = False):
+                 symmetric: bool = False, layers_per_bucket: int | None = None):
+        """``symmetric``: parameter arenas in symmetric memory, laid out as gradient buckets (the
+        fused NVLink gradient path).  ``layers_per_bucket``: transformer blocks per gradient bucket
+        (default with ``symmetric``: about a dozen buckets)."""
         self.device = torch.device(device)
         assert self.device.type == "cuda"
         if self.device.index is None:
@@ -137,7 +200,10 @@ class B200Engine:
         assert self.cfg.activation_function == "gelu_new"
         model.to(self.device)
         local_names = self._shard_experts(model)
-        self.arena = ParamArena(model, self.device, symmetric=symmetric, local_names=local_names)
+        if symmetric and layers_per_bucket is None:
+            layers_per_bucket = max(1, -(-self.cfg.n_layer // 12))
+        self.arena = ParamArena(model, self.device, symmetric=symmetric, local_names=local_names,
+                                n_layer=self.cfg.n_layer, layers_per_bucket=layers_per_bucket)
         self._moe_ctx: dict = {}
         self._moe_layers: dict = {}
         self.rms = self.cfg.norm_type == "rmsnorm"
@@ -378,7 +444,9 @@ class B200Engine:
         return self.reg.aux_loss_coef if self.reg is not None else self.cfg.aux_loss_coef
 
     # ------------------------------------------------------------- backward
-    def backward(self, B: int, T: int, seed: int) -> None:
+    def backward(self, B: int, T: int, seed: int, bucket_hook=None) -> None:
+        """``bucket_hook(b)`` is called right after the last kernel that writes a gradient of bucket
+        ``b`` of the parameter arena has been enqueued (buckets complete in order 0, 1, ...)."""
         cfg = self.cfg
         buf = self._buffers(B, T, True)
         d, V = cfg.n_embd, cfg.vocab_size
@@ -388,6 +456,7 @@ class B200Engine:
         dpre, dqkv = buf["dpre"], buf["dqkv"]
         F = cfg.ffn_dim
         dlogits = buf["logits"]
+        lpb = self.arena.layers_per_bucket
         # lm head: d h = dlogits @ wte ; d wte += dlogits^T @ h
         gemm(dlogits, self.wte[1], b_mn=True, out=dsmall)
         gemm(dlogits, buf["h"], a_mn=True, b_mn=True, out=self.wte[2], accumulate=True)
@@ -431,7 +500,13 @@ class B200Engine:
                             dyb if l > 0 else None, L["ln1_w"][2], L["ln1_b"][2], rms=self.rms,
                             drop_seed=seed, drop_stream=max(0, 2 + 3 * (l - 1)), drop_p=p_res if l > 0 else 0.0,
                             dbias=proj_bias_grad(self.layers[l - 1]) if l > 0 else None)
+            # block l was the lowest of its bucket (the bucket that also holds the embeddings is
+            # only complete after the embedding backward below)
+            if bucket_hook is not None and l > 0 and (nl - l) % lpb == 0:
+                bucket_hook((nl - 1 - l) // lpb)
         K.embed_bwd(buf["ids"], buf["pos"], dx, self.wte[2], self.wpe[2], self.ctrl_w[2], V, seed, 0, p_emb)
+        if bucket_hook is not None:
+            bucket_hook(len(self.arena.buckets) - 1)
 
     # ------------------------------------------------------------- public API
     def load_window(self, words: torch.Tensor) -> tuple[int, int]:
@@ -472,13 +547,14 @@ class B200Engine:
         self.fwd_count += 1
         return (self.seed * 0x9E3779B97F4A7C15 + self.fwd_count * 0xD1B54A32D192ED03) & ((1 << 64) - 1)
 
-    def micro_step(self, words: torch.Tensor) -> torch.Tensor:
+    def micro_step(self, words: torch.Tensor, bucket_hook=None) -> torch.Tensor:
         """Forward + backward of one micro-batch of raw words; gradients accumulate.  Returns the
-        device tensor [loss, lm_loss, value_loss, time_loss] (no host sync)."""
+        device tensor [loss, lm_loss, value_loss, time_loss] (no host sync).  ``bucket_hook``: see
+        :meth:`backward` (given on the last micro-step of an optimizer step)."""
         B, T = self.load_window(words)
         seed = self._next_seed()
         self.forward(B, T, True, seed, True, True)
-        self.backward(B, T, seed)
+        self.backward(B, T, seed, bucket_hook)
         return self.loss_out
 
     def micro_step_batch(self, batch: dict) -> torch.Tensor:

@@ -59,9 +59,10 @@ class WindowSampler:
 
     A background thread keeps the next windows gathered while the training thread launches
     kernels, so page faults of a memory-mapped stream never stall a step.  Buffers form a pool: one
-    handed out by ``next()`` goes back to the pool only after ``keep`` later ones were handed out,
-    which is far longer than its asynchronous host-to-device copy stays in flight (the launch
-    queue lets the host run at most a couple of micro-steps ahead of the device)."""
+    handed out by ``next()`` goes back to the pool after ``keep`` later ones were handed out, and
+    the producer refills it only once the CUDA event recorded behind its host-to-device copy
+    (:meth:`to_device`) has completed, so a copy still queued on the device is never overwritten
+    however far the host runs ahead."""
 
     def __init__(self, data: np.ndarray, batch_size: int, seq_len: int, pin: bool, depth: int = 8,
                  prefetch: bool = True):
@@ -75,6 +76,7 @@ class WindowSampler:
         self.rng = np.random.default_rng(int.from_bytes(os.urandom(8), "little"))
         self.offs = np.arange(seq_len, dtype=np.int64)[None, :]
         self._handed: deque = deque()
+        self._copied: dict[int, torch.cuda.Event] = {}     # buffer id -> event behind its last H2D copy
         self._free: queue.Queue = queue.Queue()
         for b in self.bufs:
             self._free.put(b)
@@ -97,6 +99,9 @@ class WindowSampler:
                 buf = self._free.get()
                 if buf is None:
                     return
+                ev = self._copied.pop(id(buf), None)
+                if ev is not None:
+                    ev.synchronize()
                 self._fill(buf)
                 self._ready.put(buf)
         except BaseException as e:      # surfaces in next(), on the training thread
@@ -106,6 +111,9 @@ class WindowSampler:
     def next(self) -> torch.Tensor:
         if self._thread is None:
             buf = self._free.get()
+            ev = self._copied.pop(id(buf), None)
+            if ev is not None:
+                ev.synchronize()
             self._fill(buf)
         else:
             buf = self._ready.get()
@@ -115,6 +123,16 @@ class WindowSampler:
         if len(self._handed) > self.keep:
             self._free.put(self._handed.popleft())
         return buf
+
+    def to_device(self, buf: torch.Tensor, device) -> torch.Tensor:
+        """Asynchronous copy of a staging buffer handed out by :meth:`next` to the device, with an
+        event behind it that the producer waits for before it reuses the buffer."""
+        out = buf.to(device, non_blocking=True)
+        if out.is_cuda:
+            ev = torch.cuda.Event()
+            ev.record()
+            self._copied[id(buf)] = ev
+        return out
 
     def close(self) -> None:
         self._stop = True
@@ -132,7 +150,20 @@ class Trainer:
                  max_iters: int = 600000, eval_interval: int = 2000, log_interval: int = 10,
                  save_interval: int = 500,
                  # extensions (absent from the reference schema, all optional)
-                 shard_optimizer: bool = False, grad_sync: str = "auto", use_wandb: bool = True):
+                 shard_optimizer: Optional[bool] = None, grad_sync: str = "auto", use_wandb: bool = True):
+        """Extensions to the reference signature: ``grad_sync`` = ``auto`` | ``fused`` (the NVLink
+        kernels: bucketed reduce-scatter under backward, optimizer state sharded over the ranks)
+        | ``collective`` (one all_reduce, replicated optimizer).  ``shard_optimizer`` is the same
+        choice as a boolean: true requires the sharded fused path, false selects ``collective``."""
+        if shard_optimizer is not None:
+            want = "fused" if shard_optimizer else "collective"
+            if grad_sync not in ("auto", want):
+                raise ValueError(f"shard_optimizer={shard_optimizer} contradicts grad_sync={grad_sync!r}")
+            grad_sync = want
+        if grad_sync not in ("auto", "fused", "collective"):
+            raise ValueError(f"grad_sync must be auto, fused or collective, not {grad_sync!r}")
+        if dtype not in ("bfloat16", "float32", "float16"):
+            raise ValueError(f"unknown dtype {dtype!r}")
         self.config = config
         self.output_dir = output_dir
         self.backend = backend
@@ -174,8 +205,12 @@ class Trainer:
         self.grad_clip = grad_clip
         self.warmup_iters, self.decay_iters, self.max_iters = warmup_iters, decay_iters, max_iters
         self.eval_interval, self.log_interval, self.save_interval = eval_interval, log_interval, save_interval
-        self.shard_optimizer = shard_optimizer
         self.grad_sync_mode = grad_sync
+        if self.device_type == "cuda" and dtype != "bfloat16":
+            # the sm_100a engine computes in bf16 with fp32 accumulation, residual stream and
+            # master weights; it has no fp32 / fp16 + loss-scaling mode (``trainer.py:114-125``)
+            raise ValueError(f"dtype={dtype!r} is not supported on CUDA: the engine trains in bfloat16 "
+                             "(fp32 master weights); use device='cpu' for an fp32 run")
         self.iter_num = 0
         self.best_val_loss = float("inf")
         self.engine = None
@@ -208,6 +243,10 @@ class Trainer:
 
         self.model = model
         logger.info(f"model parameters: {count_params(model)/1e9:.2f}B")
+        if self.device_type == "cpu" and self.dtype != "float32":
+            logger.info(f"dtype={self.dtype}: the CPU path computes in float32")
+        if self.torch_compile:
+            logger.info("torch_compile: ignored (the model runs as an explicit kernel schedule, nothing is traced)")
         if self.device_type == "cuda":
             from ..models.engine import B200Engine
 
@@ -267,13 +306,17 @@ class Trainer:
         if self.engine is not None:
             eng = self.engine
             loss = None
+            fused = self.grad_sync is not None and self.grad_sync.fused
             for ms in range(ga):
                 with tr.phase("data"):
                     w = windows[ms] if windows is not None else self.sampler.next()
                     if not w.is_cuda:
-                        w = w.to(eng.device, non_blocking=True)
+                        w = self.sampler.to_device(w, eng.device) if windows is None else w.to(eng.device, non_blocking=True)
                 with tr.phase("forward_backward"):
-                    loss = eng.micro_step(w)
+                    # on the last micro-step every finished gradient bucket goes straight to its
+                    # reduce-scatter on the side stream, under the rest of backward
+                    hook = self.grad_sync.nvl.bucket_ready if fused and ms == ga - 1 else None
+                    loss = eng.micro_step(w, bucket_hook=hook)
             world = self.ddp_world_size
             with tr.phase("grad_sync_optimizer"):
                 if self.grad_sync is not None and self.grad_sync.fused:
@@ -366,16 +409,24 @@ class Trainer:
                            self.gradient_accumulation_steps * self.ddp_world_size)
         while True:
             lr = self.get_lr()
-            if self.eval_interval > 0 and self.iter_num % self.eval_interval == 0 and (
-                    self.master_process or self.expert_parallel):
+            extra_work = False
+            if self.eval_interval > 0 and self.iter_num % self.eval_interval == 0:
                 self._drain(pending, losses, all_=True)
-                val_log = self.validate()
-                self.metrics.log({"iter": self.iter_num, "lr": lr,
-                                  "train/loss": sum(losses) / len(losses) if losses else None} | val_log)
+                val_log = self.validate()             # rank 0 evaluates; every rank joins the best.pt decision
+                if self.master_process or self.expert_parallel:
+                    self.metrics.log({"iter": self.iter_num, "lr": lr,
+                                      "train/loss": sum(losses) / len(losses) if losses else None} | val_log)
+                extra_work = True
             if self.save_interval > 0 and self.iter_num % self.save_interval == 0:
                 self._gather_optimizer_state()        # collective when the optimizer is sharded
                 if self.master_process or self.expert_parallel:
                     self.save_ckpt("last")
+                extra_work = True
+            if extra_work:
+                # rank 0 may have spent seconds evaluating or writing a file: bring the ranks back
+                # together on the host, or the others' next gradient kernels would run out of
+                # their (about one second) wait for rank 0
+                self._realign()
             loss = self.train_step()
             if loss.is_cuda:
                 host = torch.empty((), dtype=torch.float32, pin_memory=True)
@@ -394,6 +445,10 @@ class Trainer:
                 steps = max(1, self.log_interval) if self.iter_num > 0 else 1
                 logger.info(f"train - iter {self.iter_num}: loss {loss_mean:.4f}, time {dt:.2f}s")
                 self._log_throughput(dt, steps, tokens_per_step)
+                if self.engine is not None:
+                    from ..ops import _lib
+
+                    _lib.check_status()     # a device-side wait that ran out since the last log line raises here
                 if self.tracer.enabled:
                     phases = self.tracer.summary()
                     logger.info("phases - " + ", ".join(f"{k} {v['ms']:.1f} ms / {v['count']}" for k, v in phases.items()))
@@ -413,6 +468,7 @@ class Trainer:
                 self.stopped_early = True
                 return
         self._drain(pending, losses, all_=True)
+        self.sync_parameters()
         logger.info(f"training complete! total time {time.time() - t_start:.2f}s")
 
     def _log_throughput(self, dt: float, steps: int, tokens_per_step: int) -> None:
@@ -478,18 +534,46 @@ class Trainer:
                          [f"time {eval_data['time']:.2f}s"])
 
     def validate(self) -> dict[str, float]:
-        out = self.evaluate(self.val_dataset)
-        if "loss" not in out:
-            logger.info(f"val - iter {self.iter_num}: no validation data")
-            return {}
-        logger.info(f"val - iter {self.iter_num}: {self.generate_log_string(out)}")
-        if out["loss"] < self.best_val_loss:
-            logger.info(f"new best val loss {out['loss']:.4f}")
-            self.best_val_loss = out["loss"]
-            if self.expert_parallel:
-                self._gather_optimizer_state()
-            self.save_ckpt("best")
+        """Evaluates the validation set and writes ``best.pt`` on a new best loss
+        (``src/modeling/trainer.py:338-349``).  With several ranks every rank calls this: rank 0
+        evaluates (all ranks when experts are sharded), the result is shared, and on a new best
+        all ranks gather the sharded optimizer state before rank 0 writes the file."""
+        evaluates = self.master_process or self.expert_parallel
+        out = self.evaluate(self.val_dataset) if evaluates else {}
+        if evaluates:
+            if "loss" not in out:
+                logger.info(f"val - iter {self.iter_num}: no validation data")
+            else:
+                logger.info(f"val - iter {self.iter_num}: {self.generate_log_string(out)}")
+        val_loss = out.get("loss", float("inf"))
+        if self.ddp and self.ddp_world_size > 1:
+            t = torch.tensor([val_loss], dtype=torch.float64, device=self.device)
+            dist.broadcast(t, 0)
+            val_loss = float(t[0])
+        if val_loss < self.best_val_loss:
+            if self.master_process:
+                logger.info(f"new best val loss {val_loss:.4f}")
+            self.best_val_loss = val_loss
+            self._gather_optimizer_state()
+            if evaluates:
+                self.save_ckpt("best")
         return {f"val/{k}": v for k, v in out.items() if k.endswith("loss")}
+
+    def _realign(self) -> None:
+        """Host-side barrier between the ranks (no-op in a single process)."""
+        if self.ddp and self.ddp_world_size > 1:
+            if self.device_type == "cuda":
+                torch.cuda.synchronize()
+            dist.barrier()
+
+    def sync_parameters(self) -> None:
+        """Collective.  Makes ``model.parameters()`` current on every rank.  With the sharded
+        optimizer the fp32 master of a weight matrix is kept up to date only on the rank that owns
+        the slice (the other ranks compute with the bf16 copy they receive every step); anything
+        that reads parameters as fp32 tensors on a given rank - a checkpoint, ``state_dict()``,
+        a comparison in a test - needs this first.  ``train()`` calls it before it returns."""
+        if self.grad_sync is not None and self.grad_sync.fused:
+            self.grad_sync.nvl.gather_master()
 
     def test(self) -> None:
         self.load_ckpt("best")
@@ -509,14 +593,14 @@ class Trainer:
 
     # ------------------------------------------------------------ checkpoints
     def _gather_optimizer_state(self) -> None:
-        """With the fused NVLink path the Adam moments live sharded across ranks; bring them into
-        the replicated flat layout the checkpoint writer reads.  Every rank must call this."""
+        """With the fused NVLink path the Adam moments (and the fp32 masters of the weight matrices)
+        live sharded across ranks; bring them into the flat layout the checkpoint writer reads:
+        masters on every rank, moments on rank 0, which writes the file.  Every rank must call this."""
         if self.grad_sync is not None and self.grad_sync.fused and self.grad_sync.nvl.epoch > 0:
             a = self.engine.arena
-            a.ensure_state()          # rank-local (expert) moments already live behind sync_end
-            m, v = self.grad_sync.nvl.gather_state()
-            a.exp_avg[:a.sync_end].copy_(m[:a.sync_end])
-            a.exp_avg_sq[:a.sync_end].copy_(v[:a.sync_end])
+            if self.master_process or a.total > a.sync_end:
+                a.ensure_state()          # rank-local (expert) moments already live behind sync_end
+            self.grad_sync.nvl.gather_state(a.exp_avg, a.exp_avg_sq, dst=0)
 
     def load_ckpt(self, ckpt_type: str) -> None:
         from .checkpoint import load_checkpoint
@@ -524,8 +608,10 @@ class Trainer:
         path = join(self.output_dir, f"{ckpt_type}.pt")
         if os.path.exists(path):
             meta = load_checkpoint(path, self.model, self.engine, self.optimizer, self.device)
-            if self.grad_sync is not None and self.grad_sync.fused and self.engine.arena.exp_avg is not None:
-                self.grad_sync.nvl.scatter_state(self.engine.arena.exp_avg, self.engine.arena.exp_avg_sq)
+            if self.grad_sync is not None and self.grad_sync.fused:
+                self.grad_sync.nvl.masters_complete = True      # every rank just read all of them from the file
+                if self.engine.arena.exp_avg is not None:
+                    self.grad_sync.nvl.scatter_state(self.engine.arena.exp_avg, self.engine.arena.exp_avg_sq)
             self.iter_num, self.best_val_loss = meta["iter_num"], meta["best_val_loss"]
             logger.info(f"loading {ckpt_type} checkpoint from iter {self.iter_num}: "
                         f"best_val_loss {self.best_val_loss}")

@@ -1,8 +1,11 @@
 """Worker for the multi-rank trainer tests (run under torch.distributed.run).
 
-usage: ddp_worker.py <out_dir> <mode> <device> [moe]   mode: fused | collective | auto
+usage: ddp_worker.py <out_dir> <mode> <device> [moe|loop]   mode: fused | collective | auto
 Trains a tiny model for 3 optimizer steps on a fixed synthetic stream (dropout off) and writes
 the final flat parameters of every rank to <out_dir>/params_<mode>_<rank>.pt .
+With ``loop`` the steps run inside ``Trainer.train()`` with validation and checkpoints every other
+iteration, and rank 0's evaluation is slowed down on the host by more than the device-side wait
+limit of the gradient kernels.
 """
 import os
 import sys
@@ -18,9 +21,59 @@ from allie_b200.models import initialize_model
 from allie_b200.train.trainer import Trainer
 
 
+def run_loop(out_dir, mode, device):
+    """Trainer.train() with eval / save intervals on; rank 0 is slow in validate()."""
+    import json
+    import time
+
+    from allie_b200.etl.dataset import random_games
+
+    rank = int(os.environ.get("RANK", 0))
+    T, B = 128, 4
+    tr = Trainer(Config({}), output_dir=os.path.join(out_dir, f"run_{mode}"), device=device, batch_size=B,
+                 gradient_accumulation_steps=2, lr=1e-3, min_lr=1e-4, warmup_iters=0, decay_iters=100,
+                 max_iters=5, eval_interval=2, log_interval=1, save_interval=2, weight_decay=0.01,
+                 grad_clip=1.0, grad_sync=mode, use_wandb=False)
+    tok = UCITokenizer(max_length=T, vocab_size_multiple_of=128)
+    torch.manual_seed(0)
+    model = initialize_model(tok, "gpt2", use_control_token=True, use_regression_head=True, n_layer=3,
+                             n_embd=128, n_head=2, n_positions=T)
+    rng = np.random.default_rng(5)
+    stream = (rng.integers(0, 1968, size=1 << 16).astype(np.uint32)
+              | (rng.integers(1, 20, size=1 << 16).astype(np.uint32) << 16))
+    games = os.path.join(out_dir, f"val_{rank}.jsonl")
+    random_games(games, n=6, max_plies=30, seed=9)
+    val = [json.loads(l) for l in open(games)]
+    tr.setup_dataloaders(tok, stream, val, val)
+    tr.setup_model(model)
+    if rank == 0:
+        slow = tr.evaluate
+
+        def evaluate(dataset):
+            time.sleep(2.5)
+            return slow(dataset)
+
+        tr.evaluate = evaluate
+    tr.train()
+    if device.startswith("cuda"):
+        from allie_b200.ops import _lib
+
+        torch.cuda.synchronize()
+        _lib.check_status()
+    flat = torch.cat([p.detach().float().reshape(-1).cpu() for _, p in sorted(model.named_parameters())])
+    fused = bool(tr.grad_sync is not None and tr.grad_sync.fused)
+    buckets = len(tr.engine.arena.buckets) if tr.engine is not None else 0
+    torch.save({"params": flat, "rank": rank, "fused": fused, "buckets": buckets, "iter_num": tr.iter_num},
+               os.path.join(out_dir, f"params_{mode}_{rank}.pt"))
+    tr.cleanup()
+
+
 def main():
     out_dir, mode, device = sys.argv[1], sys.argv[2], sys.argv[3]
     moe = len(sys.argv) > 4 and sys.argv[4] == "moe"
+    if len(sys.argv) > 4 and sys.argv[4] == "loop":
+        os.environ["ALLIE_NO_WANDB"] = "1"
+        return run_loop(out_dir, mode, device)
     os.environ["ALLIE_NO_WANDB"] = "1"
     rank = int(os.environ.get("RANK", 0))
     T, B = 128, 4
@@ -78,7 +131,9 @@ def main():
         reload_ok = (all(torch.equal(before[n], p.detach()) for n, p in model.named_parameters())
                      and torch.equal(m_before[arena.sync_end:], arena.exp_avg[arena.sync_end:])
                      and torch.equal(v_before[arena.sync_end:], arena.exp_avg_sq[arena.sync_end:])
-                     and torch.equal(m_before[:arena.sync_end], arena.exp_avg[:arena.sync_end]))
+                     # the moments of the replicated parameters are gathered on rank 0 only (it writes the file)
+                     and (rank != 0 or torch.equal(m_before[:arena.sync_end], arena.exp_avg[:arena.sync_end])))
+    tr.sync_parameters()      # the fp32 masters of weight matrices are current only on their owner rank
     flat = torch.cat([p.detach().float().reshape(-1).cpu() for _, p in sorted(model.named_parameters())])
     fused = bool(tr.grad_sync is not None and tr.grad_sync.fused)
     named = {n: p.detach().float().cpu() for n, p in model.named_parameters()}

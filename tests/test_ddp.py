@@ -102,6 +102,40 @@ def test_expert_parallel_two_ranks_match_single_rank(tmp_path):
         assert ck2["optimizer"]["state"][i]["exp_avg"].shape == st["exp_avg"].shape, i
 
 
+@pytest.mark.gpu
+def test_fused_path_survives_a_slow_rank_zero_in_validate_and_save(tmp_path):
+    """Trainer.train() on 2 GPUs with validation and checkpoints every other iteration, rank 0's
+    evaluation slowed down on the host by more than the gradient kernels' wait limit: no device
+    wait runs out (the status word stays clean), the ranks end on identical parameters, and the
+    checkpoint rank 0 wrote holds complete fp32 weights and Adam moments."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    _launch(2, tmp_path, "fused", "cuda", 29641, {"ALLIE_NVL_MULTIMEM": "0"}, extra_args=("loop",))
+    a = torch.load(tmp_path / "params_fused_0.pt")
+    b = torch.load(tmp_path / "params_fused_1.pt")
+    assert a["fused"] and b["fused"] and a["buckets"] == 3
+    assert torch.equal(a["params"], b["params"]), (a["params"] - b["params"]).abs().max()
+    ck = torch.load(tmp_path / "run_fused" / "last.pt", weights_only=False)
+    assert ck["iter_num"] == 4
+    st = ck["optimizer"]["state"]
+    assert len(st) == len(ck["optimizer"]["param_groups"][0]["params"]) + len(ck["optimizer"]["param_groups"][1]["params"])
+    # every weight matrix is cut between the two ranks somewhere: its gathered moments must be
+    # alive over its whole extent, not only in the part rank 0 owns
+    big = [s_["exp_avg_sq"] for s_ in st.values() if s_["exp_avg_sq"].dim() == 2 and s_["exp_avg_sq"].numel() >= 128 * 128]
+    assert len(big) >= 12
+    assert all(float((v > 0).float().mean()) > 0.9 for v in big)
+    assert (tmp_path / "run_fused" / "best.pt").exists()
+
+
+def test_trainer_loop_with_eval_and_save_under_two_gloo_ranks(tmp_path):
+    """The same loop on CPU gloo ranks (host logic of the collective validate / save path)."""
+    _launch(2, tmp_path, "collective", "cpu", 29642, extra_args=("loop",))
+    a = torch.load(tmp_path / "params_collective_0.pt")
+    b = torch.load(tmp_path / "params_collective_1.pt")
+    assert torch.equal(a["params"], b["params"]) and a["iter_num"] == b["iter_num"] == 6
+    assert (tmp_path / "run_collective" / "last.pt").exists() and (tmp_path / "run_collective" / "best.pt").exists()
+
+
 def test_shard_bounds_tile_the_arena():
     from allie_b200.parallel.nvl import shard_bounds
 

@@ -66,8 +66,8 @@ def test_dense_engine_matches_oracle(n_embd, n_head):
 
     # one clipped AdamW step against torch.optim.AdamW with the same decay / no-decay split
     arena = eng.arena
-    decay = [n for n in arena.names if arena.offsets[n] < arena.decay_end]
-    no_decay = [n for n in arena.names if arena.offsets[n] >= arena.decay_end]
+    decay = [n for n in arena.names if n in arena.decay_names]
+    no_decay = [n for n in arena.names if n not in arena.decay_names]
     opt = torch.optim.AdamW([{"params": [ref_params[n] for n in decay], "weight_decay": 0.01},
                              {"params": [ref_params[n] for n in no_decay], "weight_decay": 0.0}],
                             lr=1e-3, betas=(0.9, 0.95))

@@ -32,7 +32,10 @@ def test_static_scratch_attention_backward_matches_regular_entry():
     lib = _lib.cuda()
     dev = "cuda"
     status = _lib.status_word()
-    for call, (B, T, H, hd) in enumerate([(2, 256, 3, 64), (1, 384, 2, 128)]):
+    # two head sizes, a sequence length that is not a multiple of the 128-row tile, and a problem
+    # that uses the static array to its last row (B * H * T == AB_ATTN_STATIC_MAX_ROWS)
+    for call, (B, T, H, hd) in enumerate([(2, 256, 3, 64), (1, 384, 2, 128), (3, 200, 2, 64), (128, 512, 16, 64)]):
+        assert B * H * T <= 1 << 20
         torch.manual_seed(call)
         d = H * hd
         qkv = (torch.randn(B * T, 3 * d, device=dev) * 0.6).bfloat16()
@@ -43,11 +46,18 @@ def test_static_scratch_attention_backward_matches_regular_entry():
         want = torch.zeros(B * T, 3 * d, device=dev, dtype=torch.bfloat16)
         attention_bwd(qkv, out, lse, dout, want, torch.zeros(B, H, T, device=dev), B, T, H, hd, 0.0, 0, 0)
         got = torch.full_like(want, float("nan"))
+        torch.cuda.synchronize()
         before = torch.cuda.memory_allocated()
+        free_before = torch.cuda.mem_get_info()[0]
         rc = _call_static(lib, qkv, out, lse, dout, got, B, T, H, hd, status)
         torch.cuda.synchronize()
         assert rc == 0
+        # neither through torch's allocator nor behind its back (a raw cudaMalloc inside the
+        # library would show up as less free device memory); the very first call of a process may
+        # load the kernels' code lazily, which is not an allocation of this entry point
         assert torch.cuda.memory_allocated() == before
+        if call > 0:
+            assert torch.cuda.mem_get_info()[0] >= free_before
         _lib.check_status()
         # same kernels, same inputs: the tolerance of the other attention tests is more than enough
         assert torch.allclose(got.float(), want.float(), rtol=2e-2, atol=2e-2)
