@@ -184,10 +184,18 @@ class ParamArena:
 
 class B200Engine:
     def __init__(self, model: nn.Module, device: str | torch.device = "cuda", seed: int = 1234,
-                 symmetric: bool = False, layers_per_bucket: int | None = None):
+                 symmetric: bool = False, layers_per_bucket: int | None = None, expert_parallel: bool = True):
         """``symmetric``: parameter arenas in symmetric memory, laid out as gradient buckets (the
         fused NVLink gradient path).  ``layers_per_bucket``: transformer blocks per gradient bucket
-        (default with ``symmetric``: about a dozen buckets)."""
+        (default with ``symmetric``: about a dozen buckets).  ``expert_parallel``: with several
+        ranks, spread the experts of MoE layers over the ranks (tokens travel to their experts);
+        False keeps every expert on every rank and treats expert weights like any other
+        data-parallel parameter."""
+        import torch.distributed as dist
+
+        multi = dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1
+        self.ep_world = dist.get_world_size() if multi and expert_parallel else 1
+        self.ep_rank = dist.get_rank() if multi and expert_parallel else 0
         self.device = torch.device(device)
         assert self.device.type == "cuda"
         if self.device.index is None:
@@ -224,10 +232,8 @@ class B200Engine:
     def _shard_experts(self, model: nn.Module) -> frozenset:
         """Expert parallelism: with R ranks every rank keeps experts [rank*E/R, (rank+1)*E/R) of each
         expert bank.  Returns the names of those rank-local parameters."""
-        import torch.distributed as dist
-
-        world = dist.get_world_size() if dist.is_initialized() else 1
-        rank = dist.get_rank() if dist.is_initialized() else 0
+        world, rank = self.ep_world, self.ep_rank
+        assert self.cfg.ep_world in (1, world), "the model was built for another expert-parallel layout"
         names = set()
         for mn, m in model.named_modules():
             if type(m).__name__ != "ExpertBank":

@@ -48,8 +48,7 @@ class MoEContext:
     def __init__(self, engine, M: int):
         cfg = engine.cfg
         self.eng = engine
-        self.R = dist.get_world_size() if dist.is_initialized() else 1
-        self.rank = dist.get_rank() if dist.is_initialized() else 0
+        self.R, self.rank = engine.ep_world, engine.ep_rank      # 1, 0 unless experts are spread over the ranks
         self.E, self.k = cfg.num_experts, cfg.moe_top_k
         assert self.k == 2, "the routing kernels implement top-2"
         assert self.E % self.R == 0

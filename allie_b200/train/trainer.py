@@ -150,11 +150,15 @@ class Trainer:
                  max_iters: int = 600000, eval_interval: int = 2000, log_interval: int = 10,
                  save_interval: int = 500,
                  # extensions (absent from the reference schema, all optional)
-                 shard_optimizer: Optional[bool] = None, grad_sync: str = "auto", use_wandb: bool = True):
+                 shard_optimizer: Optional[bool] = None, grad_sync: str = "auto", use_wandb: bool = True,
+                 expert_parallel: bool = True):
         """Extensions to the reference signature: ``grad_sync`` = ``auto`` | ``fused`` (the NVLink
         kernels: bucketed reduce-scatter under backward, optimizer state sharded over the ranks)
         | ``collective`` (one all_reduce, replicated optimizer).  ``shard_optimizer`` is the same
-        choice as a boolean: true requires the sharded fused path, false selects ``collective``."""
+        choice as a boolean: true requires the sharded fused path, false selects ``collective``.
+        ``expert_parallel`` (MoE models on several ranks): true spreads the experts over the ranks,
+        false replicates them and averages their gradients like any other parameter."""
+        self.expert_parallel_requested = expert_parallel
         if shard_optimizer is not None:
             want = "fused" if shard_optimizer else "collective"
             if grad_sync not in ("auto", want):
@@ -252,12 +256,14 @@ class Trainer:
 
             symmetric = self.ddp and self.ddp_world_size > 1 and self.grad_sync_mode in ("auto", "fused")
             try:
-                self.engine = B200Engine(model, self.device, seed=self.seed, symmetric=symmetric)
+                self.engine = B200Engine(model, self.device, seed=self.seed, symmetric=symmetric,
+                                         expert_parallel=self.expert_parallel_requested)
             except Exception as e:
                 if not symmetric or self.grad_sync_mode == "fused":
                     raise
                 logger.warning(f"symmetric-memory arenas unavailable ({e}); using all_reduce")
-                self.engine = B200Engine(model, self.device, seed=self.seed, symmetric=False)
+                self.engine = B200Engine(model, self.device, seed=self.seed, symmetric=False,
+                                         expert_parallel=self.expert_parallel_requested)
             logger.info("using the fused sm_100a AdamW over flat parameter arenas")
         else:
             model.to(self.device)

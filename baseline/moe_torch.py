@@ -2,17 +2,23 @@
 (the reference project has no MoE, so there is no reference implementation to run).
 
 Stack: the oracle module tree in bf16 autocast, SDPA attention, the MoE feed-forward replaced by a
-sort + ``all_to_all_single`` dispatch, a loop of cuBLAS GEMMs over the local experts, and an
-``all_to_all_single`` combine; dense gradients all-reduced with NCCL; torch fused AdamW.  No code of
-``allie_b200``'s kernels or engine runs on this path.
+sort + ``all_to_all_single`` dispatch, one ``torch._grouped_mm`` per projection over all local
+experts (a loop of cuBLAS GEMMs where that operator is missing, or with
+``ALLIE_BASELINE_MOE_LOOP=1``), and an ``all_to_all_single`` combine; dense gradients all-reduced
+with NCCL; torch fused AdamW.  No code of ``allie_b200``'s kernels or engine runs on this path.
 """
 from __future__ import annotations
+
+import os
 
 import torch
 import torch.distributed as dist
 import torch.nn.functional as F
 
 from allie_b200.models.oracle import Attention, MoEMLP, gelu_new
+
+
+GROUPED = hasattr(torch, "_grouped_mm") and os.environ.get("ALLIE_BASELINE_MOE_LOOP", "0") != "1"
 
 
 class _A2A(torch.autograd.Function):
@@ -59,12 +65,21 @@ def ep_moe_forward(self: MoEMLP, x):
         per_expert = rc.sum(0).tolist()
     else:
         xr, per_expert, perm = xs, counts.tolist(), None
-    outs, s = [], 0
-    for le, n in enumerate(per_expert):
-        h = gelu_new(F.linear(xr[s:s + n], self.c_fc.weight[le].t(), self.c_fc.bias[le]))
-        outs.append(F.linear(h, self.c_proj.weight[le].t(), self.c_proj.bias[le]))
-        s += n
-    yr = torch.cat(outs) if outs else xr.new_zeros(0, d)
+    if GROUPED and xr.is_cuda and xr.size(0) > 0:
+        # one grouped GEMM per projection; expert banks are [E_local, in, out]
+        n_rows = torch.tensor(per_expert, device=x.device)
+        offs = torch.cumsum(n_rows, 0).to(torch.int32)
+        row_expert = torch.repeat_interleave(torch.arange(len(per_expert), device=x.device), n_rows)
+        dt = torch.bfloat16
+        h = torch._grouped_mm(xr.to(dt), self.c_fc.weight.to(dt), offs=offs) + self.c_fc.bias.to(dt)[row_expert]
+        yr = torch._grouped_mm(gelu_new(h), self.c_proj.weight.to(dt), offs=offs) + self.c_proj.bias.to(dt)[row_expert]
+    else:
+        outs, s = [], 0
+        for le, n in enumerate(per_expert):
+            h = gelu_new(F.linear(xr[s:s + n], self.c_fc.weight[le].t(), self.c_fc.bias[le]))
+            outs.append(F.linear(h, self.c_proj.weight[le].t(), self.c_proj.bias[le]))
+            s += n
+        yr = torch.cat(outs) if outs else xr.new_zeros(0, d)
     if R > 1:
         inv = torch.empty_like(perm)
         inv[perm] = torch.arange(perm.numel(), device=x.device)

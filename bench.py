@@ -13,8 +13,20 @@ Synthetic uniform-random move tokens with two leading ELO tokens per window, ran
 For N > 1 launch under ``python -m torch.distributed.run --nproc-per-node N``.  Rank 0 prints one
 JSON line.  ``value`` is timed on the device with CUDA events around exactly K optimizer steps,
 max over ranks, inputs already resident on the GPU; ``e2e`` times the same K steps through
-``Trainer.train_step`` with the per-step host->device copy of the raw windows from pinned memory
-and a device->host read of the loss.
+``Trainer.train_step()`` as the training loop calls it: windows drawn by the trainer's sampler
+(host gather on its prefetch thread), the per-micro-step host->device copy of the raw windows
+from pinned memory, and a device->host read of the loss every step.
+
+After the headline the same process measures the two other headline workloads inside a time
+budget and reports them under ``secondary``: ``mcts`` (256 trees x 400 simulations per GPU,
+positions/s and per-move latency) at any N, and ``moe`` (the 9.3 B-parameter mixture-of-experts
+config, expert parallel over all ranks, tokens/s) at N = 8.  ``--impl reference`` fills the same
+object with the unmodified reference ``evaluation.decode.MCTS`` and, for the MoE config the
+reference does not have, a plain-PyTorch expert-parallel baseline (``all_to_all_single`` +
+``torch._grouped_mm``).  At N >= 2 the line also carries ``grad_sync_check``: a tiny model stepped
+through the fused NVLink gradient path and through all_reduce + replicated AdamW from the same
+state, and a tiny MoE model stepped with its experts spread over the ranks and with them
+replicated, with the largest parameter difference of each pair.
 """
 from __future__ import annotations
 
@@ -142,6 +154,147 @@ def barrier_sync(world: int):
     torch.cuda.synchronize()
 
 
+def common_config(model_name: str, ga: int, world: int) -> dict:
+    """The part of ``config`` both arms print identically (same shape, batch, accumulation)."""
+    shape = MODELS[model_name]
+    d = shape["n_embd"]
+    return {"model": f"gpt2-{model_name}-like {shape['n_layer']}L d{d} {shape['n_head']}H mlp{4 * d} ctx512 vocab2048 "
+                     "+ control token + value/time heads, dropout 0.1",
+            "global_batch": GLOBAL_BATCH, "seq_len": SEQ_LEN, "micro_batch": MICRO_BATCH, "grad_accum": ga,
+            "parallelism": f"dp{world}",
+            "l2_policy": "inputs larger than L2: each micro-step streams >1 GB of activations and 1.2 GB of "
+                         "fp32 weights+grads, distinct windows per micro-step"}
+
+
+def grad_sync_check(world: int) -> dict:
+    """Numerical check of the multi-GPU paths on tiny models, before anything is timed.  (a) Two
+    optimizer steps through the fused NVLink gradient path against the same steps through
+    all_reduce + replicated AdamW, from the same weights and windows.  (b) A tiny MoE model
+    stepped with its experts spread over the ranks (dispatch / combine through peer memory)
+    against the same model with every expert on every rank.  Reports the largest absolute
+    parameter difference of each pair (max over ranks); one Adam step moves a weight by about
+    ``lr``, and a gradient sum in another order can flip the sign of a near-zero update."""
+    import numpy as np
+    import torch
+
+    from allie_b200.config import Config
+    from allie_b200.data import UCITokenizer
+    from allie_b200.models import initialize_model
+    from allie_b200.ops import _lib
+    from allie_b200.train.trainer import Trainer
+
+    rank = dist_info()[0]
+    T, B, LR = 128, 4, 1e-3
+    tok = UCITokenizer(max_length=T, vocab_size_multiple_of=128)
+    rng = np.random.default_rng(5)
+    stream = (rng.integers(0, 1968, size=1 << 16).astype(np.uint32)
+              | (rng.integers(1, 20, size=1 << 16).astype(np.uint32) << 16))
+    wrng = np.random.default_rng(11)
+    starts = wrng.integers(0, len(stream) - T, size=(2, 2, B * world))
+    steps = [[torch.from_numpy(np.stack([stream[s:s + T] for s in starts[st][ms][rank::world]]).astype(np.uint32).view(np.int32))
+              for ms in range(2)] for st in range(2)]
+
+    def run(mode: str, moe: bool, expert_parallel: bool = True) -> "torch.Tensor":
+        tr = Trainer(Config({}), output_dir=tempfile.mkdtemp(prefix="allie_chk_"), batch_size=B,
+                     gradient_accumulation_steps=2, lr=LR, min_lr=1e-4, warmup_iters=0, decay_iters=100, max_iters=3,
+                     eval_interval=0, log_interval=-1, save_interval=0, weight_decay=0.01, grad_clip=1.0,
+                     grad_sync=mode, use_wandb=False, expert_parallel=expert_parallel)
+        torch.manual_seed(0)
+        extra = dict(num_experts=8, moe_ffn=256, moe_layer_freq=2, capacity_factor=8.0, aux_loss_coef=0.0) if moe else {}
+        model = initialize_model(tok, "gpt2", use_control_token=True, use_regression_head=True, n_layer=4 if not moe else 2,
+                                 n_embd=128, n_head=2, n_positions=T, resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0,
+                                 **extra)
+        if moe:
+            with torch.no_grad():
+                for n_, p_ in model.named_parameters():
+                    if "router" in n_:
+                        p_.mul_(20.0)      # decisive routing: no token sits on a tie between two experts
+        tr.setup_dataloaders(tok, stream, [], [])
+        tr.setup_model(model)
+        for ws in steps:
+            tr.train_step(ws)
+            tr.iter_num += 1
+        tr.sync_parameters()
+        torch.cuda.synchronize()
+        _lib.check_status()
+        named = {n: p.detach().float().clone() for n, p in model.named_parameters()}
+        tr.sampler.close()
+        return named
+
+    def worst(a: dict, b: dict, world: int) -> float:
+        d = 0.0
+        for n, p in a.items():
+            q = b[n]
+            if p.shape != q.shape:                     # expert bank: this rank's slice of the replicated bank
+                El = p.shape[0]
+                q = q[rank * El:(rank + 1) * El]
+            d = max(d, float((p - q).abs().max()))
+        return max_over_ranks(d, world)
+
+    fused, coll = run("fused", False), run("collective", False)
+    ep, rep = run("fused", True, True), run("fused", True, False)
+    return {"fused_vs_all_reduce_max_abs_diff": worst(fused, coll, world),
+            "expert_parallel_vs_replicated_max_abs_diff": worst(ep, rep, world), "lr": LR, "steps": 2,
+            "note": "tiny models (4 blocks d128 / 2 blocks with 8 experts), dropout off, same windows"}
+
+
+def secondary_mcts(world: int, reference: bool, budget_s: float) -> dict:
+    """MCTS leaf evaluation: one independent search per GPU, 256 trees x 400 simulations (the
+    reference arm: its own sequential MCTS on 8 root positions per GPU, 400 simulations)."""
+    import bench_mcts
+
+    rank = dist_info()[0]
+    if budget_s < 60:
+        return {"skipped": f"time budget exhausted ({budget_s:.0f} s left)"}
+    cfg = {"model": "gpt2-medium-like 24L d1024 16H", "sims": 400, "prefix_tokens": "1-300",
+           "data": "synthetic random legal games"}
+    out = {"metric": "MCTS leaf-eval positions/sec", "unit": "positions/s", "n_gpus": world}
+    if reference:
+        out.update(bench_mcts.run_reference(400, 8, False, seed=rank), config=dict(cfg, root_positions_per_gpu=8))
+    else:
+        out.update(bench_mcts.run_batched(256, 400, False, seed=rank), config=dict(cfg, trees_per_gpu=256), dtype="bf16")
+    return bench_mcts.combine_over_ranks(out, world)
+
+
+def secondary_moe(world: int, reference: bool, budget_s: float, force: bool) -> dict:
+    import bench_moe
+
+    if world != 8 and not force:
+        return {"skipped": "the 9.3 B-parameter MoE config needs its experts spread over 8 GPUs"}
+    if budget_s < 120:
+        return {"skipped": f"time budget exhausted ({budget_s:.0f} s left)"}
+    if world == 8:
+        return bench_moe.run_moe("torch" if reference else "ours", steps=10, warmup=3)
+    # smoke shape for fewer GPUs (--secondary all): 6 blocks, 16 experts
+    return bench_moe.run_moe("torch" if reference else "ours", steps=5, warmup=3, layers=6, experts=16)
+
+
+def run_secondary(args, world: int, reference: bool, t_start: float) -> dict:
+    """The other two headline workloads, measured after the training benchmark inside what is left
+    of ``--secondary-budget`` seconds.  A failure of one of them is reported, not raised."""
+    import gc
+    import traceback
+
+    import torch
+
+    out = {}
+    if args.secondary == "none":
+        return {"skipped": "--secondary none"}
+    for name, fn in (("mcts", lambda left: secondary_mcts(world, reference, left)),
+                     ("moe", lambda left: secondary_moe(world, reference, left, args.secondary == "all"))):
+        left = args.secondary_budget - (time.perf_counter() - t_start)
+        try:
+            gc.collect()
+            torch.cuda.empty_cache()
+            t0 = time.perf_counter()
+            out[name] = fn(left)
+            out[name]["wall_s"] = round(time.perf_counter() - t0, 1)
+        except Exception as e:
+            traceback.print_exc(file=sys.stderr)
+            out[name] = {"failed": f"{type(e).__name__}: {e}"[:300]}
+    return out
+
+
 def run_ours(args) -> dict:
     import numpy as np
     import torch
@@ -152,6 +305,7 @@ def run_ours(args) -> dict:
     from allie_b200.ops import _lib
     from allie_b200.train.trainer import Trainer
 
+    t_start = time.perf_counter()
     rank, world, local = dist_info()
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
     assert 8 % world == 0
@@ -172,6 +326,7 @@ def run_ours(args) -> dict:
     trainer.setup_model(model)
     trainer.iter_num = 1000     # mid-warmup learning rate, nonzero updates
     dev = trainer.engine.device
+    sync_check = grad_sync_check(world) if world > 1 else None
 
     # windows larger than L2 in aggregate: K*ga distinct [64, 512] windows per rank, pre-staged
     n_win = (args.steps + args.warmup) * ga
@@ -183,8 +338,9 @@ def run_ours(args) -> dict:
         return trainer.train_step(ws)
 
     def step_e2e(i, sink):
-        ws = [host_windows[(i * ga + m) % len(host_windows)] for m in range(ga)]
-        loss = trainer.train_step(ws)
+        # the call the training loop makes: the trainer draws its own windows (sampler thread,
+        # pinned staging buffers), copies them to the device and steps
+        loss = trainer.train_step()
         sink.copy_(loss, non_blocking=True)
 
     sampler = ClockSampler(local)
@@ -248,15 +404,12 @@ def run_ours(args) -> dict:
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": value / BASELINE_TOKENS_PER_S, "dtype": "bf16", "data": "synthetic",
         "impl": "allie_b200",
-        "config": {"model": f"gpt2-{args.model}-like {L}L d{d} {shape['n_head']}H mlp{4 * d} ctx512 vocab2048 "
-                            "+ control token + value/time heads, dropout 0.1",
-                   "global_batch": GLOBAL_BATCH, "seq_len": SEQ_LEN, "micro_batch": MICRO_BATCH,
-                   "grad_accum": ga, "parallelism": f"dp{world}",
-                   "l2_policy": "inputs larger than L2: each micro-step streams >1 GB of activations "
-                                "and 1.2 GB of fp32 weights+grads, distinct windows per micro-step",
-                   "grad_sync": ("fused-nvlink-multimem" if trainer.grad_sync.nvl.multimem else "fused-nvlink-p2p")
-                                if (trainer.grad_sync and trainer.grad_sync.fused)
-                                else ("all_reduce" if world > 1 else "none")},
+        "config": common_config(args.model, ga, world),
+        "arm": {"grad_sync": ("fused-nvlink-multimem" if trainer.grad_sync.nvl.multimem else "fused-nvlink-p2p")
+                             if (trainer.grad_sync and trainer.grad_sync.fused)
+                             else ("all_reduce" if world > 1 else "none"),
+                "grad_buckets": len(trainer.engine.arena.buckets),
+                "e2e_path": "Trainer.train_step(): sampler thread -> pinned windows -> H2D -> step -> loss D2H"},
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
                 "h2d_bytes_per_step": ga * MICRO_BATCH * SEQ_LEN * 4, "d2h_bytes_per_step": 4},
@@ -265,6 +418,13 @@ def run_ours(args) -> dict:
         "final_loss": final_loss,
         "model_tflops_per_gpu": value * flops_per_token / world / 1e12,
     }
+    if sync_check is not None:
+        result["grad_sync_check"] = sync_check
+    # free the training state before the secondary workloads build theirs
+    trainer.sampler.close()
+    trainer.engine = trainer.grad_sync = trainer.model = None
+    del dev_windows, host_windows, model
+    result["secondary"] = run_secondary(args, world, False, t_start)
     trainer.cleanup()
     return result
 
@@ -295,6 +455,7 @@ def run_reference(args) -> dict:
     except Exception as e:
         return {"impl": "reference", "unavailable": f"reference import failed: {type(e).__name__}: {e}"[:300]}
 
+    t_start = time.perf_counter()
     rank, world, local = dist_info()
     assert world == args.gpus
     ga = GLOBAL_BATCH // (MICRO_BATCH * world)
@@ -348,18 +509,20 @@ def run_reference(args) -> dict:
         "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms / K, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": value / BASELINE_TOKENS_PER_S, "dtype": "bf16",
         "data": "synthetic", "impl": "reference",
-        "config": {"model": ("gpt2-medium 24L d1024 16H" if args.model == "medium" else "gpt2-large-like 32L d1280 20H")
-                            + " ctx512 vocab2048 + control token + value/time heads",
-                   "global_batch": GLOBAL_BATCH, "seq_len": SEQ_LEN, "micro_batch": MICRO_BATCH,
-                   "grad_accum": ga, "parallelism": f"dp{world}",
-                   "stack": "reference Trainer.train(): autocast bf16 + torch.compile + DDP + fused AdamW",
-                   "note": "the reference loop times its own host data pipeline, H2D copies and "
-                           "loss.item() every step, so value == e2e for this arm"},
+        "config": common_config(args.model, ga, world),
+        "arm": {"stack": "reference Trainer.train(): autocast bf16 + torch.compile + DDP + fused AdamW",
+                "note": "the reference loop times its own host data pipeline, H2D copies and "
+                        "loss.item() every step, so value == e2e for this arm"},
         "clocks": state["clocks"],
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": ga * MICRO_BATCH * SEQ_LEN * (8 * 3 + 4 * 3),
                 "d2h_bytes_per_step": 4},
         "gpu_launches": 0,
     }
+    for attr in ("model", "optimizer", "model_fn"):
+        if hasattr(trainer, attr):
+            setattr(trainer, attr, None)
+    del model
+    result["secondary"] = run_secondary(args, world, True, t_start)
     trainer.cleanup()
     return result
 
@@ -372,6 +535,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default="medium", choices=sorted(MODELS),
                     help="medium = the headline config; large = the large-ablation shape (32L, d1280, 20H)")
+    ap.add_argument("--secondary", default="auto", choices=["auto", "none", "all"],
+                    help="auto: MCTS at every N, MoE at N = 8; all: also a reduced MoE shape at N < 8; none: headline only")
+    ap.add_argument("--secondary-budget", type=float, default=600.0,
+                    help="seconds (from process start) after which no further secondary benchmark is started")
     args = ap.parse_args()
     rank, world, _ = dist_info()
     if args.gpus > 1 and world == 1:

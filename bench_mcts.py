@@ -45,17 +45,22 @@ def random_games(n, tok, rng, max_tokens=300):
     return games
 
 
-def run_reference(args, tok, games) -> dict:
+def run_reference(sims: int, positions: int, small: bool, seed: int = 0) -> dict:
     """The reference package as installed under ``baseline/_ref``: its ``initialize_model`` (Hugging
     Face GPT-2 inside its two wrappers, random init), its tokenizer and its ``MCTS`` strategy at
-    ``precision="float32"`` as its evaluation CLI runs it.  A position = one forward pass of its model."""
+    ``precision="float32"`` as its evaluation CLI runs it (``src/evaluation/decode.py:309-470``,
+    ``evaluate.py:249``).  A position = one forward pass of its model."""
+    import numpy as np
     import torch
+
+    from allie_b200.data import UCITokenizer as OurTok
 
     ref_dir = os.path.join(ROOT, "baseline", "_ref")
     if not os.path.isdir(os.path.join(ref_dir, "modeling")):
         return {"unavailable": "baseline/_ref is missing (pip install --target was not run)"}
-    sys.path.insert(0, os.path.join(ROOT, "baseline", "shims"))
-    sys.path.insert(0, ref_dir)
+    for p_ in (os.path.join(ROOT, "baseline", "shims"), ref_dir):
+        if p_ not in sys.path:
+            sys.path.insert(0, p_)
     try:
         from evaluation.decode import MCTS
         from modeling.data import Game, UCITokenizer
@@ -63,15 +68,17 @@ def run_reference(args, tok, games) -> dict:
     except Exception as e:
         return {"unavailable": f"reference import failed: {type(e).__name__}: {e}"[:300]}
     dev = "cuda" if torch.cuda.is_available() else "cpu"
+    games = random_games(positions, OurTok(max_length=512, vocab_size_multiple_of=128), np.random.default_rng(seed))
     rtok = UCITokenizer(max_length=512, vocab_size_multiple_of=128)
-    shape = dict(n_layer=2, n_embd=256, n_head=4) if args.small else {}
+    shape = dict(n_layer=2, n_embd=256, n_head=4) if small else {}
     torch.manual_seed(0)
     model = initialize_model(rtok, os.path.join(ROOT, "baseline", "gpt2-medium"), use_control_token=True,
                              use_regression_head=True, use_pretrained=False, **shape).to(dev).eval()
     calls = [0]
     model.register_forward_hook(lambda *a: calls.__setitem__(0, calls[0] + 1))
     rgames = [Game(**g.to_dict()) for g in games]
-    strat = MCTS(model, rtok, sample=False, device=dev, precision="float32", n_sims=args.sims)
+    strat = MCTS(model, rtok, sample=False, device=dev, precision="float32", n_sims=sims)
+    per_move = []
     with torch.inference_mode():
         strat.score_full(rgames[0], rgames[0].legal_moves)
         if dev == "cuda":
@@ -79,28 +86,125 @@ def run_reference(args, tok, games) -> dict:
         calls[0] = 0
         t0 = time.perf_counter()
         for g in rgames:
+            t1 = time.perf_counter()
             strat.score_full(g, g.legal_moves)
-        if dev == "cuda":
-            torch.cuda.synchronize()
+            if dev == "cuda":
+                torch.cuda.synchronize()
+            per_move.append(time.perf_counter() - t1)
         dt = time.perf_counter() - t0
-    return {"value": calls[0] / dt, "seconds": dt, "positions": calls[0], "p50_move_latency_s": dt / len(rgames),
+    return {"value": calls[0] / dt, "seconds": dt, "positions": calls[0],
+            "p50_move_latency_s": sorted(per_move)[len(per_move) // 2], "dtype": "fp32 (TF32 matmuls)",
+            "root_positions": len(rgames),
             "note": "unmodified reference evaluation.decode.MCTS on its own model, one tree at a time, "
                     "batch-1 full re-encode per leaf"}
 
 
-def main():
-    import numpy as np
+def build_model(small: bool):
     import torch
 
     from allie_b200.data import UCITokenizer
     from allie_b200.models import initialize_model
+
+    torch.manual_seed(0)
+    tok = UCITokenizer(max_length=512, vocab_size_multiple_of=128)
+    shape = dict(n_layer=2, n_embd=256, n_head=4) if small else dict(n_layer=24, n_embd=1024, n_head=16)
+    model = initialize_model(tok, "gpt2-medium", use_control_token=True, use_regression_head=True,
+                             n_positions=1024, **shape)
+    return tok, model
+
+
+def run_batched(trees: int, sims: int, small: bool, seed: int = 0) -> dict:
+    """``trees`` concurrent searches of ``sims`` simulations each on the current GPU: batched C++
+    search + KV-cached sm_100a leaf evaluator.  One call of ``search`` plays one move in every
+    tree, so its duration is the per-move latency of every game in the batch."""
+    import numpy as np
+    import torch
+
+    from allie_b200.models.engine import B200Engine
+    from allie_b200.ops import _lib
+    from allie_b200.search.batched import BatchedMCTS, KVStepEvaluator
+
+    tok, model = build_model(small)
+    eng = B200Engine(model, "cuda")
+    games = random_games(trees, tok, np.random.default_rng(seed))
+    ev = KVStepEvaluator(eng, tok, trees, anc_max=128, legal_max=224, max_prefix=320, max_nodes=sims + 8)
+    bm = BatchedMCTS(tok, ev, n_trees=trees, n_sims=sims)
+    bm.search(games[:trees], n_sims=8)           # warm-up (graph capture, first launches)
+    torch.cuda.synchronize()
+    ev.positions = 0
+    bm.phase_seconds = {k: 0.0 for k in bm.phase_seconds}
+    l0 = _lib.LAUNCHES
+    t0 = time.perf_counter()
+    res = bm.search(games)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    _lib.check_status()
+    return dict(value=ev.positions / dt, seconds=dt, positions=ev.positions, steps=ev.kv.steps,
+                moves_per_s=len(games) / dt, p50_move_latency_s=dt, latency_per_move_batch_s=dt,
+                gpu_launches=_lib.LAUNCHES - l0, sims_done=int(sum(r.n_sims for r in res)),
+                phase_seconds={k: round(v, 4) for k, v in bm.phase_seconds.items()})
+
+
+def run_sequential(sims: int, positions: int, small: bool, seed: int = 0) -> dict:
+    """The reference algorithm restated on this framework's PyTorch model (fp32): one tree at a
+    time, every leaf re-encodes its whole game at batch 1 (``src/evaluation/decode.py:336-467``)."""
+    import numpy as np
+    import torch
+
+    from allie_b200.search import MCTS
+    from allie_b200.search.runner import TorchRunner
+
+    tok, model = build_model(small)
+    dev = "cuda" if torch.cuda.is_available() else "cpu"
+    model.to(dev).eval()
+    runner = TorchRunner(model, tok, dev)
+    games = random_games(positions, tok, np.random.default_rng(seed))
+    m = MCTS(model, tok, device=dev, runner=runner, n_sims=sims)
+    m.score_full(games[0], games[0].legal_moves)
+    if dev == "cuda":
+        torch.cuda.synchronize()
+    c0 = runner.calls
+    t0 = time.perf_counter()
+    for g in games:
+        m.score_full(g, g.legal_moves)
+    if dev == "cuda":
+        torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    return dict(value=(runner.calls - c0) / dt, seconds=dt, positions=runner.calls - c0,
+                p50_move_latency_s=dt / len(games),
+                note="sequential PUCT, batch-1 full re-encode per leaf, fp32 PyTorch model")
+
+
+def combine_over_ranks(out: dict, world: int) -> dict:
+    """Whole-job figures of one independent search per rank: positions summed, divided by the
+    slowest rank's time; the per-move latency is the median over ranks."""
+    if world == 1 or "positions" not in out:
+        return out
+    import torch
+    import torch.distributed as dist
+
+    dev = "cuda" if torch.cuda.is_available() else "cpu"
+    stats = torch.tensor([float(out["positions"]), float(out["seconds"]), float(out.get("p50_move_latency_s", 0.0))],
+                         dtype=torch.float64, device=dev)
+    allv = [torch.zeros_like(stats) for _ in range(world)]
+    dist.all_gather(allv, stats)
+    positions = sum(float(v[0]) for v in allv)
+    slowest = max(float(v[1]) for v in allv)
+    out.update(value=positions / slowest, positions=int(positions), seconds=slowest,
+               per_rank_seconds=[round(float(v[1]), 4) for v in allv],
+               p50_move_latency_s=sorted(float(v[2]) for v in allv)[world // 2])
+    return out
+
+
+def main():
+    import torch
 
     ap = argparse.ArgumentParser()
     ap.add_argument("--trees", type=int, default=256)
     ap.add_argument("--sims", type=int, default=400)
     ap.add_argument("--impl", default="batched", choices=["batched", "sequential", "reference"])
     ap.add_argument("--small", action="store_true", help="tiny model (smoke test)")
-    ap.add_argument("--seq-positions", type=int, default=4, help="root positions for --impl sequential")
+    ap.add_argument("--seq-positions", type=int, default=8, help="root positions for --impl sequential / reference")
     ap.add_argument("--gpus", type=int, default=1)
     args = ap.parse_args()
     rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
@@ -111,79 +215,20 @@ def main():
         import torch.distributed as dist
 
         dist.init_process_group("nccl" if torch.cuda.is_available() else "gloo")
-    torch.manual_seed(0)
-    tok = UCITokenizer(max_length=512, vocab_size_multiple_of=128)
-    shape = dict(n_layer=2, n_embd=256, n_head=4) if args.small else dict(n_layer=24, n_embd=1024, n_head=16)
-    model = initialize_model(tok, "gpt2-medium", use_control_token=True, use_regression_head=True,
-                             n_positions=1024, **shape)
-    rng = np.random.default_rng(rank)          # different root positions on every rank
     out = {"metric": "MCTS leaf-eval positions/sec", "unit": "positions/s", "impl": args.impl,
            "dtype": "bf16" if args.impl == "batched" else "fp32", "data": "synthetic random legal games, prompts of 1-300 tokens",
            "config": {"model": "tiny" if args.small else "gpt2-medium-like 24L d1024 16H", "trees": args.trees,
-                      "sims": args.sims}}
+                      "sims": args.sims}, "n_gpus": world}
     if args.impl == "batched":
-        from allie_b200.models.engine import B200Engine
-        from allie_b200.ops import _lib
-        from allie_b200.search.batched import BatchedMCTS, KVStepEvaluator
-
-        eng = B200Engine(model, "cuda")
-        games = random_games(args.trees, tok, rng)
-        ev = KVStepEvaluator(eng, tok, args.trees, anc_max=128, legal_max=224, max_prefix=320,
-                             max_nodes=args.sims + 8)
-        bm = BatchedMCTS(tok, ev, n_trees=args.trees, n_sims=args.sims)
-        bm.search(games[: args.trees], n_sims=8)           # warm-up (graph capture, first launches)
-        torch.cuda.synchronize()
-        ev.positions = 0
-        bm.phase_seconds = {k: 0.0 for k in bm.phase_seconds}
-        l0 = _lib.LAUNCHES
-        t0 = time.perf_counter()
-        res = bm.search(games)
-        torch.cuda.synchronize()
-        dt = time.perf_counter() - t0
-        _lib.check_status()
-        out.update(value=ev.positions / dt, seconds=dt, positions=ev.positions, steps=ev.kv.steps,
-                   moves_per_s=len(games) / dt, latency_per_move_batch_s=dt, gpu_launches=_lib.LAUNCHES - l0,
-                   sims_done=int(sum(r.n_sims for r in res)),
-                   phase_seconds={k: round(v, 4) for k, v in bm.phase_seconds.items()})
+        out.update(run_batched(args.trees, args.sims, args.small, seed=rank))      # different root positions per rank
     elif args.impl == "sequential":
-        from allie_b200.search import MCTS
-
-        dev = "cuda" if torch.cuda.is_available() else "cpu"
-        model.to(dev).eval()
-        from allie_b200.search.runner import TorchRunner
-
-        runner = TorchRunner(model, tok, dev)
-        games = random_games(args.seq_positions, tok, rng)
-        m = MCTS(model, tok, device=dev, runner=runner, n_sims=args.sims)
-        m.score_full(games[0], games[0].legal_moves)
-        if dev == "cuda":
-            torch.cuda.synchronize()
-        c0 = runner.calls
-        t0 = time.perf_counter()
-        for g in games:
-            m.score_full(g, g.legal_moves)
-        if dev == "cuda":
-            torch.cuda.synchronize()
-        dt = time.perf_counter() - t0
-        out.update(value=(runner.calls - c0) / dt, seconds=dt, positions=runner.calls - c0,
-                   p50_move_latency_s=dt / len(games),
-                   note="sequential PUCT, batch-1 full re-encode per leaf, fp32 PyTorch model "
-                        "(the reference's decode path, src/evaluation/decode.py:336-467)")
-    out["n_gpus"] = world
-    if args.impl == "reference":
-        out.update(run_reference(args, tok, random_games(args.seq_positions, tok, rng)))
+        out.update(run_sequential(args.sims, args.seq_positions, args.small, seed=rank))
+    else:
+        out.update(run_reference(args.sims, args.seq_positions, args.small, seed=rank))
+    out = combine_over_ranks(out, world)
     if world > 1:
         import torch.distributed as dist
 
-        dev = "cuda" if torch.cuda.is_available() else "cpu"
-        stats = torch.tensor([float(out["positions"]), float(out["seconds"])], dtype=torch.float64, device=dev)
-        allv = [torch.zeros_like(stats) for _ in range(world)]
-        dist.all_gather(allv, stats)
-        positions = sum(float(v[0]) for v in allv)
-        slowest = max(float(v[1]) for v in allv)
-        out.update(value=positions / slowest, positions=int(positions), seconds=slowest,
-                   per_rank_seconds=[round(float(v[1]), 4) for v in allv],
-                   latency_per_move_batch_s=sorted(float(v[1]) for v in allv)[world // 2])
         dist.barrier()
         dist.destroy_process_group()
     if rank == 0:

@@ -25,60 +25,60 @@ from bench import ClockSampler, barrier_sync, dist_info, max_over_ranks, synthet
 SEQ_LEN, GLOBAL_BATCH, MICRO_BATCH = 512, 512, 32
 
 
-def main():
-    global MICRO_BATCH
+def run_moe(impl: str = "ours", steps: int = 10, warmup: int = 3, layers: int = 24, experts: int = 64,
+            global_batch: int = GLOBAL_BATCH, micro_batch: int = MICRO_BATCH) -> dict:
+    """One MoE training benchmark on the ranks of the current torchrun job (or one process).
+    ``impl``: ``ours`` (this framework) or ``torch`` (plain-PyTorch expert-parallel baseline).
+    May run after another trainer in the same process: the process group is reused."""
     import numpy as np
     import torch
 
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=3)
-    ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "torch"])
-    ap.add_argument("--layers", type=int, default=24)
-    ap.add_argument("--experts", type=int, default=64)
-    ap.add_argument("--global-batch", type=int, default=GLOBAL_BATCH)
-    ap.add_argument("--micro-batch", type=int, default=MICRO_BATCH)
-    args = ap.parse_args()
-    MICRO_BATCH = args.micro_batch
     rank, world, local = dist_info()
-    assert world == args.gpus
     os.environ.setdefault("ALLIE_NO_WANDB", "1")
     from allie_b200.config import Config
     from allie_b200.data import UCITokenizer
     from allie_b200.models import initialize_model
 
-    ga = max(1, args.global_batch // (MICRO_BATCH * world))
+    ga = max(1, global_batch // (micro_batch * world))
     tok = UCITokenizer(max_length=SEQ_LEN, vocab_size_multiple_of=128)
-    shape = dict(n_layer=args.layers, n_embd=2048, n_head=16, n_inner=4096, n_positions=1024,
-                 num_experts=args.experts, moe_top_k=2, moe_ffn=4096, moe_layer_freq=3, aux_loss_coef=0.01,
+    shape = dict(n_layer=layers, n_embd=2048, n_head=16, n_inner=4096, n_positions=1024,
+                 num_experts=experts, moe_top_k=2, moe_ffn=4096, moe_layer_freq=3, aux_loss_coef=0.01,
                  capacity_factor=2.0, ep_world=world, ep_rank=rank)
     torch.manual_seed(1234)
     stream = synthetic_stream(1 << 22, len(tok), SEQ_LEN, seed=7 + rank)
-    tokens_per_step = ga * MICRO_BATCH * world * SEQ_LEN
-    if args.impl == "ours":
+    tokens_per_step = ga * micro_batch * world * SEQ_LEN
+    # both arms step at the same mid-warm-up learning rate (3e-4 * 200 / 2000): a random-init
+    # model stepped at the full rate spends its first steps in an Adam start-up blow-up
+    LR, WARM, ITER = 3e-4, 2000, 200
+    stats = lambda: {}
+    if impl == "ours":
         from allie_b200.ops import _lib
         from allie_b200.train.trainer import Trainer
 
-        trainer = Trainer(Config({}), output_dir=tempfile.mkdtemp(prefix="allie_moe_"), batch_size=MICRO_BATCH,
-                          gradient_accumulation_steps=ga, lr=3e-4, min_lr=1e-5, weight_decay=1e-2, grad_clip=1.0,
-                          warmup_iters=2000, decay_iters=2_000_000, max_iters=2_000_000, eval_interval=0,
+        trainer = Trainer(Config({}), output_dir=tempfile.mkdtemp(prefix="allie_moe_"), batch_size=micro_batch,
+                          gradient_accumulation_steps=ga, lr=LR, min_lr=1e-5, weight_decay=1e-2, grad_clip=1.0,
+                          warmup_iters=WARM, decay_iters=2_000_000, max_iters=2_000_000, eval_interval=0,
                           log_interval=-1, save_interval=0, use_wandb=False)
         model = initialize_model(tok, "gpt2-medium", use_control_token=True, use_regression_head=True, **shape)
         trainer.setup_dataloaders(tok, stream, [], [])
         trainer.setup_model(model)
-        trainer.iter_num = 2000          # past the warm-up: both arms step at lr 3e-4
+        trainer.iter_num = ITER
         dev = trainer.engine.device
         wins = [trainer.sampler.next().clone().to(dev) for _ in range(max(ga, 4))]
         step = lambda i: trainer.train_step([wins[(i * ga + m) % len(wins)] for m in range(ga)])
         counter = lambda: _lib.LAUNCHES
         check = _lib.check_status
+
+        def stats():
+            st = trainer.engine.moe_stats() or {}
+            return {"expert_load_max_over_mean": round(st.get("max_over_mean_load", 0.0), 3),
+                    "capacity_overflow": bool(st.get("overflow", False)), "aux_loss": round(st.get("aux_loss", 0.0), 4)}
     else:
         sys.path.insert(0, os.path.join(ROOT, "baseline"))
         import torch.distributed as dist
-        from moe_torch import patch_model_for_baseline
+        from moe_torch import GROUPED, patch_model_for_baseline
 
-        if world > 1:
+        if world > 1 and not dist.is_initialized():
             dist.init_process_group("nccl")
         torch.cuda.set_device(local)
         dev = torch.device("cuda", local)
@@ -87,10 +87,11 @@ def main():
         model.to(dev).train()
         local_params = {id(p) for m in model.modules() if type(m).__name__ == "ExpertBank" for p in m.parameters()}
         dense = [p for p in model.parameters() if id(p) not in local_params]
-        opt = torch.optim.AdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=1e-2, fused=True)
+        lr = LR * ITER / WARM
+        opt = torch.optim.AdamW(model.parameters(), lr=lr, betas=(0.9, 0.95), weight_decay=1e-2, fused=True)
         wins = []
         for _ in range(max(ga, 4)):
-            s = np.random.default_rng(len(wins) + rank).integers(0, len(stream) - SEQ_LEN, size=MICRO_BATCH)
+            s = np.random.default_rng(len(wins) + rank).integers(0, len(stream) - SEQ_LEN, size=micro_batch)
             w = np.stack([stream[i:i + SEQ_LEN] for i in s]).astype(np.int64)
             wins.append({k: v.to(dev) for k, v in tok.pad_and_collate(list(w.astype(np.uint32))).items()})
 
@@ -114,7 +115,7 @@ def main():
     trace = []                       # device-side loss of every step, read back after the timed region
     sampler = ClockSampler(local)
     sampler.start()
-    for i in range(args.warmup):
+    for i in range(warmup):
         trace.append(step(i).clone())
     torch.cuda.synchronize()
     check()
@@ -123,8 +124,8 @@ def main():
     l0 = counter()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for i in range(args.steps):
-        loss = step(args.warmup + i)
+    for i in range(steps):
+        loss = step(warmup + i)
         trace.append(loss.clone())
     e1.record()
     barrier_sync(world)
@@ -132,15 +133,39 @@ def main():
     ms = max_over_ranks(e0.elapsed_time(e1), world)
     check()
     n_params = sum(p.numel() for p in model.parameters())
-    res = {"metric": "train tokens/sec (MoE config)", "value": tokens_per_step * args.steps / (ms / 1e3),
-           "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-           "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "dtype": "bf16",
-           "data": "synthetic", "impl": "allie_b200" if args.impl == "ours" else "plain-pytorch-ep",
-           "config": {"model": f"{args.layers}L d2048 16H hd128, MoE every 3rd layer: {args.experts} experts x FFN 4096, top-2",
-                      "global_batch": ga * MICRO_BATCH * world, "seq_len": SEQ_LEN, "micro_batch": MICRO_BATCH,
-                      "grad_accum": ga, "parallelism": f"dp{world}+ep{world}", "params_per_rank": n_params},
+    if impl == "ours":
+        name = "allie_b200"
+    else:
+        name = "plain-pytorch-ep (all_to_all_single + " + ("torch._grouped_mm)" if GROUPED else "per-expert cuBLAS loop)")
+    res = {"metric": "train tokens/sec (MoE config)", "value": tokens_per_step * steps / (ms / 1e3),
+           "unit": "tokens/s", "n_gpus": world, "steps": steps, "warmup": warmup,
+           "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "strong", "dtype": "bf16",
+           "data": "synthetic", "impl": name,
+           "config": {"model": f"{layers}L d2048 16H hd128, MoE every 3rd layer: {experts} experts x FFN 4096, top-2",
+                      "global_batch": ga * micro_batch * world, "seq_len": SEQ_LEN, "micro_batch": micro_batch,
+                      "grad_accum": ga, "parallelism": f"dp{world}+ep{world}", "params_per_rank": n_params,
+                      "lr": LR * ITER / WARM},
            "clocks": clocks, "gpu_launches": counter() - l0, "final_loss": float(loss if loss.dim() == 0 else loss[0]),
-           "loss_per_step": [round(float(t if t.dim() == 0 else t[0]), 3) for t in trace]}
+           "loss_per_step": [round(float(t if t.dim() == 0 else t[0]), 3) for t in trace], **stats()}
+    if impl == "ours":
+        del trainer
+    return res
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "torch"])
+    ap.add_argument("--layers", type=int, default=24)
+    ap.add_argument("--experts", type=int, default=64)
+    ap.add_argument("--global-batch", type=int, default=GLOBAL_BATCH)
+    ap.add_argument("--micro-batch", type=int, default=MICRO_BATCH)
+    args = ap.parse_args()
+    rank, world, _ = dist_info()
+    assert world == args.gpus
+    res = run_moe(args.impl, args.steps, args.warmup, args.layers, args.experts, args.global_batch, args.micro_batch)
     if rank == 0:
         print(json.dumps(res), flush=True)
 

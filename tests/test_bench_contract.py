@@ -56,6 +56,19 @@ def test_model_table():
     assert bench.GLOBAL_BATCH % bench.MICRO_BATCH == 0 and bench.GLOBAL_BATCH // bench.MICRO_BATCH == 8
 
 
+def test_both_arms_share_one_config_dictionary():
+    """The two arms of the headline benchmark describe their workload with the same ``config``
+    (arm-specific detail goes elsewhere), for every model shape and rank count."""
+    for name in bench.MODELS:
+        for world in (1, 2, 4, 8):
+            ga = bench.GLOBAL_BATCH // (bench.MICRO_BATCH * world)
+            cfg = bench.common_config(name, ga, world)
+            assert cfg["global_batch"] == 512 and cfg["seq_len"] == 512 and cfg["grad_accum"] * world * 64 == 512
+            assert cfg["parallelism"] == f"dp{world}" and "dropout 0.1" in cfg["model"]
+    src = open(bench.__file__).read()
+    assert src.count('"config": common_config(args.model, ga, world)') == 2
+
+
 def test_command_dispatcher(capsys, tmp_path):
     from allie_b200.__main__ import COMMANDS, main
     import importlib

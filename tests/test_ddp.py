@@ -121,7 +121,8 @@ def test_fused_path_survives_a_slow_rank_zero_in_validate_and_save(tmp_path):
     assert len(st) == len(ck["optimizer"]["param_groups"][0]["params"]) + len(ck["optimizer"]["param_groups"][1]["params"])
     # every weight matrix is cut between the two ranks somewhere: its gathered moments must be
     # alive over its whole extent, not only in the part rank 0 owns
-    big = [s_["exp_avg_sq"] for s_ in st.values() if s_["exp_avg_sq"].dim() == 2 and s_["exp_avg_sq"].numel() >= 128 * 128]
+    decayed = ck["optimizer"]["param_groups"][0]["params"]
+    big = [st[i]["exp_avg_sq"] for i in decayed if st[i]["exp_avg_sq"].numel() >= 128 * 128]
     assert len(big) >= 12
     assert all(float((v > 0).float().mean()) > 0.9 for v in big)
     assert (tmp_path / "run_fused" / "best.pt").exists()
