@@ -149,7 +149,11 @@ colsum_bf16_kernel(const __nv_bfloat16* __restrict__ x, long long ld, int M, int
   __shared__ float part[128][9];
   const int tx = threadIdx.x & 127, ty = threadIdx.x >> 7;
   const int c = (blockIdx.x * 128 + tx) * 8;
-  if (m_limit) M = min(M, __ldg(m_limit));
+  // grouped form (blockIdx.z = group): group g owns rows [g*M, (g+1)*M) of x, row g of `out` and
+  // entry g of `m_limit`
+  x += static_cast<long long>(blockIdx.z) * M * ld;
+  out += static_cast<long long>(blockIdx.z) * N;
+  if (m_limit) M = min(M, __ldg(m_limit + blockIdx.z));
   const int r0 = blockIdx.y * CS_ROWS;
   const int r1 = min(M, r0 + CS_ROWS);
   float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -185,6 +189,15 @@ colsum_bf16_kernel(const __nv_bfloat16* __restrict__ x, long long ld, int M, int
   }
 }
 }  // namespace ab
+
+// out[g][n] += sum over the first min(cap, m_limit[g]) rows of group g of x ([groups*cap, N] bf16)
+extern "C" int ab_colsum_grouped_bf16(const void* x, long long ld, int groups, int cap, int N, float* out,
+                                      const int* m_limit, cudaStream_t stream) {
+  if ((N & 7) || (ld & 7) || groups < 1 || groups > 65535 || !m_limit) return -1;
+  dim3 grid((N / 8 + 127) / 128, (cap + ab::CS_ROWS - 1) / ab::CS_ROWS, groups);
+  ab::colsum_bf16_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, ld, cap, N, out, m_limit);
+  return (int)cudaGetLastError();
+}
 
 extern "C" int ab_colsum_bf16(const void* x, long long ld, int M, int N, float* out,
                               const int* m_limit, cudaStream_t stream) {

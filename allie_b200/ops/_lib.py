@@ -62,6 +62,15 @@ class GemmEpilogue(ctypes.Structure):
     ]
 
 
+class GroupedGemm(ctypes.Structure):
+    """``AbGroupedGemm`` of ``csrc/gemm_grouped.cuh``."""
+    _fields_ = [
+        ("groups", c_int), ("cap", c_int), ("mode", c_int), ("rows", c_void_p), ("tile_ready", c_void_p),
+        ("ret", c_void_p), ("peers", c_void_p * 8), ("flags", c_void_p * 8), ("phase", c_int),
+        ("epoch", c_uint), ("rank", c_int), ("world", c_int), ("ticket", c_void_p),
+    ]
+
+
 def ptr(t: torch.Tensor | None) -> c_void_p:
     return c_void_p(0 if t is None else t.data_ptr())
 

@@ -124,3 +124,70 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         raise RuntimeError(f"ab_gemm_bf16 failed with code {rc} for M={M} N={N} K={K}")
     _lib.count_launches(1)
     return out
+
+
+def gemm_grouped(a: torch.Tensor, b: torch.Tensor, rows: torch.Tensor, cap: int, *, mode: int, b_mn: bool = True,
+                 out: torch.Tensor | None = None, bias: torch.Tensor | None = None, act: int = 0,
+                 aux: torch.Tensor | None = None, tile_ready: torch.Tensor | None = None,
+                 scatter: dict | None = None) -> None:
+    """One launch of the grouped CTA-pair GEMM (``csrc/gemm_grouped.cu``) over all local experts.
+
+    ``rows`` (int32 [G], device): live rows per group; ``cap``: rows reserved per group.
+    mode 1: ``a`` [G*cap, K] bf16, ``b`` [G, K, N] (``b_mn``) or [G, N, K]; ``out`` / ``aux`` [G*cap, N] bf16,
+            ``bias`` [G, N] fp32, ``act`` as in :func:`gemm`.
+    mode 2: ``a`` [G*cap, M] bf16, ``b`` [G*cap, N] bf16; ``out`` [G, M, N] fp32, accumulated with
+            ``a[g]^T @ b[g]`` over each group's live rows (rounded up to 128).
+    ``tile_ready`` (uint32 / int32 [G*cap/128]): arrival counters the producer waits on.
+    ``scatter`` (mode 1): ``dict(ret=, peers=, flags=, phase=, epoch=, rank=, world=, ticket=)`` - rows
+    leave to the peers' buffers from the epilogue instead of being written to ``out``.
+    """
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.dim() == 2 and a.stride(1) == 1
+    G = rows.numel()
+    assert rows.dtype == torch.int32 and a.shape[0] == G * cap and cap % 256 == 0
+    ep = _lib.GemmEpilogue()
+    grp = _lib.GroupedGemm()
+    grp.groups, grp.cap, grp.mode = G, cap, mode
+    grp.rows = rows.data_ptr()
+    if tile_ready is not None:
+        assert tile_ready.numel() >= G * cap // 128
+        grp.tile_ready = tile_ready.data_ptr()
+    ep.alpha = 1.0
+    if mode == 1:
+        K = a.shape[1]
+        assert b.dim() == 3 and b.shape[0] == G and b.is_contiguous()
+        N = b.shape[2] if b_mn else b.shape[1]
+        assert (b.shape[1] if b_mn else b.shape[2]) == K
+        M = cap
+        ldb = b.shape[2]
+        if scatter is not None:
+            assert act == 0 and out is None
+            grp.ret = scatter["ret"].data_ptr()
+            for i in range(8):
+                grp.peers[i] = scatter["peers"][i]
+                grp.flags[i] = scatter["flags"][i]
+            grp.phase, grp.epoch = scatter["phase"], scatter["epoch"]
+            grp.rank, grp.world = scatter["rank"], scatter["world"]
+            grp.ticket = scatter["ticket"]
+        else:
+            assert out is not None and out.dtype == torch.bfloat16 and out.shape == (G * cap, N) and out.stride(1) == 1
+            ep.out, ep.ldo = out.data_ptr(), out.stride(0)
+        if bias is not None:
+            assert bias.dtype == torch.float32 and bias.numel() == G * N and bias.is_contiguous()
+            ep.bias = bias.data_ptr()
+        ep.act = act
+        if act:
+            assert aux is not None and aux.dtype == torch.bfloat16 and aux.shape == (G * cap, N)
+            ep.aux, ep.ldaux = aux.data_ptr(), aux.stride(0)
+    else:
+        assert mode == 2 and b.dim() == 2 and b.shape[0] == G * cap and b.stride(1) == 1 and b_mn
+        M, N, K = a.shape[1], b.shape[1], cap
+        ldb = b.stride(0)
+        assert out is not None and out.dtype == torch.float32 and out.shape == (G, M, N) and out.is_contiguous()
+        ep.out, ep.ldo, ep.out_fp32, ep.accumulate = out.data_ptr(), N, 1, 1
+    rc = _lib.cuda().ab_gemm_grouped_bf16(
+        _lib.ptr(a), c_longlong(a.stride(0)), _lib.ptr(b), c_int(int(b_mn)), c_longlong(ldb),
+        c_int(M), c_int(N), c_int(K), ctypes.byref(ep), ctypes.byref(grp), c_int(num_sms()),
+        _lib.ptr(_lib.status_word()), _lib.stream_ptr())
+    if rc != 0:
+        raise RuntimeError(f"ab_gemm_grouped_bf16 failed with code {rc} (mode {mode}, G={G}, cap={cap}, M={M}, N={N}, K={K})")
+    _lib.count_launches(1)

@@ -117,3 +117,13 @@ def colsum_bf16(x, out, m_limit=None) -> None:
     M, N = x.shape
     _ck(_lib.cuda().ab_colsum_bf16(ptr(x), c_longlong(x.stride(0)), c_int(M), c_int(N), ptr(out),
                                    ptr(m_limit), stream_ptr()), "ab_colsum_bf16")
+
+
+def colsum_grouped_bf16(x, out, rows, cap: int) -> None:
+    """Grouped form: ``x`` [G*cap, N] bf16, ``out`` [G, N] fp32 accumulated, ``rows`` int32 [G] = rows of
+    every group that take part."""
+    G = rows.numel()
+    N = x.shape[1]
+    assert x.shape[0] == G * cap and out.numel() == G * N
+    _ck(_lib.cuda().ab_colsum_grouped_bf16(ptr(x), c_longlong(x.stride(0)), c_int(G), c_int(cap), c_int(N),
+                                           ptr(out), ptr(rows), stream_ptr()), "ab_colsum_grouped_bf16")
