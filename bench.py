@@ -47,6 +47,7 @@ MODEL = dict(n_layer=24, n_embd=1024, n_head=16, n_positions=1024)
 MODELS = {"medium": MODEL, "large": dict(n_layer=32, n_embd=1280, n_head=20, n_positions=1024)}
 SEQ_LEN, VOCAB_MULT, GLOBAL_BATCH, MICRO_BATCH = 512, 128, 512, 64
 BASELINE_TOKENS_PER_S = 2.17e5   # derived from the reference README: 8x RTX A6000, ~2 weeks
+START_ITER = 10                  # both arms start their steps here in the 2000-iteration warm-up
 
 
 class ClockSampler:
@@ -324,7 +325,10 @@ def run_ours(args) -> dict:
     stream = synthetic_stream(64 * 1024 * SEQ_LEN // 8, len(tok), SEQ_LEN, seed=7 + rank)
     trainer.setup_dataloaders(tok, stream, [], [])
     trainer.setup_model(model)
-    trainer.iter_num = 1000     # mid-warmup learning rate, nonzero updates
+    # the first iterations of the warm-up schedule (lr = 6e-4 * iter / 2000), as a run from random
+    # init sees them; fresh Adam moments stepped at a mid-schedule rate overshoot the think-time
+    # loss a hundredfold for two steps, which would make final_loss meaningless
+    trainer.iter_num = START_ITER
     dev = trainer.engine.device
     sync_check = grad_sync_check(world) if world > 1 else None
 
@@ -474,8 +478,8 @@ def run_reference(args) -> dict:
     stream = synthetic_stream(64 * 1024 * SEQ_LEN // 8, len(tok), SEQ_LEN, seed=7 + rank)
     trainer.setup_dataloaders(tok, stream, [], [])
     trainer.setup_model(model)
-    trainer.iter_num = 1000
-    trainer.max_iters = 1000 + W + K - 1
+    trainer.iter_num = START_ITER
+    trainer.max_iters = START_ITER + W + K - 1
 
     state = {"n": 0, "ms": None, "clocks": None, "wall0": None}
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

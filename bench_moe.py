@@ -47,9 +47,10 @@ def run_moe(impl: str = "ours", steps: int = 10, warmup: int = 3, layers: int = 
     torch.manual_seed(1234)
     stream = synthetic_stream(1 << 22, len(tok), SEQ_LEN, seed=7 + rank)
     tokens_per_step = ga * micro_batch * world * SEQ_LEN
-    # both arms step at the same mid-warm-up learning rate (3e-4 * 200 / 2000): a random-init
-    # model stepped at the full rate spends its first steps in an Adam start-up blow-up
-    LR, WARM, ITER = 3e-4, 2000, 200
+    # both arms step at the learning rate of the first warm-up iterations (3e-4 * 10 / 2000): fresh
+    # Adam moments stepped at a mid-schedule rate overshoot the think-time loss a hundredfold for
+    # two steps (every parameter moves by lr along the sign of its gradient), dense model or not
+    LR, WARM, ITER = 3e-4, 2000, 10
     stats = lambda: {}
     if impl == "ours":
         from allie_b200.ops import _lib
