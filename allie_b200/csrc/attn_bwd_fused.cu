@@ -15,14 +15,6 @@
 
 namespace ab {
 
-#ifdef AB_ATTN_PROFILE
-// development aid: per-CTA cycle stamps (enabled only in private profiling builds)
-__device__ long long* g_attn_dbg = nullptr;
-#define AB_STAMP(k) do { if (g_attn_dbg && threadIdx.x == 0) \
-    g_attn_dbg[((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 16 + (k)] = clock64(); } while (0)
-#else
-#define AB_STAMP(k) do { } while (0)
-#endif
 
 constexpr int FB_MATH_WARPS = 16;
 constexpr int FB_MATH_THREADS = FB_MATH_WARPS * 32;
@@ -93,14 +85,6 @@ attn_bwd_fused64_kernel(const __grid_constant__ CUtensorMap tmQKV,
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
-  AB_STAMP(0);
-#ifdef AB_ATTN_PROFILE
-  if (g_attn_dbg && threadIdx.x == 0) {
-    unsigned smid;
-    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-    g_attn_dbg[((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 16 + 15] = smid;
-  }
-#endif
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nt = (a.T + 127) / 128;
   const int h = blockIdx.y, b = blockIdx.z;
@@ -129,7 +113,6 @@ attn_bwd_fused64_kernel(const __grid_constant__ CUtensorMap tmQKV,
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tS = tmem_base, tDP = tmem_base + 128, tDV = tmem_base + 256, tDK = tmem_base + 320,
                  tDQ = tmem_base + 384;
-  AB_STAMP(1);
 
   if (warp == FB_TMA_WARP) {
     if (lane == 0) {
@@ -261,7 +244,6 @@ attn_bwd_fused64_kernel(const __grid_constant__ CUtensorMap tmQKV,
         }
       }
       if (!mbar_wait(sdp_full, it & 1, abort_flag)) { ok = false; break; }
-      AB_STAMP(2 + 2 * it);
       if (it > 0 && !mbar_wait(pds_empty, (it - 1) & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
 #pragma unroll
@@ -298,14 +280,11 @@ attn_bwd_fused64_kernel(const __grid_constant__ CUtensorMap tmQKV,
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) { mbar_arrive(sdp_empty); mbar_arrive(pds_full); }
-      AB_STAMP(3 + 2 * it);
       // the previous pair's dQ tile finished long ago: drain it while the tensor core works
       if (it > 0) ok = drain_dq(it - 1);
     }
     if (ok) ok = drain_dq(n_iter - 1);
-    AB_STAMP(10);
     if (ok && !mbar_wait(acc_full, 0, abort_flag)) ok = false;
-    AB_STAMP(11);
     if (!ok) { *abort_flag = ST_TIMEOUT_TMEM_FULL; atomicCAS(a.status, 0, ST_TIMEOUT_TMEM_FULL); }
     if (ok) {
       tc_fence_after();
@@ -329,14 +308,11 @@ attn_bwd_fused64_kernel(const __grid_constant__ CUtensorMap tmQKV,
         }
       }
     }
-    AB_STAMP(12);
     if (lane == 0) tma_store_wait<0>();
-    AB_STAMP(13);
   }
   tc_fence_before();
   __syncthreads();
   if (warp == FB_MMA_WARP) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
-  AB_STAMP(14);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -348,14 +324,6 @@ attn_bwd_fused64_kernel(const __grid_constant__ CUtensorMap tmQKV,
 // P/dS math of the first pair of key tile w + 1, while the tensor core already works on that pair.
 // So the per-key-tile prologue (TMEM allocation, barrier set-up, first loads) and tail, which cost
 // as much as two pairs in the one-tile-per-CTA kernel, are paid once per CTA.
-#ifdef AB_ATTN_PROFILE
-// development aid: CTA 0 stamps the clock at five points of its first 64 pairs (math warp 0) and at
-// the two issue points of the MMA thread
-#define AB_PSTAMP(base, g, k) do { if (g_attn_dbg && blockIdx.x == 0 && (g) < 64) \
-    g_attn_dbg[(base) + (g) * 8 + (k)] = clock64(); } while (0)
-#else
-#define AB_PSTAMP(base, g, k) do { } while (0)
-#endif
 
 struct FbWalk {
   int bh, own, it, nt, bh_end, step;
@@ -474,7 +442,6 @@ attn_bwd_fused64_persistent_kernel(const __grid_constant__ CUtensorMap tmQKV,
         if (p.first() && !mbar_wait(&kv_full[p.w & 1], (p.w >> 1) & 1, abort_flag)) return false;
         if (!mbar_wait(&full[st], (p.g >> 1) & 1, abort_flag)) return false;
         if (p.g > 0 && !mbar_wait(sdp_empty, (p.g - 1) & 1, abort_flag)) return false;
-        AB_PSTAMP(512, p.g, 0);
         tc_fence_after();
         const uint32_t k0 = smem_u32(sK + (p.w & 1) * FB_TILE), v0 = smem_u32(sV + (p.w & 1) * FB_TILE);
         const uint32_t q = smem_u32(sQ + st * FB_TILE), dO = smem_u32(sDO + st * FB_TILE);
@@ -495,7 +462,6 @@ attn_bwd_fused64_persistent_kernel(const __grid_constant__ CUtensorMap tmQKV,
         if (p.g >= 2 && !mbar_wait(&dq_empty[p.g & 1], ((p.g - 2) >> 1) & 1, abort_flag)) return false;
         // dV / dK of the previous key tile must have been read out before they are overwritten
         if (p.first() && p.w > 0 && !mbar_wait(acc_empty, (p.w - 1) & 1, abort_flag)) return false;
-        AB_PSTAMP(512, p.g, 1);
         tc_fence_after();
         const uint32_t k0 = smem_u32(sK + (p.w & 1) * FB_TILE);
         const uint32_t q = smem_u32(sQ + st * FB_TILE), dO = smem_u32(sDO + st * FB_TILE);
@@ -746,11 +712,6 @@ attn_bwd_fused64_persistent_kernel(const __grid_constant__ CUtensorMap tmQKV,
   if (warp == FB_MMA_WARP) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
 }
 
-#ifdef AB_ATTN_PROFILE
-extern "C" int ab_attn_set_dbg(long long* p) {
-  return (int)cudaMemcpyToSymbol(g_attn_dbg, &p, sizeof(p));
-}
-#endif
 
 // dqkv[:, 0:d] = bf16(dq_acc).  A block walks whole rows (thread = one float4 column group), so
 // every access is a contiguous row segment.  The accumulator is cleared by a separate memset:

@@ -183,3 +183,16 @@ int ab_embed_bwd(const int* ids, const int* pos, const float* dx, float* dwte, f
   return (int)cudaGetLastError();
 }
 }
+
+// Host-side statement of the dropout keep decisions (the same Philox function the kernels call,
+// compiled for the CPU): out[i] = 1 when element i of stream `stream` under `seed` is kept.
+// For tests that rebuild a kernel's mask outside the kernel.  n: multiple of 8.
+extern "C" int ab_dropout_mask_host(unsigned long long seed, unsigned int stream, long long n,
+                                    unsigned int thr16, unsigned char* out) {
+  if (n & 7) return -1;
+  for (long long g = 0; g < n / 8; ++g) {
+    const uint32_t keep = ab::dropout_keep8(seed, stream, static_cast<uint64_t>(g), thr16);
+    for (int j = 0; j < 8; ++j) out[g * 8 + j] = (keep >> j) & 1u;
+  }
+  return 0;
+}

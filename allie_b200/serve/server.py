@@ -6,7 +6,10 @@ A client connects to ``localhost:port``, sends one JSON ``Game`` dict, receives 
 rating unless the system fixes one.  Unlike the reference (strictly one request at a time), all
 connections waiting in the listen backlog when a request arrives are answered as one batch: their
 positions share a single network evaluation (policy systems) or one batched tree search (MCTS
-systems).  A broken client socket never takes the server down.
+systems).  The requests of a batch are read concurrently under one shared deadline, so an idle
+connection delays its batch by that deadline at most once, not by one timeout per connection.
+Neither a broken client socket, nor a malformed request, nor an exception inside the decoder
+takes the server down: the affected connections are closed with a warning and the loop goes on.
 """
 from __future__ import annotations
 
@@ -122,6 +125,50 @@ def build_algorithm(alias: str, model, tokenizer: UCITokenizer, device: str | No
     return DECODE_STRATEGIES[system.algorithm](model, tokenizer, device=device, **system.algorithm_config)
 
 
+def read_requests(conns: list[socket.socket], timeout: float) -> list[tuple[socket.socket, dict | Exception]]:
+    """Reads one JSON document from every connection, all of them concurrently (``select``) under
+    ONE deadline of ``timeout`` seconds.  Returns, in the order of ``conns``, the parsed dict or the
+    exception that ended the attempt (closed early, oversized, timed out)."""
+    bufs = {c: b"" for c in conns}
+    done: dict[socket.socket, dict | Exception] = {}
+    for c in conns:
+        c.setblocking(False)
+    deadline = time.monotonic() + timeout
+    while len(done) < len(conns):
+        pending = [c for c in conns if c not in done]
+        left = deadline - time.monotonic()
+        if left <= 0:
+            for c in pending:
+                done[c] = TimeoutError("no complete request within the batch deadline")
+            break
+        readable = select.select(pending, [], [], left)[0]
+        for c in readable:
+            try:
+                chunk = c.recv(8192)
+            except BlockingIOError:
+                continue
+            except OSError as e:
+                done[c] = e
+                continue
+            if not chunk:
+                done[c] = ConnectionError("peer closed before a complete JSON document arrived")
+                continue
+            bufs[c] += chunk
+            if len(bufs[c]) > MAX_MESSAGE_BYTES:
+                done[c] = ValueError("message larger than any request can be")
+                continue
+            try:
+                done[c] = json.loads(bufs[c].decode())
+            except (json.JSONDecodeError, UnicodeDecodeError):
+                pass                      # not complete yet
+    for c in conns:
+        try:
+            c.setblocking(True)
+        except OSError:
+            pass
+    return [(c, done[c]) for c in conns]
+
+
 def _validated(game: Game) -> Game:
     """Type checks of a request before it reaches the model (a malformed field would otherwise
     surface as an exception in the middle of a batch)."""
@@ -131,8 +178,11 @@ def _validated(game: Game) -> Game:
         elo = getattr(game, name)
         if elo is not None and (isinstance(elo, bool) or not isinstance(elo, int) or not 0 <= elo <= 10000):
             raise ValueError(f"{name} must be an integer rating")
-    if game.white_elo is None and game.black_elo is None:
-        raise ValueError("at least the opponent's rating is needed")
+    # the bot (the side to move) takes the opponent's rating or the system's fixed one; the
+    # opponent's own rating has to come with the request, the tokenizer conditions on both
+    white_to_move = len(game.moves) % 2 == 0
+    if (game.black_elo if white_to_move else game.white_elo) is None:
+        raise ValueError("the opponent's rating (the side not to move) is needed")
     if len(game.moves) != len(game.moves_seconds) or not all(isinstance(m, str) for m in game.moves):
         raise ValueError("moves must be strings, one entry of moves_seconds per move")
     if not all(isinstance(t, (int, float)) and not isinstance(t, bool) and t >= 0 for t in game.moves_seconds):
@@ -147,7 +197,7 @@ def _answer(conn: socket.socket, res: DecodeResult) -> None:
 
 def serve(alias: str, model, tokenizer: UCITokenizer, device: str | None = None, host: str = "localhost",
           port: int | None = None, self_test: bool = True, max_requests: int | None = None,
-          max_batch: int = 64, batched: bool = True, client_timeout: float = 10.0) -> None:
+          max_batch: int = 64, batched: bool = True, client_timeout: float = 5.0) -> None:
     system = SYSTEMS[alias]
     algorithm = build_algorithm(alias, model, tokenizer, device, batched=batched, max_batch=max_batch)
     if self_test:
@@ -165,14 +215,16 @@ def serve(alias: str, model, tokenizer: UCITokenizer, device: str | None = None,
             while len(conns) < max_batch and select.select([srv], [], [], 0)[0]:
                 conns.append(srv.accept()[0])
             ready: list[tuple[socket.socket, Game]] = []
-            for conn in conns:
+            for conn, req in read_requests(conns, client_timeout):
                 try:
+                    if isinstance(req, Exception):
+                        raise req
                     conn.settimeout(client_timeout)
-                    game = assign_elo(_validated(Game(**recv_dict(conn))), system)
+                    game = assign_elo(_validated(Game(**req)), system)
                     if not game.legal_moves:              # replays the moves: an illegal game fails here
                         raise ValueError("the game is over: no legal move to answer with")
                     ready.append((conn, game))
-                except (ConnectionError, OSError, ValueError, TypeError, KeyError, AttributeError) as e:
+                except (ConnectionError, OSError, ValueError, TypeError, KeyError, AttributeError, AssertionError) as e:
                     logger.warning(f"request failed: {type(e).__name__}: {e}")     # a malformed request never ends the server
                     conn.close()
             try:
@@ -185,6 +237,12 @@ def serve(alias: str, model, tokenizer: UCITokenizer, device: str | None = None,
                         _answer(conn, res)
                     except (ConnectionError, OSError) as e:
                         logger.warning(f"reply failed: {type(e).__name__}: {e}")
+            except KeyboardInterrupt:
+                raise
+            except Exception as e:
+                # a request that passed validation but still broke the decoder: this batch's
+                # clients get a closed connection (they retry), the server keeps listening
+                logger.warning(f"decoding a batch of {len(ready)} request(s) failed: {type(e).__name__}: {e}")
             finally:
                 for conn, _ in ready:
                     conn.close()

@@ -84,3 +84,84 @@ def test_dense_engine_matches_oracle(n_embd, n_head):
         worst = max(worst, d.max().item()); total += d.sum().item(); count += d.numel()
     # the first Adam step moves every weight by about lr; a sign flip on a near-zero gradient costs 2 lr
     assert worst < 2.5e-3 and total / count < 1e-4, (worst, total / count)
+
+
+def test_dense_engine_with_dropout_matches_oracle_under_the_same_masks(monkeypatch):
+    """The configuration the benchmarks run (dropout 0.1 on embeddings, attention probabilities and
+    both residual branches), end to end: every mask the kernels apply is rebuilt on the host from
+    the same counter-based generator (attention: read back from the keep bits the forward kernel
+    stores) and handed to the fp32 oracle in call order, then losses and every parameter gradient
+    are compared.  A backward kernel that regenerated a different mask than its forward twin
+    (LayerNorm backward re-deriving the mask of the projection below it, attention backward
+    reading the stored bits) would show up here."""
+    import ctypes
+
+    import torch.nn.functional as F
+
+    from allie_b200.data import UCITokenizer
+    from allie_b200.models import initialize_model
+    from allie_b200.models.engine import B200Engine
+    from allie_b200.ops import _lib
+
+    torch.manual_seed(0)
+    B, T, d, H, L, p = 4, 256, 256, 4, 3, 0.1
+    tok = UCITokenizer(max_length=T, vocab_size_multiple_of=128)
+    model = initialize_model(tok, "gpt2", use_control_token=True, use_regression_head=True, n_layer=L, n_embd=d,
+                             n_head=H, n_positions=T, resid_pdrop=p, embd_pdrop=p, attn_pdrop=p)
+    oracle = copy.deepcopy(model).float().train()
+    words = _windows(tok, B, T, seed=3)
+    batch = tok.pad_and_collate(list(words))
+
+    eng = B200Engine(model, "cuda")
+    w = torch.from_numpy(words.astype(np.int32)).cuda()
+    eng.load_window(w)
+    seed = eng._next_seed()
+    buf = eng.forward(B, T, True, seed, True, True)
+    eng.backward(B, T, seed)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    got = eng.loss_out.tolist()
+
+    thr = _lib.dropout_thr16(p)
+    scale = 65536.0 / (65536 - thr)
+    lib = _lib.cuda()
+
+    def host_mask(stream, n):
+        out = np.empty(n, dtype=np.uint8)
+        assert lib.ab_dropout_mask_host(ctypes.c_ulonglong(seed), ctypes.c_uint(stream), ctypes.c_longlong(n),
+                                        ctypes.c_uint(thr), out.ctypes.data_as(ctypes.c_void_p)) == 0
+        return torch.from_numpy(out).float()
+
+    def attn_mask(l):
+        words_ = buf["dmask"][l].cpu().numpy().view(np.uint32)              # [B, H, T, T/32], bit = key % 32
+        bits = ((words_[..., None] >> np.arange(32, dtype=np.uint32)) & 1).reshape(B, H, T, T)
+        keep = torch.from_numpy(bits.astype(np.float32))
+        return torch.tril(keep)            # keys past the query were never generated (and carry zero weight)
+
+    # masks in the order the oracle's forward asks for them: embeddings, then per block
+    # attention probabilities, attention projection branch, MLP branch
+    masks = [host_mask(0, B * T * d).view(B, T, d)]
+    for l in range(L):
+        masks += [attn_mask(l), host_mask(1 + 3 * l, B * T * d).view(B, T, d), host_mask(2 + 3 * l, B * T * d).view(B, T, d)]
+    queue = list(masks)
+
+    def fake_dropout(x, p_=0.5, training=True, inplace=False):
+        if not training or p_ == 0.0:
+            return x
+        m = queue.pop(0)
+        assert m.shape == x.shape, (m.shape, x.shape)
+        return x * m * scale
+
+    monkeypatch.setattr(F, "dropout", fake_dropout)
+    out = oracle(**batch)
+    out["loss"].backward()
+    assert not queue
+    frac = 1.0 - float(masks[0].mean())
+    assert abs(frac - p) < 0.01                                    # the masks really drop about 10 %
+    for i, k in enumerate(("loss", "lm_loss", "value_loss", "time_loss")):
+        assert abs(got[i] - out[k].item()) < 2e-2 * max(1.0, abs(out[k].item())), (k, got[i], out[k].item())
+    ref_params = dict(oracle.named_parameters())
+    for n, prm in model.named_parameters():
+        g, gr = prm.grad.float().cpu(), ref_params[n].grad
+        scale_g = gr.abs().max().item() + 1e-12
+        assert (g - gr).abs().max().item() / scale_g < 0.08, n

@@ -67,6 +67,63 @@ def test_round_trip_and_broken_client():
     assert not th.is_alive()
 
 
+def test_missing_opponent_rating_idle_clients_and_decoder_failures_do_not_end_the_server(monkeypatch):
+    """A request that carries only the bot's own rating is refused at validation (the tokenizer
+    conditions on both ratings); several idle connections in one batch cost one shared deadline,
+    not one timeout each; an exception inside the decoder closes that batch's connections and the
+    accept loop goes on."""
+    import allie_b200.serve.server as srv_mod
+
+    torch.manual_seed(0)
+    tok = UCITokenizer(max_length=64, vocab_size_multiple_of=128)
+    model = initialize_model(tok, "gpt2", use_control_token=True, use_regression_head=True, n_layer=1,
+                             n_embd=32, n_head=1, n_positions=64).eval()
+    port = _free_port()
+    real = srv_mod.decode_batch
+    calls = {"n": 0}
+
+    def flaky(algorithm, games):
+        calls["n"] += 1
+        if calls["n"] == 1:
+            raise RuntimeError("decoder blew up")
+        return real(algorithm, games)
+
+    monkeypatch.setattr(srv_mod, "decode_batch", flaky)
+    th = threading.Thread(target=serve, kwargs=dict(alias="humanlike", model=model, tokenizer=tok, device="cpu",
+                                                    port=port, self_test=False, max_requests=9, client_timeout=1.0),
+                          daemon=True)
+    th.start()
+    for _ in range(50):
+        try:
+            socket.create_connection(("localhost", port), timeout=0.2).close()
+            break
+        except OSError:
+            time.sleep(0.1)
+    # white to move, only white's (the bot's own) rating given
+    with socket.create_connection(("localhost", port), timeout=10) as c:
+        send_dict(c, Game("180+0", 1500, None, None, False, [], []).to_dict())
+        assert c.recv(100) == b""
+    game = Game("180+0", 1500, 1600, None, False, ["e2e4", "e7e5"], [1, 2])
+    with socket.create_connection(("localhost", port), timeout=10) as c:      # first decode call raises
+        send_dict(c, game.to_dict())
+        assert c.recv(100) == b""
+    with socket.create_connection(("localhost", port), timeout=10) as c:      # the server is still there
+        send_dict(c, game.to_dict())
+        assert recv_dict(c)["move"] in game.legal_moves
+    # four idle connections and one real request arriving together: answered after ONE deadline
+    idle = [socket.create_connection(("localhost", port), timeout=10) for _ in range(4)]
+    time.sleep(0.3)
+    t0 = time.time()
+    with socket.create_connection(("localhost", port), timeout=10) as c:
+        send_dict(c, game.to_dict())
+        assert recv_dict(c)["move"] in game.legal_moves
+    assert time.time() - t0 < 3.0
+    for c in idle:
+        c.close()
+    th.join(timeout=10)
+    assert not th.is_alive()
+
+
 def test_waiting_connections_share_one_batched_search():
     """Several clients connect before the server looks at any of them; an MCTS system answers them
     from one batched search, and the stress-test client reports success against a policy system."""
