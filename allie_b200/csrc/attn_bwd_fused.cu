@@ -632,7 +632,6 @@ attn_bwd_fused64_persistent_kernel(const __grid_constant__ CUtensorMap tmQKV,
     uint32_t keep32 = 0xffffffffu;
     if (p.valid()) fetch(p, lse_raw, dlt, keep32);
     for (; p.valid() && ok; p.next()) {
-      if (threadIdx.x == 0) AB_PSTAMP(0, p.g, 0);
       if (p.it == 0 && p.own == 0) { b = p.bh / a.H; h = p.bh - b * a.H; }
       const int qi = p.own + p.it;
       const int q_idx = qi * 128 + r;
@@ -645,9 +644,7 @@ attn_bwd_fused64_persistent_kernel(const __grid_constant__ CUtensorMap tmQKV,
         q.next();
         if (q.valid()) fetch(q, n_lse, n_dlt, n_keep);
       }
-      if (threadIdx.x == 0) AB_PSTAMP(0, p.g, 5);
       if (!mbar_wait(sdp_full, p.g & 1, abort_flag)) { ok = false; break; }
-      if (threadIdx.x == 0) AB_PSTAMP(0, p.g, 1);
       tc_fence_after();
       const float lse_l2 = lse_raw * LOG2E;          // +inf for rows outside the sequence
 #pragma unroll
@@ -670,7 +667,6 @@ attn_bwd_fused64_persistent_kernel(const __grid_constant__ CUtensorMap tmQKV,
           // the shared P / dS tiles feed the previous pair's dV / dK / dQ products until
           // pds_empty completes; the first half of this pair's math has run under them
           if (p.g > 0 && !mbar_wait(pds_empty, (p.g - 1) & 1, abort_flag)) { ok = false; break; }
-          if (threadIdx.x == 0) AB_PSTAMP(0, p.g, 2);
         }
         const uint32_t poff = (col0 >> 6) * 16384;
 #pragma unroll
@@ -690,13 +686,11 @@ attn_bwd_fused64_persistent_kernel(const __grid_constant__ CUtensorMap tmQKV,
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) { mbar_arrive(sdp_empty); mbar_arrive(pds_full); }
-      if (threadIdx.x == 0) AB_PSTAMP(0, p.g, 3);
       // work left over from the previous pair, done while the tensor core runs this one
       if (p.g > 0) {
         ok = drain_dq(p.g - 1, prev_row0, prev_h);
         if (ok && p.first()) ok = finish_tile(p.w - 1, prev_b, prev_h, prev_own);
       }
-      if (threadIdx.x == 0) AB_PSTAMP(0, p.g, 4);
       prev_row0 = b * a.T + qi * 128; prev_h = h; prev_b = b; prev_own = p.own;
       lse_raw = n_lse; dlt = n_dlt; keep32 = n_keep;
     }
