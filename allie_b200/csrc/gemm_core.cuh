@@ -22,6 +22,7 @@ constexpr int PAIR_BN = 256;      // instruction N; each CTA stages PAIR_BN / 2 
 struct GemmArgs {
   int M, N, K;
   int k_splits;
+  int pdl;            // launched as a programmatic dependent: B (weights) may be fetched before griddep_wait
   AbGemmEpilogue ep;
   int* status;
 };

@@ -108,10 +108,16 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     tmem_alloc(tmem_slot, TMEM_COLS);
     tmem_relinquish();
   }
+  // the kernel behind this one in the stream may begin its own set-up now
+  if (threadIdx.x == 0) griddep_launch_dependents();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // As a programmatic dependent this kernel may be running before its predecessor has finished:
+  // only the weight operand B (and the set-up above) is touched before griddep_wait.  m_limit /
+  // k_limit are device values of earlier kernels, so such launches are never made dependent.
+  if (warp >= 2) griddep_wait();          // epilogue: residual / aux reads and every store come after
 
   const int Meff = g.ep.m_limit ? min(g.M, __ldg(g.ep.m_limit)) : g.M;
   const int Keff = g.ep.k_limit ? min(g.K, __ldg(g.ep.k_limit)) : g.K;
@@ -130,6 +136,30 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      auto load_b = [&](uint8_t* sb, uint64_t* bar, int k0, int n0) {
+        if constexpr (!B_MN) {
+          tma_load_2d(sb, &tmB, bar, k0, n0);
+        } else {
+#pragma unroll
+          for (int i = 0; i < BN / 64; ++i) tma_load_2d(sb + i * (BK * 128), &tmB, bar, n0 + i * 64, k0);
+        }
+      };
+      // dependent launch: the first ring-full of weight tiles of my first unit goes out while the
+      // kernel before this one is still running; the activations follow after griddep_wait
+      int prefetched = 0;
+      if (g.pdl) {
+        const int u = blockIdx.x;
+        if (u < num_units) {
+          const int ks = u / num_tiles, tile = u % num_tiles;
+          const int n0 = (tile % n_tiles) * BN;
+          const int kb0 = ks * kb_per, kb1 = min(kb_total, kb0 + kb_per);
+          for (int kb = kb0; kb < kb1 && prefetched < STAGES; ++kb, ++prefetched) {
+            mbar_expect_tx(&full_bar[prefetched], STAGE_BYTES);      // the stages are all free at start
+            load_b(smem + prefetched * STAGE_BYTES + A_BYTES, &full_bar[prefetched], kb * BK, n0);
+          }
+        }
+        griddep_wait();
+      }
       for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
         const int ks = u / num_tiles;
         const int tile = u % num_tiles;
@@ -146,7 +176,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           }
           uint8_t* sa = smem + stage * STAGE_BYTES;
           uint8_t* sb = sa + A_BYTES;
-          mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
+          const bool b_done = prefetched > 0;       // this stage's B tile and byte count are already out
+          if (b_done) --prefetched;
+          else mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
           const int k0 = kb * BK;
           if constexpr (!A_MN) {
             tma_load_2d(sa, &tmA, &full_bar[stage], k0, m0);
@@ -155,13 +187,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
             for (int i = 0; i < BM / 64; ++i)
               tma_load_2d(sa + i * (BK * 128), &tmA, &full_bar[stage], m0 + i * 64, k0);
           }
-          if constexpr (!B_MN) {
-            tma_load_2d(sb, &tmB, &full_bar[stage], k0, n0);
-          } else {
-#pragma unroll
-            for (int i = 0; i < BN / 64; ++i)
-              tma_load_2d(sb + i * (BK * 128), &tmB, &full_bar[stage], n0 + i * 64, k0);
-          }
+          if (!b_done) load_b(sb, &full_bar[stage], k0, n0);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -564,6 +590,19 @@ static int launch(const void* A, long long lda, const void* B, long long ldb, co
   const int units = m_tiles * n_tiles * g.k_splits;
   int grid = units < max_ctas ? units : max_ctas;
   if (grid < 1) grid = 1;
+  if (g.pdl) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    return static_cast<int>(cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmOut, tmAux, g));
+  }
   kern<<<grid, NUM_THREADS, SMEM, stream>>>(tmA, tmB, tmOut, tmAux, g);
   return static_cast<int>(cudaGetLastError());
 }
@@ -586,6 +625,9 @@ extern "C" int ab_gemm_bf16(const void* A, int a_mn, long long lda, const void* 
   if (ep->act == 1 && (ep->ldaux & 7)) return -4;
   GemmArgs g;
   g.M = M; g.N = N; g.K = K; g.k_splits = k_splits; g.ep = *ep; g.status = status;
+  // programmatic dependent launch: single-CTA kernels only, never with device-side limits (those
+  // are values of earlier kernels, read before any wait)
+  g.pdl = (ep->pdl && !ep->m_limit && !ep->k_limit) ? 1 : 0;
   if (max_ctas <= 0) max_ctas = 148;
   // narrow tiles also for skinny problems (decode steps with a few hundred rows): twice the CTAs
   const bool narrow = (N <= 128) || (M <= 256);

@@ -32,6 +32,10 @@ struct AbGemmEpilogue {
   // sized for a capacity while the actual count (e.g. tokens routed to an expert) lives on the GPU.
   const int* m_limit;
   const int* k_limit;
+  // nonzero: launch as a programmatic dependent of the kernel before it in the stream (small-M
+  // launches that take the single-CTA kernel only): set-up and the prefetch of the first weight
+  // tiles overlap that kernel; `B` must not be something it writes.
+  int pdl;
 };
 
 // C[M,N] = A[M,K] * B[K,N] on the 5th-generation tensor cores.

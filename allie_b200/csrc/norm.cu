@@ -18,6 +18,9 @@ ln_fwd_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
               const float* __restrict__ beta, __nv_bfloat16* __restrict__ y,
               float* __restrict__ mean_out, float* __restrict__ rstd_out, int M, int d, float eps,
               int rms) {
+  if (threadIdx.x == 0) griddep_launch_dependents();   // a dependent GEMM may start fetching its weights
+  griddep_wait();       // launched as a dependent itself: x comes from the kernel before (no-op otherwise)
+
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int nv = d >> 7;  // float4 per lane
   for (int row = blockIdx.x * LN_WARPS + warp; row < M; row += gridDim.x * LN_WARPS) {
@@ -233,9 +236,38 @@ ln_bwd_kernel(const LnBwdArgs a) {
 
 }  // namespace ab
 
+template <int NV>
+static int launch_ln_dependent(int grid, const float* x, const float* gamma, const float* beta, void* y,
+                               float* mean, float* rstd, int M, int d, float eps, int rms,
+                               cudaStream_t stream) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(ab::LN_WARPS * 32);
+  cfg.stream = stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  return (int)cudaLaunchKernelEx(&cfg, ab::ln_fwd_kernel<NV>, x, gamma, beta, (__nv_bfloat16*)y, mean, rstd, M, d,
+                                 eps, rms);
+}
+
 extern "C" {
 
 // d must be a multiple of 128 and at most 2048.
+// Same as ab_layernorm_fwd, launched as a programmatic dependent of the kernel before it in the
+// stream (its launch overlaps that kernel's tail; it waits for it before reading x).
+int ab_layernorm_fwd_dependent(const float* x, const float* gamma, const float* beta, void* y, float* mean,
+                               float* rstd, int M, int d, float eps, int rms, cudaStream_t stream) {
+  using namespace ab;
+  if (d % 128 != 0 || d > 2048 || M <= 0) return -1;
+  int grid = (M + LN_WARPS - 1) / LN_WARPS;
+  if (grid > 148 * 8) grid = 148 * 8;
+  if (d <= 1024) return launch_ln_dependent<8>(grid, x, gamma, beta, y, mean, rstd, M, d, eps, rms, stream);
+  return launch_ln_dependent<16>(grid, x, gamma, beta, y, mean, rstd, M, d, eps, rms, stream);
+}
+
 int ab_layernorm_fwd(const float* x, const float* gamma, const float* beta, void* y, float* mean,
                      float* rstd, int M, int d, float eps, int rms, cudaStream_t stream) {
   using namespace ab;

@@ -120,6 +120,20 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+// ---------------------------------------------- programmatic dependent launch ---
+// A kernel launched with the programmatic-stream-serialization attribute may start while the
+// kernel before it in the stream is still running (once that kernel has executed
+// griddep_launch_dependents in every CTA, or has exited).  It must call griddep_wait before it
+// touches anything the earlier kernel produces or still reads; what it does before that (barrier
+// set-up, TMEM allocation, prefetch of weights) overlaps the earlier kernel.  Both instructions
+// are no-ops in a kernel launched the ordinary way.
+__device__ __forceinline__ void griddep_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void griddep_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // ------------------------------------------------------------------- TMA ---
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");

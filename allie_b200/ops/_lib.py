@@ -58,7 +58,7 @@ class GemmEpilogue(ctypes.Structure):
         ("bias", c_void_p), ("act", c_int), ("aux", c_void_p), ("ldaux", c_longlong),
         ("resid", c_void_p), ("ldr", c_longlong),
         ("drop_seed", c_ulonglong), ("drop_stream", c_uint), ("drop_thr16", c_uint),
-        ("alpha", c_float), ("m_limit", c_void_p), ("k_limit", c_void_p),
+        ("alpha", c_float), ("m_limit", c_void_p), ("k_limit", c_void_p), ("pdl", c_int),
     ]
 
 

@@ -59,7 +59,10 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
          aux: torch.Tensor | None = None, resid: torch.Tensor | None = None,
          drop_p: float = 0.0, drop_seed: int = 0, drop_stream: int = 0,
          alpha: float = 1.0, k_splits: int | None = None, m_limit: torch.Tensor | None = None,
-         k_limit: torch.Tensor | None = None) -> torch.Tensor:
+         k_limit: torch.Tensor | None = None, dependent: bool = False) -> torch.Tensor:
+    """``dependent``: launch as a programmatic dependent of the previous kernel in the stream
+    (honoured by the small-M kernel): its set-up and first weight tiles overlap that kernel.  ``b``
+    must then be data the previous kernel does not write (weights)."""
     assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
     assert a.dim() == 2 and b.dim() == 2 and a.stride(1) == 1 and b.stride(1) == 1
     if a_mn:
@@ -115,6 +118,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         ep.m_limit = m_limit.data_ptr()
     if k_limit is not None:      # int32 device scalar: contraction length actually present
         ep.k_limit = k_limit.data_ptr()
+    ep.pdl = int(dependent)
     rc = _lib.cuda().ab_gemm_bf16(
         _lib.ptr(a), c_int(int(a_mn)), c_longlong(a.stride(0)),
         _lib.ptr(b), c_int(int(b_mn)), c_longlong(b.stride(0)),

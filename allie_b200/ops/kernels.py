@@ -18,11 +18,13 @@ def _ck(rc: int, name: str) -> None:
 
 
 # ------------------------------------------------------------------ norms ---
-def layernorm_fwd(x, gamma, beta, y, mean, rstd, eps: float, rms: bool = False) -> None:
+def layernorm_fwd(x, gamma, beta, y, mean, rstd, eps: float, rms: bool = False, dependent: bool = False) -> None:
+    """``dependent``: launch as a programmatic dependent of the previous kernel in the stream (the
+    launch overlaps that kernel's tail; the kernel waits for it before it reads ``x``)."""
     M, d = x.shape
-    _ck(_lib.cuda().ab_layernorm_fwd(ptr(x), ptr(gamma), ptr(beta), ptr(y), ptr(mean), ptr(rstd),
-                                     c_int(M), c_int(d), c_float(eps), c_int(int(rms)), stream_ptr()),
-        "ab_layernorm_fwd")
+    fn = _lib.cuda().ab_layernorm_fwd_dependent if dependent else _lib.cuda().ab_layernorm_fwd
+    _ck(fn(ptr(x), ptr(gamma), ptr(beta), ptr(y), ptr(mean), ptr(rstd),
+           c_int(M), c_int(d), c_float(eps), c_int(int(rms)), stream_ptr()), "ab_layernorm_fwd")
 
 
 def layernorm_bwd(dy, x, mean, rstd, gamma, dres_in, dx, dbranch, dgamma, dbeta, *, s0=None, w0=None,

@@ -10,6 +10,7 @@ The step is a fixed sequence of kernels over static buffers and is replayed as a
 """
 from __future__ import annotations
 
+import os
 from ctypes import c_float, c_int, c_longlong
 
 import numpy as np
@@ -106,23 +107,31 @@ class KVLeafEvaluator:
                     self.x[0], V, 0, 0, 0.0)
         x = self.x[0]
         scale = 1.0 / cfg.head_dim ** 0.5
+        # the kernels of the step are programmatic dependents of the kernel before them: a GEMM's
+        # set-up and first ring of weight tiles, the attention kernel's prompt-slot chunks and every
+        # launch overlap the previous kernel (ALLIE_DECODE_PDL=0 turns it off)
+        pdl = os.environ.get("ALLIE_DECODE_PDL", "1") != "0"
         for l, Ly in enumerate(eng.layers):
-            K.layernorm_fwd(x, Ly["ln1_w"][0], Ly["ln1_b"][0], self.ln, self.stat[0], self.stat[1], eps, eng.rms)
-            gemm(self.ln, Ly["qkv_w"][1], b_mn=True, out=self.qkv, bias=Ly["qkv_b"][0])
+            K.layernorm_fwd(x, Ly["ln1_w"][0], Ly["ln1_b"][0], self.ln, self.stat[0], self.stat[1], eps, eng.rms,
+                            dependent=pdl)
+            gemm(self.ln, Ly["qkv_w"][1], b_mn=True, out=self.qkv, bias=Ly["qkv_b"][0], dependent=pdl)
             rc = lib.ab_decode_attn(ptr(self.qkv), ptr(self.kc[l]), ptr(self.vc[l]), ptr(self.view(rd, "active")),
                                     ptr(self.view(rd, "slot")), ptr(self.view(rd, "prefix_len")),
                                     ptr(self.view(rd, "anc")), c_int(self.anc_max), ptr(self.view(rd, "n_anc")),
                                     ptr(self.att), c_int(n), c_int(cfg.n_head), c_int(cfg.head_dim),
-                                    c_int(self.S), c_float(scale), stream_ptr())
+                                    c_int(self.S), c_float(scale), c_int(int(pdl)), ptr(_lib.status_word()),
+                                    stream_ptr())
             assert rc == 0
             _lib.count_launches(1)
             # residual updates in place: with a few hundred rows they run as split-K reduce-adds
-            gemm(self.att, Ly["o_w"][1], b_mn=True, out=x, bias=Ly["o_b"][0], resid=x)
-            K.layernorm_fwd(x, Ly["ln2_w"][0], Ly["ln2_b"][0], self.ln, self.stat[0], self.stat[1], eps, eng.rms)
-            gemm(self.ln, Ly["fc_w"][1], b_mn=True, out=self.act, bias=Ly["fc_b"][0], act=1, aux=self.pre)
-            gemm(self.act, Ly["pr_w"][1], b_mn=True, out=x, bias=Ly["pr_b"][0], resid=x)
-        K.layernorm_fwd(x, eng.lnf_w[0], eng.lnf_b[0], self.h, self.stat[0], self.stat[1], eps, eng.rms)
-        gemm(self.h, eng.wte[1], b_mn=False, out=self.logits)
+            gemm(self.att, Ly["o_w"][1], b_mn=True, out=x, bias=Ly["o_b"][0], resid=x, dependent=pdl)
+            K.layernorm_fwd(x, Ly["ln2_w"][0], Ly["ln2_b"][0], self.ln, self.stat[0], self.stat[1], eps, eng.rms,
+                            dependent=pdl)
+            gemm(self.ln, Ly["fc_w"][1], b_mn=True, out=self.act, bias=Ly["fc_b"][0], act=1, aux=self.pre, dependent=pdl)
+            gemm(self.act, Ly["pr_w"][1], b_mn=True, out=x, bias=Ly["pr_b"][0], resid=x, dependent=pdl)
+        K.layernorm_fwd(x, eng.lnf_w[0], eng.lnf_b[0], self.h, self.stat[0], self.stat[1], eps, eng.rms,
+                        dependent=pdl)
+        gemm(self.h, eng.wte[1], b_mn=False, out=self.logits, dependent=pdl)
         has_heads = eng.reg is not None
         if has_heads:
             K.heads_fwd(self.h, eng.wv[0], eng.bv[0], eng.wt[0], eng.bt[0], None, None, eng.counts, 0.0, 0.0,
