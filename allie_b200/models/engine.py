@@ -6,8 +6,8 @@ state-dict names), moves every parameter into one flat fp32 arena (with matching
 gradients, Adam moments and the bf16 shadow copy the tensor cores read), and then executes
 
     forward  : unpack -> embed -> L x [LN, QKV GEMM, attention, proj GEMM(+bias+dropout+residual),
-               LN, fc GEMM(+bias+GELU), proj GEMM(+bias+dropout+residual)] -> LN -> lm_head GEMM
-               -> fused cross-entropy (loss and d logits in one pass) -> fused value/time heads
+               LN, fc GEMM(+bias+GELU), proj GEMM(+bias+dropout+residual)] -> LN -> fused lm_head
+               GEMM + cross-entropy (loss and d logits, logits never stored) -> fused value/time heads
     backward : hand-scheduled mirror image; weight gradients are accumulated in fp32 straight into
                the gradient arena by the GEMM epilogue (split-K with vector atomics)
     step     : global-norm clip + AdamW + bf16 refresh over the flat arenas (two launches)
@@ -426,11 +426,18 @@ class B200Engine:
                  resid=buf["xmid"][l], drop_p=p_res, drop_seed=seed, drop_stream=2 + 3 * l)
         nl = cfg.n_layer
         K.layernorm_fwd(x[nl], self.lnf_w[0], self.lnf_b[0], buf["h"], buf["meanf"], buf["rstdf"], eps, self.rms)
-        gemm(buf["h"], self.wte[1], b_mn=False, out=buf["logits"])
-        if compute_loss:
+        lm_coef = self.reg.lm_loss_coef if self.reg is not None else 1.0
+        if compute_loss and write_grad:
+            # training: output-embedding GEMM, softmax cross entropy and d logits in one kernel;
+            # buf["logits"] receives the gradient, the logits themselves are never stored
             self.loss_acc.zero_()
-            lm_coef = self.reg.lm_loss_coef if self.reg is not None else 1.0
-            K.ce_fwd_bwd(buf["logits"], buf["labels"], self.counts[0:1], lm_coef, self.loss_acc[0:1], write_grad)
+            K.lmhead_ce(buf["h"], self.wte[1], buf["labels"], self.counts[0:1], lm_coef, buf["logits"],
+                        self.loss_acc[0:1])
+        else:
+            gemm(buf["h"], self.wte[1], b_mn=False, out=buf["logits"])
+            if compute_loss:
+                self.loss_acc.zero_()
+                K.ce_fwd_bwd(buf["logits"], buf["labels"], self.counts[0:1], lm_coef, self.loss_acc[0:1], write_grad)
         if self.reg is not None:
             vc = self.reg.value_loss_coef
             K.heads_fwd(buf["h"], self.wv[0], self.bv[0], self.wt[0], self.bt[0],

@@ -75,6 +75,21 @@ def ce_fwd_bwd(logits, labels, n_valid, coef: float, loss_acc, write_grad: bool 
                                   c_int(int(write_grad)), stream_ptr()), "ab_ce_fwd_bwd")
 
 
+def lmhead_ce(h, wte, labels, n_valid, coef: float, dlogits, loss_acc) -> None:
+    """Fused output-embedding GEMM + cross entropy (``csrc/lmhead_ce.cu``): ``loss_acc[0]`` += the summed
+    negative log likelihood of the labelled rows, ``dlogits`` [M, V] bf16 = d loss / d logits (mean over
+    ``n_valid`` rows, times ``coef``); the logits are never stored."""
+    from .gemm import num_sms
+
+    M, K = h.shape
+    V = wte.shape[0]
+    assert h.dtype == wte.dtype == dlogits.dtype and dlogits.shape == (M, V) and wte.shape[1] == K
+    _ck(_lib.cuda().ab_lmhead_ce(ptr(h), c_longlong(h.stride(0)), ptr(wte), c_longlong(wte.stride(0)), ptr(labels),
+                                 ptr(n_valid), c_float(coef), ptr(dlogits), c_longlong(dlogits.stride(0)),
+                                 ptr(loss_acc), c_int(M), c_int(V), c_int(K), c_int(num_sms()),
+                                 ptr(_lib.status_word()), stream_ptr()), "ab_lmhead_ce")
+
+
 def heads_fwd(h, wv, bv, wt, bt, value_labels, time_labels, counts, value_coef: float,
               time_coef: float, value_out, time_out, dv, dt, acc) -> None:
     M, d = h.shape

@@ -179,3 +179,34 @@ def test_cast_to_bf16():
     K.cast_bf16(src, dst)
     _done()
     assert torch.equal(dst, src.bfloat16())
+
+
+@pytest.mark.parametrize("M,V,K", [(1000, 2048, 256), (384, 1000, 128), (128 * 150 + 7, 2048, 1024)])
+def test_fused_lmhead_cross_entropy_matches_fp32(M, V, K):
+    """Fused output-embedding GEMM + cross entropy: summed loss and d logits against plain PyTorch
+    fp32 on the same bf16 operands; ragged row count, ignored rows, a vocabulary that is not a
+    multiple of the 256-column tile, more row tiles than SMs (second unit per CTA)."""
+    import torch.nn.functional as F
+
+    from allie_b200.ops import _lib, kernels as K_
+
+    torch.manual_seed(M + V)
+    h = (torch.randn(M, K, device="cuda") * 1.0).bfloat16()
+    wte = (torch.randn(V, K, device="cuda") * 0.08).bfloat16()
+    labels = torch.randint(0, V, (M,), device="cuda", dtype=torch.int32)
+    labels[torch.rand(M, device="cuda") < 0.2] = -100
+    n_valid = (labels >= 0).sum().to(torch.int32).reshape(1)
+    coef = 0.7
+    dlogits = torch.full((M, V), 3.0, device="cuda", dtype=torch.bfloat16)
+    loss = torch.zeros(1, device="cuda")
+    K_.lmhead_ce(h, wte, labels, n_valid, coef, dlogits, loss)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    logits = (h.float() @ wte.float().t()).requires_grad_(True)
+    ref = F.cross_entropy(logits, labels.long(), ignore_index=-100, reduction="sum")
+    (ref * coef / int(n_valid)).backward()
+    assert abs(loss.item() - ref.item()) < 2e-3 * ref.item()
+    g = logits.grad
+    err = (dlogits.float() - g).abs().max().item()
+    assert err < 0.02 * g.abs().max().item() + 1e-7, (err, g.abs().max().item())
+    assert (dlogits[labels < 0].float() == 0).all()
