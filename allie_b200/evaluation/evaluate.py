@@ -202,6 +202,9 @@ def main(argv: list[str] | None = None) -> dict:
     ap.add_argument("--device", default=None)
     ap.add_argument("--sequential", action="store_true",
                     help="score one position per call like the reference, even where a batched form exists")
+    ap.add_argument("--precision", default=None, choices=["float32", "bfloat16"],
+                    help="float32: the plain PyTorch model in fp32 / TF32 on the device (what the reference's CLI always "
+                         "uses; comparable with it weight for weight); bfloat16 / default: the sm_100a engine on a CUDA device")
     ap.add_argument("--batch_size", type=int, default=256,
                     help="positions per call for the strategies that score many games at once")
     args = ap.parse_args(argv)
@@ -237,7 +240,7 @@ def main(argv: list[str] | None = None) -> dict:
     if not args.sequential and f"{args.decode}-batched" in DECODE_STRATEGIES:
         implementation = f"{args.decode}-batched"
     strategy = DECODE_STRATEGIES[implementation](model, tokenizer, sample=args.sample, device=args.device,
-                                                 precision="float32", **decode_args)
+                                                 precision=args.precision, **decode_args)
     rows = read_jsonl(args.dataset, 5 if args.debug else args.n_rows)
     mine = rows[rank::world]                       # under torchrun every rank scores every world-th game
     eval_fn, summarize = ((evaluate_quick, summarize_quick) if args.quick else

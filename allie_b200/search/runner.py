@@ -87,7 +87,25 @@ class EngineRunner(ModelRunner):
         return Evaluation(host[:, :V], host[:, V], host[:, V + 1])
 
 
-def make_runner(model, tokenizer: UCITokenizer, device: str) -> ModelRunner:
+PRECISIONS = (None, "float32", "bfloat16")
+
+
+def make_runner(model, tokenizer: UCITokenizer, device: str, precision: str | None = None) -> ModelRunner:
+    """Who evaluates positions.  On a CUDA device: ``precision`` None or ``"bfloat16"`` -> the
+    sm_100a engine (bf16 tensor-core math, fp32 accumulation and residual stream); ``"float32"`` ->
+    the plain PyTorch model in fp32 on the GPU with TF32 matrix multiplications, which is how the
+    reference's evaluation CLI runs its model (``src/evaluation/evaluate.py:249``,
+    ``src/evaluation/decode.py:58-81``), for numbers that are comparable with it weight for weight.
+    On the CPU everything is fp32."""
+    if precision not in PRECISIONS:
+        raise ValueError(f"precision must be one of 'float32', 'bfloat16' (or None for the device's default), not {precision!r}")
     if str(device).startswith("cuda") and torch.cuda.is_available():
+        if precision == "float32":
+            torch.backends.cuda.matmul.allow_tf32 = True
+            torch.backends.cudnn.allow_tf32 = True
+            if getattr(model, "_b200_engine", None) is not None:
+                raise ValueError("this model's parameters already live in an engine's bf16 / fp32 arenas; build the "
+                                 "float32 strategy on its own copy of the model")
+            return TorchRunner(model.float().to(device), tokenizer, device)
         return EngineRunner(model, tokenizer, device)
     return TorchRunner(model, tokenizer, "cpu")

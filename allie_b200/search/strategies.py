@@ -53,14 +53,17 @@ class ScoreResult:
 
 class DecodeStrategy(ABC):
     def __init__(self, model, tokenizer: UCITokenizer, sample: bool | str = False,
-                 device: Optional[str] = None, precision: str = "float32", runner: ModelRunner | None = None,
+                 device: Optional[str] = None, precision: str | None = None, runner: ModelRunner | None = None,
                  **kwargs: Any):
+        """``precision``: ``"float32"`` (what the reference's evaluation passes) runs the plain
+        PyTorch model in fp32 / TF32, on the GPU too; ``"bfloat16"`` or None runs the sm_100a engine
+        on a CUDA device (see :func:`allie_b200.search.runner.make_runner`)."""
         self.model = model
         self.tokenizer = tokenizer
         self.sample = sample
         self.device = device or ("cuda" if torch.cuda.is_available() else "cpu")
         self.precision = precision
-        self.runner = runner if runner is not None else make_runner(model, tokenizer, self.device)
+        self.runner = runner if runner is not None else make_runner(model, tokenizer, self.device, precision)
         self.init(**kwargs)
         self.check()
 

@@ -95,3 +95,23 @@ def test_adaptive_budget_and_kl(setup):
     pi = kl_regularized_policy(pri, q, n, 1.25)
     assert abs(float(pi.sum()) - 1) < 1e-6 and int(pi.argmax()) == 1
     assert set(DECODE_STRATEGIES) >= {"policy", "mcts", "adaptive-mcts"}
+
+
+def test_precision_argument_is_checked_and_cpu_stays_fp32():
+    """``precision`` is the reference's constructor argument: unknown values are refused, and on the
+    CPU both accepted values run the fp32 PyTorch model."""
+    import pytest
+
+    from allie_b200.data import UCITokenizer
+    from allie_b200.models import initialize_model
+    from allie_b200.search import DECODE_STRATEGIES
+    from allie_b200.search.runner import TorchRunner
+
+    tok = UCITokenizer(max_length=64, vocab_size_multiple_of=128)
+    model = initialize_model(tok, "gpt2", use_control_token=True, use_regression_head=True, n_layer=1, n_embd=32,
+                             n_head=1, n_positions=64).eval()
+    for prec in (None, "float32", "bfloat16"):
+        s = DECODE_STRATEGIES["policy"](model, tok, device="cpu", precision=prec)
+        assert isinstance(s.runner, TorchRunner) and next(model.parameters()).dtype == torch.float32
+    with pytest.raises(ValueError, match="precision"):
+        DECODE_STRATEGIES["policy"](model, tok, device="cpu", precision="float16")

@@ -41,3 +41,30 @@ def test_batched_strategies_on_engine():
     assert all(r.move in g.legal_moves for r, g in zip(res, games))
     torch.cuda.synchronize()
     _lib.check_status()
+
+
+def test_float32_precision_runs_the_plain_model_on_the_gpu_and_agrees_with_the_engine():
+    """``precision="float32"`` (what the reference's evaluation passes) selects the plain PyTorch
+    model in fp32 / TF32 on the GPU; the bf16 engine on the same weights gives the same move
+    distribution to within bf16 rounding."""
+    import copy
+
+    from allie_b200.data import Game, UCITokenizer
+    from allie_b200.models import initialize_model
+    from allie_b200.search import MCTS, Policy
+
+    torch.manual_seed(0)
+    tok = UCITokenizer(max_length=128, vocab_size_multiple_of=128)
+    model = initialize_model(tok, "gpt2", use_control_token=True, use_regression_head=True, n_layer=2,
+                             n_embd=256, n_head=4, n_positions=128).eval()
+    exact = Policy(copy.deepcopy(model), tok, device="cuda", precision="float32")
+    engine = Policy(model, tok, device="cuda", precision="bfloat16")
+    assert type(exact.runner).__name__ == "TorchRunner" and str(exact.runner.device).startswith("cuda")
+    assert next(exact.runner.model.parameters()).dtype == torch.float32
+    assert type(engine.runner).__name__ == "EngineRunner"
+    g = Game("180+0", 1500, 1600, None, False, ["e2e4", "e7e5", "g1f3", "b8c6"], [1, 2, 3, 4])
+    a, b = exact.score_full(g, g.legal_moves), engine.score_full(g, g.legal_moves)
+    assert torch.allclose(a.legal_move_probabilities, b.legal_move_probabilities, atol=2e-2)
+    assert abs(a.white_advantage - b.white_advantage) < 2e-2
+    search = MCTS(copy.deepcopy(model), tok, device="cuda", precision="float32", n_sims=8)
+    assert search.decode_full(g).move in g.legal_moves
