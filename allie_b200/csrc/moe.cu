@@ -217,7 +217,12 @@ __global__ void __launch_bounds__(256) moe_route_plan_dispatch_kernel(const RpdA
   }
   __syncthreads();
   if (!s_go) return;
-  // ---- (c) dispatch: one warp per (token, choice)
+  // ---- (c) dispatch: one warp per (token, choice).  A warp first stores all of its rows (lane i
+  // remembers the arrival counter of the i-th), then ONE system-scope fence per thread orders every
+  // store of the warp before the counter increments that follow: a fence per row would cost more
+  // than the row itself.
+  unsigned int* my_ctr = nullptr;
+  int n_mine = 0;
   for (int slot = warp_g; slot < a.M * MOE_K; slot += n_warps) {
     const int e = a.topi[slot];
     const int r = e / a.El, le = e % a.El;
@@ -238,11 +243,19 @@ __global__ void __launch_bounds__(256) moe_route_plan_dispatch_kernel(const RpdA
       static_cast<int*>(a.ret.ptr[r])[row] = (a.rank << 24) | slot;
       a.dest[slot] = (r << 24) | row;
     }
-    // the row is complete: every lane's stores are ordered before the counter increment
-    __threadfence_system();
-    __syncwarp();
-    if (lane == 0) red_release_sys_add(static_cast<unsigned int*>(a.ready_fwd.ptr[r]) + row / 128, 1u);
+    unsigned int* ctr = static_cast<unsigned int*>(a.ready_fwd.ptr[r]) + row / 128;
+    if (n_mine == 32) {              // more than 32 rows per warp: flush what has been collected
+      __threadfence_system();
+      __syncwarp();
+      red_release_sys_add(my_ctr, 1u);
+      n_mine = 0;
+    }
+    if (lane == n_mine) my_ctr = ctr;
+    ++n_mine;
   }
+  __threadfence_system();
+  __syncwarp();
+  if (lane < n_mine) red_release_sys_add(my_ctr, 1u);
 }
 
 // out[t] = resid[t] + dropout(sum_k gate_k * comb[2t+k]); one warp per token
@@ -313,8 +326,12 @@ __global__ void __launch_bounds__(256) moe_combine_bwd_dispatch_kernel(const Bwd
     for (long long i = blockIdx.x * 256ll + threadIdx.x; i < n8; i += gridDim.x * 256ll)
       base[i] = make_uint4(0, 0, 0, 0);
   }
-  const int slot = blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (slot < a.M * MOE_K) {
+  // one warp per (token, choice), warp-stride; the arrival counters are incremented after ONE
+  // system-scope fence per thread at the end (see the forward dispatch)
+  const int warp_g = blockIdx.x * 8 + (threadIdx.x >> 5), n_warps = gridDim.x * 8;
+  unsigned int* my_ctr = nullptr;
+  int n_mine = 0;
+  for (int slot = warp_g; slot < a.M * MOE_K; slot += n_warps) {
     const int de = a.dest[slot];
     float dot = 0.f;
     if (de >= 0) {
@@ -340,12 +357,19 @@ __global__ void __launch_bounds__(256) moe_combine_bwd_dispatch_kernel(const Bwd
     for (int o = 16; o; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
     if (lane == 0) a.dgate[slot] = dot;
     if (de >= 0) {
-      __threadfence_system();
-      __syncwarp();
-      if (lane == 0)
-        red_release_sys_add(static_cast<unsigned int*>(a.ready_bwd.ptr[de >> 24]) + (de & 0xffffff) / 128, 1u);
+      if (n_mine == 32) {
+        __threadfence_system();
+        __syncwarp();
+        red_release_sys_add(my_ctr, 1u);
+        n_mine = 0;
+      }
+      if (lane == n_mine) my_ctr = static_cast<unsigned int*>(a.ready_bwd.ptr[de >> 24]) + (de & 0xffffff) / 128;
+      ++n_mine;
     }
   }
+  __threadfence_system();
+  __syncwarp();
+  if (lane < n_mine) red_release_sys_add(my_ctr, 1u);
 }
 
 // d logits of the router from the gate gradients and the load-balance term; one warp per token.
@@ -471,7 +495,9 @@ int ab_moe_combine_bwd_dispatch(void* const* dyr, void* const* ready_bwd, void* 
   a.cap_e = cap_e;
   a.dy = (const __nv_bfloat16*)dy; a.comb = (const __nv_bfloat16*)comb; a.gates = gates; a.dest = dest;
   a.dgate = dgate; a.M = M; a.d = d; a.rank = rank; a.R = R;
-  ab::moe_combine_bwd_dispatch_kernel<<<(M * 2 + 7) / 8, 256, 0, stream>>>(a);
+  int grid = (M * 2 + 7) / 8;
+  if (grid > 148 * 8) grid = 148 * 8;
+  ab::moe_combine_bwd_dispatch_kernel<<<grid, 256, 0, stream>>>(a);
   return (int)cudaGetLastError();
 }
 

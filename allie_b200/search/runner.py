@@ -103,9 +103,10 @@ def make_runner(model, tokenizer: UCITokenizer, device: str, precision: str | No
         if precision == "float32":
             torch.backends.cuda.matmul.allow_tf32 = True
             torch.backends.cudnn.allow_tf32 = True
-            if getattr(model, "_b200_engine", None) is not None:
-                raise ValueError("this model's parameters already live in an engine's bf16 / fp32 arenas; build the "
-                                 "float32 strategy on its own copy of the model")
-            return TorchRunner(model.float().to(device), tokenizer, device)
+            # a model whose parameters already live in an engine's arenas keeps them there: they are
+            # ordinary fp32 tensors on the device (views of the master arena), shared with the engine
+            if getattr(model, "_b200_engine", None) is None:
+                model = model.float().to(device)
+            return TorchRunner(model, tokenizer, device)
         return EngineRunner(model, tokenizer, device)
     return TorchRunner(model, tokenizer, "cpu")
