@@ -8,6 +8,7 @@
 """
 from __future__ import annotations
 
+import weakref
 from dataclasses import dataclass
 
 import torch
@@ -21,6 +22,20 @@ class Evaluation:
     logits: torch.Tensor      # [n, vocab] float32, host
     value: torch.Tensor       # [n] float32 (white advantage, tanh range), host
     time: torch.Tensor        # [n] float32 (normalised think time), host
+
+
+# model -> the engine that runs it (one engine per model: its parameters live in the engine's arenas).
+# Kept beside the model, not as an attribute of it, so copying or pickling a model never drags the
+# engine (arenas, streams, buffers) along.
+_ENGINES: "weakref.WeakKeyDictionary" = weakref.WeakKeyDictionary()
+
+
+def engine_of(model):
+    return _ENGINES.get(model)
+
+
+def attach_engine(model, engine) -> None:
+    _ENGINES[model] = engine
 
 
 class ModelRunner:
@@ -60,10 +75,10 @@ class EngineRunner(ModelRunner):
         from ..models.engine import B200Engine
 
         self.tokenizer = tokenizer
-        eng = getattr(model, "_b200_engine", None)
+        eng = engine_of(model)
         if eng is None:
             eng = B200Engine(model, device)
-            model._b200_engine = eng
+            attach_engine(model, eng)
         self.engine = eng
         self.has_value_head = eng.reg is not None
         self.calls = 0
@@ -105,7 +120,7 @@ def make_runner(model, tokenizer: UCITokenizer, device: str, precision: str | No
             torch.backends.cudnn.allow_tf32 = True
             # a model whose parameters already live in an engine's arenas keeps them there: they are
             # ordinary fp32 tensors on the device (views of the master arena), shared with the engine
-            if getattr(model, "_b200_engine", None) is None:
+            if engine_of(model) is None:
                 model = model.float().to(device)
             return TorchRunner(model, tokenizer, device)
         return EngineRunner(model, tokenizer, device)

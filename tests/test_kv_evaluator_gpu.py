@@ -23,7 +23,9 @@ def test_kv_cached_leaf_matches_full_reencode():
         for p in model.parameters():
             p.mul_(1.5)
     eng = B200Engine(model, "cuda")
-    model._b200_engine = eng
+    from allie_b200.search.runner import attach_engine
+
+    attach_engine(model, eng)
     games = [Game("180+0", 1500, 1600, None, False, mv, [1] * len(mv)) for mv in
              (["e2e4", "e7e5", "g1f3"], ["d2d4", "d7d5", "c2c4", "e7e6", "b1c3", "g8f6"], [], ["f2f3", "e7e5", "g2g4"])]
     n = 4
