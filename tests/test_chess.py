@@ -78,3 +78,37 @@ def test_game_board_and_legal_moves():
     assert len(g.legal_moves) == 29
     g2 = g.make_move("g1f3")
     assert g2.moves[-1] == "g1f3" and g2.moves_seconds[-1] == 0 and len(g.moves) == 2
+
+
+def test_legal_move_order_follows_python_chess_generation_order():
+    """Golden move orders, written down by hand from python-chess's generation algorithm (not
+    produced by this repository's generator): pieces other than pawns from the highest square to the
+    lowest, each with its targets from the highest square to the lowest; then castling; then pawn
+    captures (promotions as q, r, b, n), single pushes, double pushes, en passant; in check, king
+    moves first and then the moves that capture or block the checker.  The search takes the FIRST
+    best child and indexes its priors in this order, so the order is part of the behaviour."""
+    from allie_b200.chess import Board
+
+    cases = {
+        # rook and king moves, castling, a promotion push
+        "4k3/P7/8/8/8/8/8/4K2R w K - 0 1":
+            "h1h8 h1h7 h1h6 h1h5 h1h4 h1h3 h1h2 h1g1 h1f1 e1f2 e1e2 e1d2 e1f1 e1d1 e1g1 a7a8q a7a8r a7a8b a7a8n",
+        # black to move with an en-passant capture available (generated last)
+        "4k3/8/8/8/3pP3/8/8/4K3 b - e3 0 1": "e8f8 e8d8 e8f7 e8e7 e8d7 d4d3 d4e3",
+        # in check from a rook on the king's file: only king moves off the file (the bishop's way to
+        # the blocking square is shut by its own pawn)
+        "4r1k1/8/8/8/8/8/3P4/2B1K3 w - - 0 1": "e1f2 e1f1 e1d1",
+        # king steps around a knight's attacks; capture-promotions before the plain capture, then
+        # push-promotions, single and double pushes
+        "1r2k3/P7/8/8/8/2n5/1P6/4K3 w - - 0 1":
+            "e1f2 e1d2 e1f1 a7b8q a7b8r a7b8b a7b8n b2c3 a7a8q a7a8r a7a8b a7a8n b2b3 b2b4",
+    }
+    for fen, want in cases.items():
+        assert Board(fen).legal_moves_uci() == want.split(), fen
+    # a middlegame position (Ruy Lopez after 3.Bb5, black to move)
+    b = Board()
+    for m in "e2e4 e7e5 g1f3 b8c6 f1b5".split():
+        b.push_uci(m)
+    assert b.legal_moves_uci() == (
+        "g8e7 g8h6 g8f6 f8e7 f8d6 f8c5 f8b4 f8a3 e8e7 d8e7 d8f6 d8g5 d8h4 a8b8 c6b8 c6e7 c6a5 c6d4 c6b4 "
+        "h7h6 g7g6 f7f6 d7d6 b7b6 a7a6 h7h5 g7g5 f7f5 d7d5 a7a5").split()
