@@ -21,7 +21,7 @@ import torch.nn.functional as F
 from ..data import Game, UCITokenizer, undo_time_normalization
 from ..moves import CHESS_MOVES
 from ..ops import _lib
-from .strategies import kl_regularized_policy
+from .strategies import kl_regularized_policy_np
 
 _cfg_done = False
 
@@ -248,7 +248,7 @@ class BatchedMCTS:
             lg = logits[t]
             ids = torch.from_numpy(root_legal[t].astype(np.int64))
             raw_value = float(value[t])
-            pov = 1 if g.board.turn else -1
+            pov = 1 if self.lib.mcts_root_turn(self.h, t) else -1     # the search already replayed the game
             resigned = bool(nc > 0 and float(lg[self.tok.resigned_token_id]) > float(lg[ids].max())
                             and pov * raw_value < -0.9)
             if nc == 0:
@@ -258,8 +258,7 @@ class BatchedMCTS:
             elif not self.kl:
                 policy = torch.from_numpy(visits.astype(np.float32) / visits.sum())
             else:
-                policy = kl_regularized_policy(torch.from_numpy(priors), torch.from_numpy(values),
-                                               torch.from_numpy(visits.astype(np.float32)), float(cp[t]))
+                policy = torch.from_numpy(kl_regularized_policy_np(priors, values, visits, float(cp[t])))
             results.append(SearchResult(legal, visits, priors, values, policy,
                                         undo_time_normalization(float(time[t])), resigned, raw_value, done))
         return results
