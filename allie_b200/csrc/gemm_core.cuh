@@ -48,6 +48,9 @@ __device__ __forceinline__ void epilogue_math8(const GemmArgs& g, float* v, uint
     pre.z = pack_bf16x2(v[4], v[5]); pre.w = pack_bf16x2(v[6], v[7]);
 #pragma unroll
     for (int j = 0; j < 8; ++j) v[j] = gelu_tanh(v[j]);
+  } else if (ep.act == 3) {        // GELU without keeping the pre-activation (inference)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = gelu_tanh(v[j]);
   } else if (ep.act == 2) {
     const uint4 q = *reinterpret_cast<const uint4*>(
         static_cast<const __nv_bfloat16*>(ep.aux) + (long long)m * ep.ldaux + n);

@@ -10,6 +10,7 @@ extern "C" {
 //   v += bias[n]
 //   act == 1:  aux[m][n] = bf16(v); v = gelu_new(v)
 //   act == 2:  v *= gelu_new'(aux[m][n])
+//   act == 3:  v = gelu_new(v)            (no pre-activation kept: inference)
 //   resid != null:  v = resid[m][n] + dropout(v)   (dropout only when drop_thr16 > 0)
 //   out_fp32 ? (accumulate ? out[m][n] += v (atomic) : out[m][n] = v) : out[m][n] = bf16(v)
 struct AbGemmEpilogue {

@@ -358,7 +358,7 @@ class B200Engine:
             buf["x"] = [x0 if i % 2 == 0 else x1 for i in range(nl + 1)]
             xm = e(M, d, dt=f32)
             buf["xmid"] = [xm] * nl
-            shared = {n: e(M, w) for n, w in (("ln1", d), ("qkv", 3 * d), ("attn", d), ("ln2", d), ("pre", F), ("act", F))}
+            shared = {n: e(M, w) for n, w in (("ln1", d), ("qkv", 3 * d), ("attn", d), ("ln2", d), ("act", F))}
             for n, t in shared.items():
                 buf[n] = [t] * nl
             for name in ("mean1", "rstd1", "mean2", "rstd2"):
@@ -420,8 +420,11 @@ class B200Engine:
             if L["moe"]:
                 self._moe(l, B * T, train).forward(buf["ln2"][l], buf["xmid"][l], x[l + 1], seed, 2 + 3 * l, p_res)
                 continue
-            gemm(buf["ln2"][l], L["fc_w"][1], b_mn=True, out=buf["act"][l], bias=L["fc_b"][0], act=1,
-                 aux=buf["pre"][l])
+            if train:
+                gemm(buf["ln2"][l], L["fc_w"][1], b_mn=True, out=buf["act"][l], bias=L["fc_b"][0], act=1,
+                     aux=buf["pre"][l])
+            else:       # inference: nothing needs the pre-activation
+                gemm(buf["ln2"][l], L["fc_w"][1], b_mn=True, out=buf["act"][l], bias=L["fc_b"][0], act=3)
             gemm(buf["act"][l], L["pr_w"][1], b_mn=True, out=x[l + 1], bias=L["pr_b"][0],
                  resid=buf["xmid"][l], drop_p=p_res, drop_seed=seed, drop_stream=2 + 3 * l)
         nl = cfg.n_layer

@@ -101,8 +101,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     if bias is not None:
         assert bias.dtype == torch.float32 and bias.numel() == N
         ep.bias = bias.data_ptr()
-    ep.act = act
-    if act:
+    ep.act = act            # 1: GELU, pre-activation saved in aux; 2: times GELU'(aux); 3: GELU, nothing saved
+    if act in (1, 2):
         assert aux is not None and aux.dtype == torch.bfloat16 and aux.shape == (M, N)
         ep.aux = aux.data_ptr()
         ep.ldaux = aux.stride(0)

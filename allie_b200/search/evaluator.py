@@ -48,7 +48,7 @@ class KVLeafEvaluator:
         e = lambda *s, dt=bf: torch.empty(*s, dtype=dt, device=dev)
         self.x = [e(n, d, dt=f32), e(n, d, dt=f32)]
         self.ln, self.qkv, self.att = e(n, d), e(n, 3 * d), e(n, d)
-        self.pre, self.act, self.h, self.logits = e(n, F), e(n, F), e(n, d), e(n, V)
+        self.act, self.h, self.logits = e(n, F), e(n, d), e(n, V)
         self.stat = [e(n, dt=f32) for _ in range(2)]
         self.value, self.time = e(n, dt=f32), e(n, dt=f32)
         self.resign_id = 1992
@@ -127,7 +127,7 @@ class KVLeafEvaluator:
             gemm(self.att, Ly["o_w"][1], b_mn=True, out=x, bias=Ly["o_b"][0], resid=x, dependent=pdl)
             K.layernorm_fwd(x, Ly["ln2_w"][0], Ly["ln2_b"][0], self.ln, self.stat[0], self.stat[1], eps, eng.rms,
                             dependent=pdl)
-            gemm(self.ln, Ly["fc_w"][1], b_mn=True, out=self.act, bias=Ly["fc_b"][0], act=1, aux=self.pre, dependent=pdl)
+            gemm(self.ln, Ly["fc_w"][1], b_mn=True, out=self.act, bias=Ly["fc_b"][0], act=3, dependent=pdl)
             gemm(self.act, Ly["pr_w"][1], b_mn=True, out=x, bias=Ly["pr_b"][0], resid=x, dependent=pdl)
         K.layernorm_fwd(x, eng.lnf_w[0], eng.lnf_b[0], self.h, self.stat[0], self.stat[1], eps, eng.rms,
                         dependent=pdl)
