@@ -17,8 +17,9 @@ max over ranks, inputs already resident on the GPU; ``e2e`` times the same K ste
 (host gather on its prefetch thread), the per-micro-step host->device copy of the raw windows
 from pinned memory, and a device->host read of the loss every step.
 
-After the headline the same process measures the two other headline workloads inside a time
-budget and reports them under ``secondary``: ``mcts`` (256 trees x 400 simulations per GPU,
+After the headline, rank 0 runs the two other headline workloads as jobs of their own on the same
+GPUs (the training benchmark has released them by then) inside a time budget and reports their
+results under ``secondary``: ``mcts`` (256 trees x 400 simulations per GPU,
 positions/s and per-move latency) at any N, and ``moe`` (the 9.3 B-parameter mixture-of-experts
 config, expert parallel over all ranks, tokens/s) at N = 8.  ``--impl reference`` fills the same
 object with the unmodified reference ``evaluation.decode.MCTS`` and, for the MoE config the
@@ -239,60 +240,65 @@ def grad_sync_check(world: int) -> dict:
             "note": "tiny models (4 blocks d128 / 2 blocks with 8 experts), dropout off, same windows"}
 
 
-def secondary_mcts(world: int, reference: bool, budget_s: float) -> dict:
-    """MCTS leaf evaluation: one independent search per GPU, 256 trees x 400 simulations (the
-    reference arm: its own sequential MCTS on 8 root positions per GPU, 400 simulations)."""
-    import bench_mcts
+def _run_child(script_args: list[str], world: int, timeout_s: float, port: int) -> dict:
+    """Runs one of the other benchmark scripts as its own job (``torchrun`` with ``world`` ranks, or a
+    plain process) and returns the JSON line it prints.  A process of its own means a failure
+    there (an exception, a device-side wait that ran out, a crash) cannot take the headline number
+    of this process with it."""
+    import signal
 
-    rank = dist_info()[0]
-    if budget_s < 60:
-        return {"skipped": f"time budget exhausted ({budget_s:.0f} s left)"}
-    cfg = {"model": "gpt2-medium-like 24L d1024 16H", "sims": 400, "prefix_tokens": "1-300",
-           "data": "synthetic random legal games"}
-    out = {"metric": "MCTS leaf-eval positions/sec", "unit": "positions/s", "n_gpus": world}
-    if reference:
-        out.update(bench_mcts.run_reference(400, 8, False, seed=rank), config=dict(cfg, root_positions_per_gpu=8))
+    drop = ("RANK", "WORLD_SIZE", "LOCAL_RANK", "LOCAL_WORLD_SIZE", "GROUP_RANK", "GROUP_WORLD_SIZE", "ROLE_RANK",
+            "ROLE_WORLD_SIZE", "ROLE_NAME", "MASTER_ADDR", "MASTER_PORT")
+    env = {k: v for k, v in os.environ.items() if k not in drop and not k.startswith("TORCHELASTIC_")}
+    if world > 1:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+               "--master-addr", "127.0.0.1", "--master-port", str(port), *script_args]
     else:
-        out.update(bench_mcts.run_batched(256, 400, False, seed=rank), config=dict(cfg, trees_per_gpu=256), dtype="bf16")
-    return bench_mcts.combine_over_ranks(out, world)
-
-
-def secondary_moe(world: int, reference: bool, budget_s: float, force: bool) -> dict:
-    import bench_moe
-
-    if world != 8 and not force:
-        return {"skipped": "the 9.3 B-parameter MoE config needs its experts spread over 8 GPUs"}
-    if budget_s < 120:
-        return {"skipped": f"time budget exhausted ({budget_s:.0f} s left)"}
-    if world == 8:
-        return bench_moe.run_moe("torch" if reference else "ours", steps=10, warmup=3)
-    # smoke shape for fewer GPUs (--secondary all): 6 blocks, 16 experts
-    return bench_moe.run_moe("torch" if reference else "ours", steps=5, warmup=3, layers=6, experts=16)
+        cmd = [sys.executable, *script_args]
+    proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, env=env, cwd=ROOT,
+                            start_new_session=True)
+    try:
+        out, err = proc.communicate(timeout=timeout_s)
+    except subprocess.TimeoutExpired:
+        os.killpg(proc.pid, signal.SIGKILL)       # the process group this call started, nothing else
+        proc.communicate()
+        return {"failed": f"no result within {timeout_s:.0f} s"}
+    for line in reversed(out.splitlines()):
+        line = line.strip()
+        if line.startswith("{"):
+            try:
+                return json.loads(line)
+            except json.JSONDecodeError:
+                continue
+    return {"failed": f"exit code {proc.returncode}: " + " | ".join(err.strip().splitlines()[-3:])[-300:]}
 
 
 def run_secondary(args, world: int, reference: bool, t_start: float) -> dict:
-    """The other two headline workloads, measured after the training benchmark inside what is left
-    of ``--secondary-budget`` seconds.  A failure of one of them is reported, not raised."""
-    import gc
-    import traceback
-
-    import torch
-
-    out = {}
+    """The other two headline workloads, each as a job of its own on the same GPUs, started by rank
+    0 after the training benchmark has released them, inside what is left of ``--secondary-budget``
+    seconds: MCTS leaf evaluation at every N (one independent 256-tree x 400-simulation search
+    per GPU; the reference arm: its own sequential MCTS on 8 root positions per GPU), the MoE
+    config at N = 8 (``--secondary all``: a reduced MoE shape at smaller N)."""
     if args.secondary == "none":
         return {"skipped": "--secondary none"}
-    for name, fn in (("mcts", lambda left: secondary_mcts(world, reference, left)),
-                     ("moe", lambda left: secondary_moe(world, reference, left, args.secondary == "all"))):
+    base_port = int(os.environ.get("MASTER_PORT", "29500"))
+    mcts = [os.path.join(ROOT, "bench_mcts.py"), "--gpus", str(world)]
+    mcts += ["--impl", "reference", "--seq-positions", "8"] if reference else ["--impl", "batched"]
+    moe = [os.path.join(ROOT, "bench_moe.py"), "--gpus", str(world), "--impl", "torch" if reference else "ours"]
+    if world != 8:
+        moe += ["--layers", "6", "--experts", "16", "--steps", "5"]      # reduced shape: the full one needs 8 GPUs
+    jobs = [("mcts", mcts, 60.0)]
+    if world == 8 or args.secondary == "all":
+        jobs.append(("moe", moe, 120.0))
+    out = {} if len(jobs) > 1 else {"moe": {"skipped": "the 9.3 B-parameter MoE config needs its experts spread over 8 GPUs"}}
+    for i, (name, cmd, least) in enumerate(jobs):
         left = args.secondary_budget - (time.perf_counter() - t_start)
-        try:
-            gc.collect()
-            torch.cuda.empty_cache()
-            t0 = time.perf_counter()
-            out[name] = fn(left)
-            out[name]["wall_s"] = round(time.perf_counter() - t0, 1)
-        except Exception as e:
-            traceback.print_exc(file=sys.stderr)
-            out[name] = {"failed": f"{type(e).__name__}: {e}"[:300]}
+        if left < least:
+            out[name] = {"skipped": f"time budget exhausted ({left:.0f} s left)"}
+            continue
+        t0 = time.perf_counter()
+        out[name] = _run_child(cmd, world, left, base_port + 17 + i)
+        out[name]["wall_s"] = round(time.perf_counter() - t0, 1)
     return out
 
 
@@ -424,12 +430,16 @@ def run_ours(args) -> dict:
     }
     if sync_check is not None:
         result["grad_sync_check"] = sync_check
-    # free the training state before the secondary workloads build theirs
-    trainer.sampler.close()
+    # release the GPUs (and the process group) before the secondary workloads run as their own jobs
+    trainer.cleanup()
     trainer.engine = trainer.grad_sync = trainer.model = None
     del dev_windows, host_windows, model
-    result["secondary"] = run_secondary(args, world, False, t_start)
-    trainer.cleanup()
+    import gc
+
+    gc.collect()
+    torch.cuda.empty_cache()
+    if rank == 0:
+        result["secondary"] = run_secondary(args, world, False, t_start)
     return result
 
 
@@ -522,12 +532,17 @@ def run_reference(args) -> dict:
                 "d2h_bytes_per_step": 4},
         "gpu_launches": 0,
     }
+    trainer.cleanup()
     for attr in ("model", "optimizer", "model_fn"):
         if hasattr(trainer, attr):
             setattr(trainer, attr, None)
     del model
-    result["secondary"] = run_secondary(args, world, True, t_start)
-    trainer.cleanup()
+    import gc
+
+    gc.collect()
+    torch.cuda.empty_cache()
+    if rank == 0:
+        result["secondary"] = run_secondary(args, world, True, t_start)
     return result
 
 
