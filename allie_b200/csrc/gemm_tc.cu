@@ -631,6 +631,12 @@ extern "C" int ab_gemm_bf16(const void* A, int a_mn, long long lda, const void* 
   if (max_ctas <= 0) max_ctas = 148;
   // narrow tiles also for skinny problems (decode steps with a few hundred rows): twice the CTAs
   const bool narrow = (N <= 128) || (M <= 256);
+  // A few hundred rows against a wide weight matrix (decode steps): the time goes into streaming
+  // the weights, so the columns are cut into 64-wide tiles to put twice as many SMs on them.
+  if (M <= 256 && N >= 1024 && k_splits == 1) {
+    if (!a_mn && !b_mn) return launch<64, 8, false, false>(A, lda, B, ldb, g, max_ctas, stream);
+    if (!a_mn && b_mn) return launch<64, 8, false, true>(A, lda, B, ldb, g, max_ctas, stream);
+  }
   if (narrow) {
     if (!a_mn && !b_mn) return launch<128, 6, false, false>(A, lda, B, ldb, g, max_ctas, stream);
     if (!a_mn && b_mn) return launch<128, 6, false, true>(A, lda, B, ldb, g, max_ctas, stream);
