@@ -11,6 +11,8 @@ games whose prompts are 1-300 tokens long.  Every leaf evaluation is one KV-cach
     python bench_mcts.py --impl reference      # the unmodified reference package (baseline/_ref): its own
                                                # model and MCTS strategy, python-chess replaced by a stand-in
     torchrun --nproc-per-node 8 bench_mcts.py --gpus 8   # one independent 256-tree search per GPU
+    python bench_mcts.py --ablate              # where the time of one evaluation step goes
+    ALLIE_DECODE_PDL=0 python bench_mcts.py --ablate     # the same with ordinary kernel launches
 Prints one JSON line (rank 0; with several GPUs the value is the sum of positions over the ranks
 divided by the slowest rank's time, and the p50 per-move latency is the median over ranks).
 """
@@ -145,6 +147,68 @@ def run_batched(trees: int, sims: int, small: bool, seed: int = 0) -> dict:
                 phase_seconds={k: round(v, 4) for k, v in bm.phase_seconds.items()})
 
 
+def run_ablation(trees: int, small: bool) -> dict:
+    """Where the time of one leaf-evaluation step goes: the step's CUDA graph is captured again with
+    one kind of kernel left out at a time and timed with CUDA events (50 replays each) on the
+    request left behind by a short search."""
+    import numpy as np
+    import torch
+
+    import allie_b200.search.evaluator as E
+    from allie_b200.models.engine import B200Engine
+    from allie_b200.ops import _lib, kernels as K
+    from allie_b200.search.batched import BatchedMCTS, KVStepEvaluator
+
+    tok, model = build_model(small)
+    eng = B200Engine(model, "cuda")
+    games = random_games(trees, tok, np.random.default_rng(0))
+    ev = KVStepEvaluator(eng, tok, trees, anc_max=128, legal_max=224, max_prefix=320, max_nodes=64)
+    BatchedMCTS(tok, ev, n_trees=trees, n_sims=24).search(games, n_sims=24)
+    kv = ev.kv
+    torch.cuda.synchronize()
+
+    class WithoutAttention:
+        def __init__(self, real):
+            self.real = real
+
+        def __getattr__(self, name):
+            return (lambda *a: 0) if name == "ab_decode_attn" else getattr(self.real, name)
+
+    def timed(patch: dict) -> float:
+        saved = {key: getattr(*key) for key in patch}
+        for (obj, name), fn in patch.items():
+            setattr(obj, name, fn)
+        try:
+            kv._launch_step()
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                kv._launch_step()
+        finally:
+            for (obj, name), fn in saved.items():
+                setattr(obj, name, fn)
+        for _ in range(5):
+            g.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(50):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return round(e0.elapsed_time(e1) / 50 * 1000, 1)
+
+    noop = lambda *a, **k: None
+    real_lib = _lib.cuda()
+    no_attn = {(_lib, "cuda"): lambda: WithoutAttention(real_lib)}
+    out = {"full_step_us": timed({}),
+           "without_decode_attn_us": timed(no_attn),
+           "without_layernorm_us": timed({(K, "layernorm_fwd"): noop}),
+           "without_gemms_us": timed({(E, "gemm"): noop}),
+           "gemms_only_us": timed({(K, "layernorm_fwd"): noop, **no_attn})}
+    _lib.check_status()
+    return {"metric": "leaf-evaluation step breakdown", "unit": "us per step", "trees": trees, **out}
+
+
 def run_sequential(sims: int, positions: int, small: bool, seed: int = 0) -> dict:
     """The reference algorithm restated on this framework's PyTorch model (fp32): one tree at a
     time, every leaf re-encodes its whole game at batch 1 (``src/evaluation/decode.py:336-467``)."""
@@ -206,7 +270,12 @@ def main():
     ap.add_argument("--small", action="store_true", help="tiny model (smoke test)")
     ap.add_argument("--seq-positions", type=int, default=8, help="root positions for --impl sequential / reference")
     ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--ablate", action="store_true",
+                    help="time the step's graph with one kind of kernel left out at a time (one GPU) and exit")
     args = ap.parse_args()
+    if args.ablate:
+        print(json.dumps(run_ablation(args.trees, args.small)), flush=True)
+        return
     rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
     assert world == args.gpus, "launch with torchrun --nproc-per-node <gpus>"
     if torch.cuda.is_available():
