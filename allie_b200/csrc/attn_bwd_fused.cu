@@ -749,23 +749,23 @@ int launch_attn_bwd_fused64(const CUtensorMap& tq, const CUtensorMap& td, const 
   const int mode = attn_bwd_schedule_mode();
   if (mode == 1 || (mode == 0 && a.B * a.H < 4 * 148)) {
     constexpr int SMEM = 6 * FB_TILE + 2 * FB_P + FB_MATH_WARPS * 2048 + 256;
-    static bool attr = false;
-    if (!attr) {
+    static PerDeviceOnce attr;
+    if (attr.first_use_on_device()) {
       cudaError_t e = cudaFuncSetAttribute(attn_bwd_fused64_kernel,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
       if (e != cudaSuccess) return (int)e;
-      attr = true;
+      attr.mark_device();
     }
     dim3 grid((a.T + 127) / 128, a.H, a.B);
     attn_bwd_fused64_kernel<<<grid, FB_THREADS, SMEM, stream>>>(tq, td, tdq, a);
   } else {
     constexpr int SMEM = 8 * FB_TILE + 2 * FB_P + FB_MATH_WARPS * 2048 + 256;
-    static bool attr = false;
-    if (!attr) {
+    static PerDeviceOnce attr;
+    if (attr.first_use_on_device()) {
       cudaError_t e = cudaFuncSetAttribute(attn_bwd_fused64_persistent_kernel,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
       if (e != cudaSuccess) return (int)e;
-      attr = true;
+      attr.mark_device();
     }
     CUtensorMap tdkv;     // the packed dQKV activation, boxes of 32 rows x 32 columns for dK / dV
     rc = make_tmap_2d_sw(&tdkv, a.dqkv, rows, 3 * d, 3 * d, 32, 32, 2, 64);

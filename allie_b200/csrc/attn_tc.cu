@@ -673,15 +673,15 @@ static int launch_attn_fwd(const CUtensorMap& tm, const AttnArgs& a, cudaStream_
   if (rc_o) return rc_o;
   constexpr int SMEM = 5 * 128 * HD * 2 + 128 * 128 * 2 + 1024;
   auto kern = attn_fwd_kernel<HD>;
-  static bool attr = false;
-  if (!attr) {
+  static PerDeviceOnce attr;
+  if (attr.first_use_on_device()) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (e != cudaSuccess) return (int)e;
     // two CTAs per SM only fit when the SM is configured for its largest shared-memory carve-out
     e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
                              cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return (int)e;
-    attr = true;
+    attr.mark_device();
   }
   dim3 grid((a.T + 127) / 128, a.H, a.B);
   kern<<<grid, FWD_THREADS, SMEM, stream>>>(tm, tmo, a);
@@ -694,11 +694,11 @@ static int launch_attn_bwd(const CUtensorMap& tq, const CUtensorMap& td, const A
   constexpr int STAGES = HD <= 64 ? 2 : 1;
   constexpr int SMEM = (2 + 2 * STAGES) * 128 * HD * 2 + 2 * 128 * 128 * 2 + 256;
   auto kern = attn_bwd_kernel<HD, MODE>;
-  static bool attr = false;
-  if (!attr) {
+  static PerDeviceOnce attr;
+  if (attr.first_use_on_device()) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (e != cudaSuccess) return (int)e;
-    attr = true;
+    attr.mark_device();
   }
   dim3 grid((a.T + 127) / 128, a.H, a.B);
   kern<<<grid, BWD_THREADS, SMEM, stream>>>(tq, td, a);

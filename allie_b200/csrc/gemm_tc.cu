@@ -540,11 +540,11 @@ static int launch_pair(const void* A, long long lda, const void* B, long long ld
   constexpr int SMEM = 1024 + PAIR_STAGES * (BM * BK * 2 + HALF_N * BK * 2) +
                        NUM_EPI_WARPS * PAIR_WARP_STAGING + 256;
   auto kern = gemm_bf16_tcgen05_pair_kernel<A_MN, B_MN>;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static PerDeviceOnce attr_set;
+  if (attr_set.first_use_on_device()) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (e != cudaSuccess) return static_cast<int>(e);
-    attr_set = true;
+    attr_set.mark_device();
   }
   const int m_tiles = (g.M + 2 * BM - 1) / (2 * BM), n_tiles = (g.N + PAIR_BN - 1) / PAIR_BN;
   const int units = m_tiles * n_tiles * g.k_splits;
@@ -580,11 +580,11 @@ static int launch(const void* A, long long lda, const void* B, long long ldb, co
   }
   constexpr int SMEM = 1024 + STAGES * (BM * BK * 2 + BN * BK * 2) + NUM_EPI_WARPS * 2048 + 256;
   auto kern = gemm_bf16_tcgen05_kernel<BN, STAGES, A_MN, B_MN>;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static PerDeviceOnce attr_set;
+  if (attr_set.first_use_on_device()) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (e != cudaSuccess) return static_cast<int>(e);
-    attr_set = true;
+    attr_set.mark_device();
   }
   const int m_tiles = (g.M + BM - 1) / BM, n_tiles = (g.N + BN - 1) / BN;
   const int units = m_tiles * n_tiles * g.k_splits;

@@ -305,15 +305,15 @@ int ab_layernorm_bwd(const void* dy, const float* x, const float* mean, const fl
   }
   // with parameter gradients: exactly the resident blocks, each warp keeps its column sums
   const int smem = LN_WARPS * 3 * d * (int)sizeof(float);
-  static bool attr_set = false;
-  if (!attr_set) {
+  static PerDeviceOnce attr_set;
+  if (attr_set.first_use_on_device()) {
     cudaError_t e = cudaFuncSetAttribute(ln_bwd_kernel<8, true>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, LN_WARPS * 3 * 1024 * 4);
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(ln_bwd_kernel<16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                LN_WARPS * 3 * 2048 * 4);
     if (e != cudaSuccess) return (int)e;
-    attr_set = true;
+    attr_set.mark_device();
   }
   const int resident = d <= 1024 ? 148 * 2 : 148;
   if (grid > resident) grid = resident;

@@ -10,7 +10,23 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 namespace ab {
+
+// A kernel attribute (dynamic shared memory limit, carve-out) belongs to one device's copy of the
+// kernel, so "already set" is kept per device: one bit per device ordinal in a mask that each call
+// site owns.  first_use_on_device() returns true until mark_device() was called on this device.
+struct PerDeviceOnce {
+  std::atomic<unsigned long long> mask{0};
+  unsigned long long bit() const {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    return 1ull << (dev & 63);
+  }
+  bool first_use_on_device() const { return !(mask.load(std::memory_order_acquire) & bit()); }
+  void mark_device() { mask.fetch_or(bit(), std::memory_order_release); }
+};
 
 // ---------------------------------------------------------------- status ---
 // Kernels report trouble through a device status word owned by the host

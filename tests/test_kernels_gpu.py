@@ -36,12 +36,12 @@ def test_layernorm_forward(M, d, rms):
     assert torch.allclose(y.float(), ref, rtol=1e-2, atol=2e-2)
 
 
-@pytest.mark.parametrize("rms", [False, True])
-def test_layernorm_backward_with_residual_and_params(rms):
+@pytest.mark.parametrize("M,d,rms", [(520, 1024, False), (520, 1024, True), (77, 256, False), (131, 1280, False),
+                                     (66, 2048, True), (3, 128, False)])
+def test_layernorm_backward_with_residual_and_params(M, d, rms):
     from allie_b200.ops import kernels as K
 
     torch.manual_seed(1)
-    M, d = 520, 1024
     x = (torch.randn(M, d, device=DEV) * 1.5).requires_grad_(True)
     g = torch.randn(d, device=DEV, requires_grad=True)
     b = torch.randn(d, device=DEV, requires_grad=True)
@@ -99,6 +99,43 @@ def test_layernorm_backward_dropout_copy_is_masked_and_scaled():
     frac = kept.float().mean().item()
     assert abs(frac - 0.75) < 0.01, frac
     assert torch.allclose(dbranch.float()[kept], (dx / 0.75)[kept], rtol=1e-2, atol=3e-2)
+
+
+@pytest.mark.parametrize("M,d,params", [(37, 1280, True), (21, 1024, True), (19, 2048, True), (37, 1280, False)])
+def test_layernorm_backward_dropout_mask_is_the_element_indexed_one(M, d, params):
+    """The masked copy keeps exactly the elements that the generator keeps for element index
+    row * d + column (the mask the projection's forward epilogue applied), in both backward kernels
+    (with and without parameter gradients) and at widths where a thread owns two column groups."""
+    import ctypes
+
+    import numpy as np
+
+    from allie_b200.ops import _lib
+    from allie_b200.ops import kernels as K
+
+    torch.manual_seed(4)
+    x = torch.randn(M, d, device=DEV)
+    g = torch.ones(d, device=DEV)
+    y = torch.empty(M, d, device=DEV, dtype=torch.bfloat16)
+    mean = torch.empty(M, device=DEV)
+    rstd = torch.empty(M, device=DEV)
+    K.layernorm_fwd(x, g, torch.zeros(d, device=DEV), y, mean, rstd, 1e-5)
+    dy = torch.randn(M, d, device=DEV).bfloat16()
+    dres = torch.randn(M, d, device=DEV) + 5.0     # keeps dx away from zero
+    dx = torch.empty(M, d, device=DEV)
+    dbranch = torch.empty(M, d, device=DEV, dtype=torch.bfloat16)
+    dgamma = torch.zeros(d, device=DEV) if params else None
+    dbeta = torch.zeros(d, device=DEV) if params else None
+    seed, stream, p = 1234567, 9, 0.3
+    K.layernorm_bwd(dy, x, mean, rstd, g, dres, dx, dbranch, dgamma, dbeta, drop_seed=seed, drop_stream=stream,
+                    drop_p=p)
+    _done()
+    host = np.empty(M * d, dtype=np.uint8)
+    assert _lib.cuda().ab_dropout_mask_host(ctypes.c_ulonglong(seed), ctypes.c_uint(stream), ctypes.c_longlong(M * d),
+                                            ctypes.c_uint(_lib.dropout_thr16(p)),
+                                            host.ctypes.data_as(ctypes.c_void_p)) == 0
+    want = torch.from_numpy(host).view(M, d).bool()
+    assert torch.equal((dbranch != 0).cpu(), want)
 
 
 def test_cross_entropy_loss_and_gradient():
