@@ -240,7 +240,7 @@ attn_bwd_fused64_kernel(const __grid_constant__ CUtensorMap tmQKV,
           keep32 = 0;
 #pragma unroll
           for (int g = 0; g < 4; ++g)
-            keep32 |= dropout_keep8(a.seed, a.stream_id, (row_elem0 >> 3) + g, a.thr16) << (8 * g);
+            keep32 |= dropout_keep8(salted(a.seed, a.salt), a.stream_id, (row_elem0 >> 3) + g, a.thr16) << (8 * g);
         }
       }
       if (!mbar_wait(sdp_full, it & 1, abort_flag)) { ok = false; break; }
@@ -622,7 +622,7 @@ attn_bwd_fused64_persistent_kernel(const __grid_constant__ CUtensorMap tmQKV,
           keep32 = 0;
 #pragma unroll
           for (int g4 = 0; g4 < 4; ++g4)
-            keep32 |= dropout_keep8(a.seed, a.stream_id, (row_elem0 >> 3) + g4, a.thr16) << (8 * g4);
+            keep32 |= dropout_keep8(salted(a.seed, a.salt), a.stream_id, (row_elem0 >> 3) + g4, a.thr16) << (8 * g4);
         }
       }
     };

@@ -16,6 +16,7 @@ struct AttnArgs {
   __nv_bfloat16* out;       // [B*T, H*hd]
   float* lse;               // [B, H, T]
   uint32_t* drop_mask;      // [B, H, T, T/32] keep bits written by the forward pass, or null
+  const unsigned long long* salt;   // seed_salt_ptr() at launch: folded into `seed` when not null
   int* status;
 };
 
@@ -44,6 +45,7 @@ struct AttnBwdArgs {
   __nv_bfloat16* dqkv;       // [B*T, 3*H*hd]
   const uint32_t* drop_mask; // [B,H,T,T/32] keep bits from the forward pass, or null (recompute)
   float* dq_acc;             // [B*T, H*hd] fp32 accumulator for the single-kernel backward, or null
+  const unsigned long long* salt;   // as in AttnArgs
   int* status;
 };
 

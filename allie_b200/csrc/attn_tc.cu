@@ -182,7 +182,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
         uint32_t word = 0;
 #pragma unroll
         for (int g = 0; g < 4; ++g)
-          word |= dropout_keep8(a.seed, a.stream_id, (e0 >> 3) + g, a.thr16) << (8 * g);
+          word |= dropout_keep8(salted(a.seed, a.salt), a.stream_id, (e0 >> 3) + g, a.thr16) << (8 * g);
         if (c == 0) keep_w0 = word; else keep_w1 = word;
         if (a.drop_mask && q_idx < a.T) a.drop_mask[e0 >> 5] = word;
       }
@@ -587,7 +587,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
             const uint64_t e0 = row_elem0 + hf * 16 + g * 8;
             const uint32_t keep = a.drop_mask
                 ? (q_ok ? (a.drop_mask[e0 >> 5] >> (e0 & 31)) & 0xffu : 0u)
-                : dropout_keep8(a.seed, a.stream_id, e0 >> 3, a.thr16);
+                : dropout_keep8(salted(a.seed, a.salt), a.stream_id, e0 >> 3, a.thr16);
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               const bool kp = (keep >> i) & 1u;
@@ -722,7 +722,7 @@ int ab_attn_fwd(const void* qkv, void* out, float* lse, unsigned int* drop_mask,
   if (rc) return rc;
   AttnArgs a;
   a.B = B; a.T = T; a.H = H; a.hd = hd; a.scale = scale; a.seed = seed; a.stream_id = stream_id;
-  a.thr16 = thr16; a.out = (__nv_bfloat16*)out; a.lse = lse; a.status = status;
+  a.thr16 = thr16; a.out = (__nv_bfloat16*)out; a.lse = lse; a.status = status; a.salt = seed_salt_ptr();
   a.drop_mask = drop_mask;
   return hd == 64 ? launch_attn_fwd<64>(tm, a, stream) : launch_attn_fwd<128>(tm, a, stream);
 }
@@ -748,6 +748,7 @@ int ab_attn_bwd(const void* qkv, const void* out, const float* lse, const void* 
   AttnBwdArgs a;
   a.B = B; a.T = T; a.H = H; a.hd = hd; a.scale = scale; a.seed = seed; a.stream_id = stream_id;
   a.thr16 = thr16; a.lse = lse; a.delta = delta; a.dqkv = (__nv_bfloat16*)dqkv; a.status = status;
+  a.salt = seed_salt_ptr();
   a.drop_mask = drop_mask; a.dq_acc = dq_acc;
   if (hd == 64 && dq_acc) return launch_attn_bwd_fused64(tq, td, a, stream);
   if (hd == 64) {

@@ -69,7 +69,9 @@ __global__ void __launch_bounds__(256)
 embed_fwd_kernel(const int* __restrict__ ids, const int* __restrict__ pos,
                  const float* __restrict__ wte, const float* __restrict__ wpe,
                  const float* __restrict__ ctrl, float* __restrict__ x, int M, int d, int vocab,
-                 unsigned long long seed, unsigned int stream_id, unsigned int thr16) {
+                 unsigned long long seed, unsigned int stream_id, unsigned int thr16,
+                 const unsigned long long* __restrict__ salt) {
+  seed = salted(seed, salt);
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= M) return;
@@ -117,7 +119,8 @@ __global__ void __launch_bounds__(256)
 embed_bwd_kernel(const int* __restrict__ ids, const int* __restrict__ pos,
                  const float* __restrict__ dx, float* __restrict__ dwte, float* __restrict__ dwpe,
                  float* __restrict__ dctrl, int M, int d, int vocab, unsigned long long seed,
-                 unsigned int stream_id, unsigned int thr16) {
+                 unsigned int stream_id, unsigned int thr16, const unsigned long long* __restrict__ salt) {
+  seed = salted(seed, salt);
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= M) return;
@@ -149,9 +152,27 @@ embed_bwd_kernel(const int* __restrict__ ids, const int* __restrict__ pos,
   }
 }
 
+const unsigned long long* g_seed_salt = nullptr;
+
+// *salt = next value of a 64-bit linear congruential sequence: the first node of a captured step
+__global__ void seed_salt_advance_kernel(unsigned long long* salt) {
+  *salt = *salt * 6364136223846793005ull + 1442695040888963407ull;
+}
+
 }  // namespace ab
 
 extern "C" {
+// Registers (or, with null, clears) the device word that kernels launched from now on fold into
+// their dropout seeds.  Meant to be set only around the capture of a CUDA graph.
+int ab_set_seed_salt(const void* salt) {
+  ab::g_seed_salt = static_cast<const unsigned long long*>(salt);
+  return 0;
+}
+int ab_seed_salt_advance(void* salt, cudaStream_t stream) {
+  ab::seed_salt_advance_kernel<<<1, 1, 0, stream>>>(static_cast<unsigned long long*>(salt));
+  return (int)cudaGetLastError();
+}
+
 
 int ab_unpack_window(const void* words, int B, int T, int vocab, int pad_id, float time_mean,
                      float time_std, int* ids, int* pos, int* lm_labels, float* value_labels,
@@ -170,7 +191,7 @@ int ab_embed_fwd(const int* ids, const int* pos, const float* wte, const float* 
                  unsigned int stream_id, unsigned int thr16, cudaStream_t stream) {
   if (d % 4) return -1;
   ab::embed_fwd_kernel<<<(M + 7) / 8, 256, 0, stream>>>(ids, pos, wte, wpe, ctrl, x, M, d, vocab,
-                                                        seed, stream_id, thr16);
+                                                        seed, stream_id, thr16, ab::seed_salt_ptr());
   return (int)cudaGetLastError();
 }
 
@@ -179,7 +200,7 @@ int ab_embed_bwd(const int* ids, const int* pos, const float* dx, float* dwte, f
                  unsigned int stream_id, unsigned int thr16, cudaStream_t stream) {
   if (d % 4) return -1;
   ab::embed_bwd_kernel<<<(M + 7) / 8, 256, 0, stream>>>(ids, pos, dx, dwte, dwpe, dctrl, M, d,
-                                                        vocab, seed, stream_id, thr16);
+                                                        vocab, seed, stream_id, thr16, ab::seed_salt_ptr());
   return (int)cudaGetLastError();
 }
 }

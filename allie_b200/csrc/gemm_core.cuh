@@ -24,6 +24,7 @@ struct GemmArgs {
   int k_splits;
   int pdl;            // launched as a programmatic dependent: B (weights) may be fetched before griddep_wait
   AbGemmEpilogue ep;
+  const unsigned long long* salt;   // seed_salt_ptr() at launch: folded into ep.drop_seed when not null
   int* status;
 };
 
@@ -62,7 +63,7 @@ __device__ __forceinline__ void epilogue_math8(const GemmArgs& g, float* v, uint
   if (ep.resid) {
     if (ep.drop_thr16) {
       const uint64_t group = (static_cast<uint64_t>(m) * g.N + n) >> 3;
-      const uint32_t keep = dropout_keep8(ep.drop_seed, ep.drop_stream, group, ep.drop_thr16);
+      const uint32_t keep = dropout_keep8(salted(ep.drop_seed, g.salt), ep.drop_stream, group, ep.drop_thr16);
       const float s = dropout_scale(ep.drop_thr16);
 #pragma unroll
       for (int j = 0; j < 8; ++j) v[j] = ((keep >> j) & 1u) ? v[j] * s : 0.f;

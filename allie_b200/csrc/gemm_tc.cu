@@ -624,7 +624,7 @@ extern "C" int ab_gemm_bf16(const void* A, int a_mn, long long lda, const void* 
   if ((ep->ldo * (ep->out_fp32 ? 4 : 2)) & 15) return -4;   // TMA row pitch: multiple of 16 bytes
   if (ep->act == 1 && (ep->ldaux & 7)) return -4;
   GemmArgs g;
-  g.M = M; g.N = N; g.K = K; g.k_splits = k_splits; g.ep = *ep; g.status = status;
+  g.M = M; g.N = N; g.K = K; g.k_splits = k_splits; g.ep = *ep; g.status = status; g.salt = seed_salt_ptr();
   // programmatic dependent launch: single-CTA kernels only, never with device-side limits (those
   // are values of earlier kernels, read before any wait)
   g.pdl = (ep->pdl && !ep->m_limit && !ep->k_limit) ? 1 : 0;

@@ -313,8 +313,12 @@ extern "C" int ab_lmhead_ce(const void* h, long long ldh, const void* wte, long 
   g.M = M; g.V = V; g.K = K; g.labels = labels; g.n_valid = n_valid; g.coef = coef; g.loss_acc = loss_acc;
   g.status = status;
   constexpr int SMEM = 1024 + LC_STAGES * (BM * BK * 2 + LC_BN * BK * 2) + NUM_EPI_WARPS * 2048 + 2 * 3 * 4 * BM * 4 + 256;
-  cudaError_t e = cudaFuncSetAttribute(lmhead_ce_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
-  if (e != cudaSuccess) return static_cast<int>(e);
+  static PerDeviceOnce attr_set;
+  if (attr_set.first_use_on_device()) {
+    cudaError_t e = cudaFuncSetAttribute(lmhead_ce_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_set.mark_device();
+  }
   if (max_ctas <= 0) max_ctas = 148;
   const int m_tiles = (M + BM - 1) / BM;
   const int grid = m_tiles < max_ctas ? m_tiles : max_ctas;

@@ -82,6 +82,7 @@ struct LnBwdArgs {
   const float* s0; const float* w0; const float* s1; const float* w1;
   int M, d, rms;
   unsigned long long drop_seed; unsigned int drop_stream, drop_thr16;
+  const unsigned long long* salt;   // seed_salt_ptr() at launch: folded into drop_seed when not null
 };
 
 // dy (+ rank-2 term) of lane-owned float4 column c4 of one row
@@ -191,7 +192,7 @@ ln_bwd_kernel(const LnBwdArgs a) {
           if (a.drop_thr16) {
             const uint64_t e0 = static_cast<uint64_t>(row) * d + c4 * 4;
             const uint32_t keep =
-                dropout_keep8(a.drop_seed, a.drop_stream, e0 >> 3, a.drop_thr16) >> (e0 & 7);
+                dropout_keep8(salted(a.drop_seed, a.salt), a.drop_stream, e0 >> 3, a.drop_thr16) >> (e0 & 7);
             m.x = (keep & 1u) ? m.x * dscale : 0.f;
             m.y = (keep & 2u) ? m.y * dscale : 0.f;
             m.z = (keep & 4u) ? m.z * dscale : 0.f;
@@ -295,7 +296,7 @@ int ab_layernorm_bwd(const void* dy, const float* x, const float* mean, const fl
   a.dy = (const __nv_bfloat16*)dy; a.x = x; a.mean = mean; a.rstd = rstd; a.gamma = gamma;
   a.dres_in = dres_in; a.dx = dx; a.dbranch = (__nv_bfloat16*)dbranch; a.dgamma = dgamma;
   a.dbeta = dbeta; a.dbias = dbias; a.s0 = s0; a.w0 = w0; a.s1 = s1; a.w1 = w1; a.M = M; a.d = d; a.rms = rms;
-  a.drop_seed = drop_seed; a.drop_stream = drop_stream; a.drop_thr16 = drop_thr16;
+  a.drop_seed = drop_seed; a.drop_stream = drop_stream; a.drop_thr16 = drop_thr16; a.salt = seed_salt_ptr();
   int grid = (M + LN_WARPS - 1) / LN_WARPS;
   if (!dgamma) {
     if (grid > 148 * 16) grid = 148 * 16;

@@ -412,6 +412,16 @@ __host__ __device__ __forceinline__ Philox4 philox4x32_7(uint64_t seed, uint32_t
   }
   return Philox4{c0, c1, c2, c3};
 }
+// The seed reaches a kernel by value, which a captured CUDA graph would freeze.  Every launcher
+// therefore also hands its kernel seed_salt_ptr(): null in ordinary launches (the seed is used as
+// it is), or, while a training step is being captured, the address of a device word that the
+// graph's first node advances on every replay; kernels key the generator with salted(seed, salt).
+extern const unsigned long long* g_seed_salt;       // host variable, defined in embed.cu
+inline const unsigned long long* seed_salt_ptr() { return g_seed_salt; }
+__device__ __forceinline__ unsigned long long salted(unsigned long long seed,
+                                                     const unsigned long long* salt) {
+  return salt ? (seed ^ __ldg(salt)) : seed;
+}
 // Dropout decisions come in groups of eight consecutive elements: element
 // index i uses 16 bits of philox(seed, stream, i / 8).  keep iff bits >= thr16.
 __host__ __device__ __forceinline__ uint32_t dropout_thr16(float p) {

@@ -27,6 +27,7 @@ import torch.nn as nn
 from ..config import ModelConfig
 from ..data import TIME_MEAN, TIME_STDEV
 from ..ops import _lib, kernels as K
+from ..ops._lib import ptr, stream_ptr
 from ..ops.gemm import gemm
 from . import unwrap
 from .oracle import Conv1D, MoEMLP
@@ -227,6 +228,11 @@ class B200Engine:
         self.loss_out = torch.zeros(4, dtype=torch.float32, device=self.device)
         self.counts = torch.zeros(4, dtype=torch.int32, device=self.device)
         self.kernel_launches = 0
+        # CUDA-graph replay of the micro-step (see enable_step_graph)
+        self.step_graph = False
+        self._step_graphs: dict[tuple, dict] = {}
+        self._salt = torch.tensor([(seed * 0x9E3779B97F4A7C15) & ((1 << 63) - 1)], dtype=torch.int64,
+                                  device=self.device)
 
     # ------------------------------------------------------------- experts
     def _shard_experts(self, model: nn.Module) -> frozenset:
@@ -563,10 +569,65 @@ class B200Engine:
         self.fwd_count += 1
         return (self.seed * 0x9E3779B97F4A7C15 + self.fwd_count * 0xD1B54A32D192ED03) & ((1 << 64) - 1)
 
-    def micro_step(self, words: torch.Tensor, bucket_hook=None) -> torch.Tensor:
+    # ------------------------------------------------------- captured micro-step
+    def enable_step_graph(self, on: bool = True) -> bool:
+        """Replays the micro-step (window unpack, forward, backward: a few thousand launches for
+        the medium model) as one CUDA graph per batch shape instead of launching its kernels one
+        by one.  A captured launch freezes the arguments it was given by value, and the dropout seed
+        is one of them, so while capturing, every kernel that draws a mask is also handed the address
+        of a device word (``_salt``) that it folds into its seed; the first node of the graph advances
+        that word, which gives every replay fresh masks that its forward and backward kernels agree
+        on.  Micro-steps that carry a bucket hook (their reduce-scatter launches take the cross-rank
+        epoch by value) and models with MoE layers (same, for every dispatch) keep the ordinary
+        launches.  Returns whether the mode is on."""
+        self.step_graph = bool(on) and not any(L["moe"] for L in self.layers)
+        if not self.step_graph:
+            self._step_graphs.clear()
+        return self.step_graph
+
+    def _capture_step(self, words: torch.Tensor) -> dict:
+        lib = _lib.cuda()
+        static = torch.empty_like(words)
+        seed = self._next_seed()
+        graph = torch.cuda.CUDAGraph()
+        launches0 = _lib.LAUNCHES
+        assert lib.ab_set_seed_salt(ptr(self._salt)) == 0
+        try:
+            with torch.cuda.graph(graph):
+                assert lib.ab_seed_salt_advance(ptr(self._salt), stream_ptr()) == 0
+                _lib.count_launches(1)
+                B, T = self.load_window(static)
+                self.forward(B, T, True, seed, True, True)
+                self.backward(B, T, seed, None)
+        finally:
+            lib.ab_set_seed_salt(None)
+        captured = _lib.LAUNCHES - launches0
+        _lib.count_launches(-captured)       # nothing ran yet: the launches are counted per replay
+        return {"graph": graph, "words": static, "launches": captured, "seed": seed}
+
+    def _graph_micro_step(self, words: torch.Tensor) -> torch.Tensor:
+        key = (tuple(words.shape), words.dtype)
+        entry = self._step_graphs.get(key)
+        if entry is None:
+            # the first micro-step of a shape runs the ordinary way: it creates the buffers and
+            # does every kernel's first-launch set-up, neither of which may happen under capture
+            self._step_graphs[key] = {}
+            return self.micro_step(words, _no_graph=True)
+        if not entry:
+            torch.cuda.current_stream().synchronize()
+            entry = self._step_graphs[key] = self._capture_step(words)
+        entry["words"].copy_(words, non_blocking=True)
+        entry["graph"].replay()
+        self.fwd_count += 1
+        _lib.count_launches(entry["launches"])
+        return self.loss_out
+
+    def micro_step(self, words: torch.Tensor, bucket_hook=None, _no_graph: bool = False) -> torch.Tensor:
         """Forward + backward of one micro-batch of raw words; gradients accumulate.  Returns the
         device tensor [loss, lm_loss, value_loss, time_loss] (no host sync).  ``bucket_hook``: see
         :meth:`backward` (given on the last micro-step of an optimizer step)."""
+        if self.step_graph and bucket_hook is None and not _no_graph:
+            return self._graph_micro_step(words)
         B, T = self.load_window(words)
         seed = self._next_seed()
         self.forward(B, T, True, seed, True, True)

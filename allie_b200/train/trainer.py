@@ -151,14 +151,19 @@ class Trainer:
                  save_interval: int = 500,
                  # extensions (absent from the reference schema, all optional)
                  shard_optimizer: Optional[bool] = None, grad_sync: str = "auto", use_wandb: bool = True,
-                 expert_parallel: bool = True):
+                 expert_parallel: bool = True, cuda_graph: Optional[bool] = None):
         """Extensions to the reference signature: ``grad_sync`` = ``auto`` | ``fused`` (the NVLink
         kernels: bucketed reduce-scatter under backward, optimizer state sharded over the ranks)
         | ``collective`` (one all_reduce, replicated optimizer).  ``shard_optimizer`` is the same
         choice as a boolean: true requires the sharded fused path, false selects ``collective``.
         ``expert_parallel`` (MoE models on several ranks): true spreads the experts over the ranks,
-        false replicates them and averages their gradients like any other parameter."""
+        false replicates them and averages their gradients like any other parameter.
+        ``cuda_graph``: replay the micro-step (unpack, forward, backward) as one CUDA graph instead of
+        a few thousand launches; default (None): on for dense models (1.4x on the tiny config, 7-10 %
+        on small ones, under 1 % on the medium config, where it mainly frees the host thread: 53 ms of
+        launch calls per 82 ms micro-step become 0.04 ms); MoE models keep the ordinary launches."""
         self.expert_parallel_requested = expert_parallel
+        self.cuda_graph = cuda_graph
         if shard_optimizer is not None:
             want = "fused" if shard_optimizer else "collective"
             if grad_sync not in ("auto", want):
@@ -265,6 +270,8 @@ class Trainer:
                 self.engine = B200Engine(model, self.device, seed=self.seed, symmetric=False,
                                          expert_parallel=self.expert_parallel_requested)
             logger.info("using the fused sm_100a AdamW over flat parameter arenas")
+            if self.engine.enable_step_graph(self.cuda_graph is None or self.cuda_graph):
+                logger.info("micro-steps replay as a CUDA graph")
         else:
             model.to(self.device)
             decay, no_decay = partition_parameter_names(model)

@@ -419,6 +419,7 @@ def run_ours(args) -> dict:
                              if (trainer.grad_sync and trainer.grad_sync.fused)
                              else ("all_reduce" if world > 1 else "none"),
                 "grad_buckets": len(trainer.engine.arena.buckets),
+                "micro_step_cuda_graph": bool(trainer.engine.step_graph),
                 "e2e_path": "Trainer.train_step(): sampler thread -> pinned windows -> H2D -> step -> loss D2H"},
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,

@@ -165,3 +165,74 @@ def test_dense_engine_with_dropout_matches_oracle_under_the_same_masks(monkeypat
         g, gr = prm.grad.float().cpu(), ref_params[n].grad
         scale_g = gr.abs().max().item() + 1e-12
         assert (g - gr).abs().max().item() / scale_g < 0.08, n
+
+
+def test_graph_replayed_micro_step_matches_ordinary_launches():
+    """The micro-step replayed as a CUDA graph (dropout on): every replay draws new masks (the
+    device-side salt that its first node advances) and computes what the ordinary launches compute
+    when they are given the captured seed and the same salt value."""
+    import ctypes
+
+    from allie_b200.data import UCITokenizer
+    from allie_b200.models import initialize_model
+    from allie_b200.models.engine import B200Engine
+    from allie_b200.ops import _lib
+    from allie_b200.ops._lib import ptr
+
+    torch.manual_seed(0)
+    B, T = 4, 256
+    tok = UCITokenizer(max_length=T, vocab_size_multiple_of=128)
+    kw = dict(n_layer=2, n_embd=256, n_head=4, n_positions=T, resid_pdrop=0.1, embd_pdrop=0.1, attn_pdrop=0.1)
+    model = initialize_model(tok, "gpt2", use_control_token=True, use_regression_head=True, **kw)
+    eng = B200Engine(model, "cuda")
+    assert eng.enable_step_graph(True)
+    w = torch.from_numpy(_windows(tok, B, T).astype(np.int32)).cuda()
+    params = dict(model.named_parameters())
+
+    def grads():
+        torch.cuda.synchronize()
+        _lib.check_status()
+        return {n: p.grad.float().clone() for n, p in params.items()}
+
+    eng.micro_step(w)                       # ordinary launches (first use of the shape)
+    assert not eng._step_graphs[next(iter(eng._step_graphs))]
+    eng.zero_grad()
+    launches0 = _lib.LAUNCHES
+    loss1 = eng.micro_step(w).clone()       # captured here, replay 1
+    entry = next(iter(eng._step_graphs.values()))
+    assert entry["graph"] is not None and _lib.LAUNCHES - launches0 == entry["launches"] > 50   # one replay
+    g1 = grads()
+    salt1 = int(eng._salt.item())
+    eng.zero_grad()
+    loss2 = eng.micro_step(w).clone()       # replay 2: same data, other masks
+    g2 = grads()
+    salt2 = int(eng._salt.item())
+    assert salt1 != salt2
+    assert abs(loss1[0].item() - loss2[0].item()) > 1e-6
+    assert all(torch.isfinite(v).all() for v in g2.values())
+
+    # ordinary launches with the captured seed and each replay's salt value reproduce the replays
+    lib = _lib.cuda()
+    salt = torch.zeros(1, dtype=torch.int64, device="cuda")
+    for want_loss, want_g, s in ((loss1, g1, salt1), (loss2, g2, salt2)):
+        eng.zero_grad()
+        salt.fill_(s)
+        assert lib.ab_set_seed_salt(ptr(salt)) == 0
+        try:
+            Bt, Tt = eng.load_window(w)
+            eng.forward(Bt, Tt, True, entry["seed"], True, True)
+            eng.backward(Bt, Tt, entry["seed"])
+        finally:
+            lib.ab_set_seed_salt(None)
+        got = grads()
+        assert abs(eng.loss_out[0].item() - want_loss[0].item()) < 1e-4 * max(1.0, abs(want_loss[0].item()))
+        for n in want_g:
+            scale = want_g[n].abs().max().item() + 1e-12
+            assert (got[n] - want_g[n]).abs().max().item() / scale < 1e-3, n
+
+    # a micro-step with a bucket hook keeps the ordinary launches
+    eng.zero_grad()
+    seen = []
+    eng.micro_step(w, bucket_hook=seen.append)
+    torch.cuda.synchronize()
+    assert seen == list(range(len(eng.arena.buckets)))       # called once per bucket, in order
