@@ -72,7 +72,7 @@ def ep_moe_forward(self: MoEMLP, x):
         row_expert = torch.repeat_interleave(torch.arange(len(per_expert), device=x.device), n_rows)
         dt = torch.bfloat16
         h = torch._grouped_mm(xr.to(dt), self.c_fc.weight.to(dt), offs=offs) + self.c_fc.bias.to(dt)[row_expert]
-        yr = torch._grouped_mm(gelu_new(h), self.c_proj.weight.to(dt), offs=offs) + self.c_proj.bias.to(dt)[row_expert]
+        yr = torch._grouped_mm(gelu_new(h).to(dt), self.c_proj.weight.to(dt), offs=offs) + self.c_proj.bias.to(dt)[row_expert]
     else:
         outs, s = [], 0
         for le, n in enumerate(per_expert):
