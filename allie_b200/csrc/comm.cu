@@ -53,17 +53,24 @@ struct RsArgs {
   int* status;
 };
 
+// "My gradients of this bucket are final" -> peers; wait until everyone's are.  One warp, launched
+// right before the bucket's reduce-scatter kernel on the same stream: the wait for the slowest rank
+// is then held by 32 threads on one SM.  (When the reduce-scatter blocks did this wait themselves,
+// one block per SM sat resident for as long as the ranks were apart; with its registers taken, an
+// SM holds one LayerNorm-backward block instead of two, so every bucket cost the backward pass the
+// skew between the ranks.)
+__global__ void __launch_bounds__(32)
+nvl_bucket_sync_kernel(const NvlPeers flags, int bucket, int rank, int world, uint32_t epoch, int* status) {
+  if (*reinterpret_cast<volatile int*>(status) != 0) return;     // an earlier wait of this step ran out
+  signal_phase(flags, 2 * bucket, rank, world, epoch);
+  wait_phase(static_cast<const uint32_t*>(flags.ptr[rank]), 2 * bucket, world, epoch, status);
+}
+
 __global__ void __launch_bounds__(128, 8)
 nvl_reduce_scatter_kernel(const RsArgs a) {
-  if (*reinterpret_cast<volatile int*>(a.status) != 0) return;   // an earlier wait of this step ran out
-  // "my gradients of this bucket are final" -> peers; wait until everyone's are
-  if (blockIdx.x == 0) {
-    if (threadIdx.x == 0 && a.zero_idle) a.norm_part[(a.epoch + 1) & 1] = 0.f;
-    signal_phase(a.flags, 2 * a.bucket, a.rank, a.world, a.epoch);
-  }
-  if (!wait_phase(static_cast<const uint32_t*>(a.flags.ptr[a.rank]), 2 * a.bucket, a.world, a.epoch,
-                  a.status))
-    return;
+  // the bucket's sync kernel ran before this one; if its wait (or an earlier one) ran out, stop here
+  if (*reinterpret_cast<volatile int*>(a.status) != 0) return;
+  if (blockIdx.x == 0 && threadIdx.x == 0 && a.zero_idle) a.norm_part[(a.epoch + 1) & 1] = 0.f;
   float ss = 0.f;
   float* mine = static_cast<float*>(a.grads.ptr[a.rank]) + a.shard_off;
   const long long n4 = a.shard_n >> 2;
@@ -272,6 +279,7 @@ int ab_nvl_reduce_scatter(void* const* grad_ptrs, void* const* flag_ptrs, const 
   a.mc_grads = mc_grads; a.norm_part = norm_part; a.ticket = ticket; a.shard_off = shard_off;
   a.shard_n = shard_n; a.rank = rank; a.world = world; a.epoch = epoch; a.bucket = bucket;
   a.zero_idle = zero_idle; a.status = status;
+  nvl_bucket_sync_kernel<<<1, 32, 0, stream>>>(a.flags, bucket, rank, world, epoch, status);
   nvl_reduce_scatter_kernel<<<grid, 128, 0, stream>>>(a);
   return (int)cudaGetLastError();
 }

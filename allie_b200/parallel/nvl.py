@@ -207,7 +207,7 @@ class NvlGradOptimizer:
             c_int(b), c_int(int(b == 0)), c_int(grid), ptr(_lib.status_word()), stream_ptr())
         if rc:
             raise RuntimeError(f"ab_nvl_reduce_scatter failed: {rc}")
-        _lib.count_launches(1)
+        _lib.count_launches(2)          # the bucket's one-warp sync kernel and the reduce-scatter itself
 
     def bucket_ready(self, b: int) -> None:
         """Backward hook: every gradient of bucket ``b`` has been enqueued on the current stream.
