@@ -71,9 +71,20 @@ def run_moe(impl: str = "ours", steps: int = 10, warmup: int = 3, layers: int = 
         check = _lib.check_status
 
         def stats():
-            st = trainer.engine.moe_stats() or {}
+            eng = trainer.engine
+            st = eng.moe_stats() or {}
+            # share of (token, choice) pairs beyond an expert's capacity, estimated from this rank's
+            # routing (every rank draws tokens from the same distribution): those rows are dropped
+            # (their tokens keep the residual only), so they are work the step did not do
+            sent = kept = 0.0
+            caps = {l: m.ctx.cap_e for (l, key), m in eng._moe_layers.items() if key[1]}
+            for l, counts in (st.get("expert_tokens") or {}).items():
+                for c in counts:
+                    sent += world * c
+                    kept += min(world * c, caps.get(l, world * c))
             return {"expert_load_max_over_mean": round(st.get("max_over_mean_load", 0.0), 3),
-                    "capacity_overflow": bool(st.get("overflow", False)), "aux_loss": round(st.get("aux_loss", 0.0), 4)}
+                    "capacity_overflow": bool(st.get("overflow", False)), "aux_loss": round(st.get("aux_loss", 0.0), 4),
+                    "pairs_dropped_fraction_est": round(1.0 - kept / sent, 4) if sent else 0.0}
     else:
         sys.path.insert(0, os.path.join(ROOT, "baseline"))
         import torch.distributed as dist
