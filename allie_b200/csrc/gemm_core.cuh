@@ -35,8 +35,10 @@ struct GemmArgs {
 __device__ __forceinline__ void epilogue_math8(const GemmArgs& g, float* v, uint4& pre, int m, int n,
                                                bool ok, bool add_bias, int bias_off = 0) {
   const AbGemmEpilogue& ep = g.ep;
+  if (ep.alpha != 1.f) {
 #pragma unroll
-  for (int j = 0; j < 8; ++j) v[j] *= ep.alpha;
+    for (int j = 0; j < 8; ++j) v[j] *= ep.alpha;
+  }
   if (!ok) return;
   if (ep.bias && add_bias) {      // with split-K only the first split carries the bias
     const float4 b0 = __ldg(reinterpret_cast<const float4*>(ep.bias + bias_off + n));
@@ -44,7 +46,14 @@ __device__ __forceinline__ void epilogue_math8(const GemmArgs& g, float* v, uint
     v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
     v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
   }
-  if (ep.act == 1) {
+  if (ep.act == 1 && ep.aux_grad) {
+    // the second output is gelu'(pre-activation): the backward epilogue only multiplies by it
+    float d[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = gelu_tanh_with_grad(v[j], d[j]);
+    pre.x = pack_bf16x2(d[0], d[1]); pre.y = pack_bf16x2(d[2], d[3]);
+    pre.z = pack_bf16x2(d[4], d[5]); pre.w = pack_bf16x2(d[6], d[7]);
+  } else if (ep.act == 1) {
     pre.x = pack_bf16x2(v[0], v[1]); pre.y = pack_bf16x2(v[2], v[3]);
     pre.z = pack_bf16x2(v[4], v[5]); pre.w = pack_bf16x2(v[6], v[7]);
 #pragma unroll
@@ -55,10 +64,15 @@ __device__ __forceinline__ void epilogue_math8(const GemmArgs& g, float* v, uint
   } else if (ep.act == 2) {
     const uint4 q = *reinterpret_cast<const uint4*>(
         static_cast<const __nv_bfloat16*>(ep.aux) + (long long)m * ep.ldaux + n);
+    if (ep.aux_grad) {        // aux already holds the derivative (written by an act == 1 launch with aux_grad)
+      v[0] *= bf16_lo(q.x); v[1] *= bf16_hi(q.x); v[2] *= bf16_lo(q.y); v[3] *= bf16_hi(q.y);
+      v[4] *= bf16_lo(q.z); v[5] *= bf16_hi(q.z); v[6] *= bf16_lo(q.w); v[7] *= bf16_hi(q.w);
+    } else {
     v[0] *= gelu_tanh_grad(bf16_lo(q.x)); v[1] *= gelu_tanh_grad(bf16_hi(q.x));
     v[2] *= gelu_tanh_grad(bf16_lo(q.y)); v[3] *= gelu_tanh_grad(bf16_hi(q.y));
     v[4] *= gelu_tanh_grad(bf16_lo(q.z)); v[5] *= gelu_tanh_grad(bf16_hi(q.z));
     v[6] *= gelu_tanh_grad(bf16_lo(q.w)); v[7] *= gelu_tanh_grad(bf16_hi(q.w));
+    }
   }
   if (ep.resid) {
     if (ep.drop_thr16) {

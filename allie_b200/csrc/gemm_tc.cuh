@@ -11,6 +11,8 @@ extern "C" {
 //   act == 1:  aux[m][n] = bf16(v); v = gelu_new(v)
 //   act == 2:  v *= gelu_new'(aux[m][n])
 //   act == 3:  v = gelu_new(v)            (no pre-activation kept: inference)
+//   aux_grad:  act == 1 stores aux[m][n] = bf16(gelu_new'(v)) instead of bf16(v), and act == 2
+//              multiplies by aux[m][n] as it is (forward and backward must agree on the flag)
 //   resid != null:  v = resid[m][n] + dropout(v)   (dropout only when drop_thr16 > 0)
 //   out_fp32 ? (accumulate ? out[m][n] += v (atomic) : out[m][n] = v) : out[m][n] = bf16(v)
 struct AbGemmEpilogue {
@@ -37,6 +39,7 @@ struct AbGemmEpilogue {
   // launches that take the single-CTA kernel only): set-up and the prefetch of the first weight
   // tiles overlap that kernel; `B` must not be something it writes.
   int pdl;
+  int aux_grad;
 };
 
 // C[M,N] = A[M,K] * B[K,N] on the 5th-generation tensor cores.

@@ -370,17 +370,30 @@ __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v 
 __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
 
 // gelu_new (tanh form) and its derivative.
+// GELU (tanh form) and its derivative, written for the fewest issue slots: the GEMM epilogues that
+// use them are bound by instruction issue.  With u = k0 (x + k1 x^3) = x (k0 + k0 k1 x^2), t = tanh u:
+//   gelu(x)  = 0.5 x (1 + t)                      = fma(h, t, h),  h = 0.5 x          (6 operations)
+//   gelu'(x) = 0.5 (1 + t) + 0.5 x (1 - t^2) u'   with u' = k0 + 3 k0 k1 x^2          (10 operations)
+constexpr float GELU_K0 = 0.7978845608028654f;
+constexpr float GELU_K01 = 0.7978845608028654f * 0.044715f;
 __device__ __forceinline__ float gelu_tanh(float x) {
-  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
-  float u = k0 * (x + k1 * x * x * x);
-  return 0.5f * x * (1.f + tanh_fast(u));
+  const float t = tanh_fast(x * fmaf(GELU_K01, x * x, GELU_K0));
+  const float h = 0.5f * x;
+  return fmaf(h, t, h);
 }
 __device__ __forceinline__ float gelu_tanh_grad(float x) {
-  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
-  float x2 = x * x;
-  float t = tanh_fast(k0 * (x + k1 * x * x2));
-  float dt = (1.f - t * t) * k0 * (1.f + 3.f * k1 * x2);
-  return 0.5f * (1.f + t) + 0.5f * x * dt;
+  const float x2 = x * x;
+  const float t = tanh_fast(x * fmaf(GELU_K01, x2, GELU_K0));
+  const float dt = fmaf(-t, t, 1.f) * fmaf(3.f * GELU_K01, x2, GELU_K0);
+  return fmaf(0.5f * x, dt, fmaf(0.5f, t, 0.5f));
+}
+// both at once (they share x^2 and the tanh): returns gelu(x), stores gelu'(x)
+__device__ __forceinline__ float gelu_tanh_with_grad(float x, float& grad) {
+  const float x2 = x * x;
+  const float t = tanh_fast(x * fmaf(GELU_K01, x2, GELU_K0));
+  const float h = 0.5f * x;
+  grad = fmaf(h, fmaf(-t, t, 1.f) * fmaf(3.f * GELU_K01, x2, GELU_K0), fmaf(0.5f, t, 0.5f));
+  return fmaf(h, t, h);
 }
 
 // ---------------------------------------------------------------- philox ---

@@ -427,8 +427,9 @@ class B200Engine:
                 self._moe(l, B * T, train).forward(buf["ln2"][l], buf["xmid"][l], x[l + 1], seed, 2 + 3 * l, p_res)
                 continue
             if train:
+                # buf["pre"] receives GELU'(pre-activation), all that backward needs of it
                 gemm(buf["ln2"][l], L["fc_w"][1], b_mn=True, out=buf["act"][l], bias=L["fc_b"][0], act=1,
-                     aux=buf["pre"][l])
+                     aux=buf["pre"][l], aux_grad=True)
             else:       # inference: nothing needs the pre-activation
                 gemm(buf["ln2"][l], L["fc_w"][1], b_mn=True, out=buf["act"][l], bias=L["fc_b"][0], act=3)
             gemm(buf["act"][l], L["pr_w"][1], b_mn=True, out=x[l + 1], bias=L["pr_b"][0],
@@ -503,7 +504,7 @@ class B200Engine:
                 self._moe(l, B * T, True).backward(dyb, buf["ln2"][l], dsmall, self._aux_coef())
             else:
                 gemm(buf["act"][l], dyb, a_mn=True, b_mn=True, out=L["pr_w"][2], accumulate=True)
-                gemm(dyb, L["pr_w"][1], b_mn=False, out=dpre, act=2, aux=buf["pre"][l])
+                gemm(dyb, L["pr_w"][1], b_mn=False, out=dpre, act=2, aux=buf["pre"][l], aux_grad=True)
                 gemm(buf["ln2"][l], dpre, a_mn=True, b_mn=True, out=L["fc_w"][2], accumulate=True)
                 K.colsum_bf16(dpre, L["fc_b"][2])
                 gemm(dpre, L["fc_w"][1], b_mn=False, out=dsmall)

@@ -59,6 +59,7 @@ class GemmEpilogue(ctypes.Structure):
         ("resid", c_void_p), ("ldr", c_longlong),
         ("drop_seed", c_ulonglong), ("drop_stream", c_uint), ("drop_thr16", c_uint),
         ("alpha", c_float), ("m_limit", c_void_p), ("k_limit", c_void_p), ("pdl", c_int),
+        ("aux_grad", c_int),
     ]
 
 

@@ -59,10 +59,15 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
          aux: torch.Tensor | None = None, resid: torch.Tensor | None = None,
          drop_p: float = 0.0, drop_seed: int = 0, drop_stream: int = 0,
          alpha: float = 1.0, k_splits: int | None = None, m_limit: torch.Tensor | None = None,
-         k_limit: torch.Tensor | None = None, dependent: bool = False) -> torch.Tensor:
+         k_limit: torch.Tensor | None = None, dependent: bool = False,
+         aux_grad: bool = False) -> torch.Tensor:
     """``dependent``: launch as a programmatic dependent of the previous kernel in the stream
     (honoured by the small-M kernel): its set-up and first weight tiles overlap that kernel.  ``b``
-    must then be data the previous kernel does not write (weights)."""
+    must then be data the previous kernel does not write (weights).
+    ``aux_grad``: with ``act=1`` store GELU'(pre-activation) in ``aux`` instead of the
+    pre-activation, with ``act=2`` multiply by ``aux`` as it is: the derivative is computed once,
+    beside the activation it shares its tanh with, and the backward epilogue (bound by instruction
+    issue) shrinks to a multiply."""
     assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
     assert a.dim() == 2 and b.dim() == 2 and a.stride(1) == 1 and b.stride(1) == 1
     if a_mn:
@@ -119,6 +124,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     if k_limit is not None:      # int32 device scalar: contraction length actually present
         ep.k_limit = k_limit.data_ptr()
     ep.pdl = int(dependent)
+    ep.aux_grad = int(aux_grad)
     rc = _lib.cuda().ab_gemm_bf16(
         _lib.ptr(a), c_int(int(a_mn)), c_longlong(a.stride(0)),
         _lib.ptr(b), c_int(int(b_mn)), c_longlong(b.stride(0)),
@@ -133,7 +139,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
 def gemm_grouped(a: torch.Tensor, b: torch.Tensor, rows: torch.Tensor, cap: int, *, mode: int, b_mn: bool = True,
                  out: torch.Tensor | None = None, bias: torch.Tensor | None = None, act: int = 0,
                  aux: torch.Tensor | None = None, tile_ready: torch.Tensor | None = None,
-                 scatter: dict | None = None) -> None:
+                 scatter: dict | None = None, aux_grad: bool = False) -> None:
     """One launch of the grouped CTA-pair GEMM (``csrc/gemm_grouped.cu``) over all local experts.
 
     ``rows`` (int32 [G], device): live rows per group; ``cap``: rows reserved per group.
@@ -179,6 +185,7 @@ def gemm_grouped(a: torch.Tensor, b: torch.Tensor, rows: torch.Tensor, cap: int,
             assert bias.dtype == torch.float32 and bias.numel() == G * N and bias.is_contiguous()
             ep.bias = bias.data_ptr()
         ep.act = act
+        ep.aux_grad = int(aux_grad)
         if act:
             assert aux is not None and aux.dtype == torch.bfloat16 and aux.shape == (G * cap, N)
             ep.aux, ep.ldaux = aux.data_ptr(), aux.stride(0)

@@ -154,7 +154,7 @@ class MoELayer:
             stream_ptr()), "ab_moe_route_plan_dispatch")
         # all local experts in one launch each; the first waits tile by tile for the dispatched rows
         gemm_grouped(self.xr, v["fc_w"][1], self.rows_local, c.cap_e, mode=1, b_mn=True, out=self.act,
-                     bias=v["fc_b"][0], act=1, aux=self.pre, tile_ready=c.ready_fwd)
+                     bias=v["fc_b"][0], act=1, aux=self.pre, aux_grad=True, tile_ready=c.ready_fwd)
         ep = c.next_epoch(PH_RETURN)
         gemm_grouped(self.act, v["pr_w"][1], self.rows_local, c.cap_e, mode=1, b_mn=True, bias=v["pr_b"][0],
                      scatter=self._scatter(self.p_ycomb, PH_RETURN, ep, 1))
@@ -177,7 +177,7 @@ class MoELayer:
         rows, cap = self.rows_local, c.cap_e
         gemm_grouped(self.act, c.dyr, rows, cap, mode=2, out=v["pr_w"][2], tile_ready=self.ready_bwd)
         K.colsum_grouped_bf16(c.dyr, v["pr_b"][2], rows, cap)
-        gemm_grouped(c.dyr, v["pr_w"][1], rows, cap, mode=1, b_mn=False, out=c.dpre, act=2, aux=self.pre)
+        gemm_grouped(c.dyr, v["pr_w"][1], rows, cap, mode=1, b_mn=False, out=c.dpre, act=2, aux=self.pre, aux_grad=True)
         gemm_grouped(self.xr, c.dpre, rows, cap, mode=2, out=v["fc_w"][2])
         K.colsum_grouped_bf16(c.dpre, v["fc_b"][2], rows, cap)
         ep = c.next_epoch(PH_BWD_RETURN)

@@ -162,10 +162,14 @@ class NvlGradOptimizer:
         self.h_flags = rendezvous(self.flags)
         self.h_norm = rendezvous(self.norm_part)
         self.ticket = torch.zeros(4, dtype=torch.int32, device=dev)
-        use_mc = os.environ.get("ALLIE_NVL_MULTIMEM", "0") == "1"
+        # ALLIE_NVL_MULTIMEM: 0 = plain peer loads / stores; 1 = multimem.ld_reduce for the gradients
+        # and multimem.st for the parameters; rs = multimem.ld_reduce for the gradients only
+        mode = os.environ.get("ALLIE_NVL_MULTIMEM", "0")
         mc = [int(getattr(h, "multicast_ptr", 0) or 0) for h in (self.h_grad, self.h_master, self.h_shadow)]
-        self.multimem = use_mc and all(mc)
+        self.multimem = mode == "1" and all(mc)
         self.mc_grad, self.mc_master, self.mc_shadow = mc if self.multimem else (0, 0, 0)
+        if mode == "rs" and mc[0]:
+            self.mc_grad = mc[0]
         # only the replicated region [0, sync_end) is reduced and sharded; rank-local (expert)
         # parameters behind it are updated in place by every rank for itself
         self.layout = ShardLayout(a.buckets, self.world)

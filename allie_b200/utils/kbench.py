@@ -57,6 +57,8 @@ def main(argv=None) -> dict:
     ap.add_argument("--m", type=int, default=32768); ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=1024)
     ap.add_argument("--epilogue", default="none", choices=["none", "bias", "gelu", "dgelu", "resid"])
+    ap.add_argument("--aux-grad", action="store_true",
+                    help="gelu / dgelu: the second tensor holds GELU'(pre-activation), as the training engine runs them")
     ap.add_argument("--wgrad", action="store_true")
     ap.add_argument("--batch", type=int, default=64); ap.add_argument("--seq", type=int, default=512)
     ap.add_argument("--heads", type=int, default=16); ap.add_argument("--hd", type=int, default=64)
@@ -80,10 +82,10 @@ def main(argv=None) -> dict:
                 fn = lambda: gemm(x, w, b_mn=True, bias=bias, resid=res, out=res, drop_p=0.1, drop_seed=1, drop_stream=1)
             elif a.epilogue == "gelu":
                 o = torch.empty(M, N, device=dev, dtype=torch.bfloat16); pre = torch.empty_like(o)
-                fn = lambda: gemm(x, w, b_mn=True, bias=bias, act=1, aux=pre, out=o)
+                fn = lambda: gemm(x, w, b_mn=True, bias=bias, act=1, aux=pre, out=o, aux_grad=a.aux_grad)
             elif a.epilogue == "dgelu":   # dgrad through GELU: out = (x @ w) * gelu'(saved pre-activation)
                 o = torch.empty(M, N, device=dev, dtype=torch.bfloat16); pre = torch.randn(M, N, device=dev).bfloat16()
-                fn = lambda: gemm(x, w, b_mn=True, act=2, aux=pre, out=o)
+                fn = lambda: gemm(x, w, b_mn=True, act=2, aux=pre, out=o, aux_grad=a.aux_grad)
             else:
                 o = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
                 fn = lambda: gemm(x, w, b_mn=True, bias=bias if a.epilogue == "bias" else None, out=o)

@@ -415,7 +415,8 @@ def run_ours(args) -> dict:
         "vs_baseline": value / BASELINE_TOKENS_PER_S, "dtype": "bf16", "data": "synthetic",
         "impl": "allie_b200",
         "config": common_config(args.model, ga, world),
-        "arm": {"grad_sync": ("fused-nvlink-multimem" if trainer.grad_sync.nvl.multimem else "fused-nvlink-p2p")
+        "arm": {"grad_sync": ("fused-nvlink-multimem" if trainer.grad_sync.nvl.multimem else
+                              "fused-nvlink-multimem-reduce" if trainer.grad_sync.nvl.mc_grad else "fused-nvlink-p2p")
                              if (trainer.grad_sync and trainer.grad_sync.fused)
                              else ("all_reduce" if world > 1 else "none"),
                 "grad_buckets": len(trainer.engine.arena.buckets),

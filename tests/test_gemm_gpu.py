@@ -153,3 +153,32 @@ def test_gemm_gelu_backward_epilogue_ragged(M, N, K):
     x = pre.float().requires_grad_(True)
     torch.nn.functional.gelu(x, approximate="tanh").backward(dy.float() @ wt.float().t())
     assert torch.allclose(out.float(), x.grad, rtol=3e-2, atol=3e-2), (out.float() - x.grad).abs().max().item()
+
+
+def test_gemm_gelu_derivative_kept_in_aux():
+    """act=1 / act=2 with aux_grad: the forward launch stores GELU'(pre-activation), the backward
+    launch multiplies by it; same results as the pre-activation form."""
+    from allie_b200.ops import _lib
+    from allie_b200.ops.gemm import gemm
+
+    torch.manual_seed(6)
+    dev = "cuda"
+    M, N, K = 1000, 1152, 256
+    x = torch.randn(M, K, device=dev).bfloat16()
+    w = (torch.randn(K, N, device=dev) * 0.08).bfloat16()
+    bias = torch.randn(N, device=dev)
+    act = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+    dact = torch.empty_like(act)
+    gemm(x, w, b_mn=True, bias=bias, act=1, aux=dact, out=act, aux_grad=True)
+    dy = torch.randn(M, 512, device=dev).bfloat16()
+    w2 = (torch.randn(N, 512, device=dev) * 0.05).bfloat16()
+    dpre = gemm(dy, w2, act=2, aux=dact, aux_grad=True)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    pre = (x.float() @ w.float() + bias).requires_grad_(True)
+    ref = torch.nn.functional.gelu(pre, approximate="tanh")
+    (want_d,) = torch.autograd.grad(ref.sum(), pre)
+    assert torch.allclose(act.float(), ref.detach(), rtol=2e-2, atol=2e-2)
+    assert torch.allclose(dact.float(), want_d, rtol=1e-2, atol=1e-2), (dact.float() - want_d).abs().max().item()
+    want = (dy.float() @ w2.float().t()) * want_d
+    assert torch.allclose(dpre.float(), want, rtol=3e-2, atol=3e-2), (dpre.float() - want).abs().max().item()
