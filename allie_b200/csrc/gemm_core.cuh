@@ -23,6 +23,8 @@ struct GemmArgs {
   int M, N, K;
   int k_splits;
   int pdl;            // launched as a programmatic dependent: B (weights) may be fetched before griddep_wait
+  int aux_tma;        // act == 2 in the CTA-pair kernel: the aux tile of an epilogue warp arrives by TMA in
+                      // the warp's staging tile (tmAux is a load map) instead of by row loads
   AbGemmEpilogue ep;
   const unsigned long long* salt;   // seed_salt_ptr() at launch: folded into ep.drop_seed when not null
   int* status;
@@ -33,7 +35,8 @@ struct GemmArgs {
 // act == 1.  Reads (bias, aux for act == 2, residual) are predicated by the caller's `ok`.
 // `bias_off` shifts the bias vector (grouped GEMMs: one bias row per group).
 __device__ __forceinline__ void epilogue_math8(const GemmArgs& g, float* v, uint4& pre, int m, int n,
-                                               bool ok, bool add_bias, int bias_off = 0) {
+                                               bool ok, bool add_bias, int bias_off = 0,
+                                               const uint4* aux_staged = nullptr) {
   const AbGemmEpilogue& ep = g.ep;
   if (ep.alpha != 1.f) {
 #pragma unroll
@@ -62,8 +65,10 @@ __device__ __forceinline__ void epilogue_math8(const GemmArgs& g, float* v, uint
 #pragma unroll
     for (int j = 0; j < 8; ++j) v[j] = gelu_tanh(v[j]);
   } else if (ep.act == 2) {
-    const uint4 q = *reinterpret_cast<const uint4*>(
-        static_cast<const __nv_bfloat16*>(ep.aux) + (long long)m * ep.ldaux + n);
+    // the eight aux values: from the staged tile in shared memory, or straight from global
+    const uint4 q = aux_staged ? *aux_staged
+                               : *reinterpret_cast<const uint4*>(
+                                     static_cast<const __nv_bfloat16*>(ep.aux) + (long long)m * ep.ldaux + n);
     if (ep.aux_grad) {        // aux already holds the derivative (written by an act == 1 launch with aux_grad)
       v[0] *= bf16_lo(q.x); v[1] *= bf16_hi(q.x); v[2] *= bf16_lo(q.y); v[3] *= bf16_hi(q.y);
       v[4] *= bf16_lo(q.z); v[5] *= bf16_hi(q.z); v[6] *= bf16_lo(q.w); v[7] *= bf16_hi(q.w);
@@ -148,7 +153,11 @@ template <int COLS>
 __device__ __forceinline__ void epilogue_drain_wide(const GemmArgs& g, const CUtensorMap& tmOut,
                                                     const CUtensorMap& tmAux, uint32_t taddr, int m,
                                                     int m0w, int nbase, bool row_ok, uint8_t* stg,
-                                                    int lane, bool add_bias, int bias_off = 0) {
+                                                    int lane, bool add_bias, int bias_off = 0,
+                                                    bool aux_in_stage = false) {
+  // aux_in_stage (act == 2, one bf16 output, COLS == 64): the staging tile already holds the aux
+  // tile in the layout of the output tile (same box, same swizzle), so a lane reads its eight aux
+  // values from the very chunk it then overwrites with its eight results.
   const bool two = g.ep.act == 1, f32 = g.ep.out_fp32 != 0;
   const int gcols = (f32 || two) ? 32 : 64;             // columns per TMA store (warp-uniform)
 #pragma unroll 1
@@ -171,7 +180,9 @@ __device__ __forceinline__ void epilogue_drain_wide(const GemmArgs& g, const CUt
 #pragma unroll
         for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[grp * 8 + j]);
         uint4 pre = make_uint4(0, 0, 0, 0);
-        epilogue_math8(g, v, pre, m, n, row_ok && n < g.N, add_bias, bias_off);
+        const uint4* staged = aux_in_stage
+            ? reinterpret_cast<const uint4*>(stg + lane * 128 + (((rd * 2 + grp) ^ (lane & 7)) << 4)) : nullptr;
+        epilogue_math8(g, v, pre, m, n, row_ok && n < g.N, add_bias, bias_off, staged);
         if (f32) {
           // 32 fp32 columns = 128-byte rows, 128B swizzle: 16-byte chunk index ^= row & 7
           uint8_t* rowp = stg + lane * 128;

@@ -470,7 +470,7 @@ extern "C" int ab_gemm_grouped_bf16(const void* A, long long lda, const void* B,
        reinterpret_cast<uintptr_t>(ep->out) | reinterpret_cast<uintptr_t>(ep->aux)) & 15)
     return -3;
   GemmArgs g;
-  g.M = M; g.N = N; g.K = K; g.k_splits = 1; g.pdl = 0; g.ep = *ep; g.status = status; g.salt = seed_salt_ptr();
+  g.M = M; g.N = N; g.K = K; g.k_splits = 1; g.pdl = 0; g.ep = *ep; g.status = status; g.salt = seed_salt_ptr(); g.aux_tma = 0;
   GroupedArgs ga;
   ga.groups = grp->groups; ga.cap = grp->cap; ga.mode = grp->mode; ga.rows = grp->rows;
   ga.tile_ready = grp->tile_ready; ga.ret = grp->ret; ga.phase = grp->phase; ga.epoch = grp->epoch;

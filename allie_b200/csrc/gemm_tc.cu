@@ -325,6 +325,8 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA,
   uint64_t* tempty_bar = bars + 2 * STAGES + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint64_t* aux_bar = bars + 2 * STAGES + 5;      // one per epilogue warp: its staged aux tile
+  static_assert((2 * STAGES + 5 + NUM_EPI_WARPS) * 8 <= 256, "barrier block outgrew its 256 bytes");
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -340,12 +342,13 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA,
       mbar_init(&tfull_bar[i], 1);
       mbar_init(&tempty_bar[i], 2 * NUM_EPI_WARPS);
     }
+    for (int i = 0; i < NUM_EPI_WARPS; ++i) mbar_init(&aux_bar[i], 1);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
     tma_prefetch_desc(&tmOut);
-    if (g.ep.act == 1) tma_prefetch_desc(&tmAux);
+    if (g.ep.act == 1 || g.aux_tma) tma_prefetch_desc(&tmAux);
   }
   if (warp == 1) {
     tmem_alloc_pair(tmem_slot, TMEM_COLS);
@@ -471,6 +474,23 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA,
     constexpr int COLS_PER_WARP = BN / 4;
     uint8_t* my_stage = stage_out + e * PAIR_WARP_STAGING;
     uint32_t acc_phase[2] = {0, 0};
+    // GELU backward (act == 2): the warp's 32 x 64 tile of aux values is fetched by TMA into its
+    // staging tile one unit ahead (right after the store of the unit before has read the tile), so
+    // the loads that the epilogue math depends on are in flight while the accumulator is still
+    // being computed instead of being issued, row by row, once it is ready.
+    static_assert(COLS_PER_WARP == 64, "the staged aux tile is one 64-column store group");
+    const bool stage_aux = g.aux_tma != 0;
+    uint32_t aux_phase = 0;
+    auto fetch_aux = [&](int u) {          // lane 0; the staging tile must be free
+      if (u >= num_units) return;
+      const int tile = u % num_tiles;
+      const int m0w = (tile / n_tiles) * (2 * BM) + rank * BM + quad * 32;
+      const int nbase = (tile % n_tiles) * BN + part * COLS_PER_WARP;
+      if (m0w >= g.M || nbase >= g.N) return;       // the same test skips the drain below
+      mbar_expect_tx(&aux_bar[e], 32 * 128);
+      tma_load_2d(my_stage, &tmAux, &aux_bar[e], nbase, m0w);
+    };
+    if (stage_aux && lane == 0) fetch_aux(pair_id);
     int it = 0;
     for (int u = pair_id; u < num_units; u += num_pairs, ++it) {
       const int ks = u / num_tiles;
@@ -491,14 +511,27 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA,
       tc_fence_after();
       const uint32_t taddr =
           tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + ab * BN + part * COLS_PER_WARP;
+      const bool staged = stage_aux && m0w < g.M && nbase < g.N;
+      if (staged) {
+        if (!mbar_wait(&aux_bar[e], aux_phase, abort_flag)) {
+          *abort_flag = ST_TIMEOUT_FULL;
+          atomicCAS(g.status, 0, ST_TIMEOUT_FULL);
+          break;
+        }
+        aux_phase ^= 1;
+      }
       // a warp whose 32 rows lie entirely past M has nothing to store (its accumulator rows came
       // from zero-filled loads); it still hands the buffer back
       if (m0w < g.M)
         epilogue_drain_wide<COLS_PER_WARP>(g, tmOut, tmAux, taddr, m, m0w, nbase, m < g.M, my_stage, lane,
-                                           ks == 0);
+                                           ks == 0, 0, staged);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty_bar[ab]), 0));
+      if (stage_aux && lane == 0) {
+        tma_store_wait_read<0>();           // the store just issued has read the staging tile
+        fetch_aux(u + num_pairs);
+      }
     }
     if (lane == 0) tma_store_wait<0>();
   }
@@ -531,9 +564,17 @@ static int launch_pair(const void* A, long long lda, const void* B, long long ld
   else if (ep.act == 1)  rc = make_tmap_2d_sw(&tmOut, ep.out, g.M, g.N, ep.ldo, 32, 32, 2, 64);
   else                   rc = make_tmap_2d_sw(&tmOut, ep.out, g.M, g.N, ep.ldo, 32, 64, 2, 128);
   if (rc) return rc;
+  GemmArgs ga = g;
+  ga.aux_tma = 0;
   if (ep.act == 1) {
     rc = make_tmap_2d_sw(&tmAux, ep.aux, g.M, g.N, ep.ldaux, 32, 32, 2, 64);
     if (rc) return rc;
+  } else if (ep.act == 2 && !ep.out_fp32 && !ep.accumulate && g.k_splits == 1 &&
+             (reinterpret_cast<uintptr_t>(ep.aux) & 15) == 0 && (ep.ldaux * 2) % 16 == 0) {
+    // the aux tiles travel by TMA in the geometry of the output tiles (see the kernel)
+    rc = make_tmap_2d_sw(&tmAux, ep.aux, g.M, g.N, ep.ldaux, 32, 64, 2, 128);
+    if (rc) return rc;
+    ga.aux_tma = 1;
   } else {
     tmAux = tmOut;
   }
@@ -551,7 +592,7 @@ static int launch_pair(const void* A, long long lda, const void* B, long long ld
   int pairs = max_ctas / 2;
   if (pairs > units) pairs = units;
   if (pairs < 1) pairs = 1;
-  kern<<<2 * pairs, NUM_THREADS, SMEM, stream>>>(tmA, tmB, tmOut, tmAux, g);
+  kern<<<2 * pairs, NUM_THREADS, SMEM, stream>>>(tmA, tmB, tmOut, tmAux, ga);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -624,7 +665,7 @@ extern "C" int ab_gemm_bf16(const void* A, int a_mn, long long lda, const void* 
   if ((ep->ldo * (ep->out_fp32 ? 4 : 2)) & 15) return -4;   // TMA row pitch: multiple of 16 bytes
   if (ep->act == 1 && (ep->ldaux & 7)) return -4;
   GemmArgs g;
-  g.M = M; g.N = N; g.K = K; g.k_splits = k_splits; g.ep = *ep; g.status = status; g.salt = seed_salt_ptr();
+  g.M = M; g.N = N; g.K = K; g.k_splits = k_splits; g.ep = *ep; g.status = status; g.salt = seed_salt_ptr(); g.aux_tma = 0;
   // programmatic dependent launch: single-CTA kernels only, never with device-side limits (those
   // are values of earlier kernels, read before any wait)
   g.pdl = (ep->pdl && !ep->m_limit && !ep->k_limit) ? 1 : 0;
