@@ -18,9 +18,10 @@ live only on the rank that owns the slice; the other ranks receive the bf16 copy
 read (and fp32 for the small non-decayed rest).  :meth:`NvlGradOptimizer.gather_state` brings
 moments and masters back into the replicated layout for checkpoints.
 
-The kernels move data with plain peer loads / stores by default: measured on 2 and on 8 B200s that
-was faster than the ``multimem.ld_reduce`` / ``multimem.st`` variant, which is opt-in with
-``ALLIE_NVL_MULTIMEM=1``.
+The parameter all-gather always uses plain peer stores (measured faster than ``multimem.st`` on 2
+and on 8 B200s); the gradient reduce-scatter uses plain peer loads up to 3 ranks and
+``multimem.ld_reduce`` (the NVSwitch adds the eight copies) from 4 ranks up; ``ALLIE_NVL_MULTIMEM``
+= ``0`` / ``rs`` / ``1`` forces plain / reduce-only / both.
 """
 from __future__ import annotations
 
@@ -163,8 +164,13 @@ class NvlGradOptimizer:
         self.h_norm = rendezvous(self.norm_part)
         self.ticket = torch.zeros(4, dtype=torch.int32, device=dev)
         # ALLIE_NVL_MULTIMEM: 0 = plain peer loads / stores; 1 = multimem.ld_reduce for the gradients
-        # and multimem.st for the parameters; rs = multimem.ld_reduce for the gradients only
-        mode = os.environ.get("ALLIE_NVL_MULTIMEM", "0")
+        # and multimem.st for the parameters; rs = multimem.ld_reduce for the gradients only.
+        # Unset: rs from 4 ranks up (the reduce-scatter then issues one load per 16 bytes instead of
+        # one per peer and leaves the SMs it shares with backward sooner: 84.2 against 85.2 ms per
+        # step at 8 GPUs), plain below, and plain whenever NCCL_NVLS_ENABLE=0 asks for no multicast.
+        mode = os.environ.get("ALLIE_NVL_MULTIMEM")
+        if mode is None:
+            mode = "rs" if self.world >= 4 and os.environ.get("NCCL_NVLS_ENABLE", "1") != "0" else "0"
         mc = [int(getattr(h, "multicast_ptr", 0) or 0) for h in (self.h_grad, self.h_master, self.h_shadow)]
         self.multimem = mode == "1" and all(mc)
         self.mc_grad, self.mc_master, self.mc_shadow = mc if self.multimem else (0, 0, 0)
