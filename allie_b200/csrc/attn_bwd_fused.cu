@@ -53,6 +53,7 @@ __global__ void __launch_bounds__(FB_THREADS, 1)
 attn_bwd_fused64_kernel(const __grid_constant__ CUtensorMap tmQKV,
                         const __grid_constant__ CUtensorMap tmDO,
                         const __grid_constant__ CUtensorMap tmDQ, const AttnBwdArgs a) {
+  griddep_enter();
   constexpr int HD = 64;
   constexpr uint32_t IDESC_S = make_idesc_bf16(128, 128, 0, 0);
   constexpr uint32_t IDESC_T = make_idesc_bf16(128, HD, 1, 1);
@@ -345,6 +346,7 @@ attn_bwd_fused64_persistent_kernel(const __grid_constant__ CUtensorMap tmQKV,
                                    const __grid_constant__ CUtensorMap tmDO,
                                    const __grid_constant__ CUtensorMap tmDQ,
                                    const __grid_constant__ CUtensorMap tmDKV, const AttnBwdArgs a) {
+  griddep_enter();
   constexpr int HD = 64;
   constexpr uint32_t IDESC_S = make_idesc_bf16(128, 128, 0, 0);
   constexpr uint32_t IDESC_T = make_idesc_bf16(128, HD, 1, 1);
@@ -713,6 +715,7 @@ attn_bwd_fused64_persistent_kernel(const __grid_constant__ CUtensorMap tmQKV,
 // on B200 than the read-only conversion plus a memset.
 __global__ void __launch_bounds__(256)
 attn_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dqkv, int rows, int d) {
+  griddep_enter();
   const int d4 = d >> 2;
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const float4* src = reinterpret_cast<const float4*>(acc + static_cast<long long>(row) * d);
@@ -757,7 +760,7 @@ int launch_attn_bwd_fused64(const CUtensorMap& tq, const CUtensorMap& td, const 
       attr.mark_device();
     }
     dim3 grid((a.T + 127) / 128, a.H, a.B);
-    attn_bwd_fused64_kernel<<<grid, FB_THREADS, SMEM, stream>>>(tq, td, tdq, a);
+    launch_chained(attn_bwd_fused64_kernel, dim3(grid), dim3(FB_THREADS), SMEM, stream, tq, td, tdq, a);
   } else {
     constexpr int SMEM = 8 * FB_TILE + 2 * FB_P + FB_MATH_WARPS * 2048 + 256;
     static PerDeviceOnce attr;
@@ -771,12 +774,12 @@ int launch_attn_bwd_fused64(const CUtensorMap& tq, const CUtensorMap& td, const 
     rc = make_tmap_2d_sw(&tdkv, a.dqkv, rows, 3 * d, 3 * d, 32, 32, 2, 64);
     if (rc) return rc;
     const int bh = a.B * a.H;
-    attn_bwd_fused64_persistent_kernel<<<bh < 148 ? bh : 148, FB_THREADS, SMEM, stream>>>(tq, td, tdq,
+    launch_chained(attn_bwd_fused64_persistent_kernel, dim3(bh < 148 ? bh : 148), dim3(FB_THREADS), SMEM, stream, tq, td, tdq,
                                                                                           tdkv, a);
   }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
-  attn_dq_convert_kernel<<<148 * 16, 256, 0, stream>>>(a.dq_acc, a.dqkv, (int)rows, d);
+  launch_chained(attn_dq_convert_kernel, dim3(148 * 16), dim3(256), 0, stream, a.dq_acc, a.dqkv, (int)rows, d);
   e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
   return (int)cudaMemsetAsync(a.dq_acc, 0, sizeof(float) * rows * d, stream);
@@ -794,7 +797,7 @@ extern "C" int ab_attn_bwd_schedule(int mode) {
 
 // Stand-alone entry to the dQ conversion (bf16 copy into the packed dQKV activation, then clear).
 extern "C" int ab_attn_dq_convert(float* acc, void* dqkv, int rows, int d, cudaStream_t stream) {
-  ab::attn_dq_convert_kernel<<<148 * 16, 256, 0, stream>>>(acc, (__nv_bfloat16*)dqkv, rows, d);
+  ab::launch_chained(ab::attn_dq_convert_kernel, dim3(148 * 16), dim3(256), 0, stream, acc, (__nv_bfloat16*)dqkv, rows, d);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
   return (int)cudaMemsetAsync(acc, 0, sizeof(float) * (size_t)rows * d, stream);

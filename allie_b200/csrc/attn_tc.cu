@@ -24,6 +24,7 @@ template <int HD>
 __global__ void __launch_bounds__(FWD_THREADS, HD <= 64 ? 2 : 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmO,
                 const AttnArgs a) {
+  griddep_enter();
   constexpr int PANELS = HD / 64;               // 64-column panels per Q/K/V tile
   constexpr int TILE_BYTES = 128 * HD * 2;      // one Q / K / V tile
   constexpr int P_BYTES = 128 * 128 * 2;
@@ -348,6 +349,7 @@ namespace ab {
 __global__ void __launch_bounds__(256)
 attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
                   float* __restrict__ delta, int B, int T, int H, int hd) {
+  griddep_enter();
   const int cpr = hd >> 3;                                    // chunks per (row, head): 8 or 16
   const long long total = static_cast<long long>(B) * T * H * cpr;
   const long long gid = blockIdx.x * 256ll + threadIdx.x;
@@ -380,6 +382,7 @@ template <int HD, int MODE>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmDO,
                 const AttnBwdArgs a) {
+  griddep_enter();
   constexpr int STAGES = HD <= 64 ? 2 : 1;
   constexpr int PANELS = HD / 64;
   constexpr int TILE_BYTES = 128 * HD * 2;
@@ -684,7 +687,7 @@ static int launch_attn_fwd(const CUtensorMap& tm, const AttnArgs& a, cudaStream_
     attr.mark_device();
   }
   dim3 grid((a.T + 127) / 128, a.H, a.B);
-  kern<<<grid, FWD_THREADS, SMEM, stream>>>(tm, tmo, a);
+  launch_chained(kern, grid, dim3(FWD_THREADS), SMEM, stream, tm, tmo, a);
   return (int)cudaGetLastError();
 }
 
@@ -701,7 +704,7 @@ static int launch_attn_bwd(const CUtensorMap& tq, const CUtensorMap& td, const A
     attr.mark_device();
   }
   dim3 grid((a.T + 127) / 128, a.H, a.B);
-  kern<<<grid, BWD_THREADS, SMEM, stream>>>(tq, td, a);
+  launch_chained(kern, grid, dim3(BWD_THREADS), SMEM, stream, tq, td, a);
   return (int)cudaGetLastError();
 }
 }  // namespace ab
@@ -743,8 +746,8 @@ int ab_attn_bwd(const void* qkv, const void* out, const float* lse, const void* 
   rc = make_tmap_2d(&td, dout, (uint64_t)B * T, (uint64_t)H * hd, (uint64_t)H * hd, 128, 64, 2, true);
   if (rc) return rc;
   const long long n = (long long)B * T * H * (hd / 8);
-  attn_delta_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(
-      (const __nv_bfloat16*)out, (const __nv_bfloat16*)dout, delta, B, T, H, hd);
+  launch_chained(attn_delta_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream,
+                 (const __nv_bfloat16*)out, (const __nv_bfloat16*)dout, delta, B, T, H, hd);
   AttnBwdArgs a;
   a.B = B; a.T = T; a.H = H; a.hd = hd; a.scale = scale; a.seed = seed; a.stream_id = stream_id;
   a.thr16 = thr16; a.lse = lse; a.delta = delta; a.dqkv = (__nv_bfloat16*)dqkv; a.status = status;

@@ -17,6 +17,7 @@ __global__ void unpack_window_kernel(const uint32_t* __restrict__ words, int B, 
                                      int* __restrict__ ids, int* __restrict__ pos,
                                      int* __restrict__ lm_labels, float* __restrict__ value_labels,
                                      float* __restrict__ time_labels, int* __restrict__ counts) {
+  griddep_enter();
   // counts[0] = #valid shifted LM labels, counts[1] = #valid value labels, counts[2] = #valid time
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   int c0 = 0, c1 = 0, c2 = 0;
@@ -71,6 +72,7 @@ embed_fwd_kernel(const int* __restrict__ ids, const int* __restrict__ pos,
                  const float* __restrict__ ctrl, float* __restrict__ x, int M, int d, int vocab,
                  unsigned long long seed, unsigned int stream_id, unsigned int thr16,
                  const unsigned long long* __restrict__ salt) {
+  griddep_enter();
   seed = salted(seed, salt);
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -120,6 +122,7 @@ embed_bwd_kernel(const int* __restrict__ ids, const int* __restrict__ pos,
                  const float* __restrict__ dx, float* __restrict__ dwte, float* __restrict__ dwpe,
                  float* __restrict__ dctrl, int M, int d, int vocab, unsigned long long seed,
                  unsigned int stream_id, unsigned int thr16, const unsigned long long* __restrict__ salt) {
+  griddep_enter();
   seed = salted(seed, salt);
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -153,6 +156,7 @@ embed_bwd_kernel(const int* __restrict__ ids, const int* __restrict__ pos,
 }
 
 const unsigned long long* g_seed_salt = nullptr;
+int g_pdl_chain = 0;
 
 // *salt = next value of a 64-bit linear congruential sequence: the first node of a captured step
 __global__ void seed_salt_advance_kernel(unsigned long long* salt) {
@@ -168,6 +172,13 @@ int ab_set_seed_salt(const void* salt) {
   ab::g_seed_salt = static_cast<const unsigned long long*>(salt);
   return 0;
 }
+// Nonzero: launches of the training kernels from now on are links of a programmatic chain (each
+// may become resident while the one before it drains).  Meant to be set only around the capture of
+// a training micro-step.
+int ab_set_pdl_chain(int on) {
+  ab::g_pdl_chain = on;
+  return 0;
+}
 int ab_seed_salt_advance(void* salt, cudaStream_t stream) {
   ab::seed_salt_advance_kernel<<<1, 1, 0, stream>>>(static_cast<unsigned long long*>(salt));
   return (int)cudaGetLastError();
@@ -180,7 +191,7 @@ int ab_unpack_window(const void* words, int B, int T, int vocab, int pad_id, flo
   cudaError_t e = cudaMemsetAsync(counts, 0, 3 * sizeof(int), stream);
   if (e != cudaSuccess) return (int)e;
   const int n = B * T;
-  ab::unpack_window_kernel<<<(n + 255) / 256, 256, 0, stream>>>(
+  ab::launch_chained(ab::unpack_window_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, 
       (const uint32_t*)words, B, T, vocab, pad_id, time_mean, time_std, ids, pos, lm_labels,
       value_labels, time_labels, counts);
   return (int)cudaGetLastError();
@@ -190,7 +201,7 @@ int ab_embed_fwd(const int* ids, const int* pos, const float* wte, const float* 
                  const float* ctrl, float* x, int M, int d, int vocab, unsigned long long seed,
                  unsigned int stream_id, unsigned int thr16, cudaStream_t stream) {
   if (d % 4) return -1;
-  ab::embed_fwd_kernel<<<(M + 7) / 8, 256, 0, stream>>>(ids, pos, wte, wpe, ctrl, x, M, d, vocab,
+  ab::launch_chained(ab::embed_fwd_kernel, dim3((M + 7) / 8), dim3(256), 0, stream, ids, pos, wte, wpe, ctrl, x, M, d, vocab,
                                                         seed, stream_id, thr16, ab::seed_salt_ptr());
   return (int)cudaGetLastError();
 }
@@ -199,7 +210,7 @@ int ab_embed_bwd(const int* ids, const int* pos, const float* dx, float* dwte, f
                  float* dctrl, int M, int d, int vocab, unsigned long long seed,
                  unsigned int stream_id, unsigned int thr16, cudaStream_t stream) {
   if (d % 4) return -1;
-  ab::embed_bwd_kernel<<<(M + 7) / 8, 256, 0, stream>>>(ids, pos, dx, dwte, dwpe, dctrl, M, d,
+  ab::launch_chained(ab::embed_bwd_kernel, dim3((M + 7) / 8), dim3(256), 0, stream, ids, pos, dx, dwte, dwpe, dctrl, M, d,
                                                         vocab, seed, stream_id, thr16, ab::seed_salt_ptr());
   return (int)cudaGetLastError();
 }

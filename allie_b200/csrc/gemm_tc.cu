@@ -158,8 +158,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
             load_b(smem + prefetched * STAGE_BYTES + A_BYTES, &full_bar[prefetched], kb * BK, n0);
           }
         }
-        griddep_wait();
       }
+      griddep_wait();       // no-op unless launched as a dependent (decode step, captured training step)
       for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
         const int ks = u / num_tiles;
         const int tile = u % num_tiles;
@@ -359,6 +359,10 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA,
   cluster_sync_all();     // both CTAs' barriers are initialised before either signals the other
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // link of a programmatic chain (captured training step): the set-up above may have run while the
+  // kernel before this one was draining; loads, the epilogue's reads and all stores come after
+  if (threadIdx.x == 0) griddep_launch_dependents();
+  griddep_wait();
 
   const int m_tiles = (g.M + 2 * BM - 1) / (2 * BM);
   const int n_tiles = (g.N + BN - 1) / BN;
@@ -592,7 +596,7 @@ static int launch_pair(const void* A, long long lda, const void* B, long long ld
   int pairs = max_ctas / 2;
   if (pairs > units) pairs = units;
   if (pairs < 1) pairs = 1;
-  kern<<<2 * pairs, NUM_THREADS, SMEM, stream>>>(tmA, tmB, tmOut, tmAux, ga);
+  launch_chained(kern, dim3(2 * pairs), dim3(NUM_THREADS), SMEM, stream, tmA, tmB, tmOut, tmAux, ga);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -644,7 +648,7 @@ static int launch(const void* A, long long lda, const void* B, long long ldb, co
     cfg.numAttrs = 1;
     return static_cast<int>(cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmOut, tmAux, g));
   }
-  kern<<<grid, NUM_THREADS, SMEM, stream>>>(tmA, tmB, tmOut, tmAux, g);
+  launch_chained(kern, dim3(grid), dim3(NUM_THREADS), SMEM, stream, tmA, tmB, tmOut, tmAux, g);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -35,6 +35,7 @@ struct LmCeArgs {
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 lmhead_ce_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmOut, const LmCeArgs g) {
+  griddep_enter();
   constexpr int BN = LC_BN, STAGES = LC_STAGES;
   constexpr int A_BYTES = BM * BK * 2;
   constexpr int B_BYTES = BN * BK * 2;
@@ -322,6 +323,6 @@ extern "C" int ab_lmhead_ce(const void* h, long long ldh, const void* wte, long 
   if (max_ctas <= 0) max_ctas = 148;
   const int m_tiles = (M + BM - 1) / BM;
   const int grid = m_tiles < max_ctas ? m_tiles : max_ctas;
-  lmhead_ce_kernel<<<grid, NUM_THREADS, SMEM, stream>>>(tmA, tmB, tmOut, g);
+  launch_chained(lmhead_ce_kernel, dim3(grid), dim3(NUM_THREADS), SMEM, stream, tmA, tmB, tmOut, g);
   return static_cast<int>(cudaGetLastError());
 }

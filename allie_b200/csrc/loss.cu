@@ -114,6 +114,7 @@ heads_fwd_kernel(const __nv_bfloat16* __restrict__ h, const float* __restrict__ 
                  float value_coef, float time_coef, float* __restrict__ value_out,
                  float* __restrict__ time_out, float* __restrict__ dv, float* __restrict__ dt,
                  float* __restrict__ acc, int M, int d) {
+  griddep_enter();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int row = blockIdx.x * 8 + warp;
   float lv = 0.f, lt = 0.f;
@@ -177,6 +178,7 @@ __global__ void __launch_bounds__(256)
 heads_bwd_w_kernel(const __nv_bfloat16* __restrict__ h, const float* __restrict__ dv,
                    const float* __restrict__ dt, float* __restrict__ dwv, float* __restrict__ dbv,
                    float* __restrict__ dwt, float* __restrict__ dbt, int M, int d, int rows_per_blk) {
+  griddep_enter();
   // block covers rows [r0, r1) and all columns; thread covers columns tid*4 + 1024*i
   const int r0 = blockIdx.x * rows_per_blk;
   const int r1 = min(M, r0 + rows_per_blk);
@@ -206,6 +208,7 @@ heads_bwd_w_kernel(const __nv_bfloat16* __restrict__ h, const float* __restrict_
 __global__ void loss_finalize_kernel(const float* __restrict__ acc, const int* __restrict__ counts,
                                      float lm_coef, float value_coef, float time_coef,
                                      float* __restrict__ out) {
+  griddep_enter();
   const float lm = counts[0] > 0 ? acc[0] / counts[0] : 0.f;
   const float vl = counts[1] > 0 ? acc[1] / counts[1] : 0.f;
   const float tl = counts[2] > 0 ? acc[2] / counts[2] : 0.f;
@@ -240,7 +243,7 @@ int ab_heads_fwd(const void* h, const float* wv, const float* bv, const float* w
                  float value_coef, float time_coef, float* value_out, float* time_out, float* dv,
                  float* dt, float* acc, int M, int d, cudaStream_t stream) {
   if (d % 4) return -1;
-  ab::heads_fwd_kernel<<<(M + 7) / 8, 256, 0, stream>>>(
+  ab::launch_chained(ab::heads_fwd_kernel, dim3((M + 7) / 8), dim3(256), 0, stream, 
       (const __nv_bfloat16*)h, wv, bv, wt, bt, value_labels, time_labels, counts, value_coef,
       time_coef, value_out, time_out, dv, dt, acc, M, d);
   return (int)cudaGetLastError();
@@ -250,14 +253,14 @@ int ab_heads_bwd_w(const void* h, const float* dv, const float* dt, float* dwv, 
                    float* dwt, float* dbt, int M, int d, cudaStream_t stream) {
   if (d % 4) return -1;
   const int rows_per_blk = 64;
-  ab::heads_bwd_w_kernel<<<(M + rows_per_blk - 1) / rows_per_blk, 256, 0, stream>>>(
+  ab::launch_chained(ab::heads_bwd_w_kernel, dim3((M + rows_per_blk - 1) / rows_per_blk), dim3(256), 0, stream, 
       (const __nv_bfloat16*)h, dv, dt, dwv, dbv, dwt, dbt, M, d, rows_per_blk);
   return (int)cudaGetLastError();
 }
 
 int ab_loss_finalize(const float* acc, const int* counts, float lm_coef, float value_coef,
                      float time_coef, float* out, cudaStream_t stream) {
-  ab::loss_finalize_kernel<<<1, 1, 0, stream>>>(acc, counts, lm_coef, value_coef, time_coef, out);
+  ab::launch_chained(ab::loss_finalize_kernel, dim3(1), dim3(1), 0, stream, acc, counts, lm_coef, value_coef, time_coef, out);
   return (int)cudaGetLastError();
 }
 }

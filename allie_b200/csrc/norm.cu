@@ -112,6 +112,7 @@ __device__ __forceinline__ float4 ln_dy_eff(const LnBwdArgs& a, uint2 p, bool ha
 template <int NV_MAX, bool PARAMS>
 __global__ void __launch_bounds__(LN_WARPS * 32, NV_MAX <= 8 ? 2 : 1)
 ln_bwd_kernel(const LnBwdArgs a) {
+  griddep_enter();
   extern __shared__ __align__(16) float ln_acc[];     // [LN_WARPS][3][d] when PARAMS
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int d = a.d, nv = d >> 7;
@@ -276,10 +277,10 @@ int ab_layernorm_fwd(const float* x, const float* gamma, const float* beta, void
   int grid = (M + LN_WARPS - 1) / LN_WARPS;
   if (grid > 148 * 8) grid = 148 * 8;
   if (d <= 1024)
-    ln_fwd_kernel<8><<<grid, LN_WARPS * 32, 0, stream>>>(x, gamma, beta, (__nv_bfloat16*)y, mean,
+    launch_chained(ln_fwd_kernel<8>, dim3(grid), dim3(LN_WARPS * 32), 0, stream, x, gamma, beta, (__nv_bfloat16*)y, mean,
                                                          rstd, M, d, eps, rms);
   else
-    ln_fwd_kernel<16><<<grid, LN_WARPS * 32, 0, stream>>>(x, gamma, beta, (__nv_bfloat16*)y, mean,
+    launch_chained(ln_fwd_kernel<16>, dim3(grid), dim3(LN_WARPS * 32), 0, stream, x, gamma, beta, (__nv_bfloat16*)y, mean,
                                                           rstd, M, d, eps, rms);
   return (int)cudaGetLastError();
 }
@@ -300,8 +301,8 @@ int ab_layernorm_bwd(const void* dy, const float* x, const float* mean, const fl
   int grid = (M + LN_WARPS - 1) / LN_WARPS;
   if (!dgamma) {
     if (grid > 148 * 16) grid = 148 * 16;
-    if (d <= 1024) ln_bwd_kernel<8, false><<<grid, LN_WARPS * 32, 0, stream>>>(a);
-    else           ln_bwd_kernel<16, false><<<grid, LN_WARPS * 32, 0, stream>>>(a);
+    if (d <= 1024) launch_chained(ln_bwd_kernel<8, false>, dim3(grid), dim3(LN_WARPS * 32), 0, stream, a);
+    else           launch_chained(ln_bwd_kernel<16, false>, dim3(grid), dim3(LN_WARPS * 32), 0, stream, a);
     return (int)cudaGetLastError();
   }
   // with parameter gradients: exactly the resident blocks, each warp keeps its column sums
@@ -318,8 +319,8 @@ int ab_layernorm_bwd(const void* dy, const float* x, const float* mean, const fl
   }
   const int resident = d <= 1024 ? 148 * 2 : 148;
   if (grid > resident) grid = resident;
-  if (d <= 1024) ln_bwd_kernel<8, true><<<grid, LN_WARPS * 32, smem, stream>>>(a);
-  else           ln_bwd_kernel<16, true><<<grid, LN_WARPS * 32, smem, stream>>>(a);
+  if (d <= 1024) launch_chained(ln_bwd_kernel<8, true>, dim3(grid), dim3(LN_WARPS * 32), smem, stream, a);
+  else           launch_chained(ln_bwd_kernel<16, true>, dim3(grid), dim3(LN_WARPS * 32), smem, stream, a);
   return (int)cudaGetLastError();
 }
 }

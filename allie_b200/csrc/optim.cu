@@ -146,6 +146,7 @@ constexpr int CS_ROWS = 128;
 __global__ void __launch_bounds__(256)
 colsum_bf16_kernel(const __nv_bfloat16* __restrict__ x, long long ld, int M, int N,
                    float* __restrict__ out, const int* __restrict__ m_limit) {
+  griddep_enter();
   __shared__ float part[128][9];
   const int tx = threadIdx.x & 127, ty = threadIdx.x >> 7;
   const int c = (blockIdx.x * 128 + tx) * 8;
@@ -195,7 +196,7 @@ extern "C" int ab_colsum_grouped_bf16(const void* x, long long ld, int groups, i
                                       const int* m_limit, cudaStream_t stream) {
   if ((N & 7) || (ld & 7) || groups < 1 || groups > 65535 || !m_limit) return -1;
   dim3 grid((N / 8 + 127) / 128, (cap + ab::CS_ROWS - 1) / ab::CS_ROWS, groups);
-  ab::colsum_bf16_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, ld, cap, N, out, m_limit);
+  ab::launch_chained(ab::colsum_bf16_kernel, dim3(grid), dim3(256), 0, stream, (const __nv_bfloat16*)x, ld, cap, N, out, m_limit);
   return (int)cudaGetLastError();
 }
 
@@ -203,6 +204,6 @@ extern "C" int ab_colsum_bf16(const void* x, long long ld, int M, int N, float* 
                               const int* m_limit, cudaStream_t stream) {
   if ((N & 7) || (ld & 7)) return -1;
   dim3 grid((N / 8 + 127) / 128, (M + ab::CS_ROWS - 1) / ab::CS_ROWS);
-  ab::colsum_bf16_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, ld, M, N, out, m_limit);
+  ab::launch_chained(ab::colsum_bf16_kernel, dim3(grid), dim3(256), 0, stream, (const __nv_bfloat16*)x, ld, M, N, out, m_limit);
   return (int)cudaGetLastError();
 }

@@ -150,6 +150,37 @@ __device__ __forceinline__ void griddep_launch_dependents() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
+// First statement of a kernel that can be a link of a programmatic chain (the captured training
+// micro-step): lets the kernel behind it in the stream become resident as this one drains, then
+// waits for the kernel before it.  Everything the kernel reads or writes comes after this.
+__device__ __forceinline__ void griddep_enter() {
+  if (threadIdx.x == 0) griddep_launch_dependents();
+  griddep_wait();
+}
+
+// Host side: launches made through launch_chained carry the programmatic-stream-serialization
+// attribute while g_pdl_chain is set (only around the capture of a training micro-step; defined in
+// embed.cu).  Every kernel launched this way starts with griddep_enter() or, for the GEMMs, does
+// its set-up first and then waits.
+extern int g_pdl_chain;
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                  cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute at[1];
+  if (g_pdl_chain) {
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+  }
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 // ------------------------------------------------------------------- TMA ---
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");

@@ -19,6 +19,7 @@ autocast; GEMM operands are bf16 with fp32 accumulation.
 from __future__ import annotations
 
 import math
+import os
 import re
 
 import torch
@@ -593,6 +594,11 @@ class B200Engine:
         graph = torch.cuda.CUDAGraph()
         launches0 = _lib.LAUNCHES
         assert lib.ab_set_seed_salt(ptr(self._salt)) == 0
+        # ALLIE_TRAIN_PDL=1: the captured kernels become links of a programmatic chain (each may take
+        # its place on the SMs while the one before it drains).  Off by default: on the medium model
+        # the chained graph measured 1.7 % SLOWER than ordinary graph edges (654.6 / 655.1 ms against
+        # 644.0 ms per step, same box, alternating runs), unlike the decode step, where it pays.
+        lib.ab_set_pdl_chain(int(os.environ.get("ALLIE_TRAIN_PDL", "0") == "1"))
         try:
             with torch.cuda.graph(graph):
                 assert lib.ab_seed_salt_advance(ptr(self._salt), stream_ptr()) == 0
@@ -602,6 +608,7 @@ class B200Engine:
                 self.backward(B, T, seed, None)
         finally:
             lib.ab_set_seed_salt(None)
+            lib.ab_set_pdl_chain(0)
         captured = _lib.LAUNCHES - launches0
         _lib.count_launches(-captured)       # nothing ran yet: the launches are counted per replay
         return {"graph": graph, "words": static, "launches": captured, "seed": seed}
