@@ -600,7 +600,9 @@ class B200Engine:
         # 644.0 ms per step, same box, alternating runs), unlike the decode step, where it pays.
         lib.ab_set_pdl_chain(int(os.environ.get("ALLIE_TRAIN_PDL", "0") == "1"))
         try:
-            with torch.cuda.graph(graph):
+            # thread-local capture mode: the window-prefetch thread may wait on a copy event
+            # (cudaEventSynchronize) while this thread captures
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
                 assert lib.ab_seed_salt_advance(ptr(self._salt), stream_ptr()) == 0
                 _lib.count_launches(1)
                 B, T = self.load_window(static)
