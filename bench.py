@@ -323,7 +323,7 @@ def run_ours(args) -> dict:
     trainer = Trainer(cfg, output_dir=out_dir, batch_size=MICRO_BATCH, gradient_accumulation_steps=ga,
                       lr=6e-4, min_lr=1e-5, weight_decay=1e-2, grad_clip=1.0, warmup_iters=2000,
                       decay_iters=2_000_000, max_iters=2_000_000, eval_interval=0, log_interval=-1,
-                      save_interval=0, use_wandb=False)
+                      save_interval=0, use_wandb=False, cuda_graph=False if args.no_cuda_graph else None)
     tok = UCITokenizer(max_length=SEQ_LEN, vocab_size_multiple_of=VOCAB_MULT)
     torch.manual_seed(1234)
     model = initialize_model(tok, "gpt2-medium", use_control_token=True, use_regression_head=True,
@@ -556,6 +556,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default="medium", choices=sorted(MODELS),
                     help="medium = the headline config; large = the large-ablation shape (32L, d1280, 20H)")
+    ap.add_argument("--no-cuda-graph", action="store_true",
+                    help="launch the kernels of every micro-step one by one instead of replaying a CUDA graph "
+                         "(for per-kernel profiles)")
     ap.add_argument("--secondary", default="auto", choices=["auto", "none", "all"],
                     help="auto: MCTS at every N, MoE at N = 8; all: also a reduced MoE shape at N < 8; none: headline only")
     ap.add_argument("--secondary-budget", type=float, default=600.0,
