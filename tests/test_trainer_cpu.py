@@ -242,3 +242,20 @@ def test_engine_keeps_a_bounded_number_of_inference_buffer_sets():
         raise AssertionError("expected the position-table guard")
     except ValueError as e:
         assert "positions" in str(e)
+
+
+def test_every_trainer_key_of_the_shipped_configs_is_an_argument_of_the_trainer():
+    """``Trainer(config, **config.trainer_config)`` is how the CLI builds it: a key the signature does
+    not know would only fail at launch time.  Also pins the extension keys by name."""
+    import glob
+    import inspect
+
+    params = set(inspect.signature(Trainer.__init__).parameters)
+    assert {"shard_optimizer", "grad_sync", "expert_parallel", "cuda_graph", "use_wandb"} <= params
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    files = glob.glob(os.path.join(root, "pretrain_config", "**", "*.yaml"), recursive=True)
+    assert len(files) >= 5
+    for f in files:
+        cfg = load_config(f)
+        keys = set(cfg.trainer_config.to_container()) if hasattr(cfg.trainer_config, "to_container") else set(dict(cfg.trainer_config))
+        assert keys <= params, (f, sorted(keys - params))
