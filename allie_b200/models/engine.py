@@ -625,7 +625,17 @@ class B200Engine:
             return self.micro_step(words, _no_graph=True)
         if not entry:
             torch.cuda.current_stream().synchronize()
-            entry = self._step_graphs[key] = self._capture_step(words)
+            launches0 = _lib.LAUNCHES
+            try:
+                entry = self._step_graphs[key] = self._capture_step(words)
+            except Exception as e:      # nothing ran during the failed capture: go on with ordinary launches
+                import logging
+
+                logging.getLogger(__name__).warning(f"CUDA-graph capture of the micro-step failed ({e}); "
+                                                    "continuing with ordinary launches")
+                _lib.count_launches(launches0 - _lib.LAUNCHES)
+                self.enable_step_graph(False)
+                return self.micro_step(words, _no_graph=True)
         entry["words"].copy_(words, non_blocking=True)
         entry["graph"].replay()
         self.fwd_count += 1
